@@ -1,0 +1,21 @@
+"""CPU restatement of the AMCT quantization hot path. TEST INFRASTRUCTURE ONLY.
+
+Nothing under ``amct_b200`` may import this package: it is the checker that the
+CUDA path is compared against in ``tests/``, in ``__graft_entry__.smoke()`` and
+in the CPU-baseline leg of ``bench.py``.  The product path has no CPU fallback.
+
+Modules
+-------
+intq     integer quantization arithmetic the reference implements in torch
+         (scale/offset, codes, fake-quant, SmoothQuant fold, deploy constants).
+         PINNED: checked against outputs of the imported reference, committed
+         as fixtures under ``tests/golden`` (``tests/golden/make_golden.py``).
+npu_ops  the four external ``torch_npu`` ops the deploy modules call.  The
+         reference does not contain them and its tests mock them without
+         rounding or scaling, so this part is PARITY UNPINNED: it restates the
+         documented formula and the operand construction at the call sites.
+mx       MXFP8-E4M3 / MXFP4-E2M1 with E8M0 block scales.  Absent from the
+         reference: PARITY UNPINNED, restated from the public OCP MX v1.0 rules.
+hif8     HiFloat8 encode/decode.  Absent from the reference: PARITY UNPINNED,
+         restated from the published format description.
+"""
