@@ -1,0 +1,301 @@
+"""Torch-tensor front end of the C-ABI kernels.
+
+Every function takes CUDA tensors, allocates its outputs with torch (device
+memory and streams are torch's), and enqueues the kernel on the current stream.
+Nothing here computes on the CPU: a CPU tensor raises.
+"""
+import ctypes
+from ctypes import c_int, c_int64, c_void_p
+
+import torch
+
+from . import lib as _l
+
+_DT = {torch.float32: _l.DTYPE_F32, torch.float16: _l.DTYPE_F16, torch.bfloat16: _l.DTYPE_BF16}
+SCALE_ERROR = "Param scale has invalid value inf, nan or zeros!"      # amct_pytorch/quantize_op/utils.py:66-67
+
+
+def _p(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise _l.BackendError('amct_b200 kernels need CUDA tensors (there is no CPU fallback)')
+
+
+def _dt(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise _l.BackendError(f'unsupported dtype {t.dtype}; float32/float16/bfloat16 only') from None
+
+
+def _rows2d(x):
+    """View as [rows, k] with unit inner stride; returns (tensor, rows, k, ld)."""
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) < k):
+        x2 = x2.contiguous()
+    ld = x2.stride(0) if x2.shape[0] > 1 else k
+    return x2, x2.shape[0], k, ld
+
+
+class Status:
+    """Device word the kernels OR error bits into; read back on demand."""
+
+    def __init__(self, device):
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def ptr(self):
+        return _p(self.word)
+
+    def raise_if_set(self):
+        if int(self.word.item()) & 1:
+            raise RuntimeError(SCALE_ERROR)
+
+
+def bits_of(quant_type):
+    return int(quant_type.replace('int', ''))
+
+
+# ---------------------------------------------------------------------------
+def quant_dynamic_per_token(x, smooth=None, rule='released', check=False):
+    """Per-row symmetric INT8 codes and fp32 scales of x[..., K] in one pass."""
+    _need_cuda(x, smooth)
+    x2, rows, k, ld = _rows2d(x)
+    q = torch.empty((rows, k), dtype=torch.int8, device=x.device)
+    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
+    st = Status(x.device) if check else None
+    if smooth is not None:
+        smooth = smooth.reshape(-1).to(x.dtype).contiguous()
+        assert smooth.numel() == k
+    rc = _l.load().amct_quant_dynamic_pertoken(
+        _p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), _p(smooth), c_int(_l.RULE[rule]),
+        _p(q), c_int64(k), _p(scale), st.ptr() if st else c_void_p(0), _stream())
+    _l.check(rc, 'amct_quant_dynamic_pertoken')
+    if st:
+        st.raise_if_set()
+    return q.reshape(x.shape), scale
+
+
+def _unit_count(rows, k, strategy, group):
+    if strategy == 'tensor':
+        return 1, 1
+    if strategy == 'channel':
+        return rows, 1
+    g = (k + group - 1) // group
+    return rows * g, g
+
+
+def quant_rows(w, quant_type, symmetric, strategy, group=None, scale=None, offset=None, out='none',
+               pre=None, pre_op='none', check=True):
+    """Row kernel front end.
+
+    scale is None  -> derive scale/offset from `w` (strategy channel or group).
+    out: 'none' | 'i8' | 'i32' | 'pack4' | 'fake' | 'fake_awq'.
+    Returns (scale flat fp32, offset flat int32 | None, out tensor | None).
+    """
+    _need_cuda(w, scale, offset, pre)
+    assert w.dim() == 2
+    w2, rows, k, ld = _rows2d(w)
+    bits = bits_of(quant_type)
+    compute = scale is None
+    nunits, _ = _unit_count(rows, k, strategy, group)
+    if compute:
+        scale = torch.empty(nunits, dtype=torch.float32, device=w.device)
+        offset = None if symmetric else torch.empty(nunits, dtype=torch.int32, device=w.device)
+    else:
+        scale = scale.reshape(-1).to(torch.float32).contiguous()
+        offset = None if offset is None else offset.reshape(-1).to(torch.int32).contiguous()
+        assert scale.numel() == nunits, (scale.numel(), nunits)
+    mode = {'none': _l.OUT_NONE, 'i8': _l.OUT_I8, 'i32': _l.OUT_I32, 'pack4': _l.OUT_PACK4,
+            'fake': _l.OUT_FAKE, 'fake_awq': _l.OUT_FAKE_AWQ}[out]
+    o, ld_out = None, 0
+    if out == 'i8':
+        o = torch.empty((rows, k), dtype=torch.int8, device=w.device)
+    elif out == 'i32':
+        o = torch.empty((rows, k), dtype=torch.int32, device=w.device)
+    elif out == 'pack4':
+        o = torch.empty((rows, (k + 1) // 2), dtype=torch.uint8, device=w.device)
+    elif out in ('fake', 'fake_awq'):
+        o = torch.empty((rows, k), dtype=w.dtype, device=w.device)
+    if o is not None:
+        ld_out = o.stride(0)
+    pop = {'none': _l.PRE_NONE, 'mul': _l.PRE_MUL, 'div': _l.PRE_DIV}[pre_op]
+    if pre is not None:
+        pre = pre.reshape(-1).to(w.dtype).contiguous()
+        assert pre.numel() == k
+    st = Status(w.device) if check else None
+    sym_flag = 1 if (symmetric or offset is None) else 0
+    rc = _l.load().amct_quant_rows(
+        _p(w2), c_int(_dt(w2)), c_int64(rows), c_int64(k), c_int64(ld), _p(pre), c_int(pop),
+        c_int(1 if compute else 0), c_int(_l.STRATEGY[strategy]), c_int(group or 0), c_int(bits),
+        c_int(sym_flag), _p(scale), _p(offset), c_int(mode), _p(o), c_int64(ld_out),
+        st.ptr() if st else c_void_p(0), _stream())
+    _l.check(rc, 'amct_quant_rows')
+    if st:
+        st.raise_if_set()
+    return scale, offset, o
+
+
+def minmax(x, axis, running=None):
+    """(min, max) of x viewed as [rows, K]: axis 'tensor' -> shape [1], 'column' -> [1, K].
+    running=(min, max) tensors are updated in place and returned."""
+    _need_cuda(x)
+    x2, rows, k, ld = _rows2d(x)
+    n = 1 if axis == 'tensor' else k
+    if running is None:
+        mn = torch.empty(n, dtype=x.dtype, device=x.device)
+        mx = torch.empty(n, dtype=x.dtype, device=x.device)
+        merge = 0
+    else:
+        mn, mx = running
+        assert mn.is_contiguous() and mx.is_contiguous() and mn.numel() == n and mn.dtype == x.dtype
+        merge = 1
+    L = _l.load()
+    ws = torch.empty(L.amct_minmax_workspace_bytes(c_int64(k)), dtype=torch.uint8, device=x.device)
+    st = Status(x.device)
+    rc = L.amct_minmax(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld),
+                       c_int(_l.AXIS_TENSOR if axis == 'tensor' else _l.AXIS_COLUMN), c_int(merge),
+                       _p(mn), _p(mx), _p(ws), st.ptr(), _stream())
+    _l.check(rc, 'amct_minmax')
+    if axis == 'column':
+        return mn.reshape(1, k), mx.reshape(1, k)
+    return mn, mx
+
+
+def scale_offset(vmax, vmin, symmetric, quant_type):
+    """calculate_scale_offset on device; keeps the shape of vmax."""
+    _need_cuda(vmax, vmin)
+    shape = vmax.shape
+    a = vmax.reshape(-1).contiguous()
+    b = vmin.reshape(-1).to(a.dtype).contiguous()
+    n = a.numel()
+    scale = torch.empty(n, dtype=torch.float32, device=a.device)
+    offset = None if symmetric else torch.empty(n, dtype=torch.int32, device=a.device)
+    st = Status(a.device)
+    rc = _l.load().amct_scale_offset(_p(a), _p(b), c_int(_dt(a)), c_int64(n), c_int(bits_of(quant_type)),
+                                     c_int(1 if symmetric else 0), _p(scale), _p(offset), st.ptr(), _stream())
+    _l.check(rc, 'amct_scale_offset')
+    st.raise_if_set()
+    return scale.reshape(shape), None if offset is None else offset.reshape(shape)
+
+
+def quantize_static(x, scales, zero_points, axis=-1, smooth=None):
+    """npu_quantize(..., dtype=int8, div_mode=False): per-tensor (one scale) or per-token (axis=-2)."""
+    _need_cuda(x, scales, zero_points, smooth)
+    x = x.contiguous()
+    k = x.shape[-1]
+    per_token = scales.numel() != 1
+    tokens = x.shape[-2] if x.dim() >= 2 else 1
+    if per_token:
+        if axis not in (-2, x.dim() - 2) or scales.numel() != tokens:
+            raise _l.BackendError('per-token scales need axis=-2 and one scale per token position')
+    outer = x.numel() // (tokens * k) if x.numel() else 0
+    s = scales.reshape(-1).to(x.dtype).contiguous()
+    z = None if zero_points is None else zero_points.reshape(-1).to(x.dtype).contiguous()
+    if z is not None and z.numel() != s.numel():
+        z = z.expand(s.numel()).contiguous()
+    if smooth is not None:
+        smooth = smooth.reshape(-1).to(x.dtype).contiguous()
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    rc = _l.load().amct_quantize_static(_p(x), c_int(_dt(x)), c_int64(outer), c_int64(tokens), c_int64(k),
+                                        _p(s), _p(z), c_int(1 if per_token else 0), _p(smooth), _p(q), _stream())
+    _l.check(rc, 'amct_quantize_static')
+    return q
+
+
+def rowsum_i8(wq_nk):
+    _need_cuda(wq_nk)
+    assert wq_nk.dtype == torch.int8 and wq_nk.dim() == 2 and wq_nk.stride(1) == 1
+    out = torch.empty(wq_nk.shape[0], dtype=torch.int32, device=wq_nk.device)
+    rc = _l.load().amct_rowsum_i8(_p(wq_nk), c_int64(wq_nk.shape[0]), c_int64(wq_nk.shape[1]),
+                                  c_int64(wq_nk.stride(0)), _p(out), _stream())
+    _l.check(rc, 'amct_rowsum_i8')
+    return out
+
+
+def transpose_i8(t):
+    _need_cuda(t)
+    t = t.contiguous()
+    out = torch.empty((t.shape[1], t.shape[0]), dtype=t.dtype, device=t.device)
+    rc = _l.load().amct_transpose_i8(_p(t), c_int64(t.shape[0]), c_int64(t.shape[1]), _p(out), _stream())
+    _l.check(rc, 'amct_transpose_i8')
+    return out
+
+
+# ---------------------------------------------------------------------------
+# tensor-core GEMMs
+_OUT_KIND = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.int32: 3}
+_BIAS_KIND = {torch.int32: 1, torch.float32: 2, torch.float16: 3, torch.bfloat16: 4}
+
+
+def _kmajor(t):
+    """[R, K] tensor with unit K stride and a 16-byte aligned leading dimension."""
+    if t.stride(-1) != 1 or (t.stride(0) * t.element_size()) % 16 or t.data_ptr() % 16:
+        t = t.contiguous()
+    if (t.stride(0) * t.element_size()) % 16:
+        raise _l.BackendError('K * element size must be a multiple of 16 bytes for the TMA-fed GEMM')
+    return t
+
+
+def raise_if_timed_out(status_word):
+    if int(status_word.item()) & 2:
+        raise _l.BackendError('a device-side wait in the GEMM kernel timed out')
+
+
+def gemm_w8a8(q, w_nk, deq_scale=None, pertoken_scale=None, bias=None, out_dtype=torch.bfloat16, out=None,
+              status=None):
+    """q int8 [M, K] x w_nk int8 [N, K] (K-major) -> [M, N] with the W8A8 dequant epilogue;
+    out_dtype=torch.int32 returns the raw accumulators."""
+    _need_cuda(q, w_nk, deq_scale, pertoken_scale, bias)
+    assert q.dtype == torch.int8 and w_nk.dtype == torch.int8 and q.dim() == 2 and w_nk.dim() == 2
+    q, w_nk = _kmajor(q), _kmajor(w_nk)
+    m, k = q.shape
+    n = w_nk.shape[0]
+    assert w_nk.shape[1] == k
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=q.device)
+    if deq_scale is not None:
+        deq_scale = deq_scale.reshape(-1).to(torch.float32).contiguous()
+        assert deq_scale.numel() == n
+    if pertoken_scale is not None:
+        pertoken_scale = pertoken_scale.reshape(-1).to(torch.float32).contiguous()
+        assert pertoken_scale.numel() == m
+    bk = 0
+    if bias is not None:
+        bias = bias.reshape(-1).contiguous()
+        bk = _BIAS_KIND[bias.dtype]
+    rc = _l.load().amct_gemm_w8a8(
+        _p(q), _p(w_nk), c_int64(m), c_int64(n), c_int64(k), c_int64(q.stride(0)), c_int64(w_nk.stride(0)),
+        _p(deq_scale), _p(pertoken_scale), _p(bias), c_int(bk), _p(out), c_int(_OUT_KIND[out.dtype]),
+        c_int64(out.stride(0)), _p(status) if status is not None else c_void_p(0), _stream())
+    _l.check(rc, 'amct_gemm_w8a8')
+    return out
+
+
+def gemm_f16(a, b_nk, bias=None, out_dtype=None, out=None, status=None):
+    """a [M, K] x b_nk [N, K] in fp16 or bf16 -> [M, N], fp32 accumulation."""
+    _need_cuda(a, b_nk, bias)
+    assert a.dtype == b_nk.dtype and a.dtype in (torch.float16, torch.bfloat16)
+    a, b_nk = _kmajor(a), _kmajor(b_nk)
+    m, k = a.shape
+    n = b_nk.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or a.dtype, device=a.device)
+    bk = 0
+    if bias is not None:
+        bias = bias.reshape(-1).contiguous()
+        bk = _BIAS_KIND[bias.dtype]
+    rc = _l.load().amct_gemm_f16(
+        _p(a), _p(b_nk), c_int(_dt(a)), c_int64(m), c_int64(n), c_int64(k), c_int64(a.stride(0)),
+        c_int64(b_nk.stride(0)), _p(bias), c_int(bk), _p(out), c_int(_OUT_KIND[out.dtype]), c_int64(out.stride(0)),
+        _p(status) if status is not None else c_void_p(0), _stream())
+    _l.check(rc, 'amct_gemm_f16')
+    return out

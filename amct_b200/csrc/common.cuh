@@ -1,0 +1,123 @@
+// Shared device helpers for the quantization kernels (sm_100a).
+//
+// Numerics contract shared by every kernel in this directory: fp32 arithmetic,
+// IEEE division (__fdiv_rn), round-half-to-even (rintf), no FMA contraction
+// (explicit __fmul_rn/__fadd_rn; the quant files are also compiled with
+// -fmad=false).  These choices make integer codes bit-identical to the
+// reference's torch arithmetic (amct_pytorch/utils/quant_util.py:57-93).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "../../include/amct_b200.h"
+
+#define AMCT_FLT_EPSILON 1.192092896e-7f   // amct_pytorch/quantize_op/utils.py:23
+
+#define AMCT_CHECK_LAUNCH()                                         \
+  do {                                                              \
+    cudaError_t e__ = cudaGetLastError();                           \
+    if (e__ != cudaSuccess) return AMCT_ERR_CUDA;                   \
+  } while (0)
+
+namespace amct {
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> {
+  static constexpr int kPerVec = 4;
+  __device__ static float to_f(float v) { return v; }
+  __device__ static float from_f(float v) { return v; }
+};
+template <> struct ElemTraits<__half> {
+  static constexpr int kPerVec = 8;
+  __device__ static float to_f(__half v) { return __half2float(v); }
+  __device__ static __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct ElemTraits<__nv_bfloat16> {
+  static constexpr int kPerVec = 8;
+  __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Round an fp32 value to T and back: the value a torch op on T tensors would hold.
+template <typename T> __device__ __forceinline__ float round_to(float v) {
+  return ElemTraits<T>::to_f(ElemTraits<T>::from_f(v));
+}
+template <> __device__ __forceinline__ float round_to<float>(float v) { return v; }
+
+// 16-byte vector of T.
+template <typename T> struct alignas(16) Vec16 {
+  T v[ElemTraits<T>::kPerVec];
+};
+
+template <typename T> __device__ __forceinline__ Vec16<T> ld_vec(const T* p) {
+  Vec16<T> r;
+  *reinterpret_cast<uint4*>(&r) = __ldg(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+// Streaming variant: data that is read once (evict-first).
+template <typename T> __device__ __forceinline__ Vec16<T> ld_vec_stream(const T* p) {
+  Vec16<T> r;
+  *reinterpret_cast<uint4*>(&r) = __ldcs(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Monotonic float <-> int mapping, so integer atomicMin/Max order floats.
+__device__ __forceinline__ int f2ord(float f) {
+  int b = __float_as_int(f);
+  return b >= 0 ? b : b ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ord2f(int b) {
+  return __int_as_float(b >= 0 ? b : b ^ 0x7fffffff);
+}
+
+// Scale/offset rule of the reference (amct_pytorch/quantize_op/utils.py:75-108).
+// Returns false when the scale is not finite (the reference raises there).
+__device__ __forceinline__ bool qparams_from_minmax(float mx, float mn, int bits, bool symmetric,
+                                                    float* scale, int* offset) {
+  float s, o = 0.f;
+  if (symmetric) {
+    float amx = fabsf(mx), amn = fabsf(mn);
+    float div = (float)((1 << (bits - 1)) - 1 + (amx < amn ? 1 : 0));
+    float bound = amx > amn ? amx : amn;
+    s = __fdiv_rn(bound, div);
+    if (s < AMCT_FLT_EPSILON) s = 1.f;
+  } else {
+    mx = fmaxf(mx, 0.f);
+    mn = fminf(mn, 0.f);
+    float span = (float)((1 << bits) - 1);
+    float half = (float)(1 << (bits - 1));                 // ceil(span / 2)
+    s = __fdiv_rn(__fsub_rn(mx, mn), span);
+    o = (mx != mn) ? __fsub_rn(-half, __fdiv_rn(mn, s)) : -half;
+    if (s < AMCT_FLT_EPSILON) { o = -half; s = 1.f; }
+    o = rintf(o);
+  }
+  *scale = s;
+  *offset = (int)o;
+  return isfinite(s) && isfinite(o);
+}
+
+// One element through the integer quantizer: clamp(rne(x/scale + offset)).
+__device__ __forceinline__ float quant_level(float x, float scale, float offset, bool has_offset,
+                                             float qmin, float qmax) {
+  float t = __fdiv_rn(x, scale);
+  if (has_offset) t = __fadd_rn(t, offset);
+  t = rintf(t);
+  return fminf(fmaxf(t, qmin), qmax);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace amct

@@ -1,0 +1,374 @@
+// Quantized GEMMs on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+//   C[M, N] = A[M, K] * B[N, K]^T      A and B K-major (K contiguous)
+//
+// One persistent CTA per SM walks 128 x 256 output tiles.  Warp roles:
+//   warp 0   TMA producer: cp.async.bulk.tensor tiles of A (128 x 128 B) and
+//            B (256 x 128 B) into a 4-stage, 128-byte-swizzled shared-memory ring;
+//   warp 1   MMA issuer: one elected lane issues tcgen05.mma (M128 x N256 x 32 B of K
+//            per instruction) from shared-memory descriptors into TMEM; owns the
+//            TMEM allocation (512 columns = two 128 x 256 fp32/int32 accumulators);
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (each warp its own
+//            32-lane quarter), apply the dequant epilogue, store to global.
+// The two accumulators let the epilogue of tile i overlap the main loop of tile
+// i+1.  No cluster launch, no multicast.  Every mbarrier wait is bounded; on a
+// timeout the kernel sets bit 1 of *status, drains and returns.
+//
+// Epilogues (fp32, each step separately rounded, in this order):
+//   W8A8 per-token : y = float(acc) * deq[n] * pertoken[m] + bias_f[n]
+//   W8A8 per-tensor: y = float(acc + bias_i32[n]) * deq[n]
+//   (the operand construction of amct_pytorch/deploy_op/npu_quantization_linear.py:61-68,
+//    :105-130 fixes where each bias is added; the call is
+//    torch_npu.npu_quant_matmul at :100-102)
+//   raw            : int32 accumulators as they are
+//   float kinds    : y = acc + bias_f[n]
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace amct {
+
+constexpr int kBM = 128, kBN = 256, kBKBytes = 128, kStages = 4;
+constexpr int kABytes = kBM * kBKBytes, kBBytes = kBN * kBKBytes, kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 512;
+constexpr int kGroupM = 16;                      // rasterisation: 16 m-tiles x all n-tiles per group
+constexpr int kThreads = 192;
+
+enum { KIND_I8 = 0, KIND_BF16 = 1, KIND_F16 = 2 };
+enum { BIAS_NONE = 0, BIAS_I32 = 1, BIAS_F32 = 2, BIAS_F16 = 3, BIAS_BF16 = 4 };
+enum { OUT_F32 = 0, OUT_F16 = 1, OUT_BF16 = 2, OUT_I32 = 3 };
+
+struct GemmParams {
+  int64_t m, n, k;             // k in elements
+  int kind;
+  const float* deq;            // [n] or null
+  const float* pertoken;       // [m] or null
+  const void* bias;            // [n] or null
+  int bias_kind;
+  void* out;
+  int out_kind;
+  int64_t ld_out;              // elements
+  int* status;
+};
+
+struct __align__(1024) GemmSmem {
+  uint8_t tiles[kStages][kStageBytes];
+  float epi_scale[4][kBN];
+  float epi_bias[4][kBN];
+  uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t* tm, int64_t* tn) {
+  const int64_t per_group = (int64_t)kGroupM * tiles_n;
+  const int64_t g = tile / per_group, r = tile - g * per_group;
+  const int64_t m0 = g * kGroupM;
+  const int64_t gm = (tiles_m - m0) < kGroupM ? (tiles_m - m0) : kGroupM;
+  *tn = r / gm;
+  *tm = m0 + r % gm;
+}
+
+__device__ __forceinline__ float bias_at(const void* bias, int kind, int64_t n) {
+  switch (kind) {
+    case BIAS_F32: return reinterpret_cast<const float*>(bias)[n];
+    case BIAS_F16: return __half2float(reinterpret_cast<const __half*>(bias)[n]);
+    case BIAS_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[n]);
+    case BIAS_I32: return __int_as_float(reinterpret_cast<const int*>(bias)[n]);   // carried as raw bits
+  }
+  return 0.f;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmSmem& s = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int esize = p.kind == KIND_I8 ? 1 : 2;
+  const int bk = kBKBytes / esize;                                   // K elements per stage
+  const int64_t num_kb = (p.k + bk - 1) / bk;
+  const int64_t tiles_m = (p.m + kBM - 1) / kBM, tiles_n = (p.n + kBN - 1) / kBN;
+  const int64_t num_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    for (int i = 0; i < kStages; ++i) { tc05::mbar_init(tc05::smem_u32(&s.full[i]), 1); tc05::mbar_init(tc05::smem_u32(&s.empty[i]), 1); }
+    for (int i = 0; i < 2; ++i) { tc05::mbar_init(tc05::smem_u32(&s.tmem_full[i]), 1); tc05::mbar_init(tc05::smem_u32(&s.tmem_empty[i]), 4); }
+    tc05::fence_barrier_init();
+    tc05::prefetch_tmap(&tma_a);
+    tc05::prefetch_tmap(&tma_b);
+  }
+  if (warp == 1) {
+    tc05::tmem_alloc(tc05::smem_u32(&s.tmem_base), kTmemCols);
+    tc05::tmem_relinquish();
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem_base = s.tmem_base;
+  volatile int* abort_flag = &s.abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (tc05::elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      bool alive = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        int64_t tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        for (int64_t kb = 0; kb < num_kb; ++kb) {
+          if (!tc05::mbar_wait(tc05::smem_u32(&s.empty[stage]), phase ^ 1, abort_flag)) { alive = false; break; }
+          const uint32_t bar = tc05::smem_u32(&s.full[stage]);
+          tc05::mbar_expect_tx(bar, kStageBytes);
+          const uint32_t dst = tc05::smem_u32(&s.tiles[stage][0]);
+          tc05::tma_load_2d(dst, &tma_a, bar, (int)(kb * bk), (int)(tm * kBM));
+          tc05::tma_load_2d(dst + kABytes, &tma_b, bar, (int)(kb * bk), (int)(tn * kBN));
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (tc05::elect_one()) {
+      const uint32_t idesc = p.kind == KIND_I8     ? tc05::make_idesc(2, 1, 1, kBM, kBN)
+                             : p.kind == KIND_BF16 ? tc05::make_idesc(1, 1, 1, kBM, kBN)
+                                                   : tc05::make_idesc(1, 0, 0, kBM, kBN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool alive = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+        if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_empty[acc]), acc_phase ^ 1, abort_flag)) break;
+        tc05::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int64_t kb = 0; kb < num_kb; ++kb) {
+          if (!tc05::mbar_wait(tc05::smem_u32(&s.full[stage]), phase, abort_flag)) { alive = false; break; }
+          tc05::fence_after_sync();
+          const uint32_t a0 = tc05::smem_u32(&s.tiles[stage][0]);
+          const uint32_t b0 = a0 + kABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBKBytes / 32; ++ks) {
+            const uint64_t adesc = tc05::smem_desc_sw128(a0 + ks * 32);
+            const uint64_t bdesc = tc05::smem_desc_sw128(b0 + ks * 32);
+            const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+            if (p.kind == KIND_I8) tc05::umma_i8(d_tmem, adesc, bdesc, idesc, accumulate);
+            else tc05::umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
+          }
+          tc05::umma_commit(tc05::smem_u32(&s.empty[stage]));        // frees the stage when these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!alive) break;
+        tc05::umma_commit(tc05::smem_u32(&s.tmem_full[acc]));        // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                                    // TMEM lane quarter this warp may read
+    const int ew = warp - 2;
+    float* sc = s.epi_scale[ew];
+    float* sb = s.epi_bias[ew];
+    uint32_t acc = 0, acc_phase = 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      const int64_t n0 = tn * kBN;
+      const int64_t row = tm * kBM + quarter * 32 + lane;
+      // stage the per-column factors of this tile (per warp, so only __syncwarp is needed)
+      for (int c = lane; c < kBN; c += 32) {
+        const int64_t n = n0 + c;
+        sc[c] = (p.deq && n < p.n) ? p.deq[n] : 1.f;
+        sb[c] = (p.bias_kind != BIAS_NONE && n < p.n) ? bias_at(p.bias, p.bias_kind, n) : 0.f;
+      }
+      const float pt = (p.pertoken && row < p.m) ? p.pertoken[row] : 1.f;
+      __syncwarp();
+      if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_full[acc]), acc_phase, abort_flag)) break;
+      tc05::fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBN; c0 += 32) {
+        uint32_t r[32];
+        tc05::tmem_ld_32x32(t_row + c0, r);
+        tc05::tmem_ld_wait();
+        if (row < p.m && n0 + c0 < p.n) {
+          float y[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (p.kind == KIND_I8) {
+              int a = (int)r[j];
+              if (p.bias_kind == BIAS_I32) {
+                a += __float_as_int(sb[c0 + j]);
+                y[j] = __fmul_rn((float)a, sc[c0 + j]);
+              } else {
+                float v = __fmul_rn((float)a, sc[c0 + j]);
+                if (p.pertoken) v = __fmul_rn(v, pt);
+                if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c0 + j]);
+                y[j] = v;
+              }
+            } else {
+              float v = __uint_as_float(r[j]);
+              if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c0 + j]);
+              y[j] = v;
+            }
+          }
+          const int64_t nleft = p.n - (n0 + c0);
+          const int64_t off = row * p.ld_out + n0 + c0;
+          if (p.out_kind == OUT_I32) {
+            int* o = reinterpret_cast<int*>(p.out) + off;
+            if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = (int)r[j];
+            }
+          } else if (p.out_kind == OUT_F32) {
+            float* o = reinterpret_cast<float*>(p.out) + off;
+            if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = y[j];
+            }
+          } else {
+            uint32_t h[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (p.out_kind == OUT_BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+                h[j] = *reinterpret_cast<uint32_t*>(&v);
+              } else {
+                __half2 v = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
+                h[j] = *reinterpret_cast<uint32_t*>(&v);
+              }
+            }
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + off;
+            if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(h[j], h[j + 1], h[j + 2], h[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = (uint16_t)(h[j >> 1] >> (16 * (j & 1)));
+            }
+          }
+        }
+      }
+      tc05::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc05::mbar_arrive(tc05::smem_u32(&s.tmem_empty[acc]));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, 2);
+    // let copies and MMAs already in flight land before the shared memory and TMEM go away
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc05::fence_after_sync();
+    tc05::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [rows, k] K-major matrix -> tensor map with a (128 bytes of K) x box_rows box, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int esize, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return AMCT_ERR_CUDA;
+  if (!aligned16(base) || (ld * esize) % 16 != 0) return AMCT_ERR_ALIGN;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld * esize)};
+  cuuint32_t box[2] = {(cuuint32_t)(kBKBytes / esize), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? AMCT_OK : AMCT_ERR_CUDA;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b, const GemmParams& p, cudaStream_t st) {
+  if (p.m == 0 || p.n == 0) return AMCT_OK;
+  if (p.k <= 0) return AMCT_ERR_ARG;
+  if (p.m > 0x7fffffffLL || p.n > 0x7fffffffLL || p.k > 0x7fffffffLL) return AMCT_ERR_UNSUPPORTED;
+  const int esize = p.kind == KIND_I8 ? 1 : 2;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, esize, p.m, p.k, ld_a, kBM);
+  if (rc != AMCT_OK) return rc;
+  rc = make_map(&mb, b, esize, p.n, p.k, ld_b, kBN);
+  if (rc != AMCT_OK) return rc;
+  const size_t smem = sizeof(GemmSmem) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return AMCT_ERR_CUDA;
+    attr_set = true;
+  }
+  const int64_t tiles = ((p.m + kBM - 1) / kBM) * ((p.n + kBN - 1) / kBN);
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  gemm_tcgen05_kernel<<<grid, kThreads, smem, st>>>(ma, mb, p);
+  AMCT_CHECK_LAUNCH();
+  return AMCT_OK;
+}
+
+}  // namespace amct
+
+extern "C" int amct_gemm_w8a8(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64_t k, int64_t ld_a, int64_t ld_b,
+                              const float* deq_scale, const float* pertoken_scale, const void* bias, int bias_kind,
+                              void* out, int out_kind, int64_t ld_out, int* status, void* stream) {
+  if (m < 0 || n < 0 || k < 0 || ld_a < k || ld_b < k || ld_out < n) return AMCT_ERR_ARG;
+  if (m && n && (!a || !b || !out)) return AMCT_ERR_ARG;
+  if (bias_kind < amct::BIAS_NONE || bias_kind > amct::BIAS_BF16 || (bias_kind != amct::BIAS_NONE && !bias)) return AMCT_ERR_ARG;
+  if (out_kind < amct::OUT_F32 || out_kind > amct::OUT_I32) return AMCT_ERR_ARG;
+  if (out_kind != amct::OUT_I32 && !deq_scale) return AMCT_ERR_ARG;
+  if (bias_kind == amct::BIAS_I32 && pertoken_scale) return AMCT_ERR_ARG;   // int32 bias belongs to the per-tensor mode
+  amct::GemmParams p{};
+  p.m = m; p.n = n; p.k = k; p.kind = amct::KIND_I8;
+  p.deq = deq_scale; p.pertoken = pertoken_scale; p.bias = bias; p.bias_kind = bias_kind;
+  p.out = out; p.out_kind = out_kind; p.ld_out = ld_out; p.status = status;
+  return amct::launch_gemm(a, b, ld_a, ld_b, p, (cudaStream_t)stream);
+}
+
+extern "C" int amct_gemm_f16(const void* a, const void* b, int dtype, int64_t m, int64_t n, int64_t k, int64_t ld_a,
+                             int64_t ld_b, const void* bias, int bias_kind, void* out, int out_kind, int64_t ld_out,
+                             int* status, void* stream) {
+  if (m < 0 || n < 0 || k < 0 || ld_a < k || ld_b < k || ld_out < n) return AMCT_ERR_ARG;
+  if (m && n && (!a || !b || !out)) return AMCT_ERR_ARG;
+  if (dtype != AMCT_DTYPE_F16 && dtype != AMCT_DTYPE_BF16) return AMCT_ERR_ARG;
+  if (bias_kind == amct::BIAS_I32 || bias_kind < 0 || bias_kind > amct::BIAS_BF16 || (bias_kind && !bias)) return AMCT_ERR_ARG;
+  if (out_kind < amct::OUT_F32 || out_kind > amct::OUT_BF16) return AMCT_ERR_ARG;
+  amct::GemmParams p{};
+  p.m = m; p.n = n; p.k = k; p.kind = dtype == AMCT_DTYPE_BF16 ? amct::KIND_BF16 : amct::KIND_F16;
+  p.bias = bias; p.bias_kind = bias_kind; p.out = out; p.out_kind = out_kind; p.ld_out = ld_out; p.status = status;
+  return amct::launch_gemm(a, b, ld_a, ld_b, p, (cudaStream_t)stream);
+}

@@ -1,0 +1,144 @@
+/* C ABI of the B200 (sm_100a) implementation of AMCT's quantization hot path.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless it is named host_*; the caller
+ *     owns all memory, nothing here allocates persistent device memory;
+ *   - `stream` is a cudaStream_t; calls enqueue work and return, they do not
+ *     synchronise;
+ *   - the return value is AMCT_OK or a negative AMCT_ERR_* code; arguments are
+ *     validated on the host before anything is launched;
+ *   - `status` (optional, may be NULL) is a device int; bit 0 is OR-ed in when a
+ *     kernel meets a non-finite value where the reference raises
+ *     "Param scale has invalid value inf, nan or zeros!"
+ *     (amct_pytorch/quantize_op/utils.py:54-72);
+ *   - `dtype` is AMCT_DTYPE_*; leading dimensions are in elements.
+ *
+ * Each entry point names the reference interface it stands in for (paths
+ * relative to the reference project root).
+ */
+#ifndef AMCT_B200_H_
+#define AMCT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { AMCT_OK = 0, AMCT_ERR_ARG = -1, AMCT_ERR_ALIGN = -2, AMCT_ERR_CUDA = -3, AMCT_ERR_UNSUPPORTED = -4,
+       AMCT_ERR_TIMEOUT = -5 };
+enum { AMCT_DTYPE_F32 = 0, AMCT_DTYPE_F16 = 1, AMCT_DTYPE_BF16 = 2 };
+enum { AMCT_STRATEGY_TENSOR = 0, AMCT_STRATEGY_CHANNEL = 1, AMCT_STRATEGY_GROUP = 2 };
+enum { AMCT_RULE_RELEASED = 0, AMCT_RULE_EXPERIMENTAL = 1 };
+enum { AMCT_PRE_NONE = 0, AMCT_PRE_MUL = 1, AMCT_PRE_DIV = 2 };
+enum { AMCT_OUT_NONE = 0, AMCT_OUT_I8 = 1, AMCT_OUT_I32 = 2, AMCT_OUT_PACK4 = 3, AMCT_OUT_FAKE = 4,
+       AMCT_OUT_FAKE_AWQ = 5 };
+enum { AMCT_AXIS_TENSOR = 0, AMCT_AXIS_COLUMN = 1 };
+
+/* Version of this ABI; bumped when a signature changes. */
+int amct_abi_version(void);
+
+/* Dynamic per-token symmetric INT8 activation quantization, one scale per row.
+ * Replaces the eager sequence amax/amin over K
+ * (amct_pytorch/quantize_op/minmax_module.py:99-105) -> calculate_scale_offset
+ * (amct_pytorch/quantize_op/utils.py:75-108) -> convert_dtype(x / scale)
+ * (amct_pytorch/utils/quant_util.py:57-73), and, when `smooth` is given, the
+ * `x * scale_factor` pass of NpuQuantizationLinear.forward
+ * (amct_pytorch/deploy_op/npu_quantization_linear.py:96-97).
+ * rule = AMCT_RULE_EXPERIMENTAL follows ActivationQuantizer.get_scale_zero
+ * (amct_pytorch/experimental/quantization/DeepSeekV3.2/cores/quantization/node.py:181-204).
+ * x [rows, k] (ld_x), smooth [k] in x's dtype or NULL, q int8 [rows, k] (ld_q),
+ * scale fp32 [rows]. */
+int amct_quant_dynamic_pertoken(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x,
+                                const void* smooth, int rule, int8_t* q, int64_t ld_q, float* scale,
+                                int* status, void* stream);
+
+/* Row-wise quantizer over a [rows, k] matrix; each row is read once.
+ * compute=1 derives scale/offset per row (AMCT_STRATEGY_CHANNEL) or per group of
+ * `group` elements (AMCT_STRATEGY_GROUP, a ragged last group is zero padded) and
+ * writes them; compute=0 reads them (also AMCT_STRATEGY_TENSOR: one value).
+ * Replaces get_weight_min_max_by_granularity + calculate_scale_offset
+ * (amct_pytorch/quantize_op/utils.py:75-136), quant_weight / convert_dtype
+ * (amct_pytorch/utils/quant_util.py:57-93), NpuQuantizationLinear.quant_wts
+ * (amct_pytorch/deploy_op/npu_quantization_linear.py:72-87), quant_dequant_weight
+ * (amct_pytorch/utils/quant_util.py:162-188, AMCT_OUT_FAKE) and do_quant ->
+ * convert_precision -> do_dequant (amct_pytorch/algorithm/awq.py:129-170,
+ * AMCT_OUT_FAKE_AWQ).  pre/pre_op fold apply_smooth_weight (MUL) or
+ * apply_awq_quantize_weight (DIV) (amct_pytorch/utils/quant_util.py:96-159) into
+ * the load.  AMCT_OUT_PACK4 writes two INT4 codes per byte (code + 8, even k in
+ * the low nibble), standing in for torch_npu.npu_convert_weight_to_int4pack
+ * (amct_pytorch/deploy_op/weight_npu_quant_module.py:54-57).
+ * scale fp32 / offset int32: [1] | [rows] | [rows, ceil(k/group)]; offset may be
+ * NULL when symmetric.  out: int8 | int32 | uint8 [rows, k/2] | x's dtype. */
+int amct_quant_rows(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x,
+                    const void* pre, int pre_op, int compute, int strategy, int group, int bits,
+                    int symmetric, float* scale, int* offset, int out_mode, void* out, int64_t ld_out,
+                    int* status, void* stream);
+
+/* min and max of a [rows, k] matrix over the whole tensor (AMCT_AXIS_TENSOR, one
+ * value) or per column over all rows (AMCT_AXIS_COLUMN, k values), in x's dtype.
+ * merge=1 folds the result into the values already in out_min/out_max (running
+ * observers).  Replaces torch.max/min (amct_pytorch/quantize_op/minmax_module.py:96-98,
+ * :107-110) and amax/amin over tokens
+ * (amct_pytorch/quantize_op/smooth_quant_module.py:79-91).
+ * workspace: at least amct_minmax_workspace_bytes(k) bytes of device memory. */
+int64_t amct_minmax_workspace_bytes(int64_t k);
+int amct_minmax(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int axis, int merge,
+                void* out_min, void* out_max, void* workspace, int* status, void* stream);
+
+/* scale/offset from n (max, min) pairs given in `dtype`.
+ * Replaces calculate_scale_offset (amct_pytorch/quantize_op/utils.py:75-108). */
+int amct_scale_offset(const void* vmax, const void* vmin, int dtype, int64_t n, int bits, int symmetric,
+                      float* scale, int* offset, int* status, void* stream);
+
+/* Static activation quantization q = sat_int8(rne(x * scale + offset)), scale
+ * and offset in x's dtype: one element (per-tensor) or one per token, i.e. per
+ * index of the second-to-last axis (x is [outer, tokens, k] contiguous).
+ * Stands in for torch_npu.npu_quantize(x, scales, zero_points, torch.int8, axis,
+ * div_mode=False) as called at amct_pytorch/deploy_op/npu_quantization_linear.py:98-99;
+ * `smooth` folds the multiply at :96-97. */
+int amct_quantize_static(const void* x, int dtype, int64_t outer, int64_t tokens, int64_t k,
+                         const void* scale, const void* offset, int per_token, const void* smooth,
+                         int8_t* q, void* stream);
+
+/* rowsum[n] = sum_k wq[n, k] over INT8 codes stored K-major ([n_rows, k], ld).
+ * The integer statement of the fp32 matmul that builds offset_bias
+ * (amct_pytorch/deploy_op/npu_quantization_linear.py:56-59). */
+int amct_rowsum_i8(const int8_t* wq, int64_t n_rows, int64_t k, int64_t ld, int32_t* out, void* stream);
+
+/* Out-of-place transpose of an INT8 matrix [rows, cols] -> [cols, rows]
+ * (the `torch.transpose(...)` the reference applies to the weight codes,
+ * amct_pytorch/deploy_op/npu_quantization_linear.py:54). */
+int amct_transpose_i8(const int8_t* in, int64_t rows, int64_t cols, int8_t* out, void* stream);
+
+/* ---- tensor-core GEMMs (tcgen05, TMEM accumulators, TMA-fed) -------------- */
+enum { AMCT_BIAS_NONE = 0, AMCT_BIAS_I32 = 1, AMCT_BIAS_F32 = 2, AMCT_BIAS_F16 = 3, AMCT_BIAS_BF16 = 4 };
+enum { AMCT_GEMM_OUT_F32 = 0, AMCT_GEMM_OUT_F16 = 1, AMCT_GEMM_OUT_BF16 = 2, AMCT_GEMM_OUT_I32 = 3 };
+
+/* W8A8 quantized matmul: acc_i32[m, n] = sum_k a[m, k] * b[n, k], then
+ *   bias int32 (per-tensor mode): out = float(acc + bias[n]) * deq_scale[n]
+ *   otherwise  (per-token mode) : out = float(acc) * deq_scale[n] (* pertoken_scale[m]) (+ bias[n])
+ * each step a separately rounded fp32 operation; AMCT_GEMM_OUT_I32 stores the
+ * raw accumulators.  Stands in for torch_npu.npu_quant_matmul(x1, x2, scale=,
+ * pertoken_scale=, bias=, output_dtype=) as called at
+ * amct_pytorch/deploy_op/npu_quantization_linear.py:100-102.  a [m, k] and
+ * b [n, k] are INT8, K contiguous (b is the reference's [K, N] weight buffer
+ * stored transposed); both base pointers and both leading dimensions must be
+ * multiples of 16 bytes.  bit 1 of *status is set if a device-side wait timed out. */
+int amct_gemm_w8a8(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64_t k, int64_t ld_a, int64_t ld_b,
+                   const float* deq_scale, const float* pertoken_scale, const void* bias, int bias_kind,
+                   void* out, int out_kind, int64_t ld_out, int* status, void* stream);
+
+/* 16-bit float GEMM out[m, n] = sum_k a[m, k] * b[n, k] (+ bias[n]), fp32
+ * accumulation; dtype AMCT_DTYPE_F16 or AMCT_DTYPE_BF16 for both operands.  The
+ * tensor-core stage behind npu_weight_quant_batchmatmul
+ * (amct_pytorch/deploy_op/weight_npu_quant_module.py:116-117) once the weight
+ * has been dequantized, and behind the HiFloat8 Linear. */
+int amct_gemm_f16(const void* a, const void* b, int dtype, int64_t m, int64_t n, int64_t k, int64_t ld_a,
+                  int64_t ld_b, const void* bias, int bias_kind, void* out, int out_kind, int64_t ld_out,
+                  int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AMCT_B200_H_ */
