@@ -12,6 +12,11 @@ import torch
 from . import lib as _l
 
 _DT = {torch.float32: _l.DTYPE_F32, torch.float16: _l.DTYPE_F16, torch.bfloat16: _l.DTYPE_BF16}
+# launches of this library's kernels since the counter was last reset (bench.py reads it)
+COUNTERS = {'launches': 0}
+# when set to a list, every GEMM launch appends (start event, end event, 2*M*N*K)
+GEMM_PROFILE = None
+
 SCALE_ERROR = "Param scale has invalid value inf, nan or zeros!"      # amct_pytorch/quantize_op/utils.py:66-67
 
 
@@ -79,6 +84,7 @@ def quant_dynamic_per_token(x, smooth=None, rule='released', check=False):
         _p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), _p(smooth), c_int(_l.RULE[rule]),
         _p(q), c_int64(k), _p(scale), st.ptr() if st else c_void_p(0), _stream())
     _l.check(rc, 'amct_quant_dynamic_pertoken')
+    COUNTERS['launches'] += 1
     if st:
         st.raise_if_set()
     return q.reshape(x.shape), scale
@@ -139,6 +145,7 @@ def quant_rows(w, quant_type, symmetric, strategy, group=None, scale=None, offse
         c_int(sym_flag), _p(scale), _p(offset), c_int(mode), _p(o), c_int64(ld_out),
         st.ptr() if st else c_void_p(0), _stream())
     _l.check(rc, 'amct_quant_rows')
+    COUNTERS['launches'] += 1
     if st:
         st.raise_if_set()
     return scale, offset, o
@@ -165,6 +172,7 @@ def minmax(x, axis, running=None):
                        c_int(_l.AXIS_TENSOR if axis == 'tensor' else _l.AXIS_COLUMN), c_int(merge),
                        _p(mn), _p(mx), _p(ws), st.ptr(), _stream())
     _l.check(rc, 'amct_minmax')
+    COUNTERS['launches'] += 2
     if axis == 'column':
         return mn.reshape(1, k), mx.reshape(1, k)
     return mn, mx
@@ -183,6 +191,7 @@ def scale_offset(vmax, vmin, symmetric, quant_type):
     rc = _l.load().amct_scale_offset(_p(a), _p(b), c_int(_dt(a)), c_int64(n), c_int(bits_of(quant_type)),
                                      c_int(1 if symmetric else 0), _p(scale), _p(offset), st.ptr(), _stream())
     _l.check(rc, 'amct_scale_offset')
+    COUNTERS['launches'] += 1
     st.raise_if_set()
     return scale.reshape(shape), None if offset is None else offset.reshape(shape)
 
@@ -208,6 +217,7 @@ def quantize_static(x, scales, zero_points, axis=-1, smooth=None):
     rc = _l.load().amct_quantize_static(_p(x), c_int(_dt(x)), c_int64(outer), c_int64(tokens), c_int64(k),
                                         _p(s), _p(z), c_int(1 if per_token else 0), _p(smooth), _p(q), _stream())
     _l.check(rc, 'amct_quantize_static')
+    COUNTERS['launches'] += 1
     return q
 
 
@@ -218,6 +228,7 @@ def rowsum_i8(wq_nk):
     rc = _l.load().amct_rowsum_i8(_p(wq_nk), c_int64(wq_nk.shape[0]), c_int64(wq_nk.shape[1]),
                                   c_int64(wq_nk.stride(0)), _p(out), _stream())
     _l.check(rc, 'amct_rowsum_i8')
+    COUNTERS['launches'] += 1
     return out
 
 
@@ -227,6 +238,7 @@ def transpose_i8(t):
     out = torch.empty((t.shape[1], t.shape[0]), dtype=t.dtype, device=t.device)
     rc = _l.load().amct_transpose_i8(_p(t), c_int64(t.shape[0]), c_int64(t.shape[1]), _p(out), _stream())
     _l.check(rc, 'amct_transpose_i8')
+    COUNTERS['launches'] += 1
     return out
 
 
@@ -234,6 +246,21 @@ def transpose_i8(t):
 # tensor-core GEMMs
 _OUT_KIND = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.int32: 3}
 _BIAS_KIND = {torch.int32: 1, torch.float32: 2, torch.float16: 3, torch.bfloat16: 4}
+
+
+def _prof_begin():
+    if GEMM_PROFILE is None:
+        return None
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    return e
+
+
+def _prof_end(start, n_ops):
+    if start is not None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        GEMM_PROFILE.append((start, e, n_ops))
 
 
 def _kmajor(t):
@@ -272,11 +299,14 @@ def gemm_w8a8(q, w_nk, deq_scale=None, pertoken_scale=None, bias=None, out_dtype
     if bias is not None:
         bias = bias.reshape(-1).contiguous()
         bk = _BIAS_KIND[bias.dtype]
+    prof = _prof_begin()
     rc = _l.load().amct_gemm_w8a8(
         _p(q), _p(w_nk), c_int64(m), c_int64(n), c_int64(k), c_int64(q.stride(0)), c_int64(w_nk.stride(0)),
         _p(deq_scale), _p(pertoken_scale), _p(bias), c_int(bk), _p(out), c_int(_OUT_KIND[out.dtype]),
         c_int64(out.stride(0)), _p(status) if status is not None else c_void_p(0), _stream())
     _l.check(rc, 'amct_gemm_w8a8')
+    COUNTERS['launches'] += 1
+    _prof_end(prof, 2 * m * n * k)
     return out
 
 
@@ -293,9 +323,54 @@ def gemm_f16(a, b_nk, bias=None, out_dtype=None, out=None, status=None):
     if bias is not None:
         bias = bias.reshape(-1).contiguous()
         bk = _BIAS_KIND[bias.dtype]
+    prof = _prof_begin()
     rc = _l.load().amct_gemm_f16(
         _p(a), _p(b_nk), c_int(_dt(a)), c_int64(m), c_int64(n), c_int64(k), c_int64(a.stride(0)),
         c_int64(b_nk.stride(0)), _p(bias), c_int(bk), _p(out), c_int(_OUT_KIND[out.dtype]), c_int64(out.stride(0)),
         _p(status) if status is not None else c_void_p(0), _stream())
     _l.check(rc, 'amct_gemm_f16')
+    COUNTERS['launches'] += 1
+    _prof_end(prof, 2 * m * n * k)
+    return out
+
+
+def minmax_rows(x2d, pre=None, pre_op='none', running=None):
+    """(min, max) per row of a [rows, K] view, optional element-wise pre-scale [K] in x's dtype."""
+    _need_cuda(x2d, pre)
+    x2, rows, k, ld = _rows2d(x2d)
+    if running is None:
+        mn = torch.empty(rows, dtype=x2.dtype, device=x2.device)
+        mx = torch.empty(rows, dtype=x2.dtype, device=x2.device)
+        merge = 0
+    else:
+        mn, mx = running
+        merge = 1
+    if pre is not None:
+        pre = pre.reshape(-1).to(x2.dtype).contiguous()
+        assert pre.numel() == k
+    pop = {'none': _l.PRE_NONE, 'mul': _l.PRE_MUL, 'div': _l.PRE_DIV}[pre_op]
+    st = Status(x2.device)
+    rc = _l.load().amct_minmax_rows(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), _p(pre), c_int(pop),
+                                    c_int(merge), _p(mn), _p(mx), st.ptr(), _stream())
+    _l.check(rc, 'amct_minmax_rows')
+    COUNTERS['launches'] += 1
+    return mn, mx
+
+
+def dequant_weight(codes_nk, bits, scale_gn, offset_gn, group, out=None):
+    """K-major weight codes -> [N, K] weight in the dtype of scale_gn (fp16/bf16)."""
+    _need_cuda(codes_nk, scale_gn, offset_gn)
+    n = codes_nk.shape[0]
+    k = codes_nk.shape[1] * (2 if bits == 4 else 1)
+    assert codes_nk.stride(1) == 1
+    scale_gn = scale_gn.contiguous()
+    if offset_gn is not None:
+        offset_gn = offset_gn.to(scale_gn.dtype).contiguous()
+    if out is None:
+        out = torch.empty((n, k), dtype=scale_gn.dtype, device=codes_nk.device)
+    rc = _l.load().amct_dequant_weight(_p(codes_nk), c_int(bits), c_int64(n), c_int64(k), c_int64(codes_nk.stride(0)),
+                                       _p(scale_gn), _p(offset_gn), c_int(group or 0), c_int(_dt(scale_gn)), _p(out),
+                                       c_int64(out.stride(0)), _stream())
+    _l.check(rc, 'amct_dequant_weight')
+    COUNTERS['launches'] += 1
     return out

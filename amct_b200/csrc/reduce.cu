@@ -159,6 +159,60 @@ static int run_minmax(const T* x, int64_t rows, int64_t k, int64_t ld, int axis,
   return AMCT_OK;
 }
 
+
+// One CTA per row: min/max of each row, optional element-wise pre-scale in T.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(128) minmax_rows_kernel(const T* x, int64_t k, int64_t ld, const T* pre, int pre_op,
+                                                          int merge, T* out_min, T* out_max, int* status) {
+  constexpr int E = VEC ? ElemTraits<T>::kPerVec : 1;
+  const T* row = x + (int64_t)blockIdx.x * ld;
+  float mn = INFINITY, mx = -INFINITY;
+  bool nan = false;
+  for (int64_t v = threadIdx.x; v < k / E; v += blockDim.x) {
+    float f[E];
+    if constexpr (VEC) {
+      Vec16<T> raw = ld_vec_stream(row + v * E);
+#pragma unroll
+      for (int e = 0; e < E; ++e) f[e] = ElemTraits<T>::to_f(raw.v[e]);
+    } else {
+      f[0] = ElemTraits<T>::to_f(row[v]);
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      float a = f[e];
+      if (pre_op == AMCT_PRE_MUL) a = round_to<T>(__fmul_rn(a, ElemTraits<T>::to_f(pre[v * E + e])));
+      else if (pre_op == AMCT_PRE_DIV) a = round_to<T>(__fdiv_rn(a, ElemTraits<T>::to_f(pre[v * E + e])));
+      mn = fminf(mn, a); mx = fmaxf(mx, a); nan |= (a != a);
+    }
+  }
+  if (nan && status) atomicOr(status, 1);
+  __shared__ float s[8];
+  mn = warp_min(mn); mx = warp_max(mx);
+  const int w = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) { s[w] = mn; s[4 + w] = mx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 4; ++i) { mn = fminf(mn, s[i]); mx = fmaxf(mx, s[4 + i]); }
+    if (merge) {
+      mn = fminf(mn, ElemTraits<T>::to_f(out_min[blockIdx.x]));
+      mx = fmaxf(mx, ElemTraits<T>::to_f(out_max[blockIdx.x]));
+    }
+    out_min[blockIdx.x] = ElemTraits<T>::from_f(mn);
+    out_max[blockIdx.x] = ElemTraits<T>::from_f(mx);
+  }
+}
+
+template <typename T>
+static int run_minmax_rows(const T* x, int64_t rows, int64_t k, int64_t ld, const T* pre, int pre_op, int merge,
+                           T* out_min, T* out_max, int* status, cudaStream_t st) {
+  constexpr int E = ElemTraits<T>::kPerVec;
+  const bool vec = aligned16(x) && (ld * (int64_t)sizeof(T)) % 16 == 0 && k % E == 0;
+  if (vec) minmax_rows_kernel<T, true><<<(unsigned)rows, 128, 0, st>>>(x, k, ld, pre, pre_op, merge, out_min, out_max, status);
+  else minmax_rows_kernel<T, false><<<(unsigned)rows, 128, 0, st>>>(x, k, ld, pre, pre_op, merge, out_min, out_max, status);
+  AMCT_CHECK_LAUNCH();
+  return AMCT_OK;
+}
+
 template <typename T>
 __global__ void scale_offset_kernel(const T* vmax, const T* vmin, int64_t n, int bits, int symmetric, float* scale,
                                     int* offset, int* status) {
@@ -236,6 +290,25 @@ extern "C" int amct_minmax(const void* x, int dtype, int64_t rows, int64_t k, in
     case AMCT_DTYPE_BF16:
       return amct::run_minmax<__nv_bfloat16>((const __nv_bfloat16*)x, rows, k, ld_x, axis, merge, (__nv_bfloat16*)out_min,
                                              (__nv_bfloat16*)out_max, ws, status, st);
+  }
+  return AMCT_ERR_ARG;
+}
+
+extern "C" int amct_minmax_rows(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, const void* pre,
+                                int pre_op, int merge, void* out_min, void* out_max, int* status, void* stream) {
+  if (rows <= 0 || k <= 0 || !x || !out_min || !out_max || ld_x < k || rows > 0x7fffffffLL) return AMCT_ERR_ARG;
+  if (pre_op != AMCT_PRE_NONE && !pre) return AMCT_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case AMCT_DTYPE_F32:
+      return amct::run_minmax_rows<float>((const float*)x, rows, k, ld_x, (const float*)pre, pre_op, merge, (float*)out_min,
+                                          (float*)out_max, status, st);
+    case AMCT_DTYPE_F16:
+      return amct::run_minmax_rows<__half>((const __half*)x, rows, k, ld_x, (const __half*)pre, pre_op, merge, (__half*)out_min,
+                                           (__half*)out_max, status, st);
+    case AMCT_DTYPE_BF16:
+      return amct::run_minmax_rows<__nv_bfloat16>((const __nv_bfloat16*)x, rows, k, ld_x, (const __nv_bfloat16*)pre, pre_op, merge,
+                                                  (__nv_bfloat16*)out_min, (__nv_bfloat16*)out_max, status, st);
   }
   return AMCT_ERR_ARG;
 }

@@ -1,0 +1,110 @@
+import torch
+
+from ..backend import ops
+
+
+class NpuQuantizationLinear(torch.nn.Module):
+    """W8A8 quantized Linear for deployment.
+
+    Constructor argument, buffer names, shapes and dtypes follow
+    amct_pytorch/deploy_op/npu_quantization_linear.py:22-130:
+      act_scale / act_offset  [1] or [tokens], output dtype (reciprocal activation scale, offset)
+      scale_factor            [1, K] reciprocal SmoothQuant factor (only with SmoothQuant)
+      quantized_weight        [K, N] int8
+      deq_scale               [N] fp32;  pertoken_scale [tokens] fp32 (per-token mode)
+      bias                    [N] int32 (per-tensor mode, offset_bias folded in) or float (per-token)
+    quantized_weight is a transposed VIEW of a contiguous [N, K] buffer: the MMA
+    wants both operands K-contiguous, and a view keeps the reference's shape
+    without a second copy of the weight.
+
+    forward() is two kernels: activation quantization (SmoothQuant multiply
+    folded into the load) and the tcgen05 INT8 GEMM with the dequant epilogue.
+    With a quant module marked ``dynamic_act`` the activation scale is computed
+    per token row at run time, so the token count of the input is free.
+    """
+
+    def __init__(self, quant_module):
+        super().__init__()
+        self.output_dtype = quant_module.weight.dtype
+        device = quant_module.weight.device
+        self.offset_bias = None
+        self.act_type = quant_module.act_type
+        self.dynamic_act = bool(getattr(quant_module, 'dynamic_act', False))
+        self.dynamic_rule = 'released'
+        self.act_granularity = 'PER_TENSOR'
+        self.quantize_axis = -1
+
+        scale_d = quant_module.scale_d.to(device=device)
+        offset_d = quant_module.offset_d
+        if scale_d.dim() > 1:
+            self.act_granularity = 'PER_TOKEN'
+            self.quantize_axis = -2
+        if not self.dynamic_act:
+            off = offset_d if offset_d is not None else torch.zeros(1, dtype=torch.int32, device=device)
+            off = off.to(device).repeat(scale_d.shape)
+            self.register_buffer('act_scale', (1 / scale_d).reshape(-1).to(self.output_dtype))
+            self.register_buffer('act_offset', off.reshape(-1).to(self.output_dtype))
+
+        weight = quant_module.weight.data
+        smooth = quant_module.scale
+        if smooth is not None:
+            smooth = smooth.to(device=device, dtype=weight.dtype)
+            if list(smooth.shape) != [1, weight.shape[1]]:
+                raise RuntimeError("smooth_factor shape should be {} current shape is {}".format(
+                    [1, weight.shape[1]], list(smooth.shape)))
+            self.register_buffer('scale_factor', (1 / quant_module.scale).to(device=device))
+        scale_w = quant_module.scale_w.reshape(-1).to(device=device)
+        codes_nk = self.quant_wts(weight, scale_w, quant_module.wts_type, smooth)
+        self.register_buffer('quantized_weight', codes_nk.t())
+
+        if offset_d is not None:
+            # -round(offset_d * sum_k Wq[k, n]): integer row sums instead of the fp32 matmul
+            self.offset_bias = -(offset_d.reshape(-1)[0].to(device=device, dtype=torch.int32) * ops.rowsum_i8(codes_nk))
+
+        if self.act_granularity == 'PER_TENSOR':
+            self.register_buffer('deq_scale', scale_d * scale_w)
+            self.pertoken_scale = None
+        else:
+            self.register_buffer('deq_scale', scale_w)
+            if self.dynamic_act:
+                self.pertoken_scale = None
+            else:
+                self.register_buffer('pertoken_scale', quant_module.scale_d.reshape(-1).to(torch.float32).to(device))
+        self._init_bias(quant_module, scale_d, scale_w)
+
+    @staticmethod
+    def quant_wts(weight, scale_w_tensor, wts_type, smooth=None):
+        """round(weight / scale) codes as a contiguous int8 [N, K] tensor; `smooth`
+        ([1, K]) is multiplied in first, rounded to the weight dtype."""
+        strategy = 'channel' if scale_w_tensor.shape[0] > 1 else 'tensor'
+        _, _, codes = ops.quant_rows(weight, wts_type, True, strategy, scale=scale_w_tensor, out='i8',
+                                     pre=smooth, pre_op='mul' if smooth is not None else 'none')
+        return codes
+
+    def _init_bias(self, module, scale_d, scale_w):
+        bias = module.bias
+        if bias is not None:
+            if self.act_granularity == 'PER_TENSOR':
+                bias = (bias.data / (scale_d * scale_w)).round().to(torch.int32)
+            else:
+                bias = bias.data
+            self.register_buffer('bias', bias)
+            if self.offset_bias is not None:
+                self.bias = self.bias + self.offset_bias
+        else:
+            self.bias = self.offset_bias
+
+    @torch.no_grad()
+    def forward(self, x):
+        smooth = getattr(self, 'scale_factor', None)
+        k = x.shape[-1]
+        wq_nk = self.quantized_weight.t()
+        if self.dynamic_act:
+            q, pertoken = ops.quant_dynamic_per_token(x, smooth=smooth, rule=self.dynamic_rule)
+        else:
+            q = ops.quantize_static(x, self.act_scale, self.act_offset, axis=self.quantize_axis, smooth=smooth)
+            pertoken = self.pertoken_scale
+            if pertoken is not None and x.dim() > 2:
+                pertoken = pertoken.repeat(x.numel() // (x.shape[-2] * k))
+        out = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out_dtype=self.output_dtype)
+        return out.reshape(*x.shape[:-1], -1)

@@ -1,0 +1,58 @@
+"""Scale/offset and weight statistics, computed by the CUDA kernels.
+
+Function names and return shapes follow amct_pytorch/quantize_op/utils.py:75-136;
+the arithmetic runs in amct_quant_rows / amct_minmax* / amct_scale_offset.
+"""
+import torch
+
+from ..backend import ops
+
+FLT_EPSILON = 1.192092896e-7
+
+
+def calculate_scale_offset(data_max, data_min, symmetric, data_type):
+    """(max, min) -> (scale fp32, offset int32 | None), same shape as data_max."""
+    return ops.scale_offset(data_max, data_min, symmetric, data_type)
+
+
+def _grouped_rows(weight, group_size):
+    """[N, K] -> contiguous [N * G, g] with the ragged tail zero padded
+    (amct_pytorch/utils/quant_util.py:23-53)."""
+    n, k = weight.shape
+    pad = (-k) % group_size
+    if pad:
+        weight = torch.nn.functional.pad(weight, (0, pad))
+    return weight.reshape(n * ((k + pad) // group_size), group_size), (k + pad) // group_size
+
+
+def get_weight_min_max_by_granularity(weight_data, quant_config):
+    cfg = quant_config.get('weights_cfg')
+    strategy = cfg.get('strategy')
+    n = weight_data.shape[0]
+    if strategy == 'channel':
+        mn, mx = ops.minmax_rows(weight_data)
+        return mn.reshape(n, 1), mx.reshape(n, 1)
+    if strategy == 'tensor':
+        mn, mx = ops.minmax(weight_data, 'tensor')
+        return mn.reshape(1, 1), mx.reshape(1, 1)
+    rows, groups = _grouped_rows(weight_data, cfg.get('group_size'))
+    mn, mx = ops.minmax_rows(rows)
+    return mn.reshape(n, groups, 1), mx.reshape(n, groups, 1)
+
+
+def weight_scale_offset(weight, wts_type, symmetric, strategy, group_size=None, pre=None, pre_op='none'):
+    """Fused min/max + scale rule over a weight, one read of the weight.  `pre`
+    is an optional [1, K] factor applied first in the weight dtype (SmoothQuant
+    multiply / AWQ divide).  Shapes: [N,1] | [1,1] | [N, ceil(K/g), 1]."""
+    n, k = weight.shape
+    if strategy == 'tensor':
+        w = weight
+        if pre is not None:
+            w = weight * pre.to(weight.dtype) if pre_op == 'mul' else weight / pre.to(weight.dtype)
+        mn, mx = ops.minmax(w, 'tensor')
+        scale, offset = ops.scale_offset(mx, mn, symmetric, wts_type)
+        return scale.reshape(1, 1), None if offset is None else offset.reshape(1, 1)
+    scale, offset, _ = ops.quant_rows(weight, wts_type, symmetric, strategy, group_size, out='none',
+                                      pre=pre, pre_op=pre_op if pre is not None else 'none')
+    shape = (n, 1) if strategy == 'channel' else (n, -1, 1)
+    return scale.reshape(shape), None if offset is None else offset.reshape(shape)

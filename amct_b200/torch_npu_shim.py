@@ -1,0 +1,71 @@
+"""The four backend ops of the deploy path with ``torch_npu``'s call signatures,
+running on the CUDA kernels of this package.
+
+``install()`` registers this module as ``sys.modules['torch_npu']`` so that code
+written against the reference (``import torch_npu; torch_npu.npu_quantize(...)``,
+amct_pytorch/deploy_op/npu_quantization_linear.py:95-102,
+amct_pytorch/deploy_op/weight_npu_quant_module.py:55-57,108-117) runs unchanged.
+"""
+import sys
+
+import torch
+
+from .backend import ops
+
+
+def npu_quantize(input, scales, zero_points=None, dtype=torch.int8, axis=-1, div_mode=False):
+    if dtype != torch.int8 or div_mode:
+        raise NotImplementedError('npu_quantize: only dtype=torch.int8, div_mode=False')
+    return ops.quantize_static(input, scales, zero_points, axis=axis)
+
+
+def _as_nk(w_kn):
+    """[K, N] weight -> K-contiguous [N, K] tensor (free when it already is a transposed view)."""
+    if w_kn.stride(0) == 1:
+        return w_kn.t()
+    return ops.transpose_i8(w_kn) if w_kn.dtype == torch.int8 else w_kn.t().contiguous()
+
+
+def npu_quant_matmul(x1, x2, scale, offset=None, bias=None, pertoken_scale=None, output_dtype=torch.bfloat16, **_):
+    if offset is not None:
+        raise NotImplementedError('npu_quant_matmul: offset is not used by the deploy modules')
+    k = x1.shape[-1]
+    out = ops.gemm_w8a8(x1.reshape(-1, k), _as_nk(x2), scale, pertoken_scale, bias, out_dtype=output_dtype)
+    return out.reshape(*x1.shape[:-1], -1)
+
+
+def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, quant_scale=None,
+                                 quant_offset=None, bias=None, antiquant_group_size=0, **_):
+    """x [M, K] (fp16/bf16) times the dequantized weight; weight is int8 [K, N] or packed
+    uint8 [K/2, N] as produced by npu_convert_weight_to_int4pack."""
+    bits = 4 if weight.dtype == torch.uint8 else 8
+    w = ops.dequant_weight(_as_nk(weight), bits, antiquant_scale.to(x.dtype), antiquant_offset,
+                           antiquant_group_size)
+    k = x.shape[-1]
+    out = ops.gemm_f16(x.reshape(-1, k), w, bias=bias, out_dtype=x.dtype)
+    return out.reshape(*x.shape[:-1], -1)
+
+
+def npu_convert_weight_to_int4pack(weight, inner_k_tiles=0):
+    """int32 codes [K, N] in [-8, 7] -> uint8 [K/2, N] (a transposed view of [N, K/2])."""
+    u = (weight + 8).to(torch.uint8)
+    return (u[0::2] | (u[1::2] << 4)).t().contiguous().t()
+
+
+class _Npu:
+    @staticmethod
+    def is_available():
+        return False
+
+    @staticmethod
+    def empty_cache():
+        torch.cuda.empty_cache()
+
+
+npu = _Npu()
+
+
+def install():
+    sys.modules['torch_npu'] = sys.modules[__name__]
+    if not hasattr(torch.Tensor, 'npu'):
+        torch.Tensor.npu = lambda self, *a, **k: self

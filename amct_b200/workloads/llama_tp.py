@@ -1,0 +1,166 @@
+"""Llama-architecture decoder stack whose Linears are W8A8 deploy modules, sharded
+tensor-parallel (column / row) over the ranks of one node.
+
+This is the sharded deploy workload: every Linear goes through
+amct_b200.quantize() / convert() with dynamic per-token activation quantization,
+i.e. NpuQuantizationLinear.forward = one activation-quant kernel + one tcgen05
+INT8 GEMM with the dequant epilogue.  Everything that is not a Linear (RMSNorm,
+rotary embedding, attention, SwiGLU gating, embedding, lm_head) is plain torch.
+
+Sharding (the reference has none; amct_pytorch/deploy_op/npu_quantization_linear.py
+is the unit being sharded):
+  column-parallel  q/k/v (fused) and gate/up (fused): each rank owns N/tp output
+                   channels with their weight scales; the input is replicated, so
+                   per-token activation scales are identical on every rank;
+  row-parallel     o_proj and down_proj: each rank owns K/tp input channels; the
+                   per-token scale is computed on the local K slice, the local
+                   partial is dequantized to bf16 and summed with one NCCL
+                   all-reduce per Linear.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+import amct_b200 as amct
+
+W8A8_DYNAMIC_CFG = {
+    'batch_num': 1,
+    'quant_cfg': {
+        'weights': {'type': 'int8', 'symmetric': True, 'strategy': 'channel'},
+        'inputs': {'type': 'int8', 'symmetric': True, 'strategy': 'token', 'dynamic': True},
+    },
+    'algorithm': {'minmax'},
+}
+
+
+@dataclass
+class LlamaShape:
+    hidden: int = 8192
+    n_heads: int = 64
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    intermediate: int = 28672
+    n_layers: int = 80
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+
+
+LLAMA3_70B = LlamaShape()
+LLAMA3_8B = LlamaShape(hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, intermediate=14336, n_layers=32)
+
+
+class _Shard(nn.Module):
+    """The float Linears of one rank's slice of a decoder layer (before quantization)."""
+
+    def __init__(self, shape, tp, device, gen, std=0.02):
+        super().__init__()
+        h = shape.hidden
+        qkv_out = (shape.n_heads + 2 * shape.n_kv_heads) * shape.head_dim // tp
+        inter = shape.intermediate // tp
+
+        def lin(k, n):
+            m = nn.Linear(k, n, bias=False, device='meta', dtype=torch.bfloat16)
+            m.weight = nn.Parameter(torch.empty(n, k, dtype=torch.bfloat16, device=device).normal_(0, std, generator=gen),
+                                    requires_grad=False)
+            return m
+
+        self.qkv_proj = lin(h, qkv_out)
+        self.o_proj = lin(shape.n_heads * shape.head_dim // tp, h)
+        self.gate_up_proj = lin(h, 2 * inter)
+        self.down_proj = lin(inter, h)
+
+
+def rotary_tables(shape, positions, device):
+    inv = 1.0 / (shape.rope_theta ** (torch.arange(0, shape.head_dim, 2, device=device, dtype=torch.float32) / shape.head_dim))
+    ang = positions.to(torch.float32)[:, None] * inv[None, :]
+    return ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+
+
+def apply_rotary(x, cos, sin):
+    """x [B, S, H, D]; rotate-half convention."""
+    d = x.shape[-1] // 2
+    x1, x2 = x[..., :d], x[..., d:]
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, shape, tp, group, device, gen):
+        super().__init__()
+        self.shape, self.tp, self.group = shape, tp, group
+        self.heads = shape.n_heads // tp
+        self.kv_heads = shape.n_kv_heads // tp
+        self.linears = _Shard(shape, tp, device, gen)
+        amct.quantize(self.linears, W8A8_DYNAMIC_CFG)
+        amct.convert(self.linears)
+        self.input_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+        self.post_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+
+    def _reduce(self, t):
+        if self.tp > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    def forward(self, x, cos, sin, kv_cache=None):
+        """x [B, S, hidden] bf16.  kv_cache: None (prefill, causal) or (k, v) [B, kvh, T, D]
+        holding the past keys/values (decode: S new tokens attend to T + S)."""
+        shp, lin = self.shape, self.linears
+        b, s, _ = x.shape
+        hn = F.rms_norm(x, (shp.hidden,), self.input_norm, shp.rms_eps)
+        qkv = lin.qkv_proj(hn)
+        q, k, v = qkv.split((self.heads * shp.head_dim, self.kv_heads * shp.head_dim, self.kv_heads * shp.head_dim), dim=-1)
+        q = apply_rotary(q.reshape(b, s, self.heads, shp.head_dim), cos, sin).transpose(1, 2)
+        k = apply_rotary(k.reshape(b, s, self.kv_heads, shp.head_dim), cos, sin).transpose(1, 2)
+        v = v.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
+        if kv_cache is not None:
+            k = torch.cat((kv_cache[0], k), dim=2)
+            v = torch.cat((kv_cache[1], v), dim=2)
+            attn = F.scaled_dot_product_attention(q, k, v, is_causal=False, enable_gqa=True)
+        else:
+            attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        attn = attn.transpose(1, 2).reshape(b, s, self.heads * shp.head_dim)
+        x = x + self._reduce(lin.o_proj(attn))
+        hn = F.rms_norm(x, (shp.hidden,), self.post_norm, shp.rms_eps)
+        gate, up = lin.gate_up_proj(hn).chunk(2, dim=-1)
+        x = x + self._reduce(lin.down_proj(F.silu(gate) * up))
+        return x
+
+
+class LlamaW8A8(nn.Module):
+    """Random-initialised Llama stack; rank `rank` of `tp` holds its shard of every layer."""
+
+    def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None):
+        super().__init__()
+        if shape.n_kv_heads % tp or shape.n_heads % tp or shape.intermediate % tp:
+            raise ValueError(f'tp={tp} does not divide the head / intermediate sizes')
+        self.shape, self.tp = shape, tp
+        gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+        shared = torch.Generator(device=device).manual_seed(seed)            # replicated tensors: same on every rank
+        self.embed = torch.empty(shape.vocab, shape.hidden, dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=shared)
+        self.lm_head = torch.empty(shape.vocab, shape.hidden, dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=shared)
+        self.final_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+        self.layers = nn.ModuleList(DecoderLayer(shape, tp, group, device, gen)
+                                    for _ in range(n_layers if n_layers is not None else shape.n_layers))
+
+    @torch.no_grad()
+    def forward(self, token_ids, kv_caches=None, past_len=0):
+        """token_ids [B, S] -> logits of the last position [B, vocab] (fp32)."""
+        b, s = token_ids.shape
+        x = F.embedding(token_ids, self.embed)
+        pos = torch.arange(past_len, past_len + s, device=token_ids.device)
+        cos, sin = rotary_tables(self.shape, pos, token_ids.device)
+        for i, layer in enumerate(self.layers):
+            x = layer(x, cos, sin, None if kv_caches is None else kv_caches[i])
+        x = F.rms_norm(x[:, -1], (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
+        return (x @ self.lm_head.t()).float()
+
+    def linear_ops_per_token(self):
+        """2*K*N summed over the quantized Linears of all layers (whole model, all ranks)."""
+        sh = self.shape
+        per_layer = 2 * (sh.hidden * (sh.n_heads + 2 * sh.n_kv_heads) * sh.head_dim + sh.n_heads * sh.head_dim * sh.hidden
+                         + sh.hidden * 2 * sh.intermediate + sh.intermediate * sh.hidden)
+        return per_layer * len(self.layers)

@@ -1,0 +1,272 @@
+"""Benchmark of the W8A8 deploy path on a Llama-3-70B-shaped stack (prefill).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one prefill forward of batch 32 x seq 2048 random tokens through 80
+decoder layers whose Linears are NpuQuantizationLinear deploy modules (dynamic
+per-token INT8 activation quantization + tcgen05 INT8 GEMM + dequant epilogue),
+tensor-parallel over the N ranks with NCCL all-reduce.  Total work is fixed as N
+grows (strong scaling).  Weights are random-init, data synthetic.
+
+Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
+  e2e           same metric with the token ids copied from pinned host memory and the
+                logits read back to the host inside the timed region
+  roofline      the dominant kernel (INT8 GEMM): achieved = algorithmic 2*M*N*K of every
+                launch / its CUDA-event duration, measured live in a separate profiled
+                pass of the same step; peak = 2 x the measured bf16 tensor peak
+  cpu_baseline  the CPU oracle of the same Linear path on a bounded sample (rank 0, N=1)
+  clocks        SM clock / throttle reasons sampled with nvidia-smi during the timed region
+  gpu_launches  launches of this repository's kernels inside the timed region
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = 'w8a8_llama3_70b_prefill_tokens_per_s'
+UNIT = 'tokens/s'
+BATCH, SEQ = 32, 2048
+SEED = 4
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=3)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--layers', type=int, default=80, help='debug only: fewer layers is not the benchmark')
+    ap.add_argument('--batch', type=int, default=BATCH)
+    ap.add_argument('--seq', type=int, default=SEQ)
+    ap.add_argument('--cpu-sample-tokens', type=int, default=4096)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p.get('hbm_gbs', 6650.0), p.get('bf16_tflops', 1590.0), p.get('bf16_tflops_sustained', 1400.0), 'measured'
+    return 6650.0, 1590.0, 1400.0, 'fallback'
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_linear_path(tokens, threads=None):
+    """Times the CPU oracle of one decoder layer's four quantized Linears (TP=1 shapes)
+    over `tokens` rows: dynamic per-token quantization + INT32 GEMM + dequant epilogue."""
+    from oracle import intq, npu_ops
+    from amct_b200.workloads.llama_tp import LLAMA3_70B as sh
+    if threads:
+        torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(SEED)
+    dims = [(sh.hidden, (sh.n_heads + 2 * sh.n_kv_heads) * sh.head_dim), (sh.n_heads * sh.head_dim, sh.hidden),
+            (sh.hidden, 2 * sh.intermediate), (sh.intermediate, sh.hidden)]
+    layers = []
+    for k, n in dims:
+        w_kn = torch.randint(-128, 128, (k, n), generator=g, dtype=torch.int8)
+        layers.append((torch.randn(tokens, k, generator=g).to(torch.bfloat16), w_kn, torch.rand(n, generator=g) * 1e-3))
+
+    def run():
+        for x, w_kn, sw in layers:
+            q, s = intq.dynamic_per_token(x)
+            npu_ops.npu_quant_matmul(q, w_kn, sw, s, None, torch.bfloat16, fast=True)
+
+    run()
+    t0 = time.perf_counter()
+    run()
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(tokens, n_layers):
+    sec_per_layer = cpu_linear_path(tokens)
+    tok_s = tokens / (sec_per_layer * n_layers)
+    return {'value': tok_s, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
+            'sample': f'CPU oracle (torch CPU, int8 GEMM via torch._int_mm) of the 4 quantized Linears of one decoder '
+                      f'layer over {tokens} tokens, {sec_per_layer:.3f} s; scaled x{n_layers} layers; attention/norms excluded',
+            'host_cpus': os.cpu_count()}
+
+
+def run_reference(args):
+    """--impl reference: the CPU statement of the path on the host cores, bounded sample per step."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    tokens = args.cpu_sample_tokens
+    for _ in range(min(args.warmup, 1)):
+        cpu_linear_path(tokens)
+    times = [cpu_linear_path(tokens) for _ in range(args.steps)]
+    sec = statistics.mean(times)
+    tok_s = tokens / (sec * 80)
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': args.steps,
+        'warmup': args.warmup, 'ms_per_step': (BATCH * SEQ) / tok_s * 1e3, 'higher_is_better': True, 'scaling': 'strong',
+        'vs_baseline': None, 'dtype': 'int8', 'data': 'synthetic',
+        'config': {'workload': 'llama3-70b W8A8 prefill, batch 32 x seq 2048, 80 layers (Linear path only on CPU)',
+                   'parallelism': 'cpu'},
+        'cpu_baseline': {'value': tok_s, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
+                         'sample': f'4 quantized Linears of one decoder layer over {tokens} tokens per step, scaled x80 layers'},
+        'e2e': {'value': tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    FIELDS = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+              'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--id={index}', f'--query-gpu={self.FIELDS}',
+                                          '--format=csv,noheader,nounits', '-lms', '200'],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        out, _ = self.proc.communicate(timeout=10)
+        sm, smax, reasons = [], None, set()
+        names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': smax, 'reasons': sorted(reasons),
+                'samples': len(sm)}
+
+
+def main():
+    args = parse()
+    if args.impl == 'reference':
+        return run_reference(args)
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU arm')
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    import torch.distributed as dist
+    group = None
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+        group = dist.group.WORLD
+
+    from amct_b200.backend import ops
+    from amct_b200.workloads.llama_tp import LlamaW8A8, LLAMA3_70B
+
+    t_build = time.time()
+    model = LlamaW8A8(LLAMA3_70B, tp=world, rank=rank, group=group, device=dev, seed=SEED, n_layers=args.layers)
+    torch.cuda.synchronize()
+    t_build = time.time() - t_build
+
+    gen = torch.Generator().manual_seed(SEED)
+    ids_host = torch.randint(0, LLAMA3_70B.vocab, (args.batch, args.seq), generator=gen).pin_memory()
+    ids_dev = ids_host.to(dev)
+    logits_host = torch.empty((args.batch, LLAMA3_70B.vocab), dtype=torch.float32).pin_memory()
+    tokens = args.batch * args.seq
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def step_resident():
+        return model(ids_dev)
+
+    def step_e2e():
+        ids = ids_host.to(dev, non_blocking=True)
+        logits_host.copy_(model(ids), non_blocking=True)
+
+    for _ in range(args.warmup):
+        step_resident()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ops.COUNTERS['launches'] = 0
+    ms_total = timed(step_resident, args.steps)
+    launches = ops.COUNTERS['launches']
+    clocks = sampler.stop() if sampler else None
+    ms_e2e = timed(step_e2e, args.steps)
+
+    # roofline of the dominant kernel: one more step with CUDA events around every GEMM launch
+    ops.GEMM_PROFILE = []
+    step_resident()
+    torch.cuda.synchronize()
+    gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in ops.GEMM_PROFILE)
+    gemm_ops = sum(o for _, _, o in ops.GEMM_PROFILE)
+    n_gemm = len(ops.GEMM_PROFILE)
+    ops.GEMM_PROFILE = None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    hbm, bf16_burst, bf16_sus, src = measured_peaks()
+    value = tokens * args.steps / (ms_total / 1e3)
+    achieved = gemm_ops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
+    peak = 2 * bf16_sus
+    line = {
+        'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': ms_total / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
+        'dtype': 'int8', 'data': 'synthetic',
+        'config': {'workload': f'llama3-70b W8A8 prefill, batch {args.batch} x seq {args.seq}, {args.layers} layers, '
+                               'per-channel INT8 weights, dynamic per-token INT8 activations',
+                   'parallelism': f'tp{world}', 'l2': 'per-step working set (>70 GB of weights) exceeds L2; no flush needed',
+                   'build_s': round(t_build, 1)},
+        'e2e': {'value': tokens * args.steps / (ms_e2e / 1e3), 'unit': UNIT,
+                'h2d_bytes_per_step': ids_host.numel() * ids_host.element_size(),
+                'd2h_bytes_per_step': logits_host.numel() * logits_host.element_size()},
+        'gpu_launches': launches,
+        'roofline': {'bound': 'tensor', 'kernel': 'gemm_tcgen05_kernel (kind::i8)', 'achieved': achieved, 'peak': peak,
+                     'unit': 'TOP/s', 'frac': (achieved / peak) if achieved else None, 'traffic': None,
+                     'launches_per_step': n_gemm, 'gemm_ms_per_step': gemm_ms,
+                     'peak_source': f'2 x bf16_tflops_sustained ({bf16_sus}) of {src}; no direct INT8 peak measurement'},
+        'clocks': clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line['cpu_baseline'] = cpu_baseline(args.cpu_sample_tokens, args.layers)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

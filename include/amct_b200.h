@@ -86,6 +86,15 @@ int64_t amct_minmax_workspace_bytes(int64_t k);
 int amct_minmax(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int axis, int merge,
                 void* out_min, void* out_max, void* workspace, int* status, void* stream);
 
+/* min and max of every row of a [rows, k] matrix, in x's dtype; `pre`/pre_op
+ * apply an element-wise factor [k] first (rounded to x's dtype), merge=1 folds
+ * into existing values.  Replaces torch.amax/amin over all axes but the token
+ * axis (amct_pytorch/quantize_op/minmax_module.py:99-105) and the per-token
+ * statistics of the smoothed stash
+ * (amct_pytorch/quantize_op/smooth_quant_module.py:155-168). */
+int amct_minmax_rows(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, const void* pre,
+                     int pre_op, int merge, void* out_min, void* out_max, int* status, void* stream);
+
 /* scale/offset from n (max, min) pairs given in `dtype`.
  * Replaces calculate_scale_offset (amct_pytorch/quantize_op/utils.py:75-108). */
 int amct_scale_offset(const void* vmax, const void* vmin, int dtype, int64_t n, int bits, int symmetric,
@@ -137,6 +146,18 @@ int amct_gemm_w8a8(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64
 int amct_gemm_f16(const void* a, const void* b, int dtype, int64_t m, int64_t n, int64_t k, int64_t ld_a,
                   int64_t ld_b, const void* bias, int bias_kind, void* out, int out_kind, int64_t ld_out,
                   int* status, void* stream);
+
+/* Dequantize weight codes for the weight-only Linear:
+ *   out[n, k] = (q[n, k] + offset[g(k), n]) * scale[g(k), n]   (fp32 steps, rounded to dtype)
+ * codes: INT8 [n_rows, k] (bits = 8) or two nibbles per byte [n_rows, k/2] (bits = 4,
+ * code + 8, even k in the low nibble), K contiguous.  scale / offset (may be NULL)
+ * are in `dtype` (F16 or BF16), laid out [k/group, n_rows], or [1, n_rows] when
+ * group == 0 -- the scale_w / offset_w buffers (offset already negated) of
+ * amct_pytorch/deploy_op/weight_npu_quant_module.py:59-64.  First stage of
+ * torch_npu.npu_weight_quant_batchmatmul (call site :116-117). */
+int amct_dequant_weight(const void* codes, int bits, int64_t n_rows, int64_t k, int64_t ld_codes,
+                        const void* scale, const void* offset, int group, int dtype, void* out,
+                        int64_t ld_out, void* stream);
 
 #ifdef __cplusplus
 }

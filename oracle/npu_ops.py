@@ -33,18 +33,22 @@ def npu_quantize(x, scales, zero_points, dtype=torch.int8, axis=-1, div_mode=Fal
     return y.round().clamp(-128, 127).to(torch.int8)
 
 
-def int32_matmul(q, wq_kn):
-    """Exact INT8 x INT8 -> INT32 accumulation."""
-    return (q.reshape(-1, q.shape[-1]).to(torch.int64) @ wq_kn.to(torch.int64)).to(torch.int32)
+def int32_matmul(q, wq_kn, fast=False):
+    """Exact INT8 x INT8 -> INT32 accumulation.  fast=True uses torch's CPU int8
+    GEMM (same exact result, all host threads) -- the CPU-baseline timing path."""
+    q2 = q.reshape(-1, q.shape[-1])
+    if fast:
+        return torch._int_mm(q2, wq_kn)
+    return (q2.to(torch.int64) @ wq_kn.to(torch.int64)).to(torch.int32)
 
 
-def npu_quant_matmul(q, wq_kn, scale, pertoken_scale=None, bias=None, output_dtype=torch.bfloat16):
+def npu_quant_matmul(q, wq_kn, scale, pertoken_scale=None, bias=None, output_dtype=torch.bfloat16, fast=False):
     """INT32 GEMM, then: (+ int32 bias) * scale[n] (* pertoken[m]) (+ float
     bias), in that order, each step a separately rounded fp32 operation.
     int32 bias = per-tensor mode (npu_quantization_linear.py:117-120), float
     bias = per-token mode (:121-122)."""
     lead = q.shape[:-1]
-    acc = int32_matmul(q, wq_kn)
+    acc = int32_matmul(q, wq_kn, fast)
     if bias is not None and bias.dtype == torch.int32:
         acc = acc + bias
     y = acc.float() * scale.float().reshape(1, -1)

@@ -1,0 +1,200 @@
+"""GPU parity of the integer quantization kernels, called through the C ABI.
+
+Bit-exact against (a) the golden vectors produced by the reference and (b) the
+CPU oracle on seeded inputs, including ragged / unaligned / large-K shapes."""
+import itertools
+
+import pytest
+import torch
+
+from golden_io import Golden, bits_equal
+from oracle import intq, npu_ops
+
+pytestmark = pytest.mark.gpu
+G = Golden()
+DT = {'fp32': torch.float32, 'bf16': torch.bfloat16, 'fp16': torch.float16}
+WCASES = list(itertools.product(DT, ('int8', 'int4'), (True, False), ('tensor', 'channel', 'group')))
+
+
+def ops():
+    from amct_b200.backend import ops as o
+    return o
+
+
+def dev(t):
+    return None if t is None else t.cuda()
+
+
+@pytest.mark.parametrize('qt,sym', list(itertools.product(('int8', 'int4'), (True, False))))
+def test_scale_offset_golden(qt, sym):
+    s, o = ops().scale_offset(dev(G.get('k0/max')).reshape(-1, 1), dev(G.get('k0/min')).reshape(-1, 1), sym, qt)
+    assert bits_equal(s, G.get(f'k0/{qt}/{int(sym)}/scale'))
+    assert bits_equal(o, G.get(f'k0/{qt}/{int(sym)}/offset'))
+
+
+@pytest.mark.parametrize('dname,qt,sym,strat', WCASES)
+def test_weight_paths_golden(dname, qt, sym, strat):
+    from amct_b200.quantize_op.utils import weight_scale_offset, get_weight_min_max_by_granularity
+    w = dev(G.get(f'w/{dname}/weight'))
+    gs = 32 if strat == 'group' else None
+    tag = f'w/{dname}/{qt}/{int(sym)}/{strat}'
+    s, o = weight_scale_offset(w, qt, sym, strat, gs)
+    assert bits_equal(s, G.get(tag + '/scale'))
+    assert bits_equal(o, G.get(tag + '/offset'))
+    # unfused observer + rule gives the same factors
+    cfgd = {'weights_cfg': {'strategy': strat, 'group_size': gs}}
+    mn, mx = get_weight_min_max_by_granularity(w, cfgd)
+    s2, o2 = ops().scale_offset(mx, mn, sym, qt)
+    assert bits_equal(s2, s) and bits_equal(o2, o)
+
+    gold = intq.crop_groups(G.get(tag + '/codes'), w.shape)
+    _, _, codes = ops().quant_rows(w, qt, sym, strat, gs, scale=s, offset=o, out='i8' if qt == 'int8' else 'i32')
+    assert bits_equal(codes, gold.contiguous())
+    # fused: factors and codes from one read of the weight
+    if strat != 'tensor':
+        s3, o3, codes3 = ops().quant_rows(w, qt, sym, strat, gs, out='i8' if qt == 'int8' else 'i32')
+        assert bits_equal(s3.reshape(s.shape), s) and bits_equal(codes3, gold.contiguous())
+    _, _, fake = ops().quant_rows(w, qt, sym, strat, gs, scale=s, offset=o, out='fake')
+    assert bits_equal(fake, G.get(tag + '/fake'))
+    _, _, fake_awq = ops().quant_rows(w, qt, sym, strat, gs, scale=s, offset=o, out='fake_awq')
+    assert bits_equal(fake_awq, G.get(tag + '/fake_awq'))
+    if qt == 'int4':
+        _, _, packed = ops().quant_rows(w, qt, sym, strat, gs, scale=s, offset=o, out='pack4')
+        want = npu_ops.npu_convert_weight_to_int4pack(gold.t().contiguous()).t()
+        assert bits_equal(packed, want.contiguous())
+
+
+@pytest.mark.parametrize('dname', list(DT))
+@pytest.mark.parametrize('rule', ['released', 'experimental'])
+def test_dynamic_per_token_golden(dname, rule):
+    x = dev(G.get(f'k1/{dname}/x'))
+    q, s = ops().quant_dynamic_per_token(x, rule=rule, check=True)
+    pre = 'k1' if rule == 'released' else 'k1x'
+    assert bits_equal(s, G.get(f'{pre}/{dname}/scale'))
+    assert bits_equal(q, G.get(f'{pre}/{dname}/codes'))
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('rows,k', [(1, 8), (3, 67), (5, 1000), (7, 4096), (4, 8192), (3, 28672), (2, 40000), (0, 64)])
+@pytest.mark.parametrize('smooth', [False, True])
+def test_dynamic_per_token_oracle(dtype, rows, k, smooth):
+    g = torch.Generator().manual_seed(rows * 131 + k)
+    x = torch.randn(rows, k, generator=g)
+    if rows:
+        x[:, :: max(1, k // 41)] *= 20
+        x[0, 0] = -x[0].abs().max() * 2
+    x = x.to(dtype)
+    f = (torch.rand(1, k, generator=g) + 0.5).to(dtype) if smooth else None
+    q_ref, s_ref = intq.dynamic_per_token(x, 'released', f)
+    q, s = ops().quant_dynamic_per_token(x.cuda(), smooth=dev(f))
+    assert bits_equal(s, s_ref)
+    assert bits_equal(q, q_ref)
+
+
+def test_dynamic_per_token_strided_rows_and_3d():
+    g = torch.Generator().manual_seed(5)
+    big = torch.randn(6, 512, generator=g).to(torch.bfloat16)
+    view = big[:, 128:384]                                     # ld 512, k 256, 16-byte aligned
+    q, s = ops().quant_dynamic_per_token(view.cuda())
+    q_ref, s_ref = intq.dynamic_per_token(view.contiguous())
+    assert bits_equal(q, q_ref) and bits_equal(s, s_ref)
+    x3 = torch.randn(2, 3, 136, generator=g)
+    q, s = ops().quant_dynamic_per_token(x3.cuda())
+    q_ref, s_ref = intq.dynamic_per_token(x3)
+    assert bits_equal(q, q_ref) and bits_equal(s, s_ref)
+
+
+def test_nonfinite_input_raises_like_reference():
+    x = torch.randn(4, 64)
+    x[2, 3] = float('nan')
+    with pytest.raises(RuntimeError, match='invalid value inf, nan or zeros'):
+        ops().quant_dynamic_per_token(x.cuda(), check=True)
+    w = torch.randn(8, 64)
+    w[1, 1] = float('inf')
+    with pytest.raises(RuntimeError, match='invalid value inf, nan or zeros'):
+        ops().quant_rows(w.cuda(), 'int8', True, 'channel')
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('rows,k', [(1, 1), (9, 67), (300, 256), (2049, 136), (64, 4096)])
+def test_minmax_observers(dtype, rows, k):
+    g = torch.Generator().manual_seed(rows + k)
+    x = torch.randn(rows, k, generator=g).to(dtype)
+    xc = x.cuda()
+    mn, mx = ops().minmax(xc, 'tensor')
+    assert bits_equal(mn, x.min().reshape(1)) and bits_equal(mx, x.max().reshape(1))
+    mn, mx = ops().minmax(xc, 'column')
+    assert bits_equal(mn, x.amin(0, keepdim=True)) and bits_equal(mx, x.amax(0, keepdim=True))
+    mn, mx = ops().minmax_rows(xc)
+    assert bits_equal(mn, x.amin(1)) and bits_equal(mx, x.amax(1))
+    # running merge with a second batch
+    y = (torch.randn(rows, k, generator=g) * 2).to(dtype)
+    run = ops().minmax(xc, 'column')
+    ops().minmax(y.cuda(), 'column', running=(run[0].view(-1), run[1].view(-1)))
+    both = torch.cat((x, y))
+    assert bits_equal(run[0], both.amin(0, keepdim=True)) and bits_equal(run[1], both.amax(0, keepdim=True))
+    f = (torch.rand(1, k, generator=g) + 0.5).to(dtype)
+    mn, mx = ops().minmax_rows(xc, pre=f.cuda(), pre_op='div')
+    assert bits_equal(mn, (x / f).amin(1)) and bits_equal(mx, (x / f).amax(1))
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize('shape', [(5, 64), (2, 7, 72), (3, 33), (1, 4, 16, 40)])
+@pytest.mark.parametrize('per_token,offset,smooth', [(False, False, False), (False, True, True), (True, False, False),
+                                                     (True, True, True)])
+def test_quantize_static_oracle(dtype, shape, per_token, offset, smooth):
+    g = torch.Generator().manual_seed(sum(shape))
+    x = (torch.randn(*shape, generator=g) * 3).to(dtype)
+    n = shape[-2] if per_token else 1
+    s = (torch.rand(n, generator=g) * 40 + 5).to(dtype)
+    z = torch.randint(-20, 20, (n,), generator=g).to(dtype) if offset else None
+    f = (torch.rand(1, shape[-1], generator=g) + 0.5).to(dtype) if smooth else None
+    axis = -2 if per_token else -1
+    want = npu_ops.npu_quantize(x * f if smooth else x, s, z, torch.int8, axis)
+    got = ops().quantize_static(x.cuda(), s.cuda(), dev(z), axis=axis, smooth=dev(f))
+    assert bits_equal(got, want)
+
+
+def test_rowsum_and_transpose():
+    g = torch.Generator().manual_seed(3)
+    for n, k in ((1, 1), (17, 67), (64, 4096), (33, 272)):
+        w = torch.randint(-128, 128, (n, k), generator=g, dtype=torch.int8)
+        assert bits_equal(ops().rowsum_i8(w.cuda()), w.to(torch.int32).sum(1).to(torch.int32))
+        assert bits_equal(ops().transpose_i8(w.cuda()), w.t().contiguous())
+
+
+@pytest.mark.parametrize('bits,group,offset', [(8, 0, False), (8, 0, True), (4, 32, True), (4, 128, False), (8, 64, True)])
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_dequant_weight_oracle(bits, group, offset, dtype):
+    g = torch.Generator().manual_seed(bits + group)
+    n, k = 40, 256
+    lo, hi = (-8, 8) if bits == 4 else (-128, 128)
+    q_kn = torch.randint(lo, hi, (k, n), generator=g, dtype=torch.int32)
+    ng = k // group if group else 1
+    s = (torch.rand(ng, n, generator=g) * 0.01 + 0.001).to(dtype)
+    o = torch.randint(-8, 8, (ng, n), generator=g).to(dtype) if offset else None
+    want = npu_ops.dequant_weight(q_kn, s, o, group, dtype).t().contiguous()
+    if bits == 4:
+        codes = npu_ops.npu_convert_weight_to_int4pack(q_kn).t().contiguous()
+    else:
+        codes = q_kn.to(torch.int8).t().contiguous()
+    got = ops().dequant_weight(codes.cuda(), bits, s.cuda(), dev(o), group)
+    assert bits_equal(got, want)
+
+
+def test_config1_shape_properties():
+    """Full size of the W8A8 single-Linear configuration: properties that hold at
+    any size -- codes within range, |x - q*scale| <= scale/2, idempotence."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2048, 4096, generator=g)
+    idx = torch.randperm(4096, generator=g)[:41]
+    x[:, idx] *= 20
+    xc = x.cuda()
+    q, s = ops().quant_dynamic_per_token(xc, check=True)
+    deq = q.float() * s[:, None]
+    assert (deq - xc).abs().le(s[:, None] * 0.5 * (1 + 1e-6)).all()
+    q2, s2 = ops().quant_dynamic_per_token(deq)
+    assert bits_equal(q2, q.cpu())
+    # a stripe of rows against the oracle
+    q_ref, s_ref = intq.dynamic_per_token(x[1000:1032])
+    assert bits_equal(q[1000:1032], q_ref) and bits_equal(s[1000:1032], s_ref)

@@ -1,0 +1,173 @@
+"""Host-side logic that needs no GPU: config schema, registry, type checks, the
+C-ABI library's exported symbols, and the loud failure on CPU tensors."""
+import ctypes
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+
+import amct_b200 as amct
+from amct_b200.algorithm import AlgorithmRegistry
+from amct_b200.backend import lib
+from amct_b200.config import parse_config
+from amct_b200.quantize_op.base_quant_module import BaseQuantizeModule
+
+
+class Net(nn.Module):
+    def __init__(self, dtype=torch.bfloat16):
+        super().__init__()
+        self.linear1 = nn.Linear(64, 64).to(dtype)
+        self.linear2 = nn.Linear(64, 32).to(dtype)
+        self.lm_head = nn.Linear(32, 1).to(dtype)
+
+    def forward(self, x):
+        return self.lm_head(self.linear2(self.linear1(x)))
+
+
+def cfg(weights, inputs=None, algorithm='minmax', **kw):
+    c = {'batch_num': 1, 'quant_cfg': {'weights': weights}, 'algorithm': algorithm}
+    if inputs is not None:
+        c['quant_cfg']['inputs'] = inputs
+    c.update(kw)
+    return c
+
+
+W8 = {'type': 'int8', 'symmetric': True, 'strategy': 'channel'}
+A8 = {'type': 'int8', 'symmetric': True, 'strategy': 'tensor'}
+
+
+def test_library_exports_every_declared_symbol():
+    from amct_b200.csrc import build
+    build.build()
+    names = lib.declared_symbols()
+    assert len(names) >= 12
+    handle = ctypes.CDLL(lib.LIB_PATH)
+    missing = [n for n in names if not hasattr(handle, n)]
+    assert not missing, missing
+    assert handle.amct_abi_version() >= 1
+
+
+def test_cpu_tensors_fail_loudly():
+    with pytest.raises(lib.BackendError, match='no CPU fallback'):
+        amct.quantize(Net(), cfg(W8))
+
+
+@pytest.mark.parametrize('bad,msg', [
+    ({'batch_num': 0}, 'Batch num only support positive int'),
+    ({'batch_num': 1.5}, 'Batch num only support positive int'),
+    ({'skip_layers': [1]}, 'Skip layers must be str'),
+    ({'algorithm': 'nonexistent'}, 'Not support algorithm nonexistent'),
+    ({'algorithm': {'minmax', 'smoothquant'}}, 'Algorithm only support 1 str'),
+])
+def test_top_level_field_errors(bad, msg):
+    c = cfg(W8)
+    c.update(bad)
+    with pytest.raises(ValueError, match=msg):
+        parse_config(Net(), c, AlgorithmRegistry)
+
+
+@pytest.mark.parametrize('weights,msg', [
+    ({'type': 'int2', 'symmetric': True, 'strategy': 'channel'}, 'Weights quant_dtype only support'),
+    ({'type': 'int8', 'symmetric': 1.5, 'strategy': 'channel'}, 'Weights symmetric only support bool'),
+    ({'type': 'int8', 'symmetric': True, 'strategy': 'row'}, 'Weights strategy only support'),
+    ({'type': 'int8', 'symmetric': True, 'strategy': 'channel', 'group_size': 32}, 'group_size only support strategy group'),
+    ({'type': 'int8', 'symmetric': True, 'strategy': 'group'}, 'group_size is necessary'),
+    ({'type': 'int8', 'symmetric': True, 'strategy': 'group', 'group_size': -32}, 'group_size only support positive int'),
+    ({'type': 'int4', 'symmetric': True, 'strategy': 'group', 'group_size': 48}, 'integer multiple of 32'),
+    ({'type': 'int4', 'symmetric': True, 'strategy': 'group', 'group_size': 16}, 'integer multiple of 32'),
+])
+def test_weight_field_errors(weights, msg):
+    with pytest.raises(ValueError, match=msg):
+        parse_config(Net(), cfg(weights), AlgorithmRegistry)
+
+
+@pytest.mark.parametrize('inputs,msg', [
+    ({'type': 'int4', 'symmetric': True, 'strategy': 'tensor'}, 'Inputs quant_dtype only support'),
+    ({'type': 'int8', 'symmetric': None, 'strategy': 'tensor'}, 'Inputs symmetric only support bool'),
+    ({'type': 'int8', 'symmetric': True, 'strategy': 'channel'}, 'Inputs strategy only support'),
+    ({'type': 'int8', 'symmetric': False, 'strategy': 'token'}, 'do not support asymmetric'),
+])
+def test_input_field_errors(inputs, msg):
+    with pytest.raises(ValueError, match=msg):
+        parse_config(Net(), cfg(W8, inputs), AlgorithmRegistry)
+
+
+def test_combination_rules():
+    with pytest.raises(ValueError, match='do not support weight quant strategy group'):
+        parse_config(Net(), cfg({'type': 'int8', 'symmetric': True, 'strategy': 'group', 'group_size': 32}, A8),
+                     AlgorithmRegistry)
+    with pytest.raises(ValueError, match='Do not support combination int8 int4'):
+        parse_config(Net(), cfg({'type': 'int4', 'symmetric': True, 'strategy': 'channel'}, A8), AlgorithmRegistry)
+    with pytest.raises(ValueError, match='Algorithm smoothquant do not support'):
+        parse_config(Net(), cfg(W8, None, {'smoothquant': {'smooth_strength': 0.5}}), AlgorithmRegistry)
+    with pytest.raises(ValueError, match='smooth_strength only support float'):
+        parse_config(Net(), cfg(W8, A8, {'smoothquant': {'smooth_strength': 1}}), AlgorithmRegistry)
+    with pytest.raises(ValueError, match='smooth_strength is necessary'):
+        parse_config(Net(), cfg(W8, A8, {'smoothquant': {}}), AlgorithmRegistry)
+
+
+def test_layer_selection_and_detail_config():
+    detail = parse_config(Net(), cfg(W8, skip_layers={'lm_head'}), AlgorithmRegistry)
+    assert sorted(detail) == ['linear1', 'linear2']
+    assert detail['linear1'] == {'batch_num': 1, 'weights_cfg': {'quant_type': 'int8', 'symmetric': True,
+                                 'strategy': 'channel'}, 'inputs_cfg': {'enable_quant': False},
+                                 'algorithm': {'minmax'}}
+    # int4 needs cin and cout divisible by 8: lm_head (32 -> 1) drops out; group_size must be < cin
+    d4 = parse_config(Net(), cfg({'type': 'int4', 'symmetric': False, 'strategy': 'group', 'group_size': 32}),
+                      AlgorithmRegistry)
+    assert sorted(d4) == ['linear1', 'linear2']
+    # W8A8 is refused for fp32 layers unless opted in
+    assert parse_config(Net(torch.float32), cfg(W8, A8), AlgorithmRegistry) == {}
+    assert len(parse_config(Net(torch.float32), cfg(W8, A8, allow_fp32=True), AlgorithmRegistry)) == 3
+    # algorithm spelled as str / set / dict
+    for alg in ('minmax', {'minmax'}):
+        assert len(parse_config(Net(), cfg(W8, algorithm=alg), AlgorithmRegistry)) == 3
+
+
+def test_default_config_is_int8_minmax():
+    from amct_b200.config import set_default_config
+    assert set_default_config() is amct.INT8_MINMAX_WEIGHT_QUANT_CFG
+    assert amct.INT8_SMOOTHQUANT_CFG['algorithm'] == {'smoothquant': {'smooth_strength': 0.5}}
+    assert amct.INT4_AWQ_WEIGHT_QUANT_CFG['algorithm'] == {'awq': {'grids_num': 20}}
+
+
+def test_public_api_type_checks():
+    with pytest.raises(TypeError, match='argument model must be'):
+        amct.quantize('not a model')
+    with pytest.raises(TypeError, match='argument config must be'):
+        amct.quantize(Net(), config=[1])
+    with pytest.raises(TypeError, match='argument model must be'):
+        amct.convert(3)
+    with pytest.raises(TypeError, match='argument quant_op must be'):
+        amct.algorithm_register('x', 'Linear', nn.Linear, None)
+
+
+def test_registry_custom_algorithm_and_duplicates():
+    class MyQuant(BaseQuantizeModule):
+        def __init__(self, ori_module, layer_name, quant_config):
+            super().__init__(ori_module, layer_name, quant_config)
+            self.ori_module = ori_module
+            self.seen_config = quant_config
+
+        def forward(self, x):
+            return self.ori_module(x)
+
+    name = 'custom_host_test'
+    amct.algorithm_register(name, 'Linear', MyQuant, None)
+    with pytest.raises(ValueError, match=f'{name} is already registered'):
+        amct.algorithm_register(name, 'Linear', MyQuant, None)
+    net = Net()
+    amct.quantize(net, cfg(W8, algorithm={name: {'k': 1}}))
+    assert type(net.linear1).__name__ == 'MyQuant' and net.linear1.seen_config['algorithm'] == {name: {'k': 1}}
+    with pytest.raises(RuntimeError, match='The deploy_op for MyQuant is None'):
+        amct.convert(net)
+
+
+def test_logger_tolerates_readonly_cwd(tmp_path, monkeypatch):
+    from amct_b200.utils.log import _Logger
+    ro = tmp_path / 'ro'
+    ro.mkdir()
+    os.chmod(ro, 0o500)
+    monkeypatch.chdir(ro)
+    _Logger().logi('x' * 1200, 'test')
