@@ -89,6 +89,11 @@ class InputsCfgField(_Field):
         if self.strategy == 'token' and self.symmetric is False:
             raise ValueError('Inputs strategy token do not support asymmetric quantization')
         self.value = {'quant_type': self.quant_type, 'symmetric': self.symmetric, 'strategy': self.strategy}
+        # additive key (not in the reference schema): per-token scales computed at run time
+        if config.get('dynamic', False):
+            if self.strategy != 'token':
+                raise ValueError('Inputs dynamic quantization only support strategy token')
+            self.value['dynamic'] = True
 
 
 class QuantCfgField(_Field):

@@ -1,0 +1,159 @@
+"""Per-kernel roofline measurements (one JSON line per case).
+
+    python bench_kernels.py [--only SUBSTR] [--reps 20] [--out FILE]
+
+Every case: 3 warm-up launches, then `reps` launches each preceded by an L2 flush
+(a 512 MiB buffer is overwritten, untimed), each launch bracketed by CUDA events on
+the launching stream.  Reported: median and best time, algorithmic bytes or
+operations per launch, achieved GB/s or TOP/s and the fraction of the measured peak
+(MEASURED_PEAKS.json when present: HBM copy bandwidth; 2x the bf16 burst figure for
+INT8, since a kernel is timed alone here).
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from amct_b200.backend import ops  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p['hbm_gbs'], p['bf16_tflops'], 'measured'
+    return 6650.0, 1590.0, 'fallback'
+
+
+HBM, BF16, SRC = peaks()
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(512 << 20, dtype=torch.uint8, device='cuda')
+    _flush.fill_(1)
+
+
+def time_case(fn, reps):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times), min(times)
+
+
+def report(name, med, best, nbytes=None, nops=None, out=None, peak_mult=1.0):
+    rec = {'case': name, 'ms_median': round(med, 5), 'ms_best': round(best, 5)}
+    if nbytes is not None:
+        gbs = nbytes / (med * 1e-3) / 1e9
+        rec.update(bound='hbm', bytes=nbytes, achieved=round(gbs, 1), unit='GB/s', peak=HBM, frac=round(gbs / HBM, 4))
+    if nops is not None:
+        tops = nops / (med * 1e-3) / 1e12
+        pk = BF16 * peak_mult
+        rec.update(bound='tensor', ops=nops, achieved=round(tops, 1), unit='TOP/s', peak=pk, frac=round(tops / pk, 4))
+    rec['peak_source'] = SRC
+    line = json.dumps(rec)
+    print(line, flush=True)
+    if out:
+        out.write(line + '\n')
+        out.flush()
+
+
+def cases():
+    g = torch.Generator(device='cuda').manual_seed(0)
+
+    def randn(r, k, dtype, std=1.0):
+        return (torch.randn(r, k, device='cuda', generator=g, dtype=torch.float32 if dtype == torch.float32 else torch.bfloat16) * std).to(dtype)
+
+    # ---- dynamic per-token activation quantization
+    for r, k, dt, tag in ((2048, 4096, torch.float32, 'c1'), (65536, 8192, torch.bfloat16, 'c5-h'),
+                          (65536, 28672, torch.bfloat16, 'c5-ffn'), (65536, 4096, torch.float32, 'c1-1GiB')):
+        es = 4 if dt == torch.float32 else 2
+        yield (f'quant_dynamic_pertoken {tag} [{r}x{k}] {str(dt)[6:]}', lambda r=r, k=k, dt=dt: randn(r, k, dt),
+               lambda x: (lambda: ops.quant_dynamic_per_token(x)), dict(nbytes=r * k * es + r * k + r * 4))
+    # ---- static quantize
+    yield ('quantize_static per-tensor [65536x8192] bf16', lambda: randn(65536, 8192, torch.bfloat16),
+           lambda x: (lambda s=torch.tensor([30.0], device='cuda', dtype=torch.bfloat16): ops.quantize_static(x, s, None)),
+           dict(nbytes=65536 * 8192 * 3))
+    # ---- weight quantization, fused min/max + codes
+    for n, k, dt, tag in ((4096, 4096, torch.float32, 'c1'), (28672, 8192, torch.bfloat16, 'c5 gate/up shard')):
+        es = 4 if dt == torch.float32 else 2
+        yield (f'weight_quant_i8 channel {tag} [{n}x{k}] {str(dt)[6:]}', lambda n=n, k=k, dt=dt: randn(n, k, dt, 0.02),
+               lambda w: (lambda: ops.quant_rows(w, 'int8', True, 'channel', out='i8', check=False)),
+               dict(nbytes=n * k * es + n * k + n * 4))
+    yield ('weight_quant_i4 g128 asym pack c2 [11008x4096] bf16', lambda: randn(11008, 4096, torch.bfloat16, 0.02),
+           lambda w: (lambda: ops.quant_rows(w, 'int4', False, 'group', 128, out='pack4', check=False)),
+           dict(nbytes=11008 * 4096 * 2 + 11008 * 4096 // 2 + 11008 * 32 * 8))
+    yield ('fake_quant i4 g128 asym [11008x4096] bf16', lambda: randn(11008, 4096, torch.bfloat16, 0.02),
+           lambda w: (lambda: ops.quant_rows(w, 'int4', False, 'group', 128, out='fake', check=False)),
+           dict(nbytes=11008 * 4096 * 4 + 11008 * 32 * 8))
+    # ---- observers
+    yield ('minmax column [65536x8192] bf16', lambda: randn(65536, 8192, torch.bfloat16),
+           lambda x: (lambda: ops.minmax(x, 'column')), dict(nbytes=65536 * 8192 * 2))
+    yield ('minmax tensor [65536x8192] bf16', lambda: randn(65536, 8192, torch.bfloat16),
+           lambda x: (lambda: ops.minmax(x, 'tensor')), dict(nbytes=65536 * 8192 * 2))
+    # ---- W8A8 GEMM
+    for m, n, k, od, tag in ((2048, 4096, 4096, torch.float32, 'c1'), (8192, 8192, 8192, torch.bfloat16, 'square'),
+                             (65536, 10240, 8192, torch.bfloat16, 'c5 qkv'), (65536, 8192, 8192, torch.bfloat16, 'c5 o'),
+                             (65536, 57344, 8192, torch.bfloat16, 'c5 gate+up'), (65536, 8192, 28672, torch.bfloat16, 'c5 down'),
+                             (64, 8192, 8192, torch.bfloat16, 'c5 decode o')):
+        def setup(m=m, n=n, k=k, od=od):
+            a = torch.randint(-128, 128, (m, k), device='cuda', dtype=torch.int8)
+            b = torch.randint(-128, 128, (n, k), device='cuda', dtype=torch.int8)
+            return (a, b, torch.rand(n, device='cuda') * 1e-3, torch.rand(m, device='cuda'),
+                    torch.empty(m, n, device='cuda', dtype=od))
+        yield (f'gemm_w8a8 {tag} {m}x{n}x{k} -> {str(od)[6:]}', setup,
+               lambda t: (lambda: ops.gemm_w8a8(t[0], t[1], t[2], t[3], None, out=t[4])), dict(nops=2 * m * n * k, peak_mult=2.0))
+    # ---- 16-bit GEMM
+    for m, n, k, tag in ((8192, 8192, 8192, 'square'), (4096, 11008, 4096, 'c2 M=4096'), (128, 11008, 4096, 'c2 M=128'),
+                         (16384, 14336, 4096, 'c4 gate')):
+        def setup16(m=m, n=n, k=k):
+            return (randn(m, k, torch.bfloat16), randn(n, k, torch.bfloat16, 0.02), torch.empty(m, n, device='cuda', dtype=torch.bfloat16))
+        yield (f'gemm_f16 bf16 {tag} {m}x{n}x{k}', setup16, lambda t: (lambda: ops.gemm_f16(t[0], t[1], out=t[2])),
+               dict(nops=2 * m * n * k, peak_mult=1.0))
+    # ---- weight dequant (stage 1 of the weight-only Linear)
+    def setup_dq():
+        codes = torch.randint(0, 256, (11008, 2048), device='cuda', dtype=torch.uint8)
+        s = (torch.rand(32, 11008, device='cuda') * 0.01).to(torch.bfloat16)
+        o = torch.randint(-8, 8, (32, 11008), device='cuda').to(torch.bfloat16)
+        return codes, s, o, torch.empty(11008, 4096, device='cuda', dtype=torch.bfloat16)
+    yield ('dequant_weight i4 g128 c2 [11008x4096] -> bf16', setup_dq,
+           lambda t: (lambda: ops.dequant_weight(t[0], 4, t[1], t[2], 128, out=t[3])),
+           dict(nbytes=11008 * 2048 + 11008 * 4096 * 2 + 2 * 32 * 11008 * 2))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--only', default='')
+    ap.add_argument('--reps', type=int, default=20)
+    ap.add_argument('--out', default='')
+    args = ap.parse_args()
+    out = open(args.out, 'w') if args.out else None
+    for name, setup, make, kw in cases():
+        if args.only and args.only not in name:
+            continue
+        data = setup()
+        fn = make(data)
+        med, best = time_case(fn, args.reps)
+        report(name, med, best, out=out, **kw)
+        del data, fn
+        torch.cuda.empty_cache()
+
+
+if __name__ == '__main__':
+    main()

@@ -171,3 +171,11 @@ def test_logger_tolerates_readonly_cwd(tmp_path, monkeypatch):
     os.chmod(ro, 0o500)
     monkeypatch.chdir(ro)
     _Logger().logi('x' * 1200, 'test')
+
+
+def test_dynamic_inputs_key_is_passed_through():
+    dyn = {'type': 'int8', 'symmetric': True, 'strategy': 'token', 'dynamic': True}
+    detail = parse_config(Net(), cfg(W8, dyn), AlgorithmRegistry)
+    assert detail['linear1']['inputs_cfg'] == {'quant_type': 'int8', 'symmetric': True, 'strategy': 'token', 'dynamic': True}
+    with pytest.raises(ValueError, match='dynamic quantization only support strategy token'):
+        parse_config(Net(), cfg(W8, {'type': 'int8', 'symmetric': True, 'strategy': 'tensor', 'dynamic': True}), AlgorithmRegistry)
