@@ -13,7 +13,8 @@ HEADER = os.path.join(os.path.dirname(os.path.dirname(_HERE)), 'include', 'amct_
 
 OK = 0
 ERRORS = {-1: 'invalid argument', -2: 'misaligned pointer or leading dimension', -3: 'CUDA error',
-          -4: 'unsupported shape', -5: 'device-side wait timed out'}
+          -4: 'unsupported shape', -5: 'device-side wait timed out',
+          -6: 'size exceeds the scratch memory built into the library'}
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 STRATEGY = {'tensor': 0, 'channel': 1, 'group': 2}
@@ -47,8 +48,7 @@ def load():
         lib = ctypes.CDLL(LIB_PATH)
         lib.amct_minmax_workspace_bytes.restype = ctypes.c_int64
         lib.amct_minmax_workspace_bytes.argtypes = [ctypes.c_int64]
-        if hasattr(lib, 'amct_gemm_workspace_bytes'):
-            lib.amct_gemm_workspace_bytes.restype = ctypes.c_int64
+        lib.amct_minmax_noalloc_max_k.restype = ctypes.c_int64
         _lib = lib
     return _lib
 

@@ -374,3 +374,26 @@ def dequant_weight(codes_nk, bits, scale_gn, offset_gn, group, out=None):
     _l.check(rc, 'amct_dequant_weight')
     COUNTERS['launches'] += 1
     return out
+
+
+def minmax_noalloc(x, axis, out_min, out_max, merge=False):
+    """amct_minmax without a workspace and without any allocation: the caller passes the
+    input and both outputs (in x's dtype; 1 element for axis 'tensor', K for 'column').
+    For hosts that must not allocate device memory after start-up.  Column axis: K up to
+    16384.  Calls share one built-in scratch array, so calls that could overlap on the
+    GPU must be ordered by the caller."""
+    _need_cuda(x, out_min, out_max)
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x2.stride(-1) != 1:
+        raise _l.BackendError('minmax_noalloc needs unit inner stride (it will not make a contiguous copy)')
+    rows = x2.shape[0]
+    ld = x2.stride(0) if rows > 1 else k
+    n = 1 if axis == 'tensor' else k
+    assert out_min.numel() == n and out_max.numel() == n and out_min.dtype == x.dtype and out_max.dtype == x.dtype
+    assert out_min.is_contiguous() and out_max.is_contiguous()
+    rc = _l.load().amct_minmax_noalloc(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld),
+                                       c_int(_l.AXIS_TENSOR if axis == 'tensor' else _l.AXIS_COLUMN),
+                                       c_int(1 if merge else 0), _p(out_min), _p(out_max), c_void_p(0), _stream())
+    _l.check(rc, 'amct_minmax_noalloc')
+    COUNTERS['launches'] += 2

@@ -12,6 +12,8 @@
 //
 // All of them are HBM-bound single-read reductions: algorithmic traffic is the
 // input size; partials live in a caller-provided workspace.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace amct {
@@ -266,6 +268,41 @@ __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* in, int
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Built-in scratch for amct_minmax_noalloc.
+//
+// Some hosts of this library may not allocate device memory once they are up: a
+// serving process that carves its whole memory budget at start-up and treats any
+// later cudaMalloc as a fault (it takes a device-wide lock and can stall every
+// stream), or a plugin host that only ever hands the library input and output
+// buffers and has no way to pass a workspace.  For them the partial results of
+// the reduction live in this file-scope array instead of a caller workspace.
+// Every GPU that loads the library carries these 8 MiB until the process exits.
+//
+// `g_minmax_scratch` is a device symbol: in host code the name is only a handle,
+// not an address a kernel can use.  The device address is looked up with
+// cudaGetSymbolAddress once per device (with that device current) and cached.
+constexpr int64_t kStaticScratchBytes = 8LL << 20;
+static __device__ __align__(256) unsigned char g_minmax_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_scratch_addr[kMaxDevices] = {};
+static std::mutex g_scratch_mutex;
+
+static int static_scratch(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return AMCT_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_minmax_scratch) != cudaSuccess || !p) return AMCT_ERR_CUDA;
+    g_scratch_addr[dev] = p;
+  }
+  *out = reinterpret_cast<float*>(g_scratch_addr[dev]);
+  return AMCT_OK;
+}
+
 }  // namespace amct
 
 extern "C" int amct_abi_version(void) { return 1; }
@@ -282,6 +319,32 @@ extern "C" int amct_minmax(const void* x, int dtype, int64_t rows, int64_t k, in
   if (axis != AMCT_AXIS_TENSOR && axis != AMCT_AXIS_COLUMN) return AMCT_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   float* ws = reinterpret_cast<float*>(workspace);
+  switch (dtype) {
+    case AMCT_DTYPE_F32:
+      return amct::run_minmax<float>((const float*)x, rows, k, ld_x, axis, merge, (float*)out_min, (float*)out_max, ws, status, st);
+    case AMCT_DTYPE_F16:
+      return amct::run_minmax<__half>((const __half*)x, rows, k, ld_x, axis, merge, (__half*)out_min, (__half*)out_max, ws, status, st);
+    case AMCT_DTYPE_BF16:
+      return amct::run_minmax<__nv_bfloat16>((const __nv_bfloat16*)x, rows, k, ld_x, axis, merge, (__nv_bfloat16*)out_min,
+                                             (__nv_bfloat16*)out_max, ws, status, st);
+  }
+  return AMCT_ERR_ARG;
+}
+
+extern "C" int64_t amct_minmax_noalloc_max_k(void) { return amct::kStaticScratchBytes / (2LL * amct::kMaxRowChunks * 4); }
+
+extern "C" int amct_minmax_noalloc(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int axis, int merge,
+                                   void* out_min, void* out_max, int* status, void* stream) {
+  if (rows <= 0 || k <= 0 || !x || !out_min || !out_max || ld_x < k) return AMCT_ERR_ARG;
+  if (axis != AMCT_AXIS_TENSOR && axis != AMCT_AXIS_COLUMN) return AMCT_ERR_ARG;
+  // the column reduction keeps 2 x 64 partial rows of k floats: refuse what the built-in array cannot hold
+  if (axis == AMCT_AXIS_COLUMN && amct_minmax_workspace_bytes(k) > amct::kStaticScratchBytes) return AMCT_ERR_TOO_LARGE;
+  float* ws = nullptr;
+  int rc = amct::static_scratch(&ws);
+  if (rc != AMCT_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  // Nothing in the scratch has to start at zero: every partial that the second
+  // stage reads is written by the first stage of the same call.
   switch (dtype) {
     case AMCT_DTYPE_F32:
       return amct::run_minmax<float>((const float*)x, rows, k, ld_x, axis, merge, (float*)out_min, (float*)out_max, ws, status, st);

@@ -26,7 +26,7 @@ extern "C" {
 #endif
 
 enum { AMCT_OK = 0, AMCT_ERR_ARG = -1, AMCT_ERR_ALIGN = -2, AMCT_ERR_CUDA = -3, AMCT_ERR_UNSUPPORTED = -4,
-       AMCT_ERR_TIMEOUT = -5 };
+       AMCT_ERR_TIMEOUT = -5, AMCT_ERR_TOO_LARGE = -6 };
 enum { AMCT_DTYPE_F32 = 0, AMCT_DTYPE_F16 = 1, AMCT_DTYPE_BF16 = 2 };
 enum { AMCT_STRATEGY_TENSOR = 0, AMCT_STRATEGY_CHANNEL = 1, AMCT_STRATEGY_GROUP = 2 };
 enum { AMCT_RULE_RELEASED = 0, AMCT_RULE_EXPERIMENTAL = 1 };
@@ -85,6 +85,26 @@ int amct_quant_rows(const void* x, int dtype, int64_t rows, int64_t k, int64_t l
 int64_t amct_minmax_workspace_bytes(int64_t k);
 int amct_minmax(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int axis, int merge,
                 void* out_min, void* out_max, void* workspace, int* status, void* stream);
+
+/* amct_minmax for callers that cannot give it a workspace and must not see a
+ * device allocation -- a server whose memory budget is fixed at start-up, a plugin
+ * host that passes inputs and outputs only.  Same arguments and results as
+ * amct_minmax minus `workspace`: the partials live in an 8 MiB array built into
+ * the library (held by every GPU that loads it, until the process exits).  It has
+ * no counterpart in the reference; it exists for embedding, not for parity.
+ *   - limit: AMCT_AXIS_COLUMN needs k <= amct_minmax_noalloc_max_k() (16384);
+ *     larger k returns AMCT_ERR_TOO_LARGE and launches nothing.  AMCT_AXIS_TENSOR
+ *     has no size limit.
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine.  The
+ *     first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture.
+ *   - all calls share the one array, which keeps whatever the last call left in
+ *     it (nothing needs clearing: each call overwrites what it reads).  Two calls
+ *     that can overlap on the GPU -- different streams, no ordering -- race on it:
+ *     serialize them. */
+int64_t amct_minmax_noalloc_max_k(void);
+int amct_minmax_noalloc(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int axis, int merge,
+                        void* out_min, void* out_max, int* status, void* stream);
 
 /* min and max of every row of a [rows, k] matrix, in x's dtype; `pre`/pre_op
  * apply an element-wise factor [k] first (rounded to x's dtype), merge=1 folds
