@@ -397,3 +397,85 @@ def minmax_noalloc(x, axis, out_min, out_max, merge=False):
                                        c_int(1 if merge else 0), _p(out_min), _p(out_max), c_void_p(0), _stream())
     _l.check(rc, 'amct_minmax_noalloc')
     COUNTERS['launches'] += 2
+
+
+# ---------------------------------------------------------------------------
+# MX formats
+def mx_quant(x, fmt, tiled=True, rowmajor=True):
+    """x [R, K] -> (payload uint8, scales_rowmajor uint8 [R, K/32] | None, scales_tiled uint8 | None).
+    fmt 'fp8' (E4M3, payload [R, K]) or 'fp4' (E2M1, payload [R, K/2])."""
+    _need_cuda(x)
+    assert x.dim() == 2
+    x2, rows, k, ld = _rows2d(x)
+    bits = {'fp8': 8, 'fp4': 4}[fmt]
+    payload = torch.empty((rows, k if bits == 8 else k // 2), dtype=torch.uint8, device=x.device)
+    srm = torch.empty((rows, k // 32), dtype=torch.uint8, device=x.device) if rowmajor else None
+    L = _l.load()
+    st = None
+    if tiled:
+        st = torch.zeros(L.amct_mx_tiled_scale_bytes(c_int64(rows), c_int64(k)), dtype=torch.uint8, device=x.device)
+    rc = L.amct_mx_quant(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), c_int(bits), _p(payload),
+                         _p(srm), _p(st), _stream())
+    _l.check(rc, 'amct_mx_quant')
+    COUNTERS['launches'] += 1
+    return payload, srm, st
+
+
+def gemm_mx(a_payload, a_scales_tiled, b_payload, b_scales_tiled, fmt, bias=None, out_dtype=torch.bfloat16, out=None,
+            status=None):
+    """Block-scaled GEMM of two MX tensors produced by mx_quant: [M, K] x [N, K] -> [M, N]."""
+    _need_cuda(a_payload, a_scales_tiled, b_payload, b_scales_tiled, bias)
+    bits = {'fp8': 8, 'fp4': 4}[fmt]
+    m, n = a_payload.shape[0], b_payload.shape[0]
+    k = a_payload.shape[1] * (2 if bits == 4 else 1)
+    assert b_payload.shape[1] == a_payload.shape[1] and a_payload.stride(1) == 1 and b_payload.stride(1) == 1
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a_payload.device)
+    bk = 0
+    if bias is not None:
+        bias = bias.reshape(-1).contiguous()
+        bk = _BIAS_KIND[bias.dtype]
+    prof = _prof_begin()
+    rc = _l.load().amct_gemm_mx(_p(a_payload), _p(a_scales_tiled), _p(b_payload), _p(b_scales_tiled), c_int(bits),
+                                c_int64(m), c_int64(n), c_int64(k), c_int64(a_payload.stride(0)), c_int64(b_payload.stride(0)),
+                                _p(bias), c_int(bk), _p(out), c_int(_OUT_KIND[out.dtype]), c_int64(out.stride(0)),
+                                _p(status) if status is not None else c_void_p(0), _stream())
+    _l.check(rc, 'amct_gemm_mx')
+    COUNTERS['launches'] += 1
+    _prof_end(prof, 2 * m * n * k)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# HiFloat8
+def hif8_encode(x):
+    """x (any shape, contiguous) -> uint8 HiF8 codes of the same shape."""
+    _need_cuda(x)
+    x = x.contiguous()
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    rc = _l.load().amct_hif8_encode(_p(x), c_int(_dt(x)), c_int64(x.numel()), _p(codes), c_void_p(0), _stream())
+    _l.check(rc, 'amct_hif8_encode')
+    COUNTERS['launches'] += 1
+    return codes
+
+
+def hif8_fake_quant(x):
+    """decode(encode(x)) in x's dtype, one pass."""
+    _need_cuda(x)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    rc = _l.load().amct_hif8_encode(_p(x), c_int(_dt(x)), c_int64(x.numel()), c_void_p(0), _p(out), _stream())
+    _l.check(rc, 'amct_hif8_encode')
+    COUNTERS['launches'] += 1
+    return out
+
+
+def hif8_decode(codes, dtype=torch.bfloat16, out=None):
+    _need_cuda(codes)
+    codes = codes.contiguous()
+    if out is None:
+        out = torch.empty(codes.shape, dtype=dtype, device=codes.device)
+    rc = _l.load().amct_hif8_decode(_p(codes), c_int64(codes.numel()), c_int(_DT[out.dtype]), _p(out), _stream())
+    _l.check(rc, 'amct_hif8_decode')
+    COUNTERS['launches'] += 1
+    return out

@@ -1,0 +1,203 @@
+// HiFloat8 (HiF8) encode / decode.  The reference has no HiFloat8 code; the format is
+// the published tapered-precision 8-bit float:
+//   bit 7 sign | "dot" prefix code selecting the exponent width D (11 -> 4, 10 -> 3,
+//   01 -> 2, 001 -> 1, 0001 -> 0, 0000 -> denormal) | D exponent bits (sign + magnitude
+//   under an implicit leading one) | mantissa (1 bit for D = 4, 2 for D = 3, else 3)
+//   normal (-1)^S 2^E (1 + M/2^mb), E in [-15, 15]; denormal (-1)^S 2^(M-23), M = 1..7;
+//   0x00 = +0, 0x80 = NaN, 0x6F / 0xEF = +-Inf (so the largest finite magnitude is 2^15).
+// Encoding: nearest representable value, ties away from zero, finite values saturate to
+// +-2^15, magnitudes below 2^-23 flush to +0 (build decisions, pinned by the CPU oracle).
+//
+// Both directions are elementwise and HBM-bound: encode reads sizeof(T) and writes 1 byte
+// per element, decode the reverse.  Decoding is exact in fp16, bf16 and fp32.
+#include "common.cuh"
+
+namespace amct {
+
+__device__ __forceinline__ uint32_t hif8_pack(uint32_t sign, int e, uint32_t m) {
+  const int ae = e < 0 ? -e : e;
+  const uint32_t se = e < 0 ? 1u : 0u;
+  int d, mb;
+  uint32_t dot;
+  if (ae >= 8) { d = 4; mb = 1; dot = 3; }
+  else if (ae >= 4) { d = 3; mb = 2; dot = 2; }
+  else if (ae >= 2) { d = 2; mb = 3; dot = 1; }
+  else if (ae >= 1) { d = 1; mb = 3; dot = 1; }
+  else { d = 0; mb = 3; dot = 1; }
+  uint32_t efield = 0;
+  if (d > 0) efield = (se << (d - 1)) | ((uint32_t)ae - (1u << (d - 1)));
+  return (sign << 7) | ((((dot << d) | efield) << mb) | m);
+}
+
+__device__ __forceinline__ uint32_t hif8_encode(float x) {
+  const uint32_t bits = __float_as_uint(x);
+  const uint32_t sign = bits >> 31;
+  const int e = (int)((bits >> 23) & 0xFF) - 127;
+  const uint32_t man = bits & 0x7FFFFF;
+  if (e == 128) return man ? 0x80u : (sign ? 0xEFu : 0x6Fu);       // NaN, +-Inf
+  if (e < -23) return 0u;                                          // flush (also fp32 zero / denormals)
+  if (e < -15) {                                                   // powers of two 2^-22 .. 2^-16 (or 2^-15 after rounding up)
+    const int ed = e == -23 ? -22 : e + (man >= 0x400000u ? 1 : 0);
+    const int md = ed + 23;
+    return md >= 8 ? hif8_pack(sign, -15, 0) : ((sign << 7) | (uint32_t)md);
+  }
+  if (e > 15) return sign ? 0xEEu : 0x6Eu;                         // saturate
+  const int ae = e < 0 ? -e : e;
+  const int mb = ae >= 8 ? 1 : (ae >= 4 ? 2 : 3);
+  const int shift = 23 - mb;
+  const uint32_t r = man + (1u << (shift - 1));                    // ties away: add half, truncate
+  const uint32_t carry = r >> 23;
+  const uint32_t m = carry ? 0u : ((r >> shift) & ((1u << mb) - 1));
+  const int en = e + (int)carry;
+  if (en > 15 || (en == 15 && m == 1)) return sign ? 0xEEu : 0x6Eu;
+  return hif8_pack(sign, en, m);
+}
+
+__device__ __forceinline__ float hif8_decode(uint32_t code) {
+  const uint32_t body = code & 0x7F;
+  const float sgn = (code & 0x80) ? -1.f : 1.f;
+  int d, nrest;
+  if ((body >> 5) == 3) { d = 4; nrest = 5; }
+  else if ((body >> 5) == 2) { d = 3; nrest = 5; }
+  else if ((body >> 5) == 1) { d = 2; nrest = 5; }
+  else if ((body >> 4) == 1) { d = 1; nrest = 4; }
+  else if ((body >> 3) == 1) { d = 0; nrest = 3; }
+  else {
+    const uint32_t m = body & 7;
+    if (m == 0) return (code & 0x80) ? __uint_as_float(0x7FC00000u) : 0.f;
+    return sgn * __uint_as_float((uint32_t)(127 + (int)m - 23) << 23);
+  }
+  const uint32_t rest = body & ((1u << nrest) - 1);
+  const int mb = nrest - d;
+  const uint32_t ebits = rest >> mb, m = rest & ((1u << mb) - 1);
+  int e = 0;
+  if (d > 0) {
+    const int mag = (1 << (d - 1)) | (int)(ebits & ((1u << (d - 1)) - 1));
+    e = ((ebits >> (d - 1)) & 1) ? -mag : mag;
+  }
+  if (e == 15 && m == 1) return sgn * __uint_as_float(0x7F800000u);
+  return sgn * __uint_as_float(((uint32_t)(127 + e) << 23) | (m << (23 - mb)));
+}
+
+// 8 consecutive values -> memory (dst 16-byte aligned for 16-bit T, 32-byte data for fp32)
+template <typename T> __device__ __forceinline__ void store8(T* dst, const float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    Vec16<T> r;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) r.v[e] = ElemTraits<T>::from_f(f[e]);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(&r);
+  } else {
+    *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
+// mode 0: encode x -> codes;  mode 1: fake-quantize x -> decode(encode(x)) in T
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) hif8_encode_kernel(const T* x, int64_t n, uint8_t* codes, T* fake) {
+  const int64_t nv = n / 8;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += stride) {
+    float f[8];
+    if constexpr (sizeof(T) == 2) {
+      Vec16<T> raw = ld_vec_stream(x + v * 8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = ElemTraits<T>::to_f(raw.v[e]);
+    } else {
+      Vec16<T> r0 = ld_vec_stream(x + v * 8), r1 = ld_vec_stream(x + v * 8 + 4);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { f[e] = ElemTraits<T>::to_f(r0.v[e]); f[4 + e] = ElemTraits<T>::to_f(r1.v[e]); }
+    }
+    uint32_t c[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) c[e] = hif8_encode(f[e]);
+    if constexpr (MODE == 0) {
+      uint32_t lo = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24), hi = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+      *reinterpret_cast<uint2*>(codes + v * 8) = make_uint2(lo, hi);
+    } else {
+      float d[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) d[e] = hif8_decode(c[e]);
+      store8<T>(fake + v * 8, d);
+    }
+  }
+  // tail (n not a multiple of 8): the first threads of block 0 take one element each
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nv * 8)) {
+    const int64_t i = nv * 8 + threadIdx.x;
+    const uint32_t c = hif8_encode(ElemTraits<T>::to_f(x[i]));
+    if constexpr (MODE == 0) codes[i] = (uint8_t)c;
+    else fake[i] = ElemTraits<T>::from_f(hif8_decode(c));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) hif8_decode_kernel(const uint8_t* codes, int64_t n, T* out) {
+  __shared__ float table[256];
+  table[threadIdx.x] = hif8_decode(threadIdx.x);
+  __syncthreads();
+  const int64_t nv = n / 8;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += stride) {
+    const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(codes + v * 8));
+    float d[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) d[e] = table[((e < 4 ? raw.x : raw.y) >> (8 * (e & 3))) & 0xFF];
+    store8<T>(out + v * 8, d);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nv * 8)) {
+    const int64_t i = nv * 8 + threadIdx.x;
+    out[i] = ElemTraits<T>::from_f(table[codes[i]]);
+  }
+}
+
+static unsigned grid_for(int64_t n) {
+  int64_t blocks = (n / 8 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return (unsigned)blocks;
+}
+
+template <typename T>
+static int run_encode(const T* x, int64_t n, uint8_t* codes, T* fake, cudaStream_t st) {
+  if (codes) hif8_encode_kernel<T, 0><<<grid_for(n), 256, 0, st>>>(x, n, codes, nullptr);
+  else hif8_encode_kernel<T, 1><<<grid_for(n), 256, 0, st>>>(x, n, nullptr, fake);
+  AMCT_CHECK_LAUNCH();
+  return AMCT_OK;
+}
+
+}  // namespace amct
+
+// x [n] contiguous -> HiF8 codes [n] (codes != NULL) or fake-quantized values in x's dtype (fake != NULL).
+extern "C" int amct_hif8_encode(const void* x, int dtype, int64_t n, void* codes, void* fake, void* stream) {
+  if (n < 0 || (!codes) == (!fake)) return AMCT_ERR_ARG;
+  if (n == 0) return AMCT_OK;
+  if (!x) return AMCT_ERR_ARG;
+  if (!amct::aligned16(x) || (codes && reinterpret_cast<uintptr_t>(codes) % 8) || (fake && !amct::aligned16(fake)))
+    return AMCT_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* c = reinterpret_cast<uint8_t*>(codes);
+  switch (dtype) {
+    case AMCT_DTYPE_F32: return amct::run_encode<float>((const float*)x, n, c, (float*)fake, st);
+    case AMCT_DTYPE_F16: return amct::run_encode<__half>((const __half*)x, n, c, (__half*)fake, st);
+    case AMCT_DTYPE_BF16: return amct::run_encode<__nv_bfloat16>((const __nv_bfloat16*)x, n, c, (__nv_bfloat16*)fake, st);
+  }
+  return AMCT_ERR_ARG;
+}
+
+extern "C" int amct_hif8_decode(const void* codes, int64_t n, int dtype, void* out, void* stream) {
+  if (n < 0) return AMCT_ERR_ARG;
+  if (n == 0) return AMCT_OK;
+  if (!codes || !out) return AMCT_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(codes) % 8 || !amct::aligned16(out)) return AMCT_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  const uint8_t* c = reinterpret_cast<const uint8_t*>(codes);
+  const unsigned grid = amct::grid_for(n);
+  switch (dtype) {
+    case AMCT_DTYPE_F32: amct::hif8_decode_kernel<float><<<grid, 256, 0, st>>>(c, n, (float*)out); break;
+    case AMCT_DTYPE_F16: amct::hif8_decode_kernel<__half><<<grid, 256, 0, st>>>(c, n, (__half*)out); break;
+    case AMCT_DTYPE_BF16: amct::hif8_decode_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(c, n, (__nv_bfloat16*)out); break;
+    default: return AMCT_ERR_ARG;
+  }
+  AMCT_CHECK_LAUNCH();
+  return AMCT_OK;
+}

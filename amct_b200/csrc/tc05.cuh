@@ -163,4 +163,59 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       : "memory");
 }
 
+// ---- block-scaled kinds (MX formats) ----------------------------------------
+// 1-D bulk copy global -> shared, completion on `bar`; both addresses 16-byte aligned,
+// size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// Descriptor of 32 rows x 16 bytes lying contiguously in shared memory (no swizzle;
+// 8-row groups 128 bytes apart): the source of the scale-factor copy below.
+__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffff) >> 4);
+  d |= (uint64_t)(128 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// shared -> tensor memory: 32 rows x 128 bits, replicated into the four 32-lane
+// quarters; lands in 4 consecutive 32-bit columns starting at `taddr`.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// Instruction descriptor of the block-scaled kinds (E8M0 scales, K-major A and B):
+//   [4,6) B scale id   [7,10) A format   [10,13) B format   [17,23) N >> 3
+//   [23] scale format (1 = E8M0)   [24,29) M >> 4   [29,31) A scale id
+// formats: kind::mxf8f6f4 -> 0 e4m3;  kind::mxf4 -> 1 e2m1.  A scale id selects the byte
+// (or byte pair) of the 32-bit scale word this instruction uses.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t fmt, uint32_t m, uint32_t n, uint32_t sf_id) {
+  return (sf_id << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_id << 29);
+}
+
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                          uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void umma_mxf4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                          uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+
 }  // namespace tc05

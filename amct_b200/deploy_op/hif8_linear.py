@@ -1,0 +1,49 @@
+import torch
+
+from ..backend import ops
+
+
+class HiFloat8Linear(torch.nn.Module):
+    """Linear with HiFloat8 weights and activations.
+
+    Buffers: ``quantized_weight`` uint8 HiF8 codes [K, N] (a transposed view of the
+    K-contiguous [N, K] storage), ``scale_factor`` [1, K] reciprocal smoothing factor (only
+    when the calibration produced one), ``bias``.  forward(): activations are multiplied by
+    scale_factor, rounded to HiFloat8 and back in one pass; the weight codes are decoded
+    (exactly) to the activation dtype and the product runs on the tensor cores with fp32
+    accumulation.  B200 has no HiFloat8 MMA, so the 16-bit MMA on exactly decoded operands
+    is the arithmetic definition of this layer.
+    """
+
+    def __init__(self, quant_module):
+        super().__init__()
+        weight = quant_module.weight.data
+        self.output_dtype = weight.dtype
+        smooth = quant_module.scale
+        if smooth is not None:
+            smooth = smooth.to(device=weight.device, dtype=weight.dtype)
+            weight = weight * smooth
+            self.register_buffer('scale_factor', 1 / smooth)
+        else:
+            self.scale_factor = None
+        self.register_buffer('quantized_weight', ops.hif8_encode(weight).t())
+        self.bias = None
+        if quant_module.bias is not None:
+            self.register_buffer('bias', quant_module.bias.data.to(torch.float32))
+        self._decoded = None
+        self.cache_decoded_weight = False
+
+    @torch.no_grad()
+    def forward(self, x):
+        k = x.shape[-1]
+        x2 = x.reshape(-1, k)
+        if self.scale_factor is not None:
+            x2 = x2 * self.scale_factor
+        xq = ops.hif8_fake_quant(x2)
+        w = self._decoded
+        if w is None:
+            w = ops.hif8_decode(self.quantized_weight.t(), dtype=x.dtype)
+            if self.cache_decoded_weight:
+                self._decoded = w
+        out = ops.gemm_f16(xq, w, bias=self.bias, out_dtype=x.dtype)
+        return out.reshape(*x.shape[:-1], -1)

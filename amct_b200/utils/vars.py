@@ -2,8 +2,8 @@
 amct_pytorch/utils/vars.py:19-47)."""
 import torch
 
-SUPPORT_WEIGHT_QUANT_DTYPE = ['int8', 'int4']
-SUPPORT_INPUT_QUANT_DTYPE = ['int8']
+SUPPORT_WEIGHT_QUANT_DTYPE = ['int8', 'int4', 'hifloat8']          # 'hifloat8' is additive
+SUPPORT_INPUT_QUANT_DTYPE = ['int8', 'hifloat8']
 SUPPORT_QUANT_STRATEGY_WEIGHT = ['tensor', 'channel', 'group']
 SUPPORT_QUANT_STRATEGY_INPUT = ['tensor', 'token']
 

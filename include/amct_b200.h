@@ -179,6 +179,41 @@ int amct_dequant_weight(const void* codes, int bits, int64_t n_rows, int64_t k, 
                         const void* scale, const void* offset, int group, int dtype, void* out,
                         int64_t ld_out, void* stream);
 
+/* ---- MX formats (no counterpart in the reference: amct_pytorch/utils/vars.py:19-20
+ * admits int8 / int4 only; the rule is the public OCP Microscaling v1.0 conversion) ---- */
+
+/* MXFP8-E4M3 (elem_bits = 8) or MXFP4-E2M1 (elem_bits = 4) quantization of x [rows, k]
+ * (k % 32 == 0) with one E8M0 scale per 32 elements of K.  payload: uint8 [rows, k]
+ * (E4M3 bit patterns) or [rows, k/2] (two E2M1 codes per byte, even k in the low
+ * nibble).  scales_rowmajor: uint8 [rows, k/32] or NULL.  scales_tiled: NULL or a buffer
+ * of amct_mx_tiled_scale_bytes(rows, k) bytes in the 128-row x 4-block tiling the
+ * block-scaled GEMM consumes:
+ *   offset(r, kb) = ((r/128) * ceil(k/128) + kb/4) * 512 + (r%32)*16 + ((r%128)/32)*4 + kb%4 */
+int64_t amct_mx_tiled_scale_bytes(int64_t rows, int64_t k);
+int amct_mx_quant(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int elem_bits, void* payload,
+                  void* scales_rowmajor, void* scales_tiled, void* stream);
+
+/* Block-scaled MX GEMM: out[m, n] = sum over 32-element K blocks of
+ *   2^(sfa[m,blk]-127) * 2^(sfb[n,blk]-127) * dot(a[m, blk], b[n, blk])      (+ bias[n])
+ * a [m, k] and b [n, k]: E4M3 bytes (elem_bits = 8, k % 128 == 0) or packed E2M1 nibbles
+ * (elem_bits = 4, k % 256 == 0), K contiguous, leading dimensions in BYTES (multiples of
+ * 16); sfa_tiled / sfb_tiled: the tiled scale buffers written by amct_mx_quant.  fp32
+ * accumulation on the tensor cores (tcgen05 kind::mxf8f6f4 / kind::mxf4 block_scale).
+ * bias_kind: AMCT_BIAS_NONE / F32 / F16 / BF16; out_kind: AMCT_GEMM_OUT_F32 / F16 / BF16. */
+int amct_gemm_mx(const void* a, const void* sfa_tiled, const void* b, const void* sfb_tiled, int elem_bits,
+                 int64_t m, int64_t n, int64_t k, int64_t ld_a_bytes, int64_t ld_b_bytes, const void* bias,
+                 int bias_kind, void* out, int out_kind, int64_t ld_out, int* status, void* stream);
+
+/* ---- HiFloat8 (no counterpart in the reference; format and rounding as documented in
+ * amct_b200/csrc/hif8.cu and oracle/hif8.py) ---- */
+
+/* x [n] contiguous -> HiF8 codes uint8 [n] (codes != NULL, fake == NULL), or the
+ * fake-quantized values decode(encode(x)) in x's dtype (fake != NULL, codes == NULL). */
+int amct_hif8_encode(const void* x, int dtype, int64_t n, void* codes, void* fake, void* stream);
+
+/* HiF8 codes uint8 [n] -> values in `dtype` (exact in fp16, bf16 and fp32). */
+int amct_hif8_decode(const void* codes, int64_t n, int dtype, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
