@@ -53,25 +53,38 @@ LLAMA3_70B = LlamaShape()
 LLAMA3_8B = LlamaShape(hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, intermediate=14336, n_layers=32)
 
 
+def shard_dims(shape, tp):
+    """(K, N) of the four Linears one rank holds: fused q/k/v and gate/up are split along N
+    (column-parallel), o_proj and down_proj along K (row-parallel)."""
+    if shape.n_kv_heads % tp or shape.n_heads % tp or shape.intermediate % tp:
+        raise ValueError(f'tp={tp} does not divide the head / intermediate sizes')
+    h = shape.hidden
+    return {
+        'qkv_proj': (h, (shape.n_heads + 2 * shape.n_kv_heads) * shape.head_dim // tp),
+        'o_proj': (shape.n_heads * shape.head_dim // tp, h),
+        'gate_up_proj': (h, 2 * shape.intermediate // tp),
+        'down_proj': (shape.intermediate // tp, h),
+    }
+
+
 class _Shard(nn.Module):
     """The float Linears of one rank's slice of a decoder layer (before quantization)."""
 
     def __init__(self, shape, tp, device, gen, std=0.02):
         super().__init__()
-        h = shape.hidden
-        qkv_out = (shape.n_heads + 2 * shape.n_kv_heads) * shape.head_dim // tp
-        inter = shape.intermediate // tp
+        dims = shard_dims(shape, tp)
 
-        def lin(k, n):
+        def lin(name):
+            k, n = dims[name]
             m = nn.Linear(k, n, bias=False, device='meta', dtype=torch.bfloat16)
             m.weight = nn.Parameter(torch.empty(n, k, dtype=torch.bfloat16, device=device).normal_(0, std, generator=gen),
                                     requires_grad=False)
             return m
 
-        self.qkv_proj = lin(h, qkv_out)
-        self.o_proj = lin(shape.n_heads * shape.head_dim // tp, h)
-        self.gate_up_proj = lin(h, 2 * inter)
-        self.down_proj = lin(inter, h)
+        self.qkv_proj = lin('qkv_proj')
+        self.o_proj = lin('o_proj')
+        self.gate_up_proj = lin('gate_up_proj')
+        self.down_proj = lin('down_proj')
 
 
 def rotary_tables(shape, positions, device):
