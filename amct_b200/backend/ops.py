@@ -401,9 +401,13 @@ def minmax_noalloc(x, axis, out_min, out_max, merge=False):
 
 # ---------------------------------------------------------------------------
 # MX formats
-def mx_quant(x, fmt, tiled=True, rowmajor=True):
+MX_TILE_ROWS = {'a': 128, 'b': 224}
+
+
+def mx_quant(x, fmt, operand='a', tiled=True, rowmajor=True):
     """x [R, K] -> (payload uint8, scales_rowmajor uint8 [R, K/32] | None, scales_tiled uint8 | None).
-    fmt 'fp8' (E4M3, payload [R, K]) or 'fp4' (E2M1, payload [R, K/2])."""
+    fmt 'fp8' (E4M3, payload [R, K]) or 'fp4' (E2M1, payload [R, K/2]).  operand 'a' / 'b' picks the
+    tiling of scales_tiled for the A resp. B side of gemm_mx."""
     _need_cuda(x)
     assert x.dim() == 2
     x2, rows, k, ld = _rows2d(x)
@@ -413,9 +417,10 @@ def mx_quant(x, fmt, tiled=True, rowmajor=True):
     L = _l.load()
     st = None
     if tiled:
-        st = torch.zeros(L.amct_mx_tiled_scale_bytes(c_int64(rows), c_int64(k)), dtype=torch.uint8, device=x.device)
+        st = torch.zeros(L.amct_mx_tiled_scale_bytes(c_int64(rows), c_int64(k), c_int(MX_TILE_ROWS[operand])),
+                         dtype=torch.uint8, device=x.device)
     rc = L.amct_mx_quant(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), c_int(bits), _p(payload),
-                         _p(srm), _p(st), _stream())
+                         _p(srm), _p(st), c_int(MX_TILE_ROWS[operand]), _stream())
     _l.check(rc, 'amct_mx_quant')
     COUNTERS['launches'] += 1
     return payload, srm, st

@@ -14,8 +14,9 @@
 // into tensor memory with tcgen05.cp (in order with the MMAs that use them) and issues
 // tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 per instruction, one scale byte per row)
 // or kind::mxf4.block_scale.block32 (K = 64, two scale bytes per row).
-// 224 is not a multiple of the 128-row scale atom, so B's scales are copied for the up to
-// three atoms the tile touches and addressed from column (n0 / 32) % 4 of that copy.
+// 224 is not a multiple of the 128-row scale atom and the scale address of the MMA must
+// stay aligned, so B's scales are tiled per 224-row GEMM tile by the quantizer (two atoms
+// per tile, the last 32 rows of the second one unused).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -47,7 +48,7 @@ struct Params {
 struct __align__(1024) Smem {
   uint8_t tiles[kStages][kTileBytes];
   uint8_t sfa[kStages][1024];          // up to 2 atoms (fp4) of A's 128 rows
-  uint8_t sfb[kStages][3][1024];       // up to 3 row atoms x up to 2 K atoms of B
+  uint8_t sfb[kStages][2][1024];       // 2 row atoms x up to 2 K atoms of B
   float epi_bias[4][kBN];
   uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
@@ -82,7 +83,6 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int64_t kb4_total = (p.k / 32 + 3) / 4;                   // scale atoms along K
   const int64_t tiles_m = (p.m + kBM - 1) / kBM, tiles_n = (p.n + kBN - 1) / kBN;
   const int64_t num_tiles = tiles_m * tiles_n;
-  const int64_t b_atom_rows = (p.n + 127) / 128;
 
   if (threadIdx.x == 0) {
     s.abort_flag = 0;
@@ -110,9 +110,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int64_t tm, tn;
         tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
-        const int64_t atom0 = (tn * kBN) / 128;                                   // first scale atom row of B
-        int natoms = (int)((tn * kBN + kBN - 1) / 128 - atom0 + 1);              // 2 or 3
-        if (atom0 + natoms > b_atom_rows) natoms = (int)(b_atom_rows - atom0);
+        const int64_t atom0 = tn * 2;                                             // B's scales: two atoms per 224-row tile
+        const int natoms = 2;
         const uint32_t sf_bytes = 512u * katoms;
         for (int64_t kb = 0; kb < num_kb; ++kb) {
           if (!tc05::mbar_wait(tc05::smem_u32(&s.empty[stage]), phase ^ 1, abort_flag)) { alive = false; break; }
@@ -137,7 +136,6 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int64_t tm, tn;
         tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
-        const uint32_t sfb_shift = (uint32_t)(((tn * kBN) / 32) % 4);            // tile's first 32-row group inside its atom
         if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_empty[acc]), acc_phase ^ 1, abort_flag)) break;
         tc05::fence_after_sync();
         const uint32_t d_tmem = tmem_base + (acc ? kAcc1 : kAcc0);
@@ -148,8 +146,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int j = 0; j < katoms; ++j) {
             tc05::tmem_cp_32x128b_warpx4(tmem_base + kSfaCol + 4 * j, tc05::smem_desc_sf(tc05::smem_u32(&s.sfa[stage][512 * j])));
 #pragma unroll
-            for (int a = 0; a < 3; ++a)
-              tc05::tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 12 * j + 4 * a,
+            for (int a = 0; a < 2; ++a)
+              tc05::tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 8 * j + 4 * a,
                                            tc05::smem_desc_sf(tc05::smem_u32(&s.sfb[stage][a][512 * j])));
           }
           const uint32_t a0 = tc05::smem_u32(&s.tiles[stage][0]);
@@ -162,10 +160,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             if (p.fp4) {
               const int j = ks >> 1;
               const uint32_t idesc = tc05::make_idesc_mx(1, kBM, kBN, (ks & 1) * 2);
-              tc05::umma_mxf4(d_tmem, adesc, bdesc, idesc, tmem_base + kSfaCol + 4 * j, tmem_base + kSfbCol + 12 * j + sfb_shift, accumulate);
+              tc05::umma_mxf4(d_tmem, adesc, bdesc, idesc, tmem_base + kSfaCol + 4 * j, tmem_base + kSfbCol + 8 * j, accumulate);
             } else {
               const uint32_t idesc = tc05::make_idesc_mx(0, kBM, kBN, ks);
-              tc05::umma_mxf8(d_tmem, adesc, bdesc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol + sfb_shift, accumulate);
+              tc05::umma_mxf8(d_tmem, adesc, bdesc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol, accumulate);
             }
           }
           tc05::umma_commit(tc05::smem_u32(&s.empty[stage]));

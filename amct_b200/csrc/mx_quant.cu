@@ -13,8 +13,11 @@
 // fully coalesced 16- / 8- / 4-byte accesses, the block maximum is two shuffles, and
 // the 2^-e scaling is an exact multiply by a constructed power of two.  Scales are
 // written row-major [rows, K/32] and, optionally, in the 128 x 4 tiling the
-// block-scaled tensor-core GEMM copies straight into tensor memory:
-//     offset(r, kb) = ((r/128) * ceil(K/128) + kb/4) * 512 + (r%32)*16 + ((r%128)/32)*4 + kb%4
+// block-scaled tensor-core GEMM copies straight into tensor memory: rows are cut into
+// GEMM tiles of `tile_rows` rows (128 for the A operand, 224 for the B operand), each tile
+// into atoms of 128 rows, and an atom holds 4 K blocks of its 128 rows in 512 bytes:
+//     t = r / tile_rows, q = r % tile_rows, atom = t * ceil(tile_rows/128) + q/128
+//     offset(r, kb) = (atom * ceil(K/128) + kb/4) * 512 + (q%32)*16 + ((q%128)/32)*4 + kb%4
 //
 // HBM traffic per element: sizeof(T) read + 1 (fp8) or 0.5 (fp4) + 1/32 bytes written.
 #include <cuda_fp8.h>
@@ -26,7 +29,7 @@ namespace amct {
 
 template <typename T, int FMT>
 __global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int64_t rows, int64_t k, int64_t ld, uint8_t* payload,
-                                                       uint8_t* scales_rm, uint8_t* scales_tiled) {
+                                                       uint8_t* scales_rm, uint8_t* scales_tiled, int tile_rows) {
   constexpr int EMAX = FMT == 8 ? 8 : 2;
   const int lane = threadIdx.x & 31;
   const int64_t oct_per_row = k / 8;
@@ -101,7 +104,9 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int64_t rows,
     }
 
     const int64_t kb = oct / 4;
-    const int64_t tiled_off = ((row / 128) * kb4_per_row + kb / 4) * 512 + (row % 32) * 16 + ((row % 128) / 32) * 4 + (kb % 4);
+    const int64_t tq = row % tile_rows;
+    const int64_t atom = (row / tile_rows) * ((tile_rows + 127) / 128) + tq / 128;
+    const int64_t tiled_off = (atom * kb4_per_row + kb / 4) * 512 + (tq % 32) * 16 + ((tq % 128) / 32) * 4 + (kb % 4);
     if (wide) {
       const int g16 = lane & ~15;
       uint32_t word = __shfl_sync(0xffffffffu, scale_byte, g16) | (__shfl_sync(0xffffffffu, scale_byte, g16 + 4) << 8) |
@@ -119,30 +124,33 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int64_t rows,
 
 template <typename T>
 static int run_mx(const T* x, int64_t rows, int64_t k, int64_t ld, int fmt, uint8_t* payload, uint8_t* srm, uint8_t* st,
-                  cudaStream_t stream) {
+                  int tile_rows, cudaStream_t stream) {
   const int64_t total = rows * (k / 8);
   int64_t blocks = (total + 255) / 256;
   const int64_t cap = 148LL * 8 * 8;
   if (blocks > cap) blocks = cap;
-  if (fmt == 8) mx_quant_kernel<T, 8><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st);
-  else mx_quant_kernel<T, 4><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st);
+  if (fmt == 8) mx_quant_kernel<T, 8><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st, tile_rows);
+  else mx_quant_kernel<T, 4><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st, tile_rows);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
 
 }  // namespace amct
 
-extern "C" int64_t amct_mx_tiled_scale_bytes(int64_t rows, int64_t k) {
-  if (rows < 0 || k < 0) return 0;
-  return ((rows + 127) / 128) * ((k / 32 + 3) / 4) * 512;
+extern "C" int64_t amct_mx_tiled_scale_bytes(int64_t rows, int64_t k, int tile_rows) {
+  if (rows < 0 || k < 0 || tile_rows < 32 || tile_rows % 32) return 0;
+  const int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+  return tiles * ((tile_rows + 127) / 128) * ((k / 32 + 3) / 4) * 512;
 }
 
 extern "C" int amct_mx_quant(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int elem_bits, void* payload,
-                             void* scales_rowmajor, void* scales_tiled, void* stream) {
+                             void* scales_rowmajor, void* scales_tiled, int scale_tile_rows, void* stream) {
   if (rows < 0 || k < 0 || ld_x < k || (elem_bits != 8 && elem_bits != 4)) return AMCT_ERR_ARG;
   if (rows == 0 || k == 0) return AMCT_OK;
   if (!x || !payload || (!scales_rowmajor && !scales_tiled)) return AMCT_ERR_ARG;
   if (k % 32 != 0) return AMCT_ERR_UNSUPPORTED;
+  if (scales_tiled && (scale_tile_rows < 32 || scale_tile_rows % 32 != 0)) return AMCT_ERR_ARG;
+  const int tr = scales_tiled ? scale_tile_rows : 128;
   const int esize = dtype == AMCT_DTYPE_F32 ? 4 : 2;
   if (!amct::aligned16(x) || (ld_x * esize) % 16 != 0 || reinterpret_cast<uintptr_t>(payload) % 8 != 0 ||
       (scales_rowmajor && reinterpret_cast<uintptr_t>(scales_rowmajor) % 4 != 0) ||
@@ -153,9 +161,9 @@ extern "C" int amct_mx_quant(const void* x, int dtype, int64_t rows, int64_t k, 
   uint8_t* srm = reinterpret_cast<uint8_t*>(scales_rowmajor);
   uint8_t* stl = reinterpret_cast<uint8_t*>(scales_tiled);
   switch (dtype) {
-    case AMCT_DTYPE_F32: return amct::run_mx<float>((const float*)x, rows, k, ld_x, elem_bits, p, srm, stl, st);
-    case AMCT_DTYPE_F16: return amct::run_mx<__half>((const __half*)x, rows, k, ld_x, elem_bits, p, srm, stl, st);
-    case AMCT_DTYPE_BF16: return amct::run_mx<__nv_bfloat16>((const __nv_bfloat16*)x, rows, k, ld_x, elem_bits, p, srm, stl, st);
+    case AMCT_DTYPE_F32: return amct::run_mx<float>((const float*)x, rows, k, ld_x, elem_bits, p, srm, stl, tr, st);
+    case AMCT_DTYPE_F16: return amct::run_mx<__half>((const __half*)x, rows, k, ld_x, elem_bits, p, srm, stl, tr, st);
+    case AMCT_DTYPE_BF16: return amct::run_mx<__nv_bfloat16>((const __nv_bfloat16*)x, rows, k, ld_x, elem_bits, p, srm, stl, tr, st);
   }
   return AMCT_ERR_ARG;
 }

@@ -27,9 +27,10 @@ class HiFloat8Linear(torch.nn.Module):
         else:
             self.scale_factor = None
         self.register_buffer('quantized_weight', ops.hif8_encode(weight).t())
-        self.bias = None
         if quant_module.bias is not None:
             self.register_buffer('bias', quant_module.bias.data.to(torch.float32))
+        else:
+            self.bias = None
         self._decoded = None
         self.cache_decoded_weight = False
 

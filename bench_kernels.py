@@ -7,7 +7,7 @@ Every case: 3 warm-up launches, then `reps` launches each preceded by an L2 flus
 the launching stream.  Reported: median and best time, algorithmic bytes or
 operations per launch, achieved GB/s or TOP/s and the fraction of the measured peak
 (MEASURED_PEAKS.json when present: HBM copy bandwidth; 2x the bf16 burst figure for
-INT8, since a kernel is timed alone here).
+INT8 and FP8, 4x for FP4, since a kernel is timed alone here).
 """
 import argparse
 import json
@@ -126,6 +126,29 @@ def cases():
             return (randn(m, k, torch.bfloat16), randn(n, k, torch.bfloat16, 0.02), torch.empty(m, n, device='cuda', dtype=torch.bfloat16))
         yield (f'gemm_f16 bf16 {tag} {m}x{n}x{k}', setup16, lambda t: (lambda: ops.gemm_f16(t[0], t[1], out=t[2])),
                dict(nops=2 * m * n * k, peak_mult=1.0))
+    # ---- MX quantization and block-scaled GEMM (config 3 shapes)
+    for fmt, pb in (('fp8', 1.0), ('fp4', 0.5)):
+        for r, k, opnd, tag in ((8192, 8192, 'a', 'c3 act'), (28672, 8192, 'b', 'c3 weight')):
+            yield (f'mx_quant {fmt} {tag} [{r}x{k}] bf16', lambda r=r, k=k, s=(1.0 if opnd == 'a' else 0.015): randn(r, k, torch.bfloat16, s),
+                   lambda x, fmt=fmt, opnd=opnd: (lambda: ops.mx_quant(x, fmt, operand=opnd)),
+                   dict(nbytes=int(r * k * (2 + pb) + 2 * r * k // 32)))
+    for fmt, mult in (('fp8', 2.0), ('fp4', 4.0)):
+        def setup_mx(fmt=fmt):
+            a = randn(8192, 8192, torch.bfloat16)
+            b = randn(28672, 8192, torch.bfloat16, 0.015)
+            ap, _, at = ops.mx_quant(a, fmt, operand='a', rowmajor=False)
+            bp, _, bt = ops.mx_quant(b, fmt, operand='b', rowmajor=False)
+            return ap, at, bp, bt, torch.empty(8192, 28672, device='cuda', dtype=torch.bfloat16)
+        yield (f'gemm_mx {fmt} c3 8192x28672x8192 -> bf16', setup_mx,
+               lambda t, fmt=fmt: (lambda: ops.gemm_mx(t[0], t[1], t[2], t[3], fmt, out=t[4])),
+               dict(nops=2 * 8192 * 28672 * 8192, peak_mult=mult))
+    # ---- HiFloat8
+    yield ('hif8_encode [16384x14336] bf16', lambda: randn(16384, 14336, torch.bfloat16),
+           lambda x: (lambda: ops.hif8_encode(x)), dict(nbytes=16384 * 14336 * 3))
+    yield ('hif8_fake_quant [16384x4096] bf16', lambda: randn(16384, 4096, torch.bfloat16),
+           lambda x: (lambda: ops.hif8_fake_quant(x)), dict(nbytes=16384 * 4096 * 4))
+    yield ('hif8_decode [14336x4096] -> bf16', lambda: torch.randint(0, 256, (14336, 4096), device='cuda', dtype=torch.uint8),
+           lambda c: (lambda: ops.hif8_decode(c)), dict(nbytes=14336 * 4096 * 3))
     # ---- weight dequant (stage 1 of the weight-only Linear)
     def setup_dq():
         codes = torch.randint(0, 256, (11008, 2048), device='cuda', dtype=torch.uint8)

@@ -186,18 +186,22 @@ int amct_dequant_weight(const void* codes, int bits, int64_t n_rows, int64_t k, 
  * (k % 32 == 0) with one E8M0 scale per 32 elements of K.  payload: uint8 [rows, k]
  * (E4M3 bit patterns) or [rows, k/2] (two E2M1 codes per byte, even k in the low
  * nibble).  scales_rowmajor: uint8 [rows, k/32] or NULL.  scales_tiled: NULL or a buffer
- * of amct_mx_tiled_scale_bytes(rows, k) bytes in the 128-row x 4-block tiling the
- * block-scaled GEMM consumes:
- *   offset(r, kb) = ((r/128) * ceil(k/128) + kb/4) * 512 + (r%32)*16 + ((r%128)/32)*4 + kb%4 */
-int64_t amct_mx_tiled_scale_bytes(int64_t rows, int64_t k);
+ * of amct_mx_tiled_scale_bytes(rows, k, scale_tile_rows) bytes in the tiling the
+ * block-scaled GEMM consumes.  scale_tile_rows is the GEMM tile height of the operand:
+ * AMCT_MX_TILE_ROWS_A (128) for A, AMCT_MX_TILE_ROWS_B (224) for B.  With
+ *   t = r / tile_rows, q = r % tile_rows, atom = t * ceil(tile_rows/128) + q/128:
+ *   offset(r, kb) = (atom * ceil(k/128) + kb/4) * 512 + (q%32)*16 + ((q%128)/32)*4 + kb%4 */
+enum { AMCT_MX_TILE_ROWS_A = 128, AMCT_MX_TILE_ROWS_B = 224 };
+int64_t amct_mx_tiled_scale_bytes(int64_t rows, int64_t k, int scale_tile_rows);
 int amct_mx_quant(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int elem_bits, void* payload,
-                  void* scales_rowmajor, void* scales_tiled, void* stream);
+                  void* scales_rowmajor, void* scales_tiled, int scale_tile_rows, void* stream);
 
 /* Block-scaled MX GEMM: out[m, n] = sum over 32-element K blocks of
  *   2^(sfa[m,blk]-127) * 2^(sfb[n,blk]-127) * dot(a[m, blk], b[n, blk])      (+ bias[n])
  * a [m, k] and b [n, k]: E4M3 bytes (elem_bits = 8, k % 128 == 0) or packed E2M1 nibbles
  * (elem_bits = 4, k % 256 == 0), K contiguous, leading dimensions in BYTES (multiples of
- * 16); sfa_tiled / sfb_tiled: the tiled scale buffers written by amct_mx_quant.  fp32
+ * 16); sfa_tiled / sfb_tiled: the tiled scale buffers written by amct_mx_quant with
+ * scale_tile_rows = AMCT_MX_TILE_ROWS_A resp. AMCT_MX_TILE_ROWS_B.  fp32
  * accumulation on the tensor cores (tcgen05 kind::mxf8f6f4 / kind::mxf4 block_scale).
  * bias_kind: AMCT_BIAS_NONE / F32 / F16 / BF16; out_kind: AMCT_GEMM_OUT_F32 / F16 / BF16. */
 int amct_gemm_mx(const void* a, const void* sfa_tiled, const void* b, const void* sfb_tiled, int elem_bits,
