@@ -392,6 +392,10 @@ static int dispatch_rows(int dtype, const RowParams& p, cudaStream_t st) {
   return AMCT_ERR_ARG;
 }
 
+// streaming kernel of quant_token.cu; returns 1 when the shape does not fit it
+int quant_token_try(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, const void* smooth, int8_t* q,
+                    int64_t ld_q, float* scale, int* status, cudaStream_t st);
+
 }  // namespace amct
 
 using amct::RowParams;
@@ -402,6 +406,10 @@ extern "C" int amct_quant_dynamic_pertoken(const void* x, int dtype, int64_t row
   if (rows < 0 || k < 0 || (rows && k && (!x || !q || !scale)) || ld_x < k || ld_q < k) return AMCT_ERR_ARG;
   if (rule != AMCT_RULE_RELEASED && rule != AMCT_RULE_EXPERIMENTAL) return AMCT_ERR_ARG;
   if (rows > 0x7fffffffLL) return AMCT_ERR_UNSUPPORTED;
+  if (rule == AMCT_RULE_RELEASED && rows > 0 && k > 0) {
+    int rc = amct::quant_token_try(x, dtype, rows, k, ld_x, smooth, q, ld_q, scale, status, (cudaStream_t)stream);
+    if (rc != 1) return rc;
+  }
   RowParams p{};
   p.x = x; p.rows = rows; p.k = k; p.ld = ld_x;
   p.pre = smooth; p.pre_op = smooth ? AMCT_PRE_MUL : AMCT_PRE_NONE;

@@ -1,0 +1,264 @@
+// Dynamic per-token symmetric INT8 activation quantization, streaming version.
+//
+// Same arithmetic as the per-row kernel in quant_rows.cu (row amax/amin as in
+// amct_pytorch/quantize_op/minmax_module.py:99-105, scale rule of
+// amct_pytorch/quantize_op/utils.py:75-108, codes of amct_pytorch/utils/quant_util.py:57-73,
+// optional SmoothQuant multiply of amct_pytorch/deploy_op/npu_quantization_linear.py:96-97),
+// restructured so that HBM stays busy:
+//   * persistent CTAs; rows are brought into a shared-memory ring by 1-D bulk copies
+//     (cp.async.bulk + mbarrier), several rows ahead of the one being processed;
+//   * 16-bit inputs stay packed in registers; min / max use the packed NaN-propagating
+//     half2 / bfloat162 instructions (one instruction per two elements);
+//   * the quotient x / scale is computed as x * rn(1 / scale); that product is within
+//     |q| * 2^-22 of the correctly rounded quotient, so rint() of it equals rint() of the
+//     IEEE quotient unless it falls within 2^-12 of a rounding tie -- only then (about one
+//     vector in a thousand) the vector is redone with the IEEE division.  Codes are
+//     therefore bit-identical to division everywhere;
+//   * float -> int8 conversion and packing use cvt.rni + cvt.pack.sat (saturating).
+// Algorithmic HBM traffic per row: K * sizeof(T) read, K + 4 bytes written.
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace amct {
+
+struct TokenParams {
+  const void* x;
+  int64_t rows, k, ld;       // elements
+  const void* smooth;        // [k] in T or nullptr
+  int8_t* q;
+  int64_t ld_q;
+  float* scale;
+  int* status;
+  int slots;                 // ring depth
+  int slot_bytes;            // k * sizeof(T), multiple of 16
+};
+
+// four floats -> four saturated int8 in one word (little endian)
+__device__ __forceinline__ uint32_t pack4_s8(float a, float b, float c, float d) {
+  int ia = __float2int_rn(a), ib = __float2int_rn(b), ic = __float2int_rn(c), id = __float2int_rn(d);
+  uint32_t hi, w;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(id), "r"(ic), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(ib), "r"(ia), "r"(hi));
+  return w;
+}
+
+template <typename T> struct Packed;
+template <> struct Packed<__nv_bfloat16> {
+  using V2 = __nv_bfloat162;
+  __device__ static V2 vmax(V2 a, V2 b) { return __hmax2_nan(a, b); }
+  __device__ static V2 vmin(V2 a, V2 b) { return __hmin2_nan(a, b); }
+  __device__ static float lo(V2 a) { return __low2float(a); }
+  __device__ static float hi(V2 a) { return __high2float(a); }
+  __device__ static V2 mul(V2 a, V2 b) {       // each product rounded once to bf16, like a torch bf16 multiply
+    return __floats2bfloat162_rn(__fmul_rn(__low2float(a), __low2float(b)), __fmul_rn(__high2float(a), __high2float(b)));
+  }
+};
+template <> struct Packed<__half> {
+  using V2 = __half2;
+  __device__ static V2 vmax(V2 a, V2 b) { return __hmax2_nan(a, b); }
+  __device__ static V2 vmin(V2 a, V2 b) { return __hmin2_nan(a, b); }
+  __device__ static float lo(V2 a) { return __low2float(a); }
+  __device__ static float hi(V2 a) { return __high2float(a); }
+  __device__ static V2 mul(V2 a, V2 b) {
+    return __floats2half2_rn(__fmul_rn(__low2float(a), __low2float(b)), __fmul_rn(__high2float(a), __high2float(b)));
+  }
+};
+
+__device__ __forceinline__ float max_nan(float a, float b) { return (a != a || b != b) ? NAN : fmaxf(a, b); }
+__device__ __forceinline__ float min_nan(float a, float b) { return (a != a || b != b) ? NAN : fminf(a, b); }
+
+// quantize 4 values given scale s and y = rn(1/s); falls back to the IEEE division near ties
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float s, float y) {
+  float ta = __fmul_rn(a, y), tb = __fmul_rn(b, y), tc = __fmul_rn(c, y), td = __fmul_rn(d, y);
+  float m = fmaxf(fmaxf(fabsf(ta - rintf(ta)), fabsf(tb - rintf(tb))), fmaxf(fabsf(tc - rintf(tc)), fabsf(td - rintf(td))));
+  if (m > 0.5f - 2.44140625e-4f) {   // 2^-12: a tie could be on the other side for the exact quotient
+    ta = __fdiv_rn(a, s); tb = __fdiv_rn(b, s); tc = __fdiv_rn(c, s); td = __fdiv_rn(d, s);
+  }
+  return pack4_s8(ta, tb, tc, td);
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) quant_token_kernel(TokenParams p) {
+  constexpr int E = ElemTraits<T>::kPerVec;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ uint64_t full[8];
+  __shared__ float part[2][3][8];
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+
+  const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nwarp = nthr >> 5;
+  const int nvec = (int)(p.k / E);
+  uint8_t* smooth_s = smem + (size_t)p.slots * p.slot_bytes;       // staged smooth vector (if any)
+  const int64_t my_rows = p.rows > blockIdx.x ? (p.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (tid == 0) {
+    abort_word = 0;
+    for (int i = 0; i < p.slots; ++i) tc05::mbar_init(tc05::smem_u32(&full[i]), 1);
+    tc05::fence_barrier_init();
+  }
+  if (p.smooth) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.smooth);
+    for (int v = tid; v < nvec; v += nthr) reinterpret_cast<uint4*>(smooth_s)[v] = __ldg(src + v);
+  }
+  __syncthreads();
+  const T* xbase = reinterpret_cast<const T*>(p.x);
+  if (tid == 0) {
+    for (int i = 0; i < p.slots && i < my_rows; ++i) {
+      const uint32_t bar = tc05::smem_u32(&full[i]);
+      tc05::mbar_expect_tx(bar, (uint32_t)p.slot_bytes);
+      tc05::bulk_load_1d(tc05::smem_u32(smem + (size_t)i * p.slot_bytes), xbase + (blockIdx.x + (int64_t)i * gridDim.x) * p.ld,
+                         (uint32_t)p.slot_bytes, bar);
+    }
+  }
+
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int64_t i = 0; i < my_rows; ++i) {
+    const int64_t row = blockIdx.x + i * gridDim.x;
+    // a timed-out wait does not leave the loop here: every thread goes on to the block barrier
+    // below and all of them leave together after it, so no thread is left waiting at a barrier
+    tc05::mbar_wait(tc05::smem_u32(&full[slot]), parity, abort_flag);
+    const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)slot * p.slot_bytes);
+
+    uint4 raw[NV];
+    float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = j * nthr + tid;
+      if (v < nvec) {
+        raw[j] = src[v];
+        if constexpr (sizeof(T) == 2) {
+          using P = Packed<T>;
+          typename P::V2* h = reinterpret_cast<typename P::V2*>(&raw[j]);
+          if (p.smooth) {
+            const uint4 sv = reinterpret_cast<const uint4*>(smooth_s)[v];
+            const typename P::V2* sh = reinterpret_cast<const typename P::V2*>(&sv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h[e] = P::mul(h[e], sh[e]);
+          }
+          typename P::V2 vmx = P::vmax(P::vmax(h[0], h[1]), P::vmax(h[2], h[3]));
+          typename P::V2 vmn = P::vmin(P::vmin(h[0], h[1]), P::vmin(h[2], h[3]));
+          mx = max_nan(mx, max_nan(P::lo(vmx), P::hi(vmx)));
+          mn = min_nan(mn, min_nan(P::lo(vmn), P::hi(vmn)));
+        } else {
+          float* f = reinterpret_cast<float*>(&raw[j]);
+          if (p.smooth) {
+            const float4 sv = reinterpret_cast<const float4*>(smooth_s)[v];
+            f[0] = __fmul_rn(f[0], sv.x); f[1] = __fmul_rn(f[1], sv.y); f[2] = __fmul_rn(f[2], sv.z); f[3] = __fmul_rn(f[3], sv.w);
+          }
+          mx = max_nan(mx, max_nan(max_nan(f[0], f[1]), max_nan(f[2], f[3])));
+          mn = min_nan(mn, min_nan(min_nan(f[0], f[1]), min_nan(f[2], f[3])));
+        }
+      }
+    }
+    // block reduction: NaN is carried as a flag so the shuffles can use plain min / max
+    float bad = (mx != mx || mn != mn) ? 1.f : 0.f;
+    if (bad != 0.f) { mx = 0.f; mn = 0.f; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      bad = fmaxf(bad, __shfl_xor_sync(0xffffffffu, bad, o));
+    }
+    const int buf = (int)(i & 1);
+    if (lane == 0) { part[buf][0][warp] = mx; part[buf][1][warp] = mn; part[buf][2][warp] = bad; }
+    __syncthreads();                       // every thread has also finished reading the slot
+    if (*abort_flag) break;
+    if (tid == 0 && i + p.slots < my_rows) {
+      const uint32_t bar = tc05::smem_u32(&full[slot]);
+      tc05::mbar_expect_tx(bar, (uint32_t)p.slot_bytes);
+      tc05::bulk_load_1d(tc05::smem_u32(smem + (size_t)slot * p.slot_bytes), xbase + (row + (int64_t)p.slots * gridDim.x) * p.ld,
+                         (uint32_t)p.slot_bytes, bar);
+    }
+    mx = part[buf][0][0]; mn = part[buf][1][0]; bad = part[buf][2][0];
+    for (int w = 1; w < nwarp; ++w) { mx = fmaxf(mx, part[buf][0][w]); mn = fminf(mn, part[buf][1][w]); bad = fmaxf(bad, part[buf][2][w]); }
+
+    float s; int off;
+    bool ok = qparams_from_minmax(mx, mn, 8, true, &s, &off) && bad == 0.f;
+    if (tid == 0) {
+      p.scale[row] = bad != 0.f ? NAN : s;
+      if (!ok && p.status) atomicOr(p.status, 1);
+    }
+    const float y = __frcp_rn(s);
+    int8_t* qrow = p.q + row * p.ld_q;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = j * nthr + tid;
+      if (v < nvec) {
+        if constexpr (sizeof(T) == 2) {
+          using P = Packed<T>;
+          const typename P::V2* h = reinterpret_cast<const typename P::V2*>(&raw[j]);
+          uint32_t w0 = quant4(P::lo(h[0]), P::hi(h[0]), P::lo(h[1]), P::hi(h[1]), s, y);
+          uint32_t w1 = quant4(P::lo(h[2]), P::hi(h[2]), P::lo(h[3]), P::hi(h[3]), s, y);
+          *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(w0, w1);
+        } else {
+          const float* f = reinterpret_cast<const float*>(&raw[j]);
+          *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = quant4(f[0], f[1], f[2], f[3], s, y);
+        }
+      }
+    }
+    if (++slot == p.slots) { slot = 0; parity ^= 1; }
+  }
+  if (*abort_flag) {
+    if (tid == 0 && p.status) atomicOr(p.status, 2);
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let bulk copies already in flight land
+  }
+}
+
+// Returns AMCT_OK when the streaming kernel took the call, 1 when the shape does not fit
+// it (the caller then uses the general row kernel).
+template <typename T>
+static int launch_token(const TokenParams& p0, cudaStream_t st) {
+  constexpr int E = ElemTraits<T>::kPerVec;
+  TokenParams p = p0;
+  const int64_t row_bytes = p.k * (int64_t)sizeof(T);
+  if (p.k % E || row_bytes % 16 || !aligned16(p.x) || (p.ld * (int64_t)sizeof(T)) % 16) return 1;
+  if (reinterpret_cast<uintptr_t>(p.q) % E || p.ld_q % E) return 1;
+  if (p.smooth && !aligned16(p.smooth)) return 1;
+  if (p.rows < 64 || row_bytes < 2048 || row_bytes > 96 * 1024) return 1;
+  const int64_t nvec = p.k / E;
+  const int threads = nvec <= 512 ? 128 : 256;
+  const int nv = (int)((nvec + threads - 1) / threads);
+  if (nv > 16) return 1;
+  const int64_t smooth_bytes = p.smooth ? row_bytes : 0;
+  // two CTAs per SM when a few rows fit in ~100 KB, else one CTA with the whole shared memory
+  int ctas_per_sm = 2;
+  int64_t budget = 100 * 1024 - smooth_bytes;
+  if (budget < 3 * row_bytes) { ctas_per_sm = 1; budget = 200 * 1024 - smooth_bytes; }
+  int slots = (int)(budget / row_bytes);
+  if (slots > 8) slots = 8;
+  if (slots < 2) return 1;
+  p.slots = slots;
+  p.slot_bytes = (int)row_bytes;
+  const size_t smem = (size_t)slots * row_bytes + smooth_bytes;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t grid = (int64_t)sms * ctas_per_sm;
+  if (grid > p.rows) grid = p.rows;
+#define AMCT_TOKEN_CASE(NVC)                                                                                       \
+  if (nv <= NVC) {                                                                                                 \
+    if (cudaFuncSetAttribute(quant_token_kernel<T, NVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+      return AMCT_ERR_CUDA;                                                                                        \
+    quant_token_kernel<T, NVC><<<(unsigned)grid, threads, smem, st>>>(p);                                          \
+    AMCT_CHECK_LAUNCH();                                                                                           \
+    return AMCT_OK;                                                                                                \
+  }
+  AMCT_TOKEN_CASE(1) AMCT_TOKEN_CASE(2) AMCT_TOKEN_CASE(4) AMCT_TOKEN_CASE(8) AMCT_TOKEN_CASE(16)
+#undef AMCT_TOKEN_CASE
+  return 1;
+}
+
+int quant_token_try(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, const void* smooth, int8_t* q,
+                    int64_t ld_q, float* scale, int* status, cudaStream_t st) {
+  TokenParams p{};
+  p.x = x; p.rows = rows; p.k = k; p.ld = ld_x; p.smooth = smooth; p.q = q; p.ld_q = ld_q; p.scale = scale; p.status = status;
+  switch (dtype) {
+    case AMCT_DTYPE_F32: return launch_token<float>(p, st);
+    case AMCT_DTYPE_F16: return launch_token<__half>(p, st);
+    case AMCT_DTYPE_BF16: return launch_token<__nv_bfloat16>(p, st);
+  }
+  return 1;
+}
+
+}  // namespace amct

@@ -199,3 +199,48 @@ def test_config1_shape_properties():
     # a stripe of rows against the oracle
     q_ref, s_ref = intq.dynamic_per_token(x[1000:1032])
     assert bits_equal(q[1000:1032], q_ref) and bits_equal(s[1000:1032], s_ref)
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('rows,k', [(64, 1024), (200, 4096), (333, 8192), (70, 28672), (129, 16384), (4096, 512)])
+@pytest.mark.parametrize('smooth', [False, True])
+def test_dynamic_per_token_streaming_kernel(dtype, rows, k, smooth):
+    """Shapes the shared-memory-staged kernel takes (many rows, aligned K): bit-exact codes and
+    scales, with outliers, a zero row, a negative-dominant row and a strided input."""
+    g = torch.Generator().manual_seed(rows + k)
+    x = torch.randn(rows, k, generator=g)
+    x[:, :: max(1, k // 41)] *= 20
+    x[1] = 0
+    x[2, 5] = -x[2].abs().max() * 2
+    x = x.to(dtype)
+    f = (torch.rand(1, k, generator=g) + 0.5).to(dtype) if smooth else None
+    q_ref, s_ref = intq.dynamic_per_token(x, 'released', f)
+    q, s = ops().quant_dynamic_per_token(x.cuda(), smooth=dev(f), check=True)
+    assert bits_equal(s, s_ref)
+    assert bits_equal(q, q_ref)
+
+
+def test_dynamic_per_token_rounding_ties():
+    """Quotients that sit exactly on, and one ulp around, rounding ties: the reciprocal-multiply
+    fast path must hand these to the IEEE division."""
+    rows, k = 128, 2048
+    g = torch.Generator().manual_seed(9)
+    for scale_target in (1.0, 0.37, 3.0e-3, 17.25):
+        n = torch.randint(-127, 127, (rows, k), generator=g).float() + 0.5
+        x = n * scale_target
+        ulp = torch.randint(-2, 3, (rows, k), generator=g)
+        x = (x.view(torch.int32) + ulp).view(torch.float32)          # a few ulps around each tie
+        x[:, 0] = 127 * scale_target                                  # pins the row scale
+        q_ref, s_ref = intq.dynamic_per_token(x)
+        q, s = ops().quant_dynamic_per_token(x.cuda())
+        assert bits_equal(s, s_ref) and bits_equal(q, q_ref)
+
+
+def test_dynamic_per_token_streaming_nonfinite():
+    x = torch.randn(256, 1024)
+    x[100, 77] = float('nan')
+    with pytest.raises(RuntimeError, match='invalid value inf, nan or zeros'):
+        ops().quant_dynamic_per_token(x.cuda(), check=True)
+    x[100, 77] = float('inf')
+    with pytest.raises(RuntimeError, match='invalid value inf, nan or zeros'):
+        ops().quant_dynamic_per_token(x.to(torch.bfloat16).cuda(), check=True)
