@@ -92,39 +92,68 @@ template <typename T> __device__ __forceinline__ void store8(T* dst, const float
   }
 }
 
+// With ties rounded away from zero, the code of x depends only on its sign, its exponent and
+// the top four mantissa bits (the deepest rounding position is mantissa bit 19).  So a
+// 4096-entry table indexed by bits [30:19] of the fp32 pattern encodes any magnitude; NaN
+// payloads hidden in lower mantissa bits are the one case checked separately.
+__device__ __forceinline__ uint32_t hif8_lookup(const uint8_t* tab, float x) {
+  const uint32_t bits = __float_as_uint(x);
+  const uint32_t abits = bits & 0x7fffffffu;
+  uint32_t t = tab[abits >> 19];
+  t = t ? (t | ((bits >> 24) & 0x80u)) : 0u;            // -0 and flushed negatives are +0 (0x80 means NaN)
+  return abits > 0x7f800000u ? 0x80u : t;
+}
+
 // mode 0: encode x -> codes;  mode 1: fake-quantize x -> decode(encode(x)) in T
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) hif8_encode_kernel(const T* x, int64_t n, uint8_t* codes, T* fake) {
+  __shared__ uint8_t tab[4096];
+  __shared__ float dec[256];
+  for (int i = threadIdx.x; i < 4096; i += blockDim.x) tab[i] = (uint8_t)hif8_encode(__uint_as_float((uint32_t)i << 19));
+  if (MODE == 1) dec[threadIdx.x] = hif8_decode(threadIdx.x);
+  __syncthreads();
+  constexpr int U = 2;
   const int64_t nv = n / 8;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += stride) {
-    float f[8];
-    if constexpr (sizeof(T) == 2) {
-      Vec16<T> raw = ld_vec_stream(x + v * 8);
+  for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nv; v0 += stride * U) {
+    float f[U][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = ElemTraits<T>::to_f(raw.v[e]);
-    } else {
-      Vec16<T> r0 = ld_vec_stream(x + v * 8), r1 = ld_vec_stream(x + v * 8 + 4);
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = v0 + u * stride;
+      if (v < nv) {
+        if constexpr (sizeof(T) == 2) {
+          Vec16<T> raw = ld_vec_stream(x + v * 8);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { f[e] = ElemTraits<T>::to_f(r0.v[e]); f[4 + e] = ElemTraits<T>::to_f(r1.v[e]); }
+          for (int e = 0; e < 8; ++e) f[u][e] = ElemTraits<T>::to_f(raw.v[e]);
+        } else {
+          Vec16<T> r0 = ld_vec_stream(x + v * 8), r1 = ld_vec_stream(x + v * 8 + 4);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { f[u][e] = ElemTraits<T>::to_f(r0.v[e]); f[u][4 + e] = ElemTraits<T>::to_f(r1.v[e]); }
+        }
+      }
     }
-    uint32_t c[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) c[e] = hif8_encode(f[e]);
-    if constexpr (MODE == 0) {
-      uint32_t lo = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24), hi = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
-      *reinterpret_cast<uint2*>(codes + v * 8) = make_uint2(lo, hi);
-    } else {
-      float d[8];
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = v0 + u * stride;
+      if (v >= nv) break;
+      uint32_t c[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) d[e] = hif8_decode(c[e]);
-      store8<T>(fake + v * 8, d);
+      for (int e = 0; e < 8; ++e) c[e] = hif8_lookup(tab, f[u][e]);
+      if constexpr (MODE == 0) {
+        uint32_t lo = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24), hi = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+        *reinterpret_cast<uint2*>(codes + v * 8) = make_uint2(lo, hi);
+      } else {
+        float d[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d[e] = dec[c[e]];
+        store8<T>(fake + v * 8, d);
+      }
     }
   }
   // tail (n not a multiple of 8): the first threads of block 0 take one element each
   if (blockIdx.x == 0 && threadIdx.x < (int)(n - nv * 8)) {
     const int64_t i = nv * 8 + threadIdx.x;
-    const uint32_t c = hif8_encode(ElemTraits<T>::to_f(x[i]));
+    const uint32_t c = hif8_lookup(tab, ElemTraits<T>::to_f(x[i]));
     if constexpr (MODE == 0) codes[i] = (uint8_t)c;
     else fake[i] = ElemTraits<T>::from_f(hif8_decode(c));
   }
@@ -153,7 +182,7 @@ __global__ void __launch_bounds__(256) hif8_decode_kernel(const uint8_t* codes, 
 static unsigned grid_for(int64_t n) {
   int64_t blocks = (n / 8 + 255) / 256;
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > 148 * 8) blocks = 148 * 8;
   return (unsigned)blocks;
 }
 

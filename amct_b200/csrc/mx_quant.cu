@@ -27,10 +27,98 @@
 
 namespace amct {
 
+template <typename T>
+__device__ __forceinline__ void mx_load8(const T* src, float (&v)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    Vec16<T> raw = ld_vec_stream(src);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = ElemTraits<T>::to_f(raw.v[e]);
+  } else {
+    Vec16<T> r0 = ld_vec_stream(src), r1 = ld_vec_stream(src + 4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { v[e] = ElemTraits<T>::to_f(r0.v[e]); v[4 + e] = ElemTraits<T>::to_f(r1.v[e]); }
+  }
+}
+
+// One lane's 8 elements of a 32-element block (4 adjacent lanes share the block).
+template <int FMT>
+__device__ __forceinline__ void mx_block(const float (&v)[8], bool valid, int lane, int64_t row, int64_t oct, int64_t k,
+                                         int64_t kb_per_row, int64_t kb4_per_row, bool wide, int tile_rows,
+                                         uint8_t* payload, uint8_t* scales_rm, uint8_t* scales_tiled) {
+  constexpr int EMAX = FMT == 8 ? 8 : 2;
+  // max |v| through the integer order of the magnitude bits: Inf / NaN show up as >= 0x7F800000
+  uint32_t amax_bits = 0;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) amax_bits = max(amax_bits, __float_as_uint(v[e]) & 0x7fffffffu);
+  amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 1));
+  amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 2));
+  const bool bad = amax_bits >= 0x7f800000u;
+  if (bad) {                                     // rare: the shared exponent comes from the finite part only
+    uint32_t fin = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const uint32_t b = __float_as_uint(v[e]) & 0x7fffffffu;
+      fin = max(fin, b < 0x7f800000u ? b : 0u);
+    }
+    const unsigned act = __activemask();          // the 4 lanes of a block take this branch together
+    fin = max(fin, __shfl_xor_sync(act, fin, 1));
+    fin = max(fin, __shfl_xor_sync(act, fin, 2));
+    amax_bits = fin;
+  }
+  // biased exponent of amax minus emax = shared_exp + 127; fp32 denormals and zero land on 0
+  int sb = (int)(amax_bits >> 23) - EMAX;
+  sb = sb < 0 ? 0 : (sb > 254 ? 254 : sb);
+  const int field = 254 - sb;                                            // exponent field of 2^-shared_exp
+  const float mult = __uint_as_float(field > 0 ? (uint32_t)field << 23 : 0x00400000u);
+  const uint32_t scale_byte = bad ? 0xFFu : (uint32_t)sb;
+
+  if (valid) {
+    float s[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s[e] = __fmul_rn(v[e], mult);
+    if constexpr (FMT == 8) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int e = 0; e < 4; e += 2) {
+        lo |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(s[e], s[e + 1]), __NV_SATFINITE, __NV_E4M3) << (8 * e);
+        hi |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(s[4 + e], s[5 + e]), __NV_SATFINITE, __NV_E4M3) << (8 * e);
+      }
+      if (bad) { lo = 0x7F7F7F7Fu; hi = 0x7F7F7F7Fu; }
+      *reinterpret_cast<uint2*>(payload + row * k + oct * 8) = make_uint2(lo, hi);
+    } else {
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        float a = s[e], b = s[e + 1];
+        if (bad) { a = a == a ? a : 0.f; b = b == b ? b : 0.f; }         // E2M1 has no NaN
+        word |= (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest) << (4 * e);
+      }
+      *reinterpret_cast<uint32_t*>(payload + row * (k / 2) + oct * 4) = word;
+    }
+  }
+
+  const int64_t kb = oct / 4;
+  const int64_t tq = row % tile_rows;
+  const int64_t atom = (row / tile_rows) * ((tile_rows + 127) / 128) + tq / 128;
+  const int64_t tiled_off = (atom * kb4_per_row + kb / 4) * 512 + (tq % 32) * 16 + ((tq % 128) / 32) * 4 + (kb % 4);
+  if (wide) {
+    const int g16 = lane & ~15;
+    uint32_t word = __shfl_sync(0xffffffffu, scale_byte, g16) | (__shfl_sync(0xffffffffu, scale_byte, g16 + 4) << 8) |
+                    (__shfl_sync(0xffffffffu, scale_byte, g16 + 8) << 16) | (__shfl_sync(0xffffffffu, scale_byte, g16 + 12) << 24);
+    if (valid && (lane & 15) == 0) {
+      if (scales_rm) *reinterpret_cast<uint32_t*>(scales_rm + row * kb_per_row + kb) = word;
+      if (scales_tiled) *reinterpret_cast<uint32_t*>(scales_tiled + tiled_off) = word;
+    }
+  } else if (valid && (lane & 3) == 0) {
+    if (scales_rm) scales_rm[row * kb_per_row + kb] = (uint8_t)scale_byte;
+    if (scales_tiled) scales_tiled[tiled_off] = (uint8_t)scale_byte;
+  }
+}
+
 template <typename T, int FMT>
 __global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int64_t rows, int64_t k, int64_t ld, uint8_t* payload,
                                                        uint8_t* scales_rm, uint8_t* scales_tiled, int tile_rows) {
-  constexpr int EMAX = FMT == 8 ? 8 : 2;
+  constexpr int U = 2;                                      // blocks in flight per thread
   const int lane = threadIdx.x & 31;
   const int64_t oct_per_row = k / 8;
   const int64_t total = rows * oct_per_row;
@@ -38,86 +126,27 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int64_t rows,
   const int64_t kb4_per_row = (kb_per_row + 3) / 4;
   const bool wide = (kb_per_row % 4) == 0;                  // 4 scale bytes of a row go out as one word
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += stride) {
-    const int64_t w = base + threadIdx.x;
-    const bool valid = w < total;
-    const int64_t row = valid ? w / oct_per_row : 0;
-    const int64_t oct = valid ? w - row * oct_per_row : 0;
-    float v[8];
-    if (valid) {
-      const T* src = x + row * ld + oct * 8;
-      if constexpr (sizeof(T) == 2) {
-        Vec16<T> raw = ld_vec_stream(src);
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += stride * U) {
+    float v[U][8];
+    int64_t row[U], oct[U];
+    bool valid[U];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = ElemTraits<T>::to_f(raw.v[e]);
-      } else {
-        Vec16<T> r0 = ld_vec_stream(src), r1 = ld_vec_stream(src + 4);
+    for (int u = 0; u < U; ++u) {
+      const int64_t w = base + u * stride + threadIdx.x;
+      valid[u] = w < total;
+      row[u] = valid[u] ? w / oct_per_row : 0;
+      oct[u] = valid[u] ? w - row[u] * oct_per_row : 0;
+      if (valid[u]) mx_load8<T>(x + row[u] * ld + oct[u] * 8, v[u]);
+      else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { v[e] = ElemTraits<T>::to_f(r0.v[e]); v[4 + e] = ElemTraits<T>::to_f(r1.v[e]); }
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = 0.f;
-    }
-    float amax = 0.f;
-    bool bad = false;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const bool fin = isfinite(v[e]);
-      bad |= !fin;
-      amax = fmaxf(amax, fin ? fabsf(v[e]) : 0.f);
-    }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    unsigned badmask = __ballot_sync(0xffffffffu, bad);
-    bad = (badmask >> (lane & ~3)) & 0xFu;
-
-    // biased exponent of amax minus emax = shared_exp + 127; fp32 denormals and zero land on 0
-    int sb = (int)((__float_as_uint(amax) >> 23) & 0xFF) - EMAX;
-    sb = sb < 0 ? 0 : (sb > 254 ? 254 : sb);
-    const int field = 254 - sb;                                            // exponent field of 2^-shared_exp
-    const float mult = __uint_as_float(field > 0 ? (uint32_t)field << 23 : 0x00400000u);
-    const uint32_t scale_byte = bad ? 0xFFu : (uint32_t)sb;
-
-    if (valid) {
-      float s[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) s[e] = __fmul_rn(v[e], mult);
-      if constexpr (FMT == 8) {
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int e = 0; e < 4; e += 2) {
-          lo |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(s[e], s[e + 1]), __NV_SATFINITE, __NV_E4M3) << (8 * e);
-          hi |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(s[4 + e], s[5 + e]), __NV_SATFINITE, __NV_E4M3) << (8 * e);
-        }
-        if (bad) { lo = 0x7F7F7F7Fu; hi = 0x7F7F7F7Fu; }
-        *reinterpret_cast<uint2*>(payload + row * k + oct * 8) = make_uint2(lo, hi);
-      } else {
-        uint32_t word = 0;
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          float a = s[e] == s[e] ? s[e] : 0.f, b = s[e + 1] == s[e + 1] ? s[e + 1] : 0.f;   // E2M1 has no NaN
-          word |= (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest) << (4 * e);
-        }
-        *reinterpret_cast<uint32_t*>(payload + row * (k / 2) + oct * 4) = word;
+        for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
       }
     }
-
-    const int64_t kb = oct / 4;
-    const int64_t tq = row % tile_rows;
-    const int64_t atom = (row / tile_rows) * ((tile_rows + 127) / 128) + tq / 128;
-    const int64_t tiled_off = (atom * kb4_per_row + kb / 4) * 512 + (tq % 32) * 16 + ((tq % 128) / 32) * 4 + (kb % 4);
-    if (wide) {
-      const int g16 = lane & ~15;
-      uint32_t word = __shfl_sync(0xffffffffu, scale_byte, g16) | (__shfl_sync(0xffffffffu, scale_byte, g16 + 4) << 8) |
-                      (__shfl_sync(0xffffffffu, scale_byte, g16 + 8) << 16) | (__shfl_sync(0xffffffffu, scale_byte, g16 + 12) << 24);
-      if (valid && (lane & 15) == 0) {
-        if (scales_rm) *reinterpret_cast<uint32_t*>(scales_rm + row * kb_per_row + kb) = word;
-        if (scales_tiled) *reinterpret_cast<uint32_t*>(scales_tiled + tiled_off) = word;
-      }
-    } else if (valid && (lane & 3) == 0) {
-      if (scales_rm) scales_rm[row * kb_per_row + kb] = (uint8_t)scale_byte;
-      if (scales_tiled) scales_tiled[tiled_off] = (uint8_t)scale_byte;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (base + u * stride >= total) break;                // uniform across the block
+      mx_block<FMT>(v[u], valid[u], lane, row[u], oct[u], k, kb_per_row, kb4_per_row, wide, tile_rows, payload, scales_rm,
+                    scales_tiled);
     }
   }
 }
@@ -126,8 +155,9 @@ template <typename T>
 static int run_mx(const T* x, int64_t rows, int64_t k, int64_t ld, int fmt, uint8_t* payload, uint8_t* srm, uint8_t* st,
                   int tile_rows, cudaStream_t stream) {
   const int64_t total = rows * (k / 8);
-  int64_t blocks = (total + 255) / 256;
-  const int64_t cap = 148LL * 8 * 8;
+  int64_t blocks = (total + 511) / 512;
+  if (blocks < 1) blocks = 1;
+  const int64_t cap = 148LL * 8 * 4;
   if (blocks > cap) blocks = cap;
   if (fmt == 8) mx_quant_kernel<T, 8><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st, tile_rows);
   else mx_quant_kernel<T, 4><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st, tile_rows);

@@ -434,6 +434,13 @@ extern "C" int amct_quant_rows(const void* x, int dtype, int64_t rows, int64_t k
   if (out_mode != AMCT_OUT_NONE && (!out || ld_out < (out_mode == AMCT_OUT_PACK4 ? (k + 1) / 2 : k))) return AMCT_ERR_ARG;
   if (out_mode == AMCT_OUT_PACK4 && bits != 4) return AMCT_ERR_ARG;
   if (rows > 0x7fffffffLL) return AMCT_ERR_UNSUPPORTED;
+  // per-channel symmetric INT8 codes follow exactly the per-token rule: use the streaming kernel
+  if (compute && strategy == AMCT_STRATEGY_CHANNEL && bits == 8 && symmetric && out_mode == AMCT_OUT_I8 &&
+      (pre_op == AMCT_PRE_NONE || pre_op == AMCT_PRE_MUL) && rows > 0 && k > 0) {
+    int rc = amct::quant_token_try(x, dtype, rows, k, ld_x, pre_op == AMCT_PRE_MUL ? pre : nullptr,
+                                   reinterpret_cast<int8_t*>(out), ld_out, scale, status, (cudaStream_t)stream);
+    if (rc != 1) return rc;
+  }
   RowParams p{};
   p.x = x; p.rows = rows; p.k = k; p.ld = ld_x; p.pre = pre; p.pre_op = pre_op;
   p.compute = compute; p.strategy = strategy; p.group = group; p.bits = bits; p.symmetric = symmetric;

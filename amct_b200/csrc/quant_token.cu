@@ -14,7 +14,9 @@
 //     IEEE quotient unless it falls within 2^-12 of a rounding tie -- only then (about one
 //     vector in a thousand) the vector is redone with the IEEE division.  Codes are
 //     therefore bit-identical to division everywhere;
-//   * float -> int8 conversion and packing use cvt.rni + cvt.pack.sat (saturating).
+//   * rounding uses the add-1.5*2^23 trick (a full-rate FADD whose low mantissa byte is the
+//     two's-complement code) instead of the quarter-rate FRND / F2I conversions; the only
+//     clamp this rule can need is the upper one (a negative-dominant row divides by 128).
 // Algorithmic HBM traffic per row: K * sizeof(T) read, K + 4 bytes written.
 #include "common.cuh"
 #include "tc05.cuh"
@@ -33,13 +35,13 @@ struct TokenParams {
   int slot_bytes;            // k * sizeof(T), multiple of 16
 };
 
-// four floats -> four saturated int8 in one word (little endian)
-__device__ __forceinline__ uint32_t pack4_s8(float a, float b, float c, float d) {
-  int ia = __float2int_rn(a), ib = __float2int_rn(b), ic = __float2int_rn(c), id = __float2int_rn(d);
-  uint32_t hi, w;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(id), "r"(ic), "r"(0));
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(ib), "r"(ia), "r"(hi));
-  return w;
+constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23: x + kMagic rounds x to an integer (half to even)
+
+// four quotients (|t| <= 128.0001) -> four int8 codes in one word, little endian
+__device__ __forceinline__ uint32_t pack4_s8(float ra, float rb, float rc, float rd) {
+  const uint32_t w01 = __byte_perm(__float_as_uint(ra), __float_as_uint(rb), 0x0040);
+  const uint32_t w23 = __byte_perm(__float_as_uint(rc), __float_as_uint(rd), 0x0040);
+  return __byte_perm(w01, w23, 0x5410);
 }
 
 template <typename T> struct Packed;
@@ -68,21 +70,48 @@ __device__ __forceinline__ float max_nan(float a, float b) { return (a != a || b
 __device__ __forceinline__ float min_nan(float a, float b) { return (a != a || b != b) ? NAN : fminf(a, b); }
 
 // quantize 4 values given scale s and y = rn(1/s); falls back to the IEEE division near ties
+template <bool CLAMP>
 __device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float s, float y) {
+  // only a negative-dominant row (divisor 128) can produce a quotient above 127.5
   float ta = __fmul_rn(a, y), tb = __fmul_rn(b, y), tc = __fmul_rn(c, y), td = __fmul_rn(d, y);
-  float m = fmaxf(fmaxf(fabsf(ta - rintf(ta)), fabsf(tb - rintf(tb))), fmaxf(fabsf(tc - rintf(tc)), fabsf(td - rintf(td))));
-  if (m > 0.5f - 2.44140625e-4f) {   // 2^-12: a tie could be on the other side for the exact quotient
-    ta = __fdiv_rn(a, s); tb = __fdiv_rn(b, s); tc = __fdiv_rn(c, s); td = __fdiv_rn(d, s);
+  if (CLAMP) { ta = fminf(ta, 127.f); tb = fminf(tb, 127.f); tc = fminf(tc, 127.f); td = fminf(td, 127.f); }
+  float ra = __fadd_rn(ta, kMagic), rb = __fadd_rn(tb, kMagic), rc = __fadd_rn(tc, kMagic), rd = __fadd_rn(td, kMagic);
+  // distance of each quotient from the integer it rounded to
+  const float m = fmaxf(fmaxf(fabsf(__fsub_rn(ta, __fsub_rn(ra, kMagic))), fabsf(__fsub_rn(tb, __fsub_rn(rb, kMagic)))),
+                        fmaxf(fabsf(__fsub_rn(tc, __fsub_rn(rc, kMagic))), fabsf(__fsub_rn(td, __fsub_rn(rd, kMagic)))));
+  if (m > 0.5f - 2.44140625e-4f) {   // within 2^-12 of a tie: the exact quotient could round the other way
+    ra = __fadd_rn(fminf(__fdiv_rn(a, s), 127.f), kMagic); rb = __fadd_rn(fminf(__fdiv_rn(b, s), 127.f), kMagic);
+    rc = __fadd_rn(fminf(__fdiv_rn(c, s), 127.f), kMagic); rd = __fadd_rn(fminf(__fdiv_rn(d, s), 127.f), kMagic);
   }
-  return pack4_s8(ta, tb, tc, td);
+  return pack4_s8(ra, rb, rc, rd);
+}
+
+template <typename T, int NV, bool CLAMP>
+__device__ __forceinline__ void quantize_row(const uint4 (&raw)[NV], int8_t* qrow, int nvec, int nthr, int tid, float s, float y) {
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = j * nthr + tid;
+    if (v < nvec) {
+      if constexpr (sizeof(T) == 2) {
+        using P = Packed<T>;
+        const typename P::V2* h = reinterpret_cast<const typename P::V2*>(&raw[j]);
+        const uint32_t w0 = quant4<CLAMP>(P::lo(h[0]), P::hi(h[0]), P::lo(h[1]), P::hi(h[1]), s, y);
+        const uint32_t w1 = quant4<CLAMP>(P::lo(h[2]), P::hi(h[2]), P::lo(h[3]), P::hi(h[3]), s, y);
+        *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(w0, w1);
+      } else {
+        const float* f = reinterpret_cast<const float*>(&raw[j]);
+        *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = quant4<CLAMP>(f[0], f[1], f[2], f[3], s, y);
+      }
+    }
+  }
 }
 
 template <typename T, int NV>
-__global__ void __launch_bounds__(256) quant_token_kernel(TokenParams p) {
+__global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
   constexpr int E = ElemTraits<T>::kPerVec;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full[8];
-  __shared__ float part[2][3][8];
+  __shared__ float part[2][2][16];
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
 
@@ -122,6 +151,8 @@ __global__ void __launch_bounds__(256) quant_token_kernel(TokenParams p) {
 
     uint4 raw[NV];
     float mn = INFINITY, mx = -INFINITY;
+    uint32_t pmx = 0, pmn = 0;             // packed running max / min of the 16-bit path
+    bool first = true;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int v = j * nthr + tid;
@@ -138,8 +169,13 @@ __global__ void __launch_bounds__(256) quant_token_kernel(TokenParams p) {
           }
           typename P::V2 vmx = P::vmax(P::vmax(h[0], h[1]), P::vmax(h[2], h[3]));
           typename P::V2 vmn = P::vmin(P::vmin(h[0], h[1]), P::vmin(h[2], h[3]));
-          mx = max_nan(mx, max_nan(P::lo(vmx), P::hi(vmx)));
-          mn = min_nan(mn, min_nan(P::lo(vmn), P::hi(vmn)));
+          if (!first) {
+            vmx = P::vmax(vmx, *reinterpret_cast<typename P::V2*>(&pmx));
+            vmn = P::vmin(vmn, *reinterpret_cast<typename P::V2*>(&pmn));
+          }
+          pmx = *reinterpret_cast<uint32_t*>(&vmx);
+          pmn = *reinterpret_cast<uint32_t*>(&vmn);
+          first = false;
         } else {
           float* f = reinterpret_cast<float*>(&raw[j]);
           if (p.smooth) {
@@ -151,17 +187,23 @@ __global__ void __launch_bounds__(256) quant_token_kernel(TokenParams p) {
         }
       }
     }
-    // block reduction: NaN is carried as a flag so the shuffles can use plain min / max
-    float bad = (mx != mx || mn != mn) ? 1.f : 0.f;
-    if (bad != 0.f) { mx = 0.f; mn = 0.f; }
+    if constexpr (sizeof(T) == 2) {
+      using P = Packed<T>;
+      if (!first) {
+        const typename P::V2 vmx = *reinterpret_cast<typename P::V2*>(&pmx), vmn = *reinterpret_cast<typename P::V2*>(&pmn);
+        mx = max_nan(P::lo(vmx), P::hi(vmx));
+        mn = min_nan(P::lo(vmn), P::hi(vmn));
+      }
+    }
+    // a NaN anywhere in the row becomes max = +inf: the scale is then infinite and the row is flagged
+    if (mx != mx || mn != mn) { mx = INFINITY; mn = 0.f; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-      bad = fmaxf(bad, __shfl_xor_sync(0xffffffffu, bad, o));
     }
     const int buf = (int)(i & 1);
-    if (lane == 0) { part[buf][0][warp] = mx; part[buf][1][warp] = mn; part[buf][2][warp] = bad; }
+    if (lane == 0) { part[buf][0][warp] = mx; part[buf][1][warp] = mn; }
     __syncthreads();                       // every thread has also finished reading the slot
     if (*abort_flag) break;
     if (tid == 0 && i + p.slots < my_rows) {
@@ -170,33 +212,23 @@ __global__ void __launch_bounds__(256) quant_token_kernel(TokenParams p) {
       tc05::bulk_load_1d(tc05::smem_u32(smem + (size_t)slot * p.slot_bytes), xbase + (row + (int64_t)p.slots * gridDim.x) * p.ld,
                          (uint32_t)p.slot_bytes, bar);
     }
-    mx = part[buf][0][0]; mn = part[buf][1][0]; bad = part[buf][2][0];
-    for (int w = 1; w < nwarp; ++w) { mx = fmaxf(mx, part[buf][0][w]); mn = fminf(mn, part[buf][1][w]); bad = fmaxf(bad, part[buf][2][w]); }
+    mx = part[buf][0][0]; mn = part[buf][1][0];
+    for (int w = 1; w < nwarp; ++w) { mx = fmaxf(mx, part[buf][0][w]); mn = fminf(mn, part[buf][1][w]); }
 
-    float s; int off;
-    bool ok = qparams_from_minmax(mx, mn, 8, true, &s, &off) && bad == 0.f;
+    // symmetric INT8 rule (amct_pytorch/quantize_op/utils.py:87-91): divisor 127, or 128 when the
+    // largest magnitude is negative; a scale below FLT_EPSILON becomes 1
+    const float amx = fabsf(mx), amn = fabsf(mn);
+    const bool neg_dom = amx < amn;
+    float s = __fdiv_rn(neg_dom ? amn : amx, neg_dom ? 128.f : 127.f);
+    if (s < AMCT_FLT_EPSILON) s = 1.f;
     if (tid == 0) {
-      p.scale[row] = bad != 0.f ? NAN : s;
-      if (!ok && p.status) atomicOr(p.status, 1);
+      p.scale[row] = s;
+      if (!isfinite(s) && p.status) atomicOr(p.status, 1);
     }
     const float y = __frcp_rn(s);
     int8_t* qrow = p.q + row * p.ld_q;
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int v = j * nthr + tid;
-      if (v < nvec) {
-        if constexpr (sizeof(T) == 2) {
-          using P = Packed<T>;
-          const typename P::V2* h = reinterpret_cast<const typename P::V2*>(&raw[j]);
-          uint32_t w0 = quant4(P::lo(h[0]), P::hi(h[0]), P::lo(h[1]), P::hi(h[1]), s, y);
-          uint32_t w1 = quant4(P::lo(h[2]), P::hi(h[2]), P::lo(h[3]), P::hi(h[3]), s, y);
-          *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(w0, w1);
-        } else {
-          const float* f = reinterpret_cast<const float*>(&raw[j]);
-          *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = quant4(f[0], f[1], f[2], f[3], s, y);
-        }
-      }
-    }
+    if (neg_dom) quantize_row<T, NV, true>(raw, qrow, nvec, nthr, tid, s, y);       // uniform per row
+    else quantize_row<T, NV, false>(raw, qrow, nvec, nthr, tid, s, y);
     if (++slot == p.slots) { slot = 0; parity ^= 1; }
   }
   if (*abort_flag) {
@@ -215,16 +247,17 @@ static int launch_token(const TokenParams& p0, cudaStream_t st) {
   if (p.k % E || row_bytes % 16 || !aligned16(p.x) || (p.ld * (int64_t)sizeof(T)) % 16) return 1;
   if (reinterpret_cast<uintptr_t>(p.q) % E || p.ld_q % E) return 1;
   if (p.smooth && !aligned16(p.smooth)) return 1;
-  if (p.rows < 64 || row_bytes < 2048 || row_bytes > 96 * 1024) return 1;
+  if (p.rows < 64 || row_bytes < 2048 || row_bytes > 64 * 1024) return 1;
   const int64_t nvec = p.k / E;
-  const int threads = nvec <= 512 ? 128 : 256;
+  // up to 8 vectors per thread: more elements per thread amortise the per-row reduction
+  const int threads = nvec <= 1024 ? 128 : (nvec <= 2048 ? 256 : 512);
   const int nv = (int)((nvec + threads - 1) / threads);
-  if (nv > 16) return 1;
+  if (nv > 8) return 1;
   const int64_t smooth_bytes = p.smooth ? row_bytes : 0;
-  // two CTAs per SM when a few rows fit in ~100 KB, else one CTA with the whole shared memory
-  int ctas_per_sm = 2;
-  int64_t budget = 100 * 1024 - smooth_bytes;
-  if (budget < 3 * row_bytes) { ctas_per_sm = 1; budget = 200 * 1024 - smooth_bytes; }
+  // as many CTAs per SM as fit with at least 3 rows in flight each (about 200 KB of shared memory per SM)
+  int ctas_per_sm = 2048 / threads > 4 ? 4 : 2048 / threads;
+  while (ctas_per_sm > 1 && (200 * 1024 / ctas_per_sm - smooth_bytes - 1024) < 3 * row_bytes) --ctas_per_sm;
+  const int64_t budget = 200 * 1024 / ctas_per_sm - smooth_bytes - 1024;
   int slots = (int)(budget / row_bytes);
   if (slots > 8) slots = 8;
   if (slots < 2) return 1;
@@ -244,7 +277,7 @@ static int launch_token(const TokenParams& p0, cudaStream_t st) {
     AMCT_CHECK_LAUNCH();                                                                                           \
     return AMCT_OK;                                                                                                \
   }
-  AMCT_TOKEN_CASE(1) AMCT_TOKEN_CASE(2) AMCT_TOKEN_CASE(4) AMCT_TOKEN_CASE(8) AMCT_TOKEN_CASE(16)
+  AMCT_TOKEN_CASE(1) AMCT_TOKEN_CASE(2) AMCT_TOKEN_CASE(4) AMCT_TOKEN_CASE(8)
 #undef AMCT_TOKEN_CASE
   return 1;
 }

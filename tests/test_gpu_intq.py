@@ -228,7 +228,7 @@ def test_dynamic_per_token_rounding_ties():
     for scale_target in (1.0, 0.37, 3.0e-3, 17.25):
         n = torch.randint(-127, 127, (rows, k), generator=g).float() + 0.5
         x = n * scale_target
-        ulp = torch.randint(-2, 3, (rows, k), generator=g)
+        ulp = torch.randint(-2, 3, (rows, k), generator=g, dtype=torch.int32)
         x = (x.view(torch.int32) + ulp).view(torch.float32)          # a few ulps around each tie
         x[:, 0] = 127 * scale_target                                  # pins the row scale
         q_ref, s_ref = intq.dynamic_per_token(x)
@@ -244,3 +244,19 @@ def test_dynamic_per_token_streaming_nonfinite():
     x[100, 77] = float('inf')
     with pytest.raises(RuntimeError, match='invalid value inf, nan or zeros'):
         ops().quant_dynamic_per_token(x.to(torch.bfloat16).cuda(), check=True)
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize('smooth', [False, True])
+def test_channel_int8_weight_quant_streaming_path(dtype, smooth):
+    """Per-channel symmetric INT8 weight codes on a shape large enough for the streaming kernel."""
+    g = torch.Generator().manual_seed(17)
+    w = (torch.randn(320, 4096, generator=g) * 0.02).to(dtype)
+    w[5] = 0
+    w[9] = -w[9].abs()
+    f = (torch.rand(1, 4096, generator=g) + 0.5).to(dtype) if smooth else None
+    ws = intq.fold_smooth_into_weight(w, f) if smooth else w
+    s_ref, _ = intq.weight_scale_offset(ws, 'int8', True, 'channel')
+    q_ref = intq.weight_codes(ws, 'int8', s_ref)
+    s, o, q = ops().quant_rows(w.cuda(), 'int8', True, 'channel', out='i8', pre=dev(f), pre_op='mul' if smooth else 'none')
+    assert o is None and bits_equal(s.reshape(-1, 1), s_ref) and bits_equal(q, q_ref)
