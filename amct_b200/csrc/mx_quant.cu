@@ -98,8 +98,9 @@ __device__ __forceinline__ void mx_block(const float (&v)[8], bool valid, int la
   }
 
   const int64_t kb = oct / 4;
-  const int64_t tq = row % tile_rows;
-  const int64_t atom = (row / tile_rows) * ((tile_rows + 127) / 128) + tq / 128;
+  const uint32_t r32 = (uint32_t)row;                                  // rows < 2^31 (checked on the host)
+  const uint32_t tile = r32 / (uint32_t)tile_rows, tq = r32 - tile * (uint32_t)tile_rows;
+  const int64_t atom = (int64_t)tile * ((tile_rows + 127) / 128) + tq / 128;
   const int64_t tiled_off = (atom * kb4_per_row + kb / 4) * 512 + (tq % 32) * 16 + ((tq % 128) / 32) * 4 + (kb % 4);
   if (wide) {
     const int g16 = lane & ~15;
@@ -151,9 +152,53 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int64_t rows,
   }
 }
 
+// Row-tiled variant for K >= 1024: blockIdx.x picks a 2048-element span of the row,
+// blockIdx.y strides over rows, so no thread ever divides to find its row, and the tile /
+// atom position of the scale layout advances incrementally.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) mx_quant_rows_kernel(const T* x, int rows, int k, int64_t ld, uint8_t* payload,
+                                                            uint8_t* scales_rm, uint8_t* scales_tiled, int tile_rows) {
+  constexpr int U = 2;                                      // rows in flight per thread
+  const int lane = threadIdx.x & 31;
+  const int oct_per_row = k / 8;
+  const int oct = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool in_row = oct < oct_per_row;
+  const int kb_per_row = k / 32;
+  const int kb4_per_row = (kb_per_row + 3) / 4;
+  const bool wide = (kb_per_row % 4) == 0;
+  for (int r0 = blockIdx.y * U; r0 < rows; r0 += gridDim.y * U) {
+    float v[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (in_row && r0 + u < rows) mx_load8<T>(x + (int64_t)(r0 + u) * ld + (int64_t)oct * 8, v[u]);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (r0 + u >= rows) break;                            // uniform across the block
+      mx_block<FMT>(v[u], in_row, lane, r0 + u, in_row ? oct : 0, k, kb_per_row, kb4_per_row, wide, tile_rows, payload,
+                    scales_rm, scales_tiled);
+    }
+  }
+}
+
 template <typename T>
 static int run_mx(const T* x, int64_t rows, int64_t k, int64_t ld, int fmt, uint8_t* payload, uint8_t* srm, uint8_t* st,
                   int tile_rows, cudaStream_t stream) {
+  if (k >= 1024 && rows < (1LL << 30) && k < (1LL << 30)) {
+    dim3 grid((unsigned)((k / 8 + 255) / 256), 1);
+    int64_t gy = (148LL * 8 + grid.x - 1) / grid.x;        // about 8 CTAs per SM
+    const int64_t need = (rows + 1) / 2;
+    if (gy > need) gy = need;
+    grid.y = (unsigned)(gy < 1 ? 1 : gy);
+    if (fmt == 8) mx_quant_rows_kernel<T, 8><<<grid, 256, 0, stream>>>(x, (int)rows, (int)k, ld, payload, srm, st, tile_rows);
+    else mx_quant_rows_kernel<T, 4><<<grid, 256, 0, stream>>>(x, (int)rows, (int)k, ld, payload, srm, st, tile_rows);
+    AMCT_CHECK_LAUNCH();
+    return AMCT_OK;
+  }
   const int64_t total = rows * (k / 8);
   int64_t blocks = (total + 511) / 512;
   if (blocks < 1) blocks = 1;
@@ -178,7 +223,7 @@ extern "C" int amct_mx_quant(const void* x, int dtype, int64_t rows, int64_t k, 
   if (rows < 0 || k < 0 || ld_x < k || (elem_bits != 8 && elem_bits != 4)) return AMCT_ERR_ARG;
   if (rows == 0 || k == 0) return AMCT_OK;
   if (!x || !payload || (!scales_rowmajor && !scales_tiled)) return AMCT_ERR_ARG;
-  if (k % 32 != 0) return AMCT_ERR_UNSUPPORTED;
+  if (k % 32 != 0 || rows > 0x7fffffffLL) return AMCT_ERR_UNSUPPORTED;
   if (scales_tiled && (scale_tile_rows < 32 || scale_tile_rows % 32 != 0)) return AMCT_ERR_ARG;
   const int tr = scales_tiled ? scale_tile_rows : 128;
   const int esize = dtype == AMCT_DTYPE_F32 ? 4 : 2;

@@ -14,49 +14,64 @@
 
 namespace amct {
 
+// grid.x covers the 8-element chunks of a row, grid.y strides over rows (two in flight).
 template <typename T, int BITS>
-__global__ void __launch_bounds__(256) dequant_weight_kernel(const uint8_t* codes, int64_t n_rows, int64_t k, int64_t ld_codes,
+__global__ void __launch_bounds__(256) dequant_weight_kernel(const uint8_t* codes, int n_rows, int k, int64_t ld_codes,
                                                              const T* scale, const T* offset, int group, T* out, int64_t ld_out) {
-  const int64_t chunks = k / 8;
-  const int64_t total = n_rows * chunks;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t n = i / chunks, c = i - n * chunks;
-    const int64_t k0 = c * 8;
-    int q[8];
-    if (BITS == 8) {
-      uint2 raw = *reinterpret_cast<const uint2*>(codes + n * ld_codes + k0);
+  constexpr int U = 2;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= k / 8) return;
+  const int k0 = c * 8;
+  const int g = group ? k0 / group : 0;
+  for (int n0 = blockIdx.y * U; n0 < n_rows; n0 += gridDim.y * U) {
+    uint2 raw[U];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        q[e] = (int)(int8_t)(raw.x >> (8 * e));
-        q[4 + e] = (int)(int8_t)(raw.y >> (8 * e));
+    for (int u = 0; u < U; ++u) {
+      if (n0 + u < n_rows) {
+        if (BITS == 8) raw[u] = __ldcs(reinterpret_cast<const uint2*>(codes + (int64_t)(n0 + u) * ld_codes + k0));
+        else raw[u] = make_uint2(__ldcs(reinterpret_cast<const uint32_t*>(codes + (int64_t)(n0 + u) * ld_codes + k0 / 2)), 0u);
       }
-    } else {
-      uint32_t raw = *reinterpret_cast<const uint32_t*>(codes + n * ld_codes + k0 / 2);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) q[e] = (int)((raw >> (4 * e)) & 0xF) - 8;
     }
-    const int64_t g = group ? k0 / group : 0;
-    const float s = ElemTraits<T>::to_f(scale[g * n_rows + n]);
-    const float o = offset ? ElemTraits<T>::to_f(offset[g * n_rows + n]) : 0.f;
-    Vec16<T> r;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float v = (float)q[e];
-      if (offset) v = __fadd_rn(v, o);
-      r.v[e] = ElemTraits<T>::from_f(__fmul_rn(v, s));
+    for (int u = 0; u < U; ++u) {
+      const int n = n0 + u;
+      if (n >= n_rows) break;
+      int q[8];
+      if (BITS == 8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          q[e] = (int)(int8_t)(raw[u].x >> (8 * e));
+          q[4 + e] = (int)(int8_t)(raw[u].y >> (8 * e));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q[e] = (int)((raw[u].x >> (4 * e)) & 0xF) - 8;
+      }
+      const float s = ElemTraits<T>::to_f(scale[(int64_t)g * n_rows + n]);
+      const float o = offset ? ElemTraits<T>::to_f(offset[(int64_t)g * n_rows + n]) : 0.f;
+      Vec16<T> r;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float v = (float)q[e];
+        if (offset) v = __fadd_rn(v, o);
+        r.v[e] = ElemTraits<T>::from_f(__fmul_rn(v, s));
+      }
+      *reinterpret_cast<uint4*>(out + (int64_t)n * ld_out + k0) = *reinterpret_cast<uint4*>(&r);
     }
-    *reinterpret_cast<uint4*>(out + n * ld_out + k0) = *reinterpret_cast<uint4*>(&r);
   }
 }
 
 template <typename T>
 static int run_dequant(const uint8_t* codes, int bits, int64_t n_rows, int64_t k, int64_t ld_codes, const T* scale,
                        const T* offset, int group, T* out, int64_t ld_out, cudaStream_t st) {
-  const int64_t total = n_rows * (k / 8);
-  int64_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  if (bits == 8) dequant_weight_kernel<T, 8><<<(unsigned)blocks, 256, 0, st>>>(codes, n_rows, k, ld_codes, scale, offset, group, out, ld_out);
-  else dequant_weight_kernel<T, 4><<<(unsigned)blocks, 256, 0, st>>>(codes, n_rows, k, ld_codes, scale, offset, group, out, ld_out);
+  if (n_rows >= (1LL << 30) || k >= (1LL << 30)) return AMCT_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)((k / 8 + 255) / 256), 1);
+  int64_t gy = (148LL * 8 + grid.x - 1) / grid.x;
+  const int64_t need = (n_rows + 1) / 2;
+  if (gy > need) gy = need;
+  grid.y = (unsigned)(gy < 1 ? 1 : gy);
+  if (bits == 8) dequant_weight_kernel<T, 8><<<grid, 256, 0, st>>>(codes, (int)n_rows, (int)k, ld_codes, scale, offset, group, out, ld_out);
+  else dequant_weight_kernel<T, 4><<<grid, 256, 0, st>>>(codes, (int)n_rows, (int)k, ld_codes, scale, offset, group, out, ld_out);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
