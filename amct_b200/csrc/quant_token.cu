@@ -69,44 +69,48 @@ template <> struct Packed<__half> {
 __device__ __forceinline__ float max_nan(float a, float b) { return (a != a || b != b) ? NAN : fmaxf(a, b); }
 __device__ __forceinline__ float min_nan(float a, float b) { return (a != a || b != b) ? NAN : fminf(a, b); }
 
-// quantize 4 values given scale s and y = rn(1/s); falls back to the IEEE division near ties
+// exact quotients for a vector whose fast-path quotients came too close to a tie (rare; kept
+// out of line so the hot loop stays small)
+__device__ __noinline__ uint32_t quant4_exact(float a, float b, float c, float d, float s) {
+  const float ra = __fadd_rn(fminf(__fdiv_rn(a, s), 127.f), kMagic), rb = __fadd_rn(fminf(__fdiv_rn(b, s), 127.f), kMagic);
+  const float rc = __fadd_rn(fminf(__fdiv_rn(c, s), 127.f), kMagic), rd = __fadd_rn(fminf(__fdiv_rn(d, s), 127.f), kMagic);
+  return pack4_s8(ra, rb, rc, rd);
+}
+
+// quantize 4 values given scale s and y = rn(1/s)
 template <bool CLAMP>
 __device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float s, float y) {
   // only a negative-dominant row (divisor 128) can produce a quotient above 127.5
   float ta = __fmul_rn(a, y), tb = __fmul_rn(b, y), tc = __fmul_rn(c, y), td = __fmul_rn(d, y);
   if (CLAMP) { ta = fminf(ta, 127.f); tb = fminf(tb, 127.f); tc = fminf(tc, 127.f); td = fminf(td, 127.f); }
-  float ra = __fadd_rn(ta, kMagic), rb = __fadd_rn(tb, kMagic), rc = __fadd_rn(tc, kMagic), rd = __fadd_rn(td, kMagic);
+  const float ra = __fadd_rn(ta, kMagic), rb = __fadd_rn(tb, kMagic), rc = __fadd_rn(tc, kMagic), rd = __fadd_rn(td, kMagic);
   // distance of each quotient from the integer it rounded to
   const float m = fmaxf(fmaxf(fabsf(__fsub_rn(ta, __fsub_rn(ra, kMagic))), fabsf(__fsub_rn(tb, __fsub_rn(rb, kMagic)))),
                         fmaxf(fabsf(__fsub_rn(tc, __fsub_rn(rc, kMagic))), fabsf(__fsub_rn(td, __fsub_rn(rd, kMagic)))));
-  if (m > 0.5f - 2.44140625e-4f) {   // within 2^-12 of a tie: the exact quotient could round the other way
-    ra = __fadd_rn(fminf(__fdiv_rn(a, s), 127.f), kMagic); rb = __fadd_rn(fminf(__fdiv_rn(b, s), 127.f), kMagic);
-    rc = __fadd_rn(fminf(__fdiv_rn(c, s), 127.f), kMagic); rd = __fadd_rn(fminf(__fdiv_rn(d, s), 127.f), kMagic);
-  }
+  if (m > 0.5f - 2.44140625e-4f) return quant4_exact(a, b, c, d, s);   // within 2^-12 of a tie
   return pack4_s8(ra, rb, rc, rd);
 }
 
-template <typename T, int NV, bool CLAMP>
-__device__ __forceinline__ void quantize_row(const uint4 (&raw)[NV], int8_t* qrow, int nvec, int nthr, int tid, float s, float y) {
-#pragma unroll
-  for (int j = 0; j < NV; ++j) {
-    const int v = j * nthr + tid;
-    if (v < nvec) {
-      if constexpr (sizeof(T) == 2) {
-        using P = Packed<T>;
-        const typename P::V2* h = reinterpret_cast<const typename P::V2*>(&raw[j]);
-        const uint32_t w0 = quant4<CLAMP>(P::lo(h[0]), P::hi(h[0]), P::lo(h[1]), P::hi(h[1]), s, y);
-        const uint32_t w1 = quant4<CLAMP>(P::lo(h[2]), P::hi(h[2]), P::lo(h[3]), P::hi(h[3]), s, y);
-        *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(w0, w1);
-      } else {
-        const float* f = reinterpret_cast<const float*>(&raw[j]);
-        *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = quant4<CLAMP>(f[0], f[1], f[2], f[3], s, y);
-      }
+// second pass over the row held in shared memory: quantize and store
+template <typename T, bool CLAMP>
+__device__ __forceinline__ void quantize_row(const uint4* src, int8_t* qrow, int nvec, int nthr, int tid, float s, float y) {
+#pragma unroll 2
+  for (int v = tid; v < nvec; v += nthr) {
+    const uint4 raw = src[v];
+    if constexpr (sizeof(T) == 2) {
+      using P = Packed<T>;
+      const typename P::V2* h = reinterpret_cast<const typename P::V2*>(&raw);
+      const uint32_t w0 = quant4<CLAMP>(P::lo(h[0]), P::hi(h[0]), P::lo(h[1]), P::hi(h[1]), s, y);
+      const uint32_t w1 = quant4<CLAMP>(P::lo(h[2]), P::hi(h[2]), P::lo(h[3]), P::hi(h[3]), s, y);
+      *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(w0, w1);
+    } else {
+      const float* f = reinterpret_cast<const float*>(&raw);
+      *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = quant4<CLAMP>(f[0], f[1], f[2], f[3], s, y);
     }
   }
 }
 
-template <typename T, int NV>
+template <typename T>
 __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
   constexpr int E = ElemTraits<T>::kPerVec;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -119,6 +123,7 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
   const int nvec = (int)(p.k / E);
   uint8_t* smooth_s = smem + (size_t)p.slots * p.slot_bytes;       // staged smooth vector (if any)
   const int64_t my_rows = p.rows > blockIdx.x ? (p.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const T* xbase = reinterpret_cast<const T*>(p.x);
 
   if (tid == 0) {
     abort_word = 0;
@@ -130,15 +135,16 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
     for (int v = tid; v < nvec; v += nthr) reinterpret_cast<uint4*>(smooth_s)[v] = __ldg(src + v);
   }
   __syncthreads();
-  const T* xbase = reinterpret_cast<const T*>(p.x);
-  if (tid == 0) {
-    for (int i = 0; i < p.slots && i < my_rows; ++i) {
-      const uint32_t bar = tc05::smem_u32(&full[i]);
-      tc05::mbar_expect_tx(bar, (uint32_t)p.slot_bytes);
-      tc05::bulk_load_1d(tc05::smem_u32(smem + (size_t)i * p.slot_bytes), xbase + (blockIdx.x + (int64_t)i * gridDim.x) * p.ld,
-                         (uint32_t)p.slot_bytes, bar);
-    }
-  }
+  // rows 0 .. slots-2 are requested up front; row i + slots - 1 is requested during row i
+  auto request = [&](int64_t i) {
+    const int sl = (int)(i % p.slots);
+    const uint32_t bar = tc05::smem_u32(&full[sl]);
+    tc05::mbar_expect_tx(bar, (uint32_t)p.slot_bytes);
+    tc05::bulk_load_1d(tc05::smem_u32(smem + (size_t)sl * p.slot_bytes), xbase + (blockIdx.x + i * gridDim.x) * p.ld,
+                       (uint32_t)p.slot_bytes, bar);
+  };
+  if (tid == 0)
+    for (int64_t i = 0; i < p.slots - 1 && i < my_rows; ++i) request(i);
 
   int slot = 0;
   uint32_t parity = 0;
@@ -147,52 +153,47 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
     // a timed-out wait does not leave the loop here: every thread goes on to the block barrier
     // below and all of them leave together after it, so no thread is left waiting at a barrier
     tc05::mbar_wait(tc05::smem_u32(&full[slot]), parity, abort_flag);
-    const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)slot * p.slot_bytes);
+    uint4* src = reinterpret_cast<uint4*>(smem + (size_t)slot * p.slot_bytes);
 
-    uint4 raw[NV];
+    // ---- pass 1: (smooth multiply, written back to shared memory) + min / max
     float mn = INFINITY, mx = -INFINITY;
-    uint32_t pmx = 0, pmn = 0;             // packed running max / min of the 16-bit path
-    bool first = true;
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int v = j * nthr + tid;
-      if (v < nvec) {
-        raw[j] = src[v];
-        if constexpr (sizeof(T) == 2) {
-          using P = Packed<T>;
-          typename P::V2* h = reinterpret_cast<typename P::V2*>(&raw[j]);
-          if (p.smooth) {
-            const uint4 sv = reinterpret_cast<const uint4*>(smooth_s)[v];
-            const typename P::V2* sh = reinterpret_cast<const typename P::V2*>(&sv);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) h[e] = P::mul(h[e], sh[e]);
-          }
-          typename P::V2 vmx = P::vmax(P::vmax(h[0], h[1]), P::vmax(h[2], h[3]));
-          typename P::V2 vmn = P::vmin(P::vmin(h[0], h[1]), P::vmin(h[2], h[3]));
-          if (!first) {
-            vmx = P::vmax(vmx, *reinterpret_cast<typename P::V2*>(&pmx));
-            vmn = P::vmin(vmn, *reinterpret_cast<typename P::V2*>(&pmn));
-          }
-          pmx = *reinterpret_cast<uint32_t*>(&vmx);
-          pmn = *reinterpret_cast<uint32_t*>(&vmn);
-          first = false;
-        } else {
-          float* f = reinterpret_cast<float*>(&raw[j]);
-          if (p.smooth) {
-            const float4 sv = reinterpret_cast<const float4*>(smooth_s)[v];
-            f[0] = __fmul_rn(f[0], sv.x); f[1] = __fmul_rn(f[1], sv.y); f[2] = __fmul_rn(f[2], sv.z); f[3] = __fmul_rn(f[3], sv.w);
-          }
-          mx = max_nan(mx, max_nan(max_nan(f[0], f[1]), max_nan(f[2], f[3])));
-          mn = min_nan(mn, min_nan(min_nan(f[0], f[1]), min_nan(f[2], f[3])));
-        }
-      }
-    }
     if constexpr (sizeof(T) == 2) {
       using P = Packed<T>;
+      typename P::V2 vmx, vmn;
+      bool first = true;
+#pragma unroll 4
+      for (int v = tid; v < nvec; v += nthr) {
+        uint4 raw = src[v];
+        typename P::V2* h = reinterpret_cast<typename P::V2*>(&raw);
+        if (p.smooth) {
+          const uint4 sv = reinterpret_cast<const uint4*>(smooth_s)[v];
+          const typename P::V2* sh = reinterpret_cast<const typename P::V2*>(&sv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h[e] = P::mul(h[e], sh[e]);
+          src[v] = raw;
+        }
+        typename P::V2 a = P::vmax(P::vmax(h[0], h[1]), P::vmax(h[2], h[3]));
+        typename P::V2 b = P::vmin(P::vmin(h[0], h[1]), P::vmin(h[2], h[3]));
+        vmx = first ? a : P::vmax(vmx, a);
+        vmn = first ? b : P::vmin(vmn, b);
+        first = false;
+      }
       if (!first) {
-        const typename P::V2 vmx = *reinterpret_cast<typename P::V2*>(&pmx), vmn = *reinterpret_cast<typename P::V2*>(&pmn);
         mx = max_nan(P::lo(vmx), P::hi(vmx));
         mn = min_nan(P::lo(vmn), P::hi(vmn));
+      }
+    } else {
+#pragma unroll 4
+      for (int v = tid; v < nvec; v += nthr) {
+        uint4 raw = src[v];
+        float* f = reinterpret_cast<float*>(&raw);
+        if (p.smooth) {
+          const float4 sv = reinterpret_cast<const float4*>(smooth_s)[v];
+          f[0] = __fmul_rn(f[0], sv.x); f[1] = __fmul_rn(f[1], sv.y); f[2] = __fmul_rn(f[2], sv.z); f[3] = __fmul_rn(f[3], sv.w);
+          src[v] = raw;
+        }
+        mx = max_nan(mx, max_nan(max_nan(f[0], f[1]), max_nan(f[2], f[3])));
+        mn = min_nan(mn, min_nan(min_nan(f[0], f[1]), min_nan(f[2], f[3])));
       }
     }
     // a NaN anywhere in the row becomes max = +inf: the scale is then infinite and the row is flagged
@@ -204,13 +205,11 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
     }
     const int buf = (int)(i & 1);
     if (lane == 0) { part[buf][0][warp] = mx; part[buf][1][warp] = mn; }
-    __syncthreads();                       // every thread has also finished reading the slot
+    __syncthreads();                       // also: every thread has finished pass 2 of the previous row
     if (*abort_flag) break;
-    if (tid == 0 && i + p.slots < my_rows) {
-      const uint32_t bar = tc05::smem_u32(&full[slot]);
-      tc05::mbar_expect_tx(bar, (uint32_t)p.slot_bytes);
-      tc05::bulk_load_1d(tc05::smem_u32(smem + (size_t)slot * p.slot_bytes), xbase + (row + (int64_t)p.slots * gridDim.x) * p.ld,
-                         (uint32_t)p.slot_bytes, bar);
+    if (tid == 0 && i + p.slots - 1 < my_rows) {
+      tc05::fence_proxy_async();           // generic-proxy accesses to that slot are ordered before the bulk copy
+      request(i + p.slots - 1);            // into the slot row i-1 just left
     }
     mx = part[buf][0][0]; mn = part[buf][1][0];
     for (int w = 1; w < nwarp; ++w) { mx = fmaxf(mx, part[buf][0][w]); mn = fminf(mn, part[buf][1][w]); }
@@ -227,8 +226,9 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
     }
     const float y = __frcp_rn(s);
     int8_t* qrow = p.q + row * p.ld_q;
-    if (neg_dom) quantize_row<T, NV, true>(raw, qrow, nvec, nthr, tid, s, y);       // uniform per row
-    else quantize_row<T, NV, false>(raw, qrow, nvec, nthr, tid, s, y);
+    // ---- pass 2 (uniform branch per row)
+    if (neg_dom) quantize_row<T, true>(src, qrow, nvec, nthr, tid, s, y);
+    else quantize_row<T, false>(src, qrow, nvec, nthr, tid, s, y);
     if (++slot == p.slots) { slot = 0; parity ^= 1; }
   }
   if (*abort_flag) {
@@ -251,8 +251,6 @@ static int launch_token(const TokenParams& p0, cudaStream_t st) {
   const int64_t nvec = p.k / E;
   // up to 8 vectors per thread: more elements per thread amortise the per-row reduction
   const int threads = nvec <= 1024 ? 128 : (nvec <= 2048 ? 256 : 512);
-  const int nv = (int)((nvec + threads - 1) / threads);
-  if (nv > 8) return 1;
   const int64_t smooth_bytes = p.smooth ? row_bytes : 0;
   // as many CTAs per SM as fit with at least 3 rows in flight each (about 200 KB of shared memory per SM)
   int ctas_per_sm = 2048 / threads > 4 ? 4 : 2048 / threads;
@@ -269,17 +267,11 @@ static int launch_token(const TokenParams& p0, cudaStream_t st) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int64_t grid = (int64_t)sms * ctas_per_sm;
   if (grid > p.rows) grid = p.rows;
-#define AMCT_TOKEN_CASE(NVC)                                                                                       \
-  if (nv <= NVC) {                                                                                                 \
-    if (cudaFuncSetAttribute(quant_token_kernel<T, NVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
-      return AMCT_ERR_CUDA;                                                                                        \
-    quant_token_kernel<T, NVC><<<(unsigned)grid, threads, smem, st>>>(p);                                          \
-    AMCT_CHECK_LAUNCH();                                                                                           \
-    return AMCT_OK;                                                                                                \
-  }
-  AMCT_TOKEN_CASE(1) AMCT_TOKEN_CASE(2) AMCT_TOKEN_CASE(4) AMCT_TOKEN_CASE(8)
-#undef AMCT_TOKEN_CASE
-  return 1;
+  if (cudaFuncSetAttribute(quant_token_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return AMCT_ERR_CUDA;
+  quant_token_kernel<T><<<(unsigned)grid, threads, smem, st>>>(p);
+  AMCT_CHECK_LAUNCH();
+  return AMCT_OK;
 }
 
 int quant_token_try(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, const void* smooth, int8_t* q,
