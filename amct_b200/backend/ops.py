@@ -484,3 +484,30 @@ def hif8_decode(codes, dtype=torch.bfloat16, out=None):
     _l.check(rc, 'amct_hif8_decode')
     COUNTERS['launches'] += 1
     return out
+
+
+def gemm_w8a8_swiglu(q, w_nk, deq_scale, pertoken_scale=None, bias=None, out=None, status=None):
+    """W8A8 GEMM of a gate/up projection with 128-row interleaved weights and a fused SwiGLU
+    epilogue: returns bf16 [M, N/2]."""
+    _need_cuda(q, w_nk, deq_scale, pertoken_scale, bias)
+    q, w_nk = _kmajor(q), _kmajor(w_nk)
+    m, k = q.shape
+    n = w_nk.shape[0]
+    if out is None:
+        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=q.device)
+    deq_scale = deq_scale.reshape(-1).to(torch.float32).contiguous()
+    if pertoken_scale is not None:
+        pertoken_scale = pertoken_scale.reshape(-1).to(torch.float32).contiguous()
+    bk = 0
+    if bias is not None:
+        bias = bias.reshape(-1).contiguous()
+        bk = _BIAS_KIND[bias.dtype]
+    prof = _prof_begin()
+    rc = _l.load().amct_gemm_w8a8_swiglu(
+        _p(q), _p(w_nk), c_int64(m), c_int64(n), c_int64(k), c_int64(q.stride(0)), c_int64(w_nk.stride(0)),
+        _p(deq_scale), _p(pertoken_scale), _p(bias), c_int(bk), _p(out), c_int64(out.stride(0)),
+        _p(status) if status is not None else c_void_p(0), _stream())
+    _l.check(rc, 'amct_gemm_w8a8_swiglu')
+    COUNTERS['launches'] += 1
+    _prof_end(prof, 2 * m * n * k)
+    return out

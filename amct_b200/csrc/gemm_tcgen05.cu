@@ -50,6 +50,7 @@ struct GemmParams {
   int out_kind;
   int64_t ld_out;              // elements
   int* status;
+  int act;                     // 0 none, 1 SwiGLU over interleaved [128 gate | 128 up] column blocks
 };
 
 struct __align__(1024) GemmSmem {
@@ -78,6 +79,14 @@ __device__ __forceinline__ float bias_at(const void* bias, int kind, int64_t n) 
     case BIAS_I32: return __int_as_float(reinterpret_cast<const int*>(bias)[n]);   // carried as raw bits
   }
   return 0.f;
+}
+
+// dequant epilogue of one INT8 accumulator in per-token mode
+__device__ __forceinline__ float epi_token(int acc, float deq, float pt, bool has_pt, float bias, bool has_bias) {
+  float v = __fmul_rn((float)acc, deq);
+  if (has_pt) v = __fmul_rn(v, pt);
+  if (has_bias) v = __fadd_rn(v, bias);
+  return v;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -185,6 +194,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_full[acc]), acc_phase, abort_flag)) break;
       tc05::fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN;
+      if (p.act == 1) {
+        // SwiGLU: the tile holds 128 gate columns followed by their 128 up columns.  Both are
+        // dequantized and rounded to bf16 as the unfused Linear would output them, then
+        // out = bf16(bf16(silu(gate)) * up); the output has N/2 columns.
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN / 2; c0 += 32) {
+          uint32_t rg[32], ru[32];
+          tc05::tmem_ld_32x32(t_row + c0, rg);
+          tc05::tmem_ld_32x32(t_row + kBN / 2 + c0, ru);
+          tc05::tmem_ld_wait();
+          if (row < p.m) {
+            uint32_t h[16];
+            const bool has_b = p.bias_kind != BIAS_NONE;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float o2[2];
+#pragma unroll
+              for (int t = 0; t < 2; ++t) {
+                float g = epi_token((int)rg[j + t], sc[c0 + j + t], pt, p.pertoken != nullptr, sb[c0 + j + t], has_b);
+                float u = epi_token((int)ru[j + t], sc[kBN / 2 + c0 + j + t], pt, p.pertoken != nullptr, sb[kBN / 2 + c0 + j + t], has_b);
+                g = __bfloat162float(__float2bfloat16_rn(g));
+                u = __bfloat162float(__float2bfloat16_rn(u));
+                const float sg = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g)))));
+                o2[t] = __fmul_rn(sg, u);
+              }
+              __nv_bfloat162 v = __floats2bfloat162_rn(o2[0], o2[1]);
+              h[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + row * p.ld_out + tn * (kBN / 2) + c0;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(h[j], h[j + 1], h[j + 2], h[j + 3]);
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < kBN; c0 += 32) {
         uint32_t r[32];
@@ -356,6 +399,22 @@ extern "C" int amct_gemm_w8a8(const int8_t* a, const int8_t* b, int64_t m, int64
   p.m = m; p.n = n; p.k = k; p.kind = amct::KIND_I8;
   p.deq = deq_scale; p.pertoken = pertoken_scale; p.bias = bias; p.bias_kind = bias_kind;
   p.out = out; p.out_kind = out_kind; p.ld_out = ld_out; p.status = status;
+  return amct::launch_gemm(a, b, ld_a, ld_b, p, (cudaStream_t)stream);
+}
+
+extern "C" int amct_gemm_w8a8_swiglu(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64_t k, int64_t ld_a,
+                                     int64_t ld_b, const float* deq_scale, const float* pertoken_scale, const void* bias,
+                                     int bias_kind, void* out, int64_t ld_out, int* status, void* stream) {
+  if (m < 0 || n < 0 || k < 0 || ld_a < k || ld_b < k || ld_out < n / 2) return AMCT_ERR_ARG;
+  if (m && n && (!a || !b || !out || !deq_scale)) return AMCT_ERR_ARG;
+  if (n % amct::kBN != 0) return AMCT_ERR_UNSUPPORTED;                 // whole [128 gate | 128 up] blocks only
+  if (bias_kind == amct::BIAS_I32 || bias_kind < amct::BIAS_NONE || bias_kind > amct::BIAS_BF16 || (bias_kind && !bias))
+    return AMCT_ERR_ARG;
+  if (!amct::aligned16(out) || (ld_out * 2) % 16 != 0) return AMCT_ERR_ALIGN;
+  amct::GemmParams p{};
+  p.m = m; p.n = n; p.k = k; p.kind = amct::KIND_I8;
+  p.deq = deq_scale; p.pertoken = pertoken_scale; p.bias = bias; p.bias_kind = bias_kind;
+  p.out = out; p.out_kind = amct::OUT_BF16; p.ld_out = ld_out; p.status = status; p.act = 1;
   return amct::launch_gemm(a, b, ld_a, ld_b, p, (cudaStream_t)stream);
 }
 

@@ -31,6 +31,9 @@ class NpuQuantizationLinear(torch.nn.Module):
         self.act_type = quant_module.act_type
         self.dynamic_act = bool(getattr(quant_module, 'dynamic_act', False))
         self.dynamic_rule = 'released'
+        # opt-in (not in the reference): 'swiglu' fuses silu(gate) * up into the GEMM epilogue of a fused
+        # gate/up projection whose weight rows are interleaved in blocks of 128 (see interleave_gate_up)
+        self.fused_act = None
         self.act_granularity = 'PER_TENSOR'
         self.quantize_axis = -1
 
@@ -106,5 +109,16 @@ class NpuQuantizationLinear(torch.nn.Module):
             pertoken = self.pertoken_scale
             if pertoken is not None and x.dim() > 2:
                 pertoken = pertoken.repeat(x.numel() // (x.shape[-2] * k))
+        if self.fused_act == 'swiglu':
+            out = ops.gemm_w8a8_swiglu(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias)
+            return out.reshape(*x.shape[:-1], -1)
         out = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out_dtype=self.output_dtype)
         return out.reshape(*x.shape[:-1], -1)
+
+
+def interleave_gate_up(w_gate, w_up, block=128):
+    """Rows of a fused gate/up weight in the order the SwiGLU epilogue expects: 128 gate rows,
+    then the 128 matching up rows, and so on.  [I, K] + [I, K] -> [2 I, K] (I % 128 == 0)."""
+    i, k = w_gate.shape
+    assert w_up.shape == w_gate.shape and i % block == 0
+    return torch.stack((w_gate.reshape(i // block, block, k), w_up.reshape(i // block, block, k)), dim=1).reshape(2 * i, k)

@@ -102,7 +102,7 @@ def apply_rotary(x, cos, sin):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, shape, tp, group, device, gen):
+    def __init__(self, shape, tp, group, device, gen, fused_swiglu=True):
         super().__init__()
         self.shape, self.tp, self.group = shape, tp, group
         self.heads = shape.n_heads // tp
@@ -110,6 +110,10 @@ class DecoderLayer(nn.Module):
         self.linears = _Shard(shape, tp, device, gen)
         amct.quantize(self.linears, W8A8_DYNAMIC_CFG)
         amct.convert(self.linears)
+        # the random gate/up rows are taken to be interleaved in blocks of 128, so SwiGLU runs in the GEMM epilogue
+        self.fused_swiglu = fused_swiglu and (shape.intermediate // tp) % 128 == 0
+        if self.fused_swiglu:
+            self.linears.gate_up_proj.fused_act = 'swiglu'
         self.input_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
         self.post_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
 
@@ -138,15 +142,19 @@ class DecoderLayer(nn.Module):
         attn = attn.transpose(1, 2).reshape(b, s, self.heads * shp.head_dim)
         x = x + self._reduce(lin.o_proj(attn))
         hn = F.rms_norm(x, (shp.hidden,), self.post_norm, shp.rms_eps)
-        gate, up = lin.gate_up_proj(hn).chunk(2, dim=-1)
-        x = x + self._reduce(lin.down_proj(F.silu(gate) * up))
+        if self.fused_swiglu:
+            act = lin.gate_up_proj(hn)
+        else:
+            gate, up = lin.gate_up_proj(hn).chunk(2, dim=-1)
+            act = F.silu(gate) * up
+        x = x + self._reduce(lin.down_proj(act))
         return x
 
 
 class LlamaW8A8(nn.Module):
     """Random-initialised Llama stack; rank `rank` of `tp` holds its shard of every layer."""
 
-    def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None):
+    def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None, fused_swiglu=True):
         super().__init__()
         if shape.n_kv_heads % tp or shape.n_heads % tp or shape.intermediate % tp:
             raise ValueError(f'tp={tp} does not divide the head / intermediate sizes')
@@ -156,7 +164,7 @@ class LlamaW8A8(nn.Module):
         self.embed = torch.empty(shape.vocab, shape.hidden, dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=shared)
         self.lm_head = torch.empty(shape.vocab, shape.hidden, dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=shared)
         self.final_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
-        self.layers = nn.ModuleList(DecoderLayer(shape, tp, group, device, gen)
+        self.layers = nn.ModuleList(DecoderLayer(shape, tp, group, device, gen, fused_swiglu)
                                     for _ in range(n_layers if n_layers is not None else shape.n_layers))
 
     @torch.no_grad()

@@ -158,6 +158,18 @@ int amct_gemm_w8a8(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64
                    const float* deq_scale, const float* pertoken_scale, const void* bias, int bias_kind,
                    void* out, int out_kind, int64_t ld_out, int* status, void* stream);
 
+/* amct_gemm_w8a8 in per-token mode with a SwiGLU epilogue, for a fused gate/up projection
+ * whose weight rows are interleaved in blocks of 128: rows [256 j, 256 j + 128) are gate
+ * channels [128 j, 128 j + 128) and the next 128 rows the matching up channels (n % 256 == 0).
+ * gate and up are dequantized and rounded to bf16 exactly as amct_gemm_w8a8 would store
+ * them; out[m, c] = bf16(bf16(silu(gate[m, c])) * up[m, c]), bf16 [m, n/2].  Saves writing
+ * and re-reading the [m, n] intermediate of the Llama MLP; the reference has no such
+ * fusion (its deploy forward ends at npu_quant_matmul,
+ * amct_pytorch/deploy_op/npu_quantization_linear.py:100-102). */
+int amct_gemm_w8a8_swiglu(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64_t k, int64_t ld_a,
+                          int64_t ld_b, const float* deq_scale, const float* pertoken_scale, const void* bias,
+                          int bias_kind, void* out, int64_t ld_out, int* status, void* stream);
+
 /* 16-bit float GEMM out[m, n] = sum_k a[m, k] * b[n, k] (+ bias[n]), fp32
  * accumulation; dtype AMCT_DTYPE_F16 or AMCT_DTYPE_BF16 for both operands.  The
  * tensor-core stage behind npu_weight_quant_batchmatmul

@@ -226,3 +226,33 @@ def test_dynamic_w8a8_linear_matches_oracle():
         q, s = intq.dynamic_per_token(x)
         want = npu_ops.npu_quant_matmul(q.reshape(-1, 256), wq.t(), sw.reshape(-1), s, b, torch.bfloat16).reshape(*shape[:-1], -1)
         assert bits_equal(got, want)
+
+
+def test_swiglu_epilogue_matches_unfused_path():
+    """The fused gate/up GEMM + SwiGLU epilogue against the unfused sequence on the same device:
+    plain W8A8 GEMM (bf16 out) -> de-interleave -> torch silu * up."""
+    from amct_b200.deploy_op.npu_quantization_linear import interleave_gate_up
+    g = torch.Generator().manual_seed(21)
+    m, inter, k = 200, 384, 512
+    a = rand_i8(g, m, k).cuda()
+    wg, wu = rand_i8(g, inter, k), rand_i8(g, inter, k)
+    w = interleave_gate_up(wg, wu).cuda()
+    deq = (torch.rand(2 * inter, generator=g) * 2e-4 + 1e-5).cuda()
+    pt = (torch.rand(m, generator=g) * 0.05 + 0.01).cuda()
+    bias = (torch.randn(2 * inter, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    st = status()
+    fused = ops().gemm_w8a8_swiglu(a, w, deq, pt, bias, status=st)
+    plain = ops().gemm_w8a8(a, w, deq, pt, bias, out_dtype=torch.bfloat16, status=st)
+    ops().raise_if_timed_out(st)
+    blocks = plain.reshape(m, inter // 128, 2, 128)
+    gate, up = blocks[:, :, 0].reshape(m, inter), blocks[:, :, 1].reshape(m, inter)
+    want = torch.nn.functional.silu(gate) * up
+    assert fused.shape == (m, inter)
+    diff = (fused.float() - want.float()).abs().max().item()
+    assert bits_equal(fused, want), diff
+    # and against the CPU oracle's GEMM with a CPU silu, within bf16 tolerance
+    ref = npu_ops.npu_quant_matmul(a.cpu(), w.cpu().t(), deq.cpu(), pt.cpu(), bias.cpu(), torch.bfloat16)
+    rb = ref.reshape(m, inter // 128, 2, 128)
+    want_cpu = torch.nn.functional.silu(rb[:, :, 0].reshape(m, inter)) * rb[:, :, 1].reshape(m, inter)
+    err = ((fused.cpu().float() - want_cpu.float()).abs().max() / want_cpu.float().abs().max()).item()
+    assert err < TOL_16, err
