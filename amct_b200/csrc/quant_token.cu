@@ -77,35 +77,42 @@ __device__ __noinline__ uint32_t quant4_exact(float a, float b, float c, float d
   return pack4_s8(ra, rb, rc, rd);
 }
 
-// quantize 4 values given scale s and y = rn(1/s)
+// fast path for 4 values: quotient by reciprocal, rounded with the magic add; returns the packed
+// codes and raises `dist` to the largest distance of a quotient from the integer it rounded to
 template <bool CLAMP>
-__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float s, float y) {
+__device__ __forceinline__ uint32_t quant4_fast(float a, float b, float c, float d, float y, float& dist) {
   // only a negative-dominant row (divisor 128) can produce a quotient above 127.5
   float ta = __fmul_rn(a, y), tb = __fmul_rn(b, y), tc = __fmul_rn(c, y), td = __fmul_rn(d, y);
   if (CLAMP) { ta = fminf(ta, 127.f); tb = fminf(tb, 127.f); tc = fminf(tc, 127.f); td = fminf(td, 127.f); }
   const float ra = __fadd_rn(ta, kMagic), rb = __fadd_rn(tb, kMagic), rc = __fadd_rn(tc, kMagic), rd = __fadd_rn(td, kMagic);
-  // distance of each quotient from the integer it rounded to
-  const float m = fmaxf(fmaxf(fabsf(__fsub_rn(ta, __fsub_rn(ra, kMagic))), fabsf(__fsub_rn(tb, __fsub_rn(rb, kMagic)))),
-                        fmaxf(fabsf(__fsub_rn(tc, __fsub_rn(rc, kMagic))), fabsf(__fsub_rn(td, __fsub_rn(rd, kMagic)))));
-  if (m > 0.5f - 2.44140625e-4f) return quant4_exact(a, b, c, d, s);   // within 2^-12 of a tie
+  dist = fmaxf(dist, fmaxf(fmaxf(fabsf(__fsub_rn(ta, __fsub_rn(ra, kMagic))), fabsf(__fsub_rn(tb, __fsub_rn(rb, kMagic)))),
+                           fmaxf(fabsf(__fsub_rn(tc, __fsub_rn(rc, kMagic))), fabsf(__fsub_rn(td, __fsub_rn(rd, kMagic))))));
   return pack4_s8(ra, rb, rc, rd);
 }
+
+constexpr float kTieGuard = 0.5f - 2.44140625e-4f;   // within 2^-12 of a tie the exact quotient decides
 
 // second pass over the row held in shared memory: quantize and store
 template <typename T, bool CLAMP>
 __device__ __forceinline__ void quantize_row(const uint4* src, int8_t* qrow, int nvec, int nthr, int tid, float s, float y) {
-#pragma unroll 2
+#pragma unroll 4
   for (int v = tid; v < nvec; v += nthr) {
     const uint4 raw = src[v];
+    float dist = 0.f;
     if constexpr (sizeof(T) == 2) {
       using P = Packed<T>;
       const typename P::V2* h = reinterpret_cast<const typename P::V2*>(&raw);
-      const uint32_t w0 = quant4<CLAMP>(P::lo(h[0]), P::hi(h[0]), P::lo(h[1]), P::hi(h[1]), s, y);
-      const uint32_t w1 = quant4<CLAMP>(P::lo(h[2]), P::hi(h[2]), P::lo(h[3]), P::hi(h[3]), s, y);
+      const float f0 = P::lo(h[0]), f1 = P::hi(h[0]), f2 = P::lo(h[1]), f3 = P::hi(h[1]);
+      const float f4 = P::lo(h[2]), f5 = P::hi(h[2]), f6 = P::lo(h[3]), f7 = P::hi(h[3]);
+      uint32_t w0 = quant4_fast<CLAMP>(f0, f1, f2, f3, y, dist);
+      uint32_t w1 = quant4_fast<CLAMP>(f4, f5, f6, f7, y, dist);
+      if (dist > kTieGuard) { w0 = quant4_exact(f0, f1, f2, f3, s); w1 = quant4_exact(f4, f5, f6, f7, s); }
       *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(w0, w1);
     } else {
       const float* f = reinterpret_cast<const float*>(&raw);
-      *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = quant4<CLAMP>(f[0], f[1], f[2], f[3], s, y);
+      uint32_t w0 = quant4_fast<CLAMP>(f[0], f[1], f[2], f[3], y, dist);
+      if (dist > kTieGuard) w0 = quant4_exact(f[0], f[1], f[2], f[3], s);
+      *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = w0;
     }
   }
 }
@@ -159,8 +166,9 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
     float mn = INFINITY, mx = -INFINITY;
     if constexpr (sizeof(T) == 2) {
       using P = Packed<T>;
-      typename P::V2 vmx, vmn;
-      bool first = true;
+      // every thread owns at least one vector (nvec >= blockDim.x is a launch condition)
+      typename P::V2 vmx = reinterpret_cast<const typename P::V2*>(src + tid)[0], vmn = vmx;
+      if (p.smooth) vmx = vmn = P::mul(vmx, reinterpret_cast<const typename P::V2*>(reinterpret_cast<const uint4*>(smooth_s) + tid)[0]);
 #pragma unroll 4
       for (int v = tid; v < nvec; v += nthr) {
         uint4 raw = src[v];
@@ -174,15 +182,13 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
         }
         typename P::V2 a = P::vmax(P::vmax(h[0], h[1]), P::vmax(h[2], h[3]));
         typename P::V2 b = P::vmin(P::vmin(h[0], h[1]), P::vmin(h[2], h[3]));
-        vmx = first ? a : P::vmax(vmx, a);
-        vmn = first ? b : P::vmin(vmn, b);
-        first = false;
+        vmx = P::vmax(vmx, a);
+        vmn = P::vmin(vmn, b);
       }
-      if (!first) {
-        mx = max_nan(P::lo(vmx), P::hi(vmx));
-        mn = min_nan(P::lo(vmn), P::hi(vmn));
-      }
+      mx = max_nan(P::lo(vmx), P::hi(vmx));
+      mn = min_nan(P::lo(vmn), P::hi(vmn));
     } else {
+      float poison = 0.f;
 #pragma unroll 4
       for (int v = tid; v < nvec; v += nthr) {
         uint4 raw = src[v];
@@ -192,9 +198,12 @@ __global__ void __launch_bounds__(512) quant_token_kernel(TokenParams p) {
           f[0] = __fmul_rn(f[0], sv.x); f[1] = __fmul_rn(f[1], sv.y); f[2] = __fmul_rn(f[2], sv.z); f[3] = __fmul_rn(f[3], sv.w);
           src[v] = raw;
         }
-        mx = max_nan(mx, max_nan(max_nan(f[0], f[1]), max_nan(f[2], f[3])));
-        mn = min_nan(mn, min_nan(min_nan(f[0], f[1]), min_nan(f[2], f[3])));
+        mx = fmaxf(mx, fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])));
+        mn = fminf(mn, fminf(fminf(f[0], f[1]), fminf(f[2], f[3])));
+        // fmaxf / fminf drop NaN: x * 0 is NaN exactly for NaN and Inf inputs, and accumulates
+        poison = __fmaf_rn(f[0], 0.f, __fmaf_rn(f[1], 0.f, __fmaf_rn(f[2], 0.f, __fmaf_rn(f[3], 0.f, poison))));
       }
+      if (poison != poison) mx = NAN;
     }
     // a NaN anywhere in the row becomes max = +inf: the scale is then infinite and the row is flagged
     if (mx != mx || mn != mn) { mx = INFINITY; mn = 0.f; }
