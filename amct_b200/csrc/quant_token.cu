@@ -95,7 +95,7 @@ constexpr float kTieGuard = 0.5f - 2.44140625e-4f;   // within 2^-12 of a tie th
 // second pass over the row held in shared memory: quantize and store
 template <typename T, bool CLAMP>
 __device__ __forceinline__ void quantize_row(const uint4* src, int8_t* qrow, int nvec, int nthr, int tid, float s, float y) {
-#pragma unroll 4
+#pragma unroll 2
   for (int v = tid; v < nvec; v += nthr) {
     const uint4 raw = src[v];
     float dist = 0.f;
