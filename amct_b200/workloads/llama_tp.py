@@ -168,14 +168,40 @@ class LlamaW8A8(nn.Module):
                                     for _ in range(n_layers if n_layers is not None else shape.n_layers))
 
     @torch.no_grad()
-    def forward(self, token_ids, kv_caches=None, past_len=0):
-        """token_ids [B, S] -> logits of the last position [B, vocab] (fp32)."""
+    def forward(self, token_ids, kv_caches=None, past_len=0, micro_batches=None):
+        """token_ids [B, S] -> logits of the last position [B, vocab] (fp32).
+
+        With tp > 1 the batch is cut into micro-batches that run on separate CUDA streams,
+        layer by layer: while one micro-batch waits for its all-reduce the other one's
+        kernels run, so the NVLink transfer overlaps the GEMMs."""
         b, s = token_ids.shape
-        x = F.embedding(token_ids, self.embed)
+        if micro_batches is None:
+            micro_batches = 2 if (self.tp > 1 and kv_caches is None and b >= 2) else 1
         pos = torch.arange(past_len, past_len + s, device=token_ids.device)
         cos, sin = rotary_tables(self.shape, pos, token_ids.device)
-        for i, layer in enumerate(self.layers):
-            x = layer(x, cos, sin, None if kv_caches is None else kv_caches[i])
+        if micro_batches == 1:
+            x = F.embedding(token_ids, self.embed)
+            for i, layer in enumerate(self.layers):
+                x = layer(x, cos, sin, None if kv_caches is None else kv_caches[i])
+        else:
+            main = torch.cuda.current_stream()
+            if getattr(self, '_streams', None) is None or len(self._streams) != micro_batches:
+                self._streams = [torch.cuda.Stream(device=token_ids.device) for _ in range(micro_batches)]
+            parts = list(token_ids.chunk(micro_batches, dim=0))
+            xs = [None] * len(parts)
+            for st in self._streams:
+                st.wait_stream(main)
+            for j, ids in enumerate(parts):
+                with torch.cuda.stream(self._streams[j]):
+                    xs[j] = F.embedding(ids, self.embed)
+            for layer in self.layers:
+                for j in range(len(parts)):
+                    with torch.cuda.stream(self._streams[j]):
+                        xs[j] = layer(xs[j], cos, sin, None)
+            for j, st in enumerate(self._streams[:len(parts)]):
+                main.wait_stream(st)
+                xs[j].record_stream(main)
+            x = torch.cat([t[:, -1:] for t in xs], dim=0)
         x = F.rms_norm(x[:, -1], (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
         return (x @ self.lm_head.t()).float()
 

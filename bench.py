@@ -63,6 +63,8 @@ def measured_peaks():
 
 # ----------------------------------------------------------------------------- CPU arm
 def cpu_linear_path(tokens, threads=None):
+    # a launcher may have pinned OMP_NUM_THREADS=1: use every core this process may run on
+    threads = threads or len(os.sched_getaffinity(0))
     """Times the CPU oracle of one decoder layer's four quantized Linears (TP=1 shapes)
     over `tokens` rows: dynamic per-token quantization + INT32 GEMM + dequant epilogue."""
     from oracle import intq, npu_ops
