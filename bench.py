@@ -49,6 +49,7 @@ def parse():
     ap.add_argument('--seq', type=int, default=SEQ)
     ap.add_argument('--cpu-sample-tokens', type=int, default=4096)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (2 streams when N > 1)')
     return ap.parse_args()
 
 
@@ -63,10 +64,10 @@ def measured_peaks():
 
 # ----------------------------------------------------------------------------- CPU arm
 def cpu_linear_path(tokens, threads=None):
-    # a launcher may have pinned OMP_NUM_THREADS=1: use every core this process may run on
-    threads = threads or len(os.sched_getaffinity(0))
     """Times the CPU oracle of one decoder layer's four quantized Linears (TP=1 shapes)
     over `tokens` rows: dynamic per-token quantization + INT32 GEMM + dequant epilogue."""
+    # a launcher may have pinned OMP_NUM_THREADS=1: use every core this process may run on
+    threads = threads or len(os.sched_getaffinity(0))
     from oracle import intq, npu_ops
     from amct_b200.workloads.llama_tp import LLAMA3_70B as sh
     if threads:
@@ -212,12 +213,14 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    mb = args.micro_batches or None
+
     def step_resident():
-        return model(ids_dev)
+        return model(ids_dev, micro_batches=mb)
 
     def step_e2e():
         ids = ids_host.to(dev, non_blocking=True)
-        logits_host.copy_(model(ids), non_blocking=True)
+        logits_host.copy_(model(ids, micro_batches=mb), non_blocking=True)
 
     for _ in range(args.warmup):
         step_resident()
