@@ -29,9 +29,11 @@
 
 namespace amct {
 
-constexpr int kBM = 128, kBN = 256, kBKBytes = 128, kStages = 4;
-constexpr int kABytes = kBM * kBKBytes, kBBytes = kBN * kBKBytes, kStageBytes = kABytes + kBBytes;
-constexpr int kTmemCols = 512;
+constexpr int kBM = 128, kBKBytes = 128;
+constexpr int kABytes = kBM * kBKBytes;
+// two tile shapes: 128 x 256 with a 4-stage ring (large M), and 128 x 64 with an 8-stage ring for
+// M <= 128, where the job is to stream the weight once: more, smaller tiles keep every SM loading
+constexpr int kBNLarge = 256, kStagesLarge = 4, kBNSmall = 64, kStagesSmall = 8;
 constexpr int kGroupM = 16;                      // rasterisation: 16 m-tiles x all n-tiles per group
 constexpr int kThreads = 192;
 
@@ -53,11 +55,12 @@ struct GemmParams {
   int act;                     // 0 none, 1 SwiGLU over interleaved [128 gate | 128 up] column blocks
 };
 
+template <int BN, int STAGES>
 struct __align__(1024) GemmSmem {
-  uint8_t tiles[kStages][kStageBytes];
-  float epi_scale[4][kBN];
-  float epi_bias[4][kBN];
-  uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
+  uint8_t tiles[STAGES][kABytes + BN * kBKBytes];
+  float epi_scale[4][BN];
+  float epi_bias[4][BN];
+  uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -89,10 +92,14 @@ __device__ __forceinline__ float epi_token(int acc, float deq, float pt, bool ha
   return v;
 }
 
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
+  constexpr int kBN = BN, kStages = STAGES, kStageBytes = kABytes + BN * kBKBytes;
+  constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; a power of two >= 32
+  using Smem = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
-  GemmSmem& s = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const int esize = p.kind == KIND_I8 ? 1 : 2;
@@ -368,18 +375,31 @@ static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b,
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, esize, p.m, p.k, ld_a, kBM);
   if (rc != AMCT_OK) return rc;
-  rc = make_map(&mb, b, esize, p.n, p.k, ld_b, kBN);
+  rc = make_map(&mb, b, esize, p.n, p.k, ld_b, (p.m <= 128 && p.act == 0) ? kBNSmall : kBNLarge);
   if (rc != AMCT_OK) return rc;
-  const size_t smem = sizeof(GemmSmem) + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return AMCT_ERR_CUDA;
-    attr_set = true;
-  }
-  const int64_t tiles = ((p.m + kBM - 1) / kBM) * ((p.n + kBN - 1) / kBN);
+  const bool small = p.m <= 128 && p.act == 0;
+  const int bn = small ? kBNSmall : kBNLarge;
+  const int64_t tiles = ((p.m + kBM - 1) / kBM) * ((p.n + bn - 1) / bn);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_tcgen05_kernel<<<grid, kThreads, smem, st>>>(ma, mb, p);
+  if (small) {
+    const size_t smem = sizeof(GemmSmem<kBNSmall, kStagesSmall>) + 1024;
+    static bool attr_small = false;
+    if (!attr_small) {
+      if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNSmall, kStagesSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return AMCT_ERR_CUDA;
+      attr_small = true;
+    }
+    gemm_tcgen05_kernel<kBNSmall, kStagesSmall><<<grid, kThreads, smem, st>>>(ma, mb, p);
+  } else {
+    const size_t smem = sizeof(GemmSmem<kBNLarge, kStagesLarge>) + 1024;
+    static bool attr_large = false;
+    if (!attr_large) {
+      if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNLarge, kStagesLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return AMCT_ERR_CUDA;
+      attr_large = true;
+    }
+    gemm_tcgen05_kernel<kBNLarge, kStagesLarge><<<grid, kThreads, smem, st>>>(ma, mb, p);
+  }
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -407,7 +427,7 @@ extern "C" int amct_gemm_w8a8_swiglu(const int8_t* a, const int8_t* b, int64_t m
                                      int bias_kind, void* out, int64_t ld_out, int* status, void* stream) {
   if (m < 0 || n < 0 || k < 0 || ld_a < k || ld_b < k || ld_out < n / 2) return AMCT_ERR_ARG;
   if (m && n && (!a || !b || !out || !deq_scale)) return AMCT_ERR_ARG;
-  if (n % amct::kBN != 0) return AMCT_ERR_UNSUPPORTED;                 // whole [128 gate | 128 up] blocks only
+  if (n % amct::kBNLarge != 0) return AMCT_ERR_UNSUPPORTED;                 // whole [128 gate | 128 up] blocks only
   if (bias_kind == amct::BIAS_I32 || bias_kind < amct::BIAS_NONE || bias_kind > amct::BIAS_BF16 || (bias_kind && !bias))
     return AMCT_ERR_ARG;
   if (!amct::aligned16(out) || (ld_out * 2) % 16 != 0) return AMCT_ERR_ALIGN;
