@@ -123,8 +123,8 @@ class DecoderLayer(nn.Module):
         return t
 
     def forward(self, x, cos, sin, kv_cache=None):
-        """x [B, S, hidden] bf16.  kv_cache: None (prefill, causal) or (k, v) [B, kvh, T, D]
-        holding the past keys/values (decode: S new tokens attend to T + S)."""
+        """x [B, S, hidden] bf16.  kv_cache: None (prefill, causal) or (k, v, past) with k, v
+        [B, kvh, >= past + S, D] holding `past` keys/values (decode: S new tokens attend to past + S)."""
         shp, lin = self.shape, self.linears
         b, s, _ = x.shape
         hn = F.rms_norm(x, (shp.hidden,), self.input_norm, shp.rms_eps)
@@ -134,9 +134,12 @@ class DecoderLayer(nn.Module):
         k = apply_rotary(k.reshape(b, s, self.kv_heads, shp.head_dim), cos, sin).transpose(1, 2)
         v = v.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
         if kv_cache is not None:
-            k = torch.cat((kv_cache[0], k), dim=2)
-            v = torch.cat((kv_cache[1], v), dim=2)
-            attn = F.scaled_dot_product_attention(q, k, v, is_causal=False, enable_gqa=True)
+            # kv_cache = (k, v, past): buffers [B, kvh, past + S, D] whose first `past` positions are filled;
+            # the new keys / values are written in place behind them
+            kc, vc, past = kv_cache
+            kc[:, :, past:past + s].copy_(k)
+            vc[:, :, past:past + s].copy_(v)
+            attn = F.scaled_dot_product_attention(q, kc[:, :, :past + s], vc[:, :, :past + s], is_causal=False, enable_gqa=True)
         else:
             attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b, s, self.heads * shp.head_dim)

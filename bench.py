@@ -51,6 +51,7 @@ def parse():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mode', default='prefill', choices=['prefill', 'decode'],
                     help='decode: one new token for 64 sequences against a 2048-token KV cache (not the headline metric)')
+    ap.add_argument('--no-cuda-graph', action='store_true')
     ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (2 streams when N > 1)')
     return ap.parse_args()
 
@@ -197,8 +198,9 @@ def main():
         args.batch, args.seq, past = 64, 1, 2048
         sh = LLAMA3_70B
         dgen = torch.Generator(device=dev).manual_seed(SEED + 1)
-        kv_caches = [tuple(torch.randn(args.batch, sh.n_kv_heads // world, past, sh.head_dim, device=dev, dtype=torch.bfloat16,
-                                       generator=dgen) for _ in range(2)) for _ in range(args.layers)]
+        kv_caches = [(torch.randn(args.batch, sh.n_kv_heads // world, past + 1, sh.head_dim, device=dev, dtype=torch.bfloat16, generator=dgen),
+                      torch.randn(args.batch, sh.n_kv_heads // world, past + 1, sh.head_dim, device=dev, dtype=torch.bfloat16, generator=dgen),
+                      past) for _ in range(args.layers)]
     ids_host = torch.randint(0, LLAMA3_70B.vocab, (args.batch, args.seq), generator=gen).pin_memory()
     ids_dev = ids_host.to(dev)
     logits_host = torch.empty((args.batch, LLAMA3_70B.vocab), dtype=torch.float32).pin_memory()
@@ -233,6 +235,25 @@ def main():
 
     for _ in range(args.warmup):
         step_resident()
+    graph = None
+    if args.mode == 'decode' and not args.no_cuda_graph:
+        # the decode step is launch-bound (hundreds of small kernels): replay it as one CUDA graph
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_logits = step_resident()
+        eager_resident = step_resident
+
+        def step_resident():
+            graph.replay()
+            return graph_logits
+
+        def step_e2e():
+            ids_dev.copy_(ids_host, non_blocking=True)
+            graph.replay()
+            logits_host.copy_(graph_logits, non_blocking=True)
+        for _ in range(2):
+            step_resident()
     sampler = ClockSampler(local) if rank == 0 else None
     ops.COUNTERS['launches'] = 0
     ms_total = timed(step_resident, args.steps)
@@ -242,7 +263,7 @@ def main():
 
     # roofline of the dominant kernel: one more step with CUDA events around every GEMM launch
     ops.GEMM_PROFILE = []
-    step_resident()
+    (eager_resident if graph is not None else step_resident)()
     torch.cuda.synchronize()
     gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in ops.GEMM_PROFILE)
     gemm_ops = sum(o for _, _, o in ops.GEMM_PROFILE)
