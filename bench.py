@@ -240,8 +240,10 @@ def main():
         # the decode step is launch-bound (hundreds of small kernels): replay it as one CUDA graph
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        ops.COUNTERS['launches'] = 0
         with torch.cuda.graph(graph):
             graph_logits = step_resident()
+        launches_per_replay = ops.COUNTERS['launches']
         eager_resident = step_resident
 
         def step_resident():
@@ -257,7 +259,7 @@ def main():
     sampler = ClockSampler(local) if rank == 0 else None
     ops.COUNTERS['launches'] = 0
     ms_total = timed(step_resident, args.steps)
-    launches = ops.COUNTERS['launches']
+    launches = ops.COUNTERS['launches'] if graph is None else launches_per_replay * args.steps
     clocks = sampler.stop() if sampler else None
     ms_e2e = timed(step_e2e, args.steps)
 
