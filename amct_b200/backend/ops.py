@@ -511,3 +511,58 @@ def gemm_w8a8_swiglu(q, w_nk, deq_scale, pertoken_scale=None, bias=None, out=Non
     COUNTERS['launches'] += 1
     _prof_end(prof, 2 * m * n * k)
     return out
+
+
+def addnorm_quant_per_token(x, gamma, eps, residual=None, want_norm=False, check=False):
+    """(x [+ residual]) -> RMSNorm -> dynamic per-token INT8 codes, one kernel.
+
+    Returns (q int8 like x, scale fp32 [rows], h, n): h = x + residual in x's dtype (None without
+    residual), n = the normalised values the codes were taken from (only with want_norm)."""
+    _need_cuda(x, gamma, residual)
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise _l.BackendError('addnorm_quant_per_token: float16 / bfloat16 only')
+    x2, rows, k, ld = _rows2d(x)
+    r2, ld_r = None, 0
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError('residual must match x in shape and dtype')
+        r2, _, _, ld_r = _rows2d(residual)
+    gamma = gamma.reshape(-1).to(x.dtype).contiguous()
+    if gamma.numel() != k:
+        raise ValueError('gamma must have K elements')
+    q = torch.empty((rows, k), dtype=torch.int8, device=x.device)
+    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
+    h = torch.empty((rows, k), dtype=x.dtype, device=x.device) if residual is not None else None
+    n = torch.empty((rows, k), dtype=x.dtype, device=x.device) if want_norm else None
+    st = Status(x.device) if check else None
+    rc = _l.load().amct_addnorm_quant_pertoken(
+        _p(x2), _p(r2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), c_int64(ld_r), _p(gamma),
+        ctypes.c_float(eps), _p(h), c_int64(k), _p(n), c_int64(k), _p(q), c_int64(k), _p(scale),
+        st.ptr() if st else c_void_p(0), _stream())
+    _l.check(rc, 'amct_addnorm_quant_pertoken')
+    COUNTERS['launches'] += 1
+    if st:
+        st.raise_if_set()
+    return (q.reshape(x.shape), scale, h.reshape(x.shape) if h is not None else None,
+            n.reshape(x.shape) if n is not None else None)
+
+
+def rope_inplace(x, heads, head_dim, cos, sin):
+    """Rotate-half rotary embedding in place on the first `heads` heads of x[..., ld]; cos / sin
+    [seq, head_dim / 2] in x's dtype, row t of the flattened x uses table row t % seq."""
+    _need_cuda(x, cos, sin)
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise _l.BackendError('rope_inplace: float16 / bfloat16 only')
+    ld = x.shape[-1]
+    if not x.is_contiguous():
+        raise ValueError('rope_inplace needs a contiguous tensor (it works in place)')
+    cos = cos.to(x.dtype).contiguous()
+    sin = sin.to(x.dtype).contiguous()
+    if cos.shape != sin.shape or cos.shape[-1] != head_dim // 2:
+        raise ValueError('cos / sin must be [seq, head_dim / 2]')
+    tokens = x.numel() // ld
+    rc = _l.load().amct_rope_inplace(_p(x), c_int(_dt(x)), c_int64(tokens), c_int64(ld), c_int(heads), c_int(head_dim),
+                                     _p(cos), _p(sin), c_int64(cos.shape[0]), _stream())
+    _l.check(rc, 'amct_rope_inplace')
+    COUNTERS['launches'] += 1
+    return x

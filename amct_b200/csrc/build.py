@@ -17,7 +17,8 @@ LIB_PATH = os.path.join(LIB_DIR, 'libamct_b200.so')
 INCLUDE = os.path.join(os.path.dirname(os.path.dirname(HERE)), 'include')
 
 # numerics-critical files: no FMA contraction so that x*s+z rounds twice like torch
-STRICT = {'quant_rows.cu', 'quant_token.cu', 'quant_static.cu', 'reduce.cu', 'mx_quant.cu', 'hif8.cu'}
+STRICT = {'quant_rows.cu', 'quant_token.cu', 'quant_static.cu', 'reduce.cu', 'mx_quant.cu', 'hif8.cu', 'norm_quant.cu',
+          'rope.cu'}
 
 
 def sources():

@@ -1,0 +1,236 @@
+// Residual add + RMSNorm + dynamic per-token symmetric INT8 quantization in one pass.
+//
+// The decoder-layer sequence  h = x + residual;  n = rms_norm(h) * gamma;  q, scale = quant(n)
+// reads and writes the hidden state three times when it runs as three kernels.  Here one CTA
+// keeps a token row in registers from the add to the codes: x and the residual are read once,
+// the new residual and the codes are written once.
+//
+// The quantizer is the dynamic per-token rule of the deploy Linear (row amax / amin as in
+// amct_pytorch/quantize_op/minmax_module.py:99-105, scale rule of
+// amct_pytorch/quantize_op/utils.py:75-108, codes of amct_pytorch/utils/quant_util.py:57-73)
+// applied to the normalised values after they have been rounded to the tensor dtype, i.e. the
+// codes are those the separate quant kernel produces from `norm_out`.  The add rounds once to
+// the tensor dtype like a torch add.  The norm is evaluated in fp32:
+// rstd = rn(1 / sqrt(mean(h^2) + eps)), n = round_T((h * rstd) * gamma); the order of the fp32
+// sum of squares is this kernel's own (torch's differs), so n may differ from torch's
+// rms_norm by one unit in the last place of T on a few elements.
+//
+// Algorithmic HBM traffic per row: 2 K sizeof(T) read (K sizeof(T) without residual),
+// K sizeof(T) + K + 4 written (K + 4 without residual output).
+#include "common.cuh"
+
+namespace amct {
+
+constexpr float kMagicNQ = 12582912.0f;                  // 1.5 * 2^23
+constexpr float kTieGuardNQ = 0.5f - 2.44140625e-4f;     // within 2^-12 of a tie the IEEE quotient decides
+
+struct NormQuantParams {
+  const void* x;
+  const void* residual;       // nullable
+  const void* gamma;          // [k]
+  void* residual_out;         // nullable
+  void* norm_out;             // nullable
+  int8_t* q;
+  float* scale;
+  int* status;
+  int64_t rows, k, ld_x, ld_res, ld_res_out, ld_norm, ld_q;
+  float eps;
+};
+
+__device__ __forceinline__ uint32_t nq_pack4(float ra, float rb, float rc, float rd) {
+  const uint32_t w01 = __byte_perm(__float_as_uint(ra), __float_as_uint(rb), 0x0040);
+  const uint32_t w23 = __byte_perm(__float_as_uint(rc), __float_as_uint(rd), 0x0040);
+  return __byte_perm(w01, w23, 0x5410);
+}
+
+__device__ __noinline__ uint32_t nq_quant4_exact(float a, float b, float c, float d, float s) {
+  const float ra = __fadd_rn(fminf(__fdiv_rn(a, s), 127.f), kMagicNQ), rb = __fadd_rn(fminf(__fdiv_rn(b, s), 127.f), kMagicNQ);
+  const float rc = __fadd_rn(fminf(__fdiv_rn(c, s), 127.f), kMagicNQ), rd = __fadd_rn(fminf(__fdiv_rn(d, s), 127.f), kMagicNQ);
+  return nq_pack4(ra, rb, rc, rd);
+}
+
+// x * rn(1/s) rounded with the magic add; `dist` collects the largest distance from the chosen integer
+__device__ __forceinline__ uint32_t nq_quant4_fast(float a, float b, float c, float d, float y, float& dist) {
+  const float ta = fminf(__fmul_rn(a, y), 127.f), tb = fminf(__fmul_rn(b, y), 127.f);
+  const float tc = fminf(__fmul_rn(c, y), 127.f), td = fminf(__fmul_rn(d, y), 127.f);
+  const float ra = __fadd_rn(ta, kMagicNQ), rb = __fadd_rn(tb, kMagicNQ), rc = __fadd_rn(tc, kMagicNQ), rd = __fadd_rn(td, kMagicNQ);
+  dist = fmaxf(dist, fmaxf(fmaxf(fabsf(__fsub_rn(ta, __fsub_rn(ra, kMagicNQ))), fabsf(__fsub_rn(tb, __fsub_rn(rb, kMagicNQ)))),
+                           fmaxf(fabsf(__fsub_rn(tc, __fsub_rn(rc, kMagicNQ))), fabsf(__fsub_rn(td, __fsub_rn(rd, kMagicNQ))))));
+  return nq_pack4(ra, rb, rc, rd);
+}
+
+// block-wide sum; the caller alternates `part` between rows so one barrier per reduction is enough
+template <int NW>
+__device__ __forceinline__ float block_sum(float v, float* part, int warp, int lane) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if (lane == 0) part[warp] = v;
+  __syncthreads();
+  float t = part[0];
+#pragma unroll
+  for (int w = 1; w < NW; ++w) t = __fadd_rn(t, part[w]);
+  return t;
+}
+
+// 16-bit T only; NV 16-byte vectors (8 elements each) per thread, NT threads per row.
+template <typename T, int NV, int NT>
+__global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
+  constexpr int E = 8;
+  constexpr int NW = NT / 32;
+  __shared__ float part_sum[2][NW];
+  __shared__ float part_mx[2][NW], part_mn[2][NW];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nvec = (int)(p.k / E);
+  const T* gamma = reinterpret_cast<const T*>(p.gamma);
+  int it = 0;
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, it ^= 1) {
+    const T* xr = reinterpret_cast<const T*>(p.x) + row * p.ld_x;
+    Vec16<T> h[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = tid + j * NT;
+      if (v < nvec) h[j] = ld_vec_stream(xr + v * E);
+    }
+    if (p.residual) {
+      const T* rr = reinterpret_cast<const T*>(p.residual) + row * p.ld_res;
+      Vec16<T> r[NV];
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int v = tid + j * NT;
+        if (v < nvec) r[j] = ld_vec_stream(rr + v * E);
+      }
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int v = tid + j * NT;
+        if (v < nvec) {
+#pragma unroll
+          for (int e = 0; e < E; ++e)
+            h[j].v[e] = ElemTraits<T>::from_f(__fadd_rn(ElemTraits<T>::to_f(h[j].v[e]), ElemTraits<T>::to_f(r[j].v[e])));
+          if (p.residual_out)
+            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.residual_out) + row * p.ld_res_out + v * E) =
+                *reinterpret_cast<const uint4*>(&h[j]);
+        }
+      }
+    }
+    // ---- mean of squares (fp32)
+    float ssq = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (tid + j * NT < nvec) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float f = ElemTraits<T>::to_f(h[j].v[e]);
+          ssq = __fmaf_rn(f, f, ssq);
+        }
+      }
+    }
+    const float total = block_sum<NW>(ssq, part_sum[it], warp, lane);
+    const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)p.k), p.eps));
+    // ---- normalise, round to T, min / max
+    float mx = -INFINITY, mn = INFINITY;
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = tid + j * NT;
+      if (v < nvec) {
+        const Vec16<T> g = ld_vec(gamma + v * E);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const T n = ElemTraits<T>::from_f(__fmul_rn(__fmul_rn(ElemTraits<T>::to_f(h[j].v[e]), rstd), ElemTraits<T>::to_f(g.v[e])));
+          h[j].v[e] = n;
+          const float f = ElemTraits<T>::to_f(n);
+          mx = fmaxf(mx, f);
+          mn = fminf(mn, f);
+          bad |= (f != f);
+        }
+        if (p.norm_out)
+          *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.norm_out) + row * p.ld_norm + v * E) = *reinterpret_cast<const uint4*>(&h[j]);
+      }
+    }
+    if (bad) { mx = INFINITY; mn = 0.f; }           // a NaN in the row: infinite scale, row flagged
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    }
+    if (lane == 0) { part_mx[it][warp] = mx; part_mn[it][warp] = mn; }
+    __syncthreads();
+    mx = part_mx[it][0]; mn = part_mn[it][0];
+#pragma unroll
+    for (int w = 1; w < NW; ++w) { mx = fmaxf(mx, part_mx[it][w]); mn = fminf(mn, part_mn[it][w]); }
+    // symmetric INT8 rule: divisor 127, or 128 when the largest magnitude is negative
+    const float amx = fabsf(mx), amn = fabsf(mn);
+    const bool neg_dom = amx < amn;
+    float s = __fdiv_rn(neg_dom ? amn : amx, neg_dom ? 128.f : 127.f);
+    if (s < AMCT_FLT_EPSILON) s = 1.f;
+    if (tid == 0) {
+      p.scale[row] = s;
+      if (!isfinite(s) && p.status) atomicOr(p.status, 1);
+    }
+    const float y = __frcp_rn(s);
+    int8_t* qrow = p.q + row * p.ld_q;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = tid + j * NT;
+      if (v < nvec) {
+        float f[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) f[e] = ElemTraits<T>::to_f(h[j].v[e]);
+        float dist = 0.f;
+        uint32_t w0 = nq_quant4_fast(f[0], f[1], f[2], f[3], y, dist);
+        uint32_t w1 = nq_quant4_fast(f[4], f[5], f[6], f[7], y, dist);
+        if (dist > kTieGuardNQ) { w0 = nq_quant4_exact(f[0], f[1], f[2], f[3], s); w1 = nq_quant4_exact(f[4], f[5], f[6], f[7], s); }
+        *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(w0, w1);
+      }
+    }
+  }
+}
+
+template <typename T>
+static int launch_norm_quant(const NormQuantParams& p, cudaStream_t st) {
+  const int64_t nvec = p.k / 8;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // two vectors per thread keep the row within 64 registers, so 1024 threads stay resident per SM
+  int64_t grid = (int64_t)sms * 8;
+  if (grid > p.rows) grid = p.rows;
+  const unsigned g = (unsigned)grid;
+  if (nvec <= 128) addnorm_quant_kernel<T, 1, 128><<<g, 128, 0, st>>>(p);
+  else if (nvec <= 256) addnorm_quant_kernel<T, 1, 256><<<g, 256, 0, st>>>(p);
+  else if (nvec <= 512) addnorm_quant_kernel<T, 2, 256><<<g, 256, 0, st>>>(p);
+  else if (nvec <= 1024) addnorm_quant_kernel<T, 2, 512><<<g, 512, 0, st>>>(p);
+  else if (nvec <= 2048) addnorm_quant_kernel<T, 4, 512><<<g, 512, 0, st>>>(p);
+  else return AMCT_ERR_UNSUPPORTED;
+  AMCT_CHECK_LAUNCH();
+  return AMCT_OK;
+}
+
+}  // namespace amct
+
+extern "C" int amct_addnorm_quant_pertoken(const void* x, const void* residual, int dtype, int64_t rows, int64_t k,
+                                           int64_t ld_x, int64_t ld_res, const void* gamma, float eps,
+                                           void* residual_out, int64_t ld_res_out, void* norm_out, int64_t ld_norm,
+                                           int8_t* q, int64_t ld_q, float* scale, int* status, void* stream) {
+  if (rows < 0 || k <= 0 || !gamma) return AMCT_ERR_ARG;
+  if (rows == 0) return AMCT_OK;
+  if (!x || !q || !scale) return AMCT_ERR_ARG;
+  if (dtype != AMCT_DTYPE_F16 && dtype != AMCT_DTYPE_BF16) return AMCT_ERR_UNSUPPORTED;
+  if (k % 8 || k > 2048 * 8) return AMCT_ERR_UNSUPPORTED;
+  if (ld_x < k || ld_q < k || (residual && ld_res < k) || (residual_out && ld_res_out < k) || (norm_out && ld_norm < k))
+    return AMCT_ERR_ARG;
+  if (residual_out && !residual) return AMCT_ERR_ARG;
+  auto ok16 = [](const void* ptr, int64_t ld_elems) { return amct::aligned16(ptr) && (ld_elems * 2) % 16 == 0; };
+  if (!ok16(x, ld_x) || !amct::aligned16(gamma) || (residual && !ok16(residual, ld_res)) ||
+      (residual_out && !ok16(residual_out, ld_res_out)) || (norm_out && !ok16(norm_out, ld_norm)) ||
+      reinterpret_cast<uintptr_t>(q) % 8 || ld_q % 8)
+    return AMCT_ERR_ALIGN;
+  amct::NormQuantParams p{};
+  p.x = x; p.residual = residual; p.gamma = gamma; p.residual_out = residual_out; p.norm_out = norm_out;
+  p.q = q; p.scale = scale; p.status = status;
+  p.rows = rows; p.k = k; p.ld_x = ld_x; p.ld_res = ld_res; p.ld_res_out = ld_res_out; p.ld_norm = ld_norm; p.ld_q = ld_q;
+  p.eps = eps;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == AMCT_DTYPE_F16) return amct::launch_norm_quant<__half>(p, st);
+  return amct::launch_norm_quant<__nv_bfloat16>(p, st);
+}

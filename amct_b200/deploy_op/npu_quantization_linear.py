@@ -109,11 +109,25 @@ class NpuQuantizationLinear(torch.nn.Module):
             pertoken = self.pertoken_scale
             if pertoken is not None and x.dim() > 2:
                 pertoken = pertoken.repeat(x.numel() // (x.shape[-2] * k))
+        return self._gemm(q, pertoken)
+
+    def _gemm(self, q, pertoken):
+        k = q.shape[-1]
+        wq_nk = self.quantized_weight.t()
         if self.fused_act == 'swiglu':
             out = ops.gemm_w8a8_swiglu(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias)
-            return out.reshape(*x.shape[:-1], -1)
+            return out.reshape(*q.shape[:-1], -1)
         out = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out_dtype=self.output_dtype)
-        return out.reshape(*x.shape[:-1], -1)
+        return out.reshape(*q.shape[:-1], -1)
+
+    @torch.no_grad()
+    def forward_quantized(self, q, pertoken_scale):
+        """The GEMM half of forward() for an input some producer kernel has already quantized with
+        the dynamic per-token rule (q int8 [..., K], pertoken_scale fp32 [rows]); not in the
+        reference.  Only for modules with dynamic activation scales and no SmoothQuant factor."""
+        if not self.dynamic_act or getattr(self, 'scale_factor', None) is not None:
+            raise RuntimeError('forward_quantized needs dynamic per-token activation scales and no smooth factor')
+        return self._gemm(q, pertoken_scale)
 
 
 def interleave_gate_up(w_gate, w_up, block=128):

@@ -4,8 +4,11 @@ tensor-parallel (column / row) over the ranks of one node.
 This is the sharded deploy workload: every Linear goes through
 amct_b200.quantize() / convert() with dynamic per-token activation quantization,
 i.e. NpuQuantizationLinear.forward = one activation-quant kernel + one tcgen05
-INT8 GEMM with the dequant epilogue.  Everything that is not a Linear (RMSNorm,
-rotary embedding, attention, SwiGLU gating, embedding, lm_head) is plain torch.
+INT8 GEMM with the dequant epilogue.  With ``fused_glue`` (the default) the residual
+add, the RMSNorm and the activation quantization in front of the qkv and gate/up
+projections are one kernel (ops.addnorm_quant_per_token), the rotary embedding is one
+in-place kernel on the qkv output, and SwiGLU runs in the gate/up GEMM's epilogue;
+attention, embedding and lm_head are plain torch.
 
 Sharding (the reference has none; amct_pytorch/deploy_op/npu_quantization_linear.py
 is the unit being sharded):
@@ -25,6 +28,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 import amct_b200 as amct
+from amct_b200.backend import ops
 
 W8A8_DYNAMIC_CFG = {
     'batch_num': 1,
@@ -102,9 +106,10 @@ def apply_rotary(x, cos, sin):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, shape, tp, group, device, gen, fused_swiglu=True):
+    def __init__(self, shape, tp, group, device, gen, fused_swiglu=True, fused_glue=True):
         super().__init__()
         self.shape, self.tp, self.group = shape, tp, group
+        self.fused_glue = fused_glue
         self.heads = shape.n_heads // tp
         self.kv_heads = shape.n_kv_heads // tp
         self.linears = _Shard(shape, tp, device, gen)
@@ -122,16 +127,29 @@ class DecoderLayer(nn.Module):
             torch.distributed.all_reduce(t, group=self.group)
         return t
 
-    def forward(self, x, cos, sin, kv_cache=None):
-        """x [B, S, hidden] bf16.  kv_cache: None (prefill, causal) or (k, v, past) with k, v
-        [B, kvh, >= past + S, D] holding `past` keys/values (decode: S new tokens attend to past + S)."""
+    def forward(self, x, cos, sin, kv_cache=None, branch=None):
+        """x [B, S, hidden] bf16 (the residual stream).  kv_cache: None (prefill, causal) or (k, v, past)
+        with k, v [B, kvh, >= past + S, D] holding `past` keys/values (decode: S new tokens attend to
+        past + S).  With fused_glue the layer returns (x, branch): the residual stream BEFORE the MLP
+        output `branch` is added -- the next layer's first kernel does that add."""
         shp, lin = self.shape, self.linears
         b, s, _ = x.shape
-        hn = F.rms_norm(x, (shp.hidden,), self.input_norm, shp.rms_eps)
-        qkv = lin.qkv_proj(hn)
-        q, k, v = qkv.split((self.heads * shp.head_dim, self.kv_heads * shp.head_dim, self.kv_heads * shp.head_dim), dim=-1)
-        q = apply_rotary(q.reshape(b, s, self.heads, shp.head_dim), cos, sin).transpose(1, 2)
-        k = apply_rotary(k.reshape(b, s, self.kv_heads, shp.head_dim), cos, sin).transpose(1, 2)
+        if self.fused_glue:
+            q8, ps, h, _ = ops.addnorm_quant_per_token(x if branch is None else branch, self.input_norm, shp.rms_eps,
+                                                       residual=None if branch is None else x)
+            if h is not None:
+                x = h
+            qkv = lin.qkv_proj.forward_quantized(q8, ps)
+            ops.rope_inplace(qkv, self.heads + self.kv_heads, shp.head_dim, cos, sin)
+            q, k, v = qkv.split((self.heads * shp.head_dim, self.kv_heads * shp.head_dim, self.kv_heads * shp.head_dim), dim=-1)
+            q = q.reshape(b, s, self.heads, shp.head_dim).transpose(1, 2)
+            k = k.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
+        else:
+            hn = F.rms_norm(x, (shp.hidden,), self.input_norm, shp.rms_eps)
+            qkv = lin.qkv_proj(hn)
+            q, k, v = qkv.split((self.heads * shp.head_dim, self.kv_heads * shp.head_dim, self.kv_heads * shp.head_dim), dim=-1)
+            q = apply_rotary(q.reshape(b, s, self.heads, shp.head_dim), cos, sin).transpose(1, 2)
+            k = apply_rotary(k.reshape(b, s, self.kv_heads, shp.head_dim), cos, sin).transpose(1, 2)
         v = v.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
         if kv_cache is not None:
             # kv_cache = (k, v, past): buffers [B, kvh, past + S, D] whose first `past` positions are filled;
@@ -139,10 +157,25 @@ class DecoderLayer(nn.Module):
             kc, vc, past = kv_cache
             kc[:, :, past:past + s].copy_(k)
             vc[:, :, past:past + s].copy_(v)
-            attn = F.scaled_dot_product_attention(q, kc[:, :, :past + s], vc[:, :, :past + s], is_causal=False, enable_gqa=True)
+            if past == 0:
+                attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            elif s == 1:
+                attn = F.scaled_dot_product_attention(q, kc[:, :, :past + 1], vc[:, :, :past + 1], is_causal=False, enable_gqa=True)
+            else:
+                # new token i sees the cached positions and new tokens 0..i
+                mask = torch.ones(s, past + s, dtype=torch.bool, device=x.device).tril(diagonal=past)
+                attn = F.scaled_dot_product_attention(q, kc[:, :, :past + s], vc[:, :, :past + s], attn_mask=mask, enable_gqa=True)
         else:
             attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b, s, self.heads * shp.head_dim)
+        if self.fused_glue:
+            o = self._reduce(lin.o_proj(attn))
+            q8, ps, x, _ = ops.addnorm_quant_per_token(o, self.post_norm, shp.rms_eps, residual=x)
+            act = lin.gate_up_proj.forward_quantized(q8, ps)
+            if not self.fused_swiglu:
+                gate, up = act.chunk(2, dim=-1)
+                act = F.silu(gate) * up
+            return x, self._reduce(lin.down_proj(act))
         x = x + self._reduce(lin.o_proj(attn))
         hn = F.rms_norm(x, (shp.hidden,), self.post_norm, shp.rms_eps)
         if self.fused_swiglu:
@@ -157,7 +190,8 @@ class DecoderLayer(nn.Module):
 class LlamaW8A8(nn.Module):
     """Random-initialised Llama stack; rank `rank` of `tp` holds its shard of every layer."""
 
-    def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None, fused_swiglu=True):
+    def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None, fused_swiglu=True,
+                 fused_glue=True):
         super().__init__()
         if shape.n_kv_heads % tp or shape.n_heads % tp or shape.intermediate % tp:
             raise ValueError(f'tp={tp} does not divide the head / intermediate sizes')
@@ -167,7 +201,8 @@ class LlamaW8A8(nn.Module):
         self.embed = torch.empty(shape.vocab, shape.hidden, dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=shared)
         self.lm_head = torch.empty(shape.vocab, shape.hidden, dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=shared)
         self.final_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
-        self.layers = nn.ModuleList(DecoderLayer(shape, tp, group, device, gen, fused_swiglu)
+        self.fused_glue = fused_glue
+        self.layers = nn.ModuleList(DecoderLayer(shape, tp, group, device, gen, fused_swiglu, fused_glue)
                                     for _ in range(n_layers if n_layers is not None else shape.n_layers))
 
     @torch.no_grad()
@@ -183,9 +218,7 @@ class LlamaW8A8(nn.Module):
         pos = torch.arange(past_len, past_len + s, device=token_ids.device)
         cos, sin = rotary_tables(self.shape, pos, token_ids.device)
         if micro_batches == 1:
-            x = F.embedding(token_ids, self.embed)
-            for i, layer in enumerate(self.layers):
-                x = layer(x, cos, sin, None if kv_caches is None else kv_caches[i])
+            x = self._stack(F.embedding(token_ids, self.embed), cos, sin, kv_caches)
         else:
             main = torch.cuda.current_stream()
             if getattr(self, '_streams', None) is None or len(self._streams) != micro_batches:
@@ -197,16 +230,37 @@ class LlamaW8A8(nn.Module):
             for j, ids in enumerate(parts):
                 with torch.cuda.stream(self._streams[j]):
                     xs[j] = F.embedding(ids, self.embed)
+            branches = [None] * len(parts)
             for layer in self.layers:
                 for j in range(len(parts)):
                     with torch.cuda.stream(self._streams[j]):
-                        xs[j] = layer(xs[j], cos, sin, None)
+                        if self.fused_glue:
+                            xs[j], branches[j] = layer(xs[j], cos, sin, None, branches[j])
+                        else:
+                            xs[j] = layer(xs[j], cos, sin, None)
+            if self.fused_glue:
+                for j in range(len(parts)):
+                    with torch.cuda.stream(self._streams[j]):
+                        xs[j] = xs[j][:, -1:] + branches[j][:, -1:]
             for j, st in enumerate(self._streams[:len(parts)]):
                 main.wait_stream(st)
                 xs[j].record_stream(main)
             x = torch.cat([t[:, -1:] for t in xs], dim=0)
         x = F.rms_norm(x[:, -1], (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
         return (x @ self.lm_head.t()).float()
+
+    def _stack(self, x, cos, sin, kv_caches):
+        """All decoder layers on one stream; returns the final residual stream."""
+        branch = None
+        for i, layer in enumerate(self.layers):
+            cache = None if kv_caches is None else kv_caches[i]
+            if self.fused_glue:
+                x, branch = layer(x, cos, sin, cache, branch)
+            else:
+                x = layer(x, cos, sin, cache)
+        if branch is not None:
+            x = x[:, -1:] + branch[:, -1:]          # only the last position feeds the logits
+        return x
 
     def linear_ops_per_token(self):
         """2*K*N summed over the quantized Linears of all layers (whole model, all ranks)."""

@@ -86,6 +86,18 @@ def cases():
         es = 4 if dt == torch.float32 else 2
         yield (f'quant_dynamic_pertoken {tag} [{r}x{k}] {str(dt)[6:]}', lambda r=r, k=k, dt=dt: randn(r, k, dt),
                lambda x: (lambda: ops.quant_dynamic_per_token(x)), dict(nbytes=r * k * es + r * k + r * 4))
+    # ---- decoder-layer glue: add + RMSNorm + quant in one pass; rotary embedding in place
+    def setup_an():
+        return randn(65536, 8192, torch.bfloat16), randn(65536, 8192, torch.bfloat16), torch.ones(8192, device='cuda', dtype=torch.bfloat16)
+    yield ('addnorm_quant c5-h [65536x8192] bf16 (+residual)', setup_an,
+           lambda t: (lambda: ops.addnorm_quant_per_token(t[0], t[2], 1e-5, residual=t[1])),
+           dict(nbytes=65536 * 8192 * (2 + 2 + 2 + 1) + 65536 * 4))
+
+    def setup_rope():
+        ang = torch.rand(2048, 64, device='cuda') * 6.28
+        return randn(65536, 10240, torch.bfloat16), ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+    yield ('rope_inplace c5 qkv [65536x10240], 72 heads of 128, bf16', setup_rope,
+           lambda t: (lambda: ops.rope_inplace(t[0], 72, 128, t[1], t[2])), dict(nbytes=65536 * 72 * 128 * 2 * 2))
     # ---- static quantize
     yield ('quantize_static per-tensor [65536x8192] bf16', lambda: randn(65536, 8192, torch.bfloat16),
            lambda x: (lambda s=torch.tensor([30.0], device='cuda', dtype=torch.bfloat16): ops.quantize_static(x, s, None)),

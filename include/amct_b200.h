@@ -230,6 +230,27 @@ int amct_hif8_encode(const void* x, int dtype, int64_t n, void* codes, void* fak
 /* HiF8 codes uint8 [n] -> values in `dtype` (exact in fp16, bf16 and fp32). */
 int amct_hif8_decode(const void* codes, int64_t n, int dtype, void* out, void* stream);
 
+/* ---- Glue of the sharded deploy workload (no counterpart in the reference) ---- */
+
+/* h = x + residual (rounded to dtype; residual may be NULL: h = x); n = round(h * rstd * gamma) with
+ * rstd = 1 / sqrt(mean(h^2) + eps) in fp32; then the dynamic per-token symmetric INT8 rule of
+ * amct_quant_dynamic_pertoken (AMCT_RULE_RELEASED) applied to n: q int8 [rows, k], scale fp32 [rows].
+ * residual_out (NULL or [rows, k]) receives h, norm_out (NULL or [rows, k]) receives n.
+ * fp16 / bf16 only, k % 8 == 0, k <= 16384, 16-byte aligned rows; other shapes: AMCT_ERR_UNSUPPORTED.
+ * One pass: replaces a torch add, a torch rms_norm and the activation-quant kernel of
+ * NpuQuantizationLinear.forward (amct_pytorch/deploy_op/npu_quantization_linear.py:95-99). */
+int amct_addnorm_quant_pertoken(const void* x, const void* residual, int dtype, int64_t rows, int64_t k,
+                                int64_t ld_x, int64_t ld_res, const void* gamma, float eps,
+                                void* residual_out, int64_t ld_res_out, void* norm_out, int64_t ld_norm,
+                                int8_t* q, int64_t ld_q, float* scale, int* status, void* stream);
+
+/* Rotary embedding (rotate-half) in place on the first `heads` heads of each row of x [tokens, ld]:
+ * head h occupies columns [h * head_dim, (h + 1) * head_dim).  cos_table / sin_table [seq, head_dim / 2]
+ * in x's dtype; token t uses table row t % seq.  fp16 / bf16, head_dim % 16 == 0.  Each product and sum
+ * is rounded to dtype, like the same expression in torch ops. */
+int amct_rope_inplace(void* x, int dtype, int64_t tokens, int64_t ld, int heads, int head_dim,
+                      const void* cos_table, const void* sin_table, int64_t seq, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -172,6 +172,20 @@ def dynamic_per_token(x, rule='released', smooth_recip=None):
     return q.to(torch.int8).reshape(x.shape), scale.reshape(-1).float()
 
 
+def addnorm_dynamic_per_token(x, gamma, eps, residual=None):
+    """Decoder-layer glue in front of a dynamic W8A8 Linear: h = x + residual (a torch add in
+    the tensor dtype), n = RMSNorm(h) * gamma evaluated in fp32 and rounded once to the tensor
+    dtype, then ``dynamic_per_token(n)``.  Returns (h, n, codes, scale).  The reference has no
+    fused form; the quantizer is the one of deploy_op/npu_quantization_linear.py's input path
+    with per-token dynamic scales, applied to the rounded n."""
+    h = x if residual is None else x + residual
+    hf = h.float()
+    rstd = torch.rsqrt(hf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    n = ((hf * rstd) * gamma.float()).to(x.dtype)
+    q, scale = dynamic_per_token(n)
+    return h, n, q, scale
+
+
 # --------------------------------------------------------------------------
 # K7  fake quantization
 # --------------------------------------------------------------------------
