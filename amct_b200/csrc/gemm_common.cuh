@@ -1,0 +1,180 @@
+// Pieces shared by the tcgen05 GEMM kernels: parameters, tile rasterisation and the
+// epilogue that turns one 128-row accumulator tile in tensor memory into output values.
+//
+// Epilogues (fp32, each step separately rounded, in this order):
+//   W8A8 per-token : y = float(acc) * deq[n] * pertoken[m] + bias_f[n]
+//   W8A8 per-tensor: y = float(acc + bias_i32[n]) * deq[n]
+//   (the operand construction of amct_pytorch/deploy_op/npu_quantization_linear.py:61-68,
+//    :105-130 fixes where each bias is added; the call is
+//    torch_npu.npu_quant_matmul at :100-102)
+//   raw            : int32 accumulators as they are
+//   float kinds    : y = acc + bias_f[n]
+#pragma once
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace amct {
+
+constexpr int kBM = 128, kBKBytes = 128;
+constexpr int kABytes = kBM * kBKBytes;
+
+enum { KIND_I8 = 0, KIND_BF16 = 1, KIND_F16 = 2 };
+enum { BIAS_NONE = 0, BIAS_I32 = 1, BIAS_F32 = 2, BIAS_F16 = 3, BIAS_BF16 = 4 };
+enum { OUT_F32 = 0, OUT_F16 = 1, OUT_BF16 = 2, OUT_I32 = 3 };
+
+struct GemmParams {
+  int64_t m, n, k;             // k in elements
+  int kind;
+  const float* deq;            // [n] or null
+  const float* pertoken;       // [m] or null
+  const void* bias;            // [n] or null
+  int bias_kind;
+  void* out;
+  int out_kind;
+  int64_t ld_out;              // elements
+  int* status;
+  int act;                     // 0 none, 1 SwiGLU over interleaved [128 gate | 128 up] column blocks
+};
+
+// Rasterisation: GROUP m-tiles x all n-tiles per group, m fastest, so that the tiles in flight
+// at one time share a few A row blocks and a few B row blocks in L2.
+template <int GROUP>
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t* tm, int64_t* tn) {
+  const int64_t per_group = (int64_t)GROUP * tiles_n;
+  const int64_t g = tile / per_group, r = tile - g * per_group;
+  const int64_t m0 = g * GROUP;
+  const int64_t gm = (tiles_m - m0) < GROUP ? (tiles_m - m0) : GROUP;
+  *tn = r / gm;
+  *tm = m0 + r % gm;
+}
+
+__device__ __forceinline__ float bias_at(const void* bias, int kind, int64_t n) {
+  switch (kind) {
+    case BIAS_F32: return reinterpret_cast<const float*>(bias)[n];
+    case BIAS_F16: return __half2float(reinterpret_cast<const __half*>(bias)[n]);
+    case BIAS_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[n]);
+    case BIAS_I32: return __int_as_float(reinterpret_cast<const int*>(bias)[n]);   // carried as raw bits
+  }
+  return 0.f;
+}
+
+// dequant epilogue of one INT8 accumulator in per-token mode
+__device__ __forceinline__ float epi_token(int acc, float deq, float pt, bool has_pt, float bias, bool has_bias) {
+  float v = __fmul_rn((float)acc, deq);
+  if (has_pt) v = __fmul_rn(v, pt);
+  if (has_bias) v = __fadd_rn(v, bias);
+  return v;
+}
+
+// One warp's share of an accumulator tile: the 32 rows starting at TMEM address t_row (lane =
+// row), kBN columns.  `row` is this lane's output row, n0 the tile's first output column, tn the
+// tile's column index; sc / sb hold the tile's per-column scale and bias, pt the row's scale.
+template <int kBN>
+__device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_row, int64_t row, int64_t n0, int64_t tn,
+                                              const float* sc, const float* sb, float pt) {
+  if (p.act == 1) {
+    // SwiGLU: the tile holds 128 gate columns followed by their 128 up columns.  Both are
+    // dequantized and rounded to bf16 as the unfused Linear would output them, then
+    // out = bf16(bf16(silu(gate)) * up); the output has N/2 columns.
+#pragma unroll 1
+    for (int c0 = 0; c0 < kBN / 2; c0 += 32) {
+      uint32_t rg[32], ru[32];
+      tc05::tmem_ld_32x32(t_row + c0, rg);
+      tc05::tmem_ld_32x32(t_row + kBN / 2 + c0, ru);
+      tc05::tmem_ld_wait();
+      if (row < p.m) {
+        uint32_t h[16];
+        const bool has_b = p.bias_kind != BIAS_NONE;
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float o2[2];
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            float g = epi_token((int)rg[j + t], sc[c0 + j + t], pt, p.pertoken != nullptr, sb[c0 + j + t], has_b);
+            float u = epi_token((int)ru[j + t], sc[kBN / 2 + c0 + j + t], pt, p.pertoken != nullptr, sb[kBN / 2 + c0 + j + t], has_b);
+            g = __bfloat162float(__float2bfloat16_rn(g));
+            u = __bfloat162float(__float2bfloat16_rn(u));
+            const float sg = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g)))));
+            o2[t] = __fmul_rn(sg, u);
+          }
+          __nv_bfloat162 v = __floats2bfloat162_rn(o2[0], o2[1]);
+          h[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + row * p.ld_out + tn * (kBN / 2) + c0;
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(h[j], h[j + 1], h[j + 2], h[j + 3]);
+      }
+    }
+  } else
+#pragma unroll 1
+  for (int c0 = 0; c0 < kBN; c0 += 32) {
+    uint32_t r[32];
+    tc05::tmem_ld_32x32(t_row + c0, r);
+    tc05::tmem_ld_wait();
+    if (row < p.m && n0 + c0 < p.n) {
+      float y[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (p.kind == KIND_I8) {
+          int a = (int)r[j];
+          if (p.bias_kind == BIAS_I32) {
+            a += __float_as_int(sb[c0 + j]);
+            y[j] = __fmul_rn((float)a, sc[c0 + j]);
+          } else {
+            float v = __fmul_rn((float)a, sc[c0 + j]);
+            if (p.pertoken) v = __fmul_rn(v, pt);
+            if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c0 + j]);
+            y[j] = v;
+          }
+        } else {
+          float v = __uint_as_float(r[j]);
+          if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c0 + j]);
+          y[j] = v;
+        }
+      }
+      const int64_t nleft = p.n - (n0 + c0);
+      const int64_t off = row * p.ld_out + n0 + c0;
+      if (p.out_kind == OUT_I32) {
+        int* o = reinterpret_cast<int*>(p.out) + off;
+        if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = (int)r[j];
+        }
+      } else if (p.out_kind == OUT_F32) {
+        float* o = reinterpret_cast<float*>(p.out) + off;
+        if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = y[j];
+        }
+      } else {
+        uint32_t h[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (p.out_kind == OUT_BF16) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+            h[j] = *reinterpret_cast<uint32_t*>(&v);
+          } else {
+            __half2 v = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
+            h[j] = *reinterpret_cast<uint32_t*>(&v);
+          }
+        }
+        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + off;
+        if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(h[j], h[j + 1], h[j + 2], h[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = (uint16_t)(h[j >> 1] >> (16 * (j & 1)));
+        }
+      }
+    }
+  }
+}
+
+}  // namespace amct

@@ -2,6 +2,8 @@
 //
 //   C[M, N] = A[M, K] * B[N, K]^T      A and B K-major (K contiguous)
 //
+// This file: the one-CTA kernel (M <= 128, and M > 128 when asked for) and the C entry points;
+// M > 128 normally runs the CTA-pair kernel of gemm_tcgen05_pair.cu.
 // One persistent CTA per SM walks 128 x 256 output tiles.  Warp roles:
 //   warp 0   TMA producer: cp.async.bulk.tensor tiles of A (128 x 128 B) and
 //            B (256 x 128 B) into a 4-stage, 128-byte-swizzled shared-memory ring;
@@ -23,37 +25,17 @@
 //   raw            : int32 accumulators as they are
 //   float kinds    : y = acc + bias_f[n]
 #include <cuda.h>
+#include <stdlib.h>
 
-#include "common.cuh"
-#include "tc05.cuh"
+#include "gemm_common.cuh"
 
 namespace amct {
 
-constexpr int kBM = 128, kBKBytes = 128;
-constexpr int kABytes = kBM * kBKBytes;
 // two tile shapes: 128 x 256 with a 4-stage ring (large M), and 128 x 64 with an 8-stage ring for
 // M <= 128, where the job is to stream the weight once: more, smaller tiles keep every SM loading
 constexpr int kBNLarge = 256, kStagesLarge = 4, kBNSmall = 64, kStagesSmall = 8;
 constexpr int kGroupM = 16;                      // rasterisation: 16 m-tiles x all n-tiles per group
 constexpr int kThreads = 192;
-
-enum { KIND_I8 = 0, KIND_BF16 = 1, KIND_F16 = 2 };
-enum { BIAS_NONE = 0, BIAS_I32 = 1, BIAS_F32 = 2, BIAS_F16 = 3, BIAS_BF16 = 4 };
-enum { OUT_F32 = 0, OUT_F16 = 1, OUT_BF16 = 2, OUT_I32 = 3 };
-
-struct GemmParams {
-  int64_t m, n, k;             // k in elements
-  int kind;
-  const float* deq;            // [n] or null
-  const float* pertoken;       // [m] or null
-  const void* bias;            // [n] or null
-  int bias_kind;
-  void* out;
-  int out_kind;
-  int64_t ld_out;              // elements
-  int* status;
-  int act;                     // 0 none, 1 SwiGLU over interleaved [128 gate | 128 up] column blocks
-};
 
 template <int BN, int STAGES>
 struct __align__(1024) GemmSmem {
@@ -64,33 +46,6 @@ struct __align__(1024) GemmSmem {
   uint32_t tmem_base;
   volatile int abort_flag;
 };
-
-__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int64_t* tm, int64_t* tn) {
-  const int64_t per_group = (int64_t)kGroupM * tiles_n;
-  const int64_t g = tile / per_group, r = tile - g * per_group;
-  const int64_t m0 = g * kGroupM;
-  const int64_t gm = (tiles_m - m0) < kGroupM ? (tiles_m - m0) : kGroupM;
-  *tn = r / gm;
-  *tm = m0 + r % gm;
-}
-
-__device__ __forceinline__ float bias_at(const void* bias, int kind, int64_t n) {
-  switch (kind) {
-    case BIAS_F32: return reinterpret_cast<const float*>(bias)[n];
-    case BIAS_F16: return __half2float(reinterpret_cast<const __half*>(bias)[n]);
-    case BIAS_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[n]);
-    case BIAS_I32: return __int_as_float(reinterpret_cast<const int*>(bias)[n]);   // carried as raw bits
-  }
-  return 0.f;
-}
-
-// dequant epilogue of one INT8 accumulator in per-token mode
-__device__ __forceinline__ float epi_token(int acc, float deq, float pt, bool has_pt, float bias, bool has_bias) {
-  float v = __fmul_rn((float)acc, deq);
-  if (has_pt) v = __fmul_rn(v, pt);
-  if (has_bias) v = __fadd_rn(v, bias);
-  return v;
-}
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -133,7 +88,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool alive = true;
       for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int64_t tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        tile_coords<kGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
           if (!tc05::mbar_wait(tc05::smem_u32(&s.empty[stage]), phase ^ 1, abort_flag)) { alive = false; break; }
           const uint32_t bar = tc05::smem_u32(&s.full[stage]);
@@ -187,7 +142,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t acc = 0, acc_phase = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      tile_coords<kGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
       const int64_t n0 = tn * kBN;
       const int64_t row = tm * kBM + quarter * 32 + lane;
       // stage the per-column factors of this tile (per warp, so only __syncwarp is needed)
@@ -201,109 +156,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_full[acc]), acc_phase, abort_flag)) break;
       tc05::fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN;
-      if (p.act == 1) {
-        // SwiGLU: the tile holds 128 gate columns followed by their 128 up columns.  Both are
-        // dequantized and rounded to bf16 as the unfused Linear would output them, then
-        // out = bf16(bf16(silu(gate)) * up); the output has N/2 columns.
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBN / 2; c0 += 32) {
-          uint32_t rg[32], ru[32];
-          tc05::tmem_ld_32x32(t_row + c0, rg);
-          tc05::tmem_ld_32x32(t_row + kBN / 2 + c0, ru);
-          tc05::tmem_ld_wait();
-          if (row < p.m) {
-            uint32_t h[16];
-            const bool has_b = p.bias_kind != BIAS_NONE;
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              float o2[2];
-#pragma unroll
-              for (int t = 0; t < 2; ++t) {
-                float g = epi_token((int)rg[j + t], sc[c0 + j + t], pt, p.pertoken != nullptr, sb[c0 + j + t], has_b);
-                float u = epi_token((int)ru[j + t], sc[kBN / 2 + c0 + j + t], pt, p.pertoken != nullptr, sb[kBN / 2 + c0 + j + t], has_b);
-                g = __bfloat162float(__float2bfloat16_rn(g));
-                u = __bfloat162float(__float2bfloat16_rn(u));
-                const float sg = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g)))));
-                o2[t] = __fmul_rn(sg, u);
-              }
-              __nv_bfloat162 v = __floats2bfloat162_rn(o2[0], o2[1]);
-              h[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
-            }
-            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + row * p.ld_out + tn * (kBN / 2) + c0;
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(h[j], h[j + 1], h[j + 2], h[j + 3]);
-          }
-        }
-      } else
-#pragma unroll 1
-      for (int c0 = 0; c0 < kBN; c0 += 32) {
-        uint32_t r[32];
-        tc05::tmem_ld_32x32(t_row + c0, r);
-        tc05::tmem_ld_wait();
-        if (row < p.m && n0 + c0 < p.n) {
-          float y[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (p.kind == KIND_I8) {
-              int a = (int)r[j];
-              if (p.bias_kind == BIAS_I32) {
-                a += __float_as_int(sb[c0 + j]);
-                y[j] = __fmul_rn((float)a, sc[c0 + j]);
-              } else {
-                float v = __fmul_rn((float)a, sc[c0 + j]);
-                if (p.pertoken) v = __fmul_rn(v, pt);
-                if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c0 + j]);
-                y[j] = v;
-              }
-            } else {
-              float v = __uint_as_float(r[j]);
-              if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c0 + j]);
-              y[j] = v;
-            }
-          }
-          const int64_t nleft = p.n - (n0 + c0);
-          const int64_t off = row * p.ld_out + n0 + c0;
-          if (p.out_kind == OUT_I32) {
-            int* o = reinterpret_cast<int*>(p.out) + off;
-            if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = (int)r[j];
-            }
-          } else if (p.out_kind == OUT_F32) {
-            float* o = reinterpret_cast<float*>(p.out) + off;
-            if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = y[j];
-            }
-          } else {
-            uint32_t h[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (p.out_kind == OUT_BF16) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
-                h[j] = *reinterpret_cast<uint32_t*>(&v);
-              } else {
-                __half2 v = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
-                h[j] = *reinterpret_cast<uint32_t*>(&v);
-              }
-            }
-            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + off;
-            if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4) *reinterpret_cast<uint4*>(o + 2 * j) = make_uint4(h[j], h[j + 1], h[j + 2], h[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < nleft) o[j] = (uint16_t)(h[j >> 1] >> (16 * (j & 1)));
-            }
-          }
-        }
-      }
+      epilogue_rows<kBN>(p, t_row, row, n0, tn, sc, sb, pt);
       tc05::fence_before_sync();
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(tc05::smem_u32(&s.tmem_empty[acc]));
@@ -367,6 +220,20 @@ static int sm_count() {
   return n;
 }
 
+int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st);
+
+// Which kernel takes M > 128.  The CTA-pair kernel does more work per clock; at the power limit it
+// wins while the B operand stays in L2 and loses when B streams from HBM (measured on B200), hence
+// the size rule.  AMCT_GEMM_VARIANT=single|pair in the environment overrides it (tests, comparisons).
+constexpr int64_t kPairMaxBBytes = 96LL << 20;
+static bool use_pair_kernel(const GemmParams& p, int esize) {
+  if (p.m <= 128) return false;
+  const char* e = getenv("AMCT_GEMM_VARIANT");
+  if (e && e[0] == 's') return false;
+  if (e && e[0] == 'p') return true;
+  return p.n * p.k * esize <= kPairMaxBBytes;
+}
+
 static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b, const GemmParams& p, cudaStream_t st) {
   if (p.m == 0 || p.n == 0) return AMCT_OK;
   if (p.k <= 0) return AMCT_ERR_ARG;
@@ -375,6 +242,12 @@ static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b,
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, esize, p.m, p.k, ld_a, kBM);
   if (rc != AMCT_OK) return rc;
+  if (use_pair_kernel(p, esize)) {
+    // CTA pairs on 256 x 256 tiles: each CTA loads 128 rows of A and 128 rows (half a tile) of B
+    rc = make_map(&mb, b, esize, p.n, p.k, ld_b, 128);
+    if (rc != AMCT_OK) return rc;
+    return launch_gemm_pair(ma, mb, p, st);
+  }
   rc = make_map(&mb, b, esize, p.n, p.k, ld_b, (p.m <= 128 && p.act == 0) ? kBNSmall : kBNLarge);
   if (rc != AMCT_OK) return rc;
   const bool small = p.m <= 128 && p.act == 0;

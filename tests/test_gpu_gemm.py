@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 # max-relative-error bound for bf16 / fp16 outputs (relative to the largest reference magnitude)
 TOL_16 = 1e-2
 SHAPES = [(1, 8, 16), (7, 24, 48), (128, 256, 128), (129, 264, 272), (300, 520, 4096), (64, 1024, 1040),
-          (2048, 512, 384)]
+          (2048, 512, 384), (257, 256, 64), (1000, 777 * 8, 16 * 9)]
 
 
 def ops():
@@ -28,8 +28,18 @@ def status():
     return torch.zeros(1, dtype=torch.int32, device='cuda')
 
 
+@pytest.fixture(params=['auto', 'single', 'pair'])
+def variant(request, monkeypatch):
+    """Which kernel takes M > 128: the size rule, the one-CTA kernel, or the CTA-pair kernel."""
+    if request.param != 'auto':
+        monkeypatch.setenv('AMCT_GEMM_VARIANT', request.param)
+    else:
+        monkeypatch.delenv('AMCT_GEMM_VARIANT', raising=False)
+    return request.param
+
+
 @pytest.mark.parametrize('m,n,k', SHAPES)
-def test_w8a8_raw_accumulators_exact(m, n, k):
+def test_w8a8_raw_accumulators_exact(m, n, k, variant):
     g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
     a, b = rand_i8(g, m, k), rand_i8(g, n, k)
     st = status()
@@ -41,7 +51,7 @@ def test_w8a8_raw_accumulators_exact(m, n, k):
 @pytest.mark.parametrize('m,n,k', [(7, 24, 48), (129, 264, 272), (300, 520, 1024)])
 @pytest.mark.parametrize('out_dtype', [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize('mode', ['token', 'token_nobias', 'tensor', 'tensor_nobias'])
-def test_w8a8_epilogues(m, n, k, out_dtype, mode):
+def test_w8a8_epilogues(m, n, k, out_dtype, mode, variant):
     g = torch.Generator().manual_seed(m + n + k)
     a, b = rand_i8(g, m, k), rand_i8(g, n, k)
     deq = torch.rand(n, generator=g) * 1e-3 + 1e-4
@@ -75,7 +85,7 @@ def test_w8a8_strided_operands_and_repeat():
 
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize('m,n,k', [(5, 16, 64), (129, 264, 136), (256, 512, 2048)])
-def test_f16_gemm(dtype, m, n, k):
+def test_f16_gemm(dtype, m, n, k, variant):
     g = torch.Generator().manual_seed(m + k)
     a = torch.randn(m, k, generator=g).to(dtype)
     b = (torch.randn(n, k, generator=g) * 0.05).to(dtype)
@@ -91,7 +101,7 @@ def test_f16_gemm(dtype, m, n, k):
     assert err16 < TOL_16, err16
 
 
-def test_w8a8_full_size_checksums():
+def test_w8a8_full_size_checksums(variant):
     """M=2048, K=N=4096 (the single-Linear benchmark shape): row and column
     checksums of the INT32 result against int64 matrix-vector products."""
     g = torch.Generator().manual_seed(0)
@@ -228,7 +238,7 @@ def test_dynamic_w8a8_linear_matches_oracle():
         assert bits_equal(got, want)
 
 
-def test_swiglu_epilogue_matches_unfused_path():
+def test_swiglu_epilogue_matches_unfused_path(variant):
     """The fused gate/up GEMM + SwiGLU epilogue against the unfused sequence on the same device:
     plain W8A8 GEMM (bf16 out) -> de-interleave -> torch silu * up."""
     from amct_b200.deploy_op.npu_quantization_linear import interleave_gate_up
