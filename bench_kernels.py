@@ -1,6 +1,7 @@
 """Per-kernel roofline measurements (one JSON line per case).
 
     python bench_kernels.py [--only SUBSTR] [--reps 20] [--out FILE]
+    python bench_kernels.py --only SUBSTR --steady SECONDS [--library-refs]
 
 Every case: 3 warm-up launches, then `reps` launches each preceded by an L2 flush
 (a 512 MiB buffer is overwritten, untimed), each launch bracketed by CUDA events on
@@ -8,6 +9,12 @@ the launching stream.  Reported: median and best time, algorithmic bytes or
 operations per launch, achieved GB/s or TOP/s and the fraction of the measured peak
 (MEASURED_PEAKS.json when present: HBM copy bandwidth; 2x the bf16 burst figure for
 INT8 and FP8, 4x for FP4, since a kernel is timed alone here).
+
+--steady S runs each selected case back to back for S seconds instead (no L2 flush), samples
+the SM clock and the board power through NVML every 50 ms, and reports the rate of the first
+10 launches and of the last quarter of the run: the figure that holds at the power limit.
+--library-refs adds cuBLASLt INT8 (torch._int_mm) and cuBLAS bf16 (torch.matmul) lines for
+context; they are never part of this repository's path.
 """
 import argparse
 import json
@@ -55,6 +62,49 @@ def time_case(fn, reps):
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
     return statistics.median(times), min(times)
+
+
+def steady_case(name, fn, secs, nops=None, nbytes=None, out=None):
+    import threading
+    import time
+    import pynvml
+    pynvml.nvmlInit()
+    h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+    samples, stop = [], []
+
+    def sampler():
+        while not stop:
+            samples.append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM), pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0))
+            time.sleep(0.05)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    th = threading.Thread(target=sampler)
+    th.start()
+    t0, evs = time.time(), []
+    while time.time() - t0 < secs:
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+    stop.append(1)
+    th.join()
+    ms = [a.elapsed_time(b) for a, b in evs]
+    last, ls = ms[len(ms) * 3 // 4:], samples[len(samples) * 3 // 4:]
+    work, unit = (nops, 'TOP/s') if nops is not None else (nbytes, 'TB/s')
+    rec = {'case': name, 'mode': f'steady {secs}s', 'launches': len(ms), 'unit': unit,
+           'first10': round(work / statistics.median(ms[:10]) / 1e9, 1), 'steady': round(work / statistics.median(last) / 1e9, 1),
+           'sm_mhz_steady': statistics.median([c for c, _ in ls]) if ls else None,
+           'power_w_steady': round(statistics.median([w for _, w in ls])) if ls else None,
+           'variant': os.environ.get('AMCT_GEMM_VARIANT', 'auto')}
+    line = json.dumps(rec)
+    print(line, flush=True)
+    if out:
+        out.write(line + '\n')
+        out.flush()
 
 
 def report(name, med, best, nbytes=None, nops=None, out=None, peak_mult=1.0):
@@ -121,7 +171,7 @@ def cases():
            lambda x: (lambda: ops.minmax(x, 'tensor')), dict(nbytes=65536 * 8192 * 2))
     # ---- W8A8 GEMM
     for m, n, k, od, tag in ((2048, 4096, 4096, torch.float32, 'c1'), (8192, 8192, 8192, torch.bfloat16, 'square'),
-                             (65536, 10240, 8192, torch.bfloat16, 'c5 qkv'), (65536, 8192, 8192, torch.bfloat16, 'c5 o'),
+                             (16384, 8192, 8192, torch.bfloat16, 'mid'), (65536, 10240, 8192, torch.bfloat16, 'c5 qkv'), (65536, 8192, 8192, torch.bfloat16, 'c5 o'),
                              (65536, 57344, 8192, torch.bfloat16, 'c5 gate+up'), (65536, 8192, 28672, torch.bfloat16, 'c5 down'),
                              (64, 8192, 8192, torch.bfloat16, 'c5 decode o')):
         def setup(m=m, n=n, k=k, od=od):
@@ -177,13 +227,31 @@ def main():
     ap.add_argument('--only', default='')
     ap.add_argument('--reps', type=int, default=20)
     ap.add_argument('--out', default='')
+    ap.add_argument('--steady', type=float, default=0.0, help='seconds of back-to-back launches per case')
+    ap.add_argument('--library-refs', action='store_true', help='add cuBLASLt / cuBLAS reference lines (context only)')
     args = ap.parse_args()
     out = open(args.out, 'w') if args.out else None
-    for name, setup, make, kw in cases():
+    todo = list(cases())
+    if args.library_refs:
+        for m, n, k in ((16384, 8192, 8192),):
+            def setup_ref(m=m, n=n, k=k):
+                return (torch.randint(-128, 128, (m, k), device='cuda', dtype=torch.int8),
+                        torch.randint(-128, 128, (n, k), device='cuda', dtype=torch.int8).t(),
+                        torch.randn(m, k, device='cuda', dtype=torch.bfloat16), torch.randn(n, k, device='cuda', dtype=torch.bfloat16).t())
+            todo.append((f'library ref cublaslt int8 {m}x{n}x{k} -> int32', setup_ref, lambda t: (lambda: torch._int_mm(t[0], t[1])),
+                         dict(nops=2 * m * n * k, peak_mult=2.0)))
+            todo.append((f'library ref cublas bf16 {m}x{n}x{k}', setup_ref, lambda t: (lambda: torch.matmul(t[2], t[3])),
+                         dict(nops=2 * m * n * k, peak_mult=1.0)))
+    for name, setup, make, kw in todo:
         if args.only and args.only not in name:
             continue
         data = setup()
         fn = make(data)
+        if args.steady > 0:
+            steady_case(name, fn, args.steady, nops=kw.get('nops'), nbytes=kw.get('nbytes'), out=out)
+            del data, fn
+            torch.cuda.empty_cache()
+            continue
         med, best = time_case(fn, args.reps)
         report(name, med, best, out=out, **kw)
         del data, fn
