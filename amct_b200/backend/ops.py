@@ -513,11 +513,13 @@ def gemm_w8a8_swiglu(q, w_nk, deq_scale, pertoken_scale=None, bias=None, out=Non
     return out
 
 
-def addnorm_quant_per_token(x, gamma, eps, residual=None, want_norm=False, check=False):
+def addnorm_quant_per_token(x, gamma, eps, residual=None, want_norm=False, check=False, out_q=None, out_scale=None):
     """(x [+ residual]) -> RMSNorm -> dynamic per-token INT8 codes, one kernel.
 
     Returns (q int8 like x, scale fp32 [rows], h, n): h = x + residual in x's dtype (None without
-    residual), n = the normalised values the codes were taken from (only with want_norm)."""
+    residual), n = the normalised values the codes were taken from (only with want_norm).
+    out_q (int8 [rows, K] contiguous) / out_scale (fp32 [rows]) receive the codes and scales in
+    place, e.g. a rank's slice of an all-gather buffer."""
     _need_cuda(x, gamma, residual)
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise _l.BackendError('addnorm_quant_per_token: float16 / bfloat16 only')
@@ -530,8 +532,12 @@ def addnorm_quant_per_token(x, gamma, eps, residual=None, want_norm=False, check
     gamma = gamma.reshape(-1).to(x.dtype).contiguous()
     if gamma.numel() != k:
         raise ValueError('gamma must have K elements')
-    q = torch.empty((rows, k), dtype=torch.int8, device=x.device)
-    scale = torch.empty(rows, dtype=torch.float32, device=x.device)
+    q = out_q if out_q is not None else torch.empty((rows, k), dtype=torch.int8, device=x.device)
+    scale = out_scale if out_scale is not None else torch.empty(rows, dtype=torch.float32, device=x.device)
+    if q.dtype != torch.int8 or q.numel() != rows * k or not q.is_contiguous() or not q.is_cuda:
+        raise ValueError('out_q must be a contiguous CUDA int8 tensor of rows * K elements')
+    if scale.dtype != torch.float32 or scale.numel() != rows or not scale.is_contiguous() or not scale.is_cuda:
+        raise ValueError('out_scale must be a contiguous CUDA float32 tensor of `rows` elements')
     h = torch.empty((rows, k), dtype=x.dtype, device=x.device) if residual is not None else None
     n = torch.empty((rows, k), dtype=x.dtype, device=x.device) if want_norm else None
     st = Status(x.device) if check else None

@@ -17,8 +17,15 @@ is the unit being sharded):
                    per-token activation scales are identical on every rank;
   row-parallel     o_proj and down_proj: each rank owns K/tp input channels; the
                    per-token scale is computed on the local K slice, the local
-                   partial is dequantized to bf16 and summed with one NCCL
-                   all-reduce per Linear.
+                   partial is dequantized to bf16 and summed over the ranks.
+Two ways to do that sum.  `seq_parallel` (prefill default for tp > 1): the residual stream
+is kept token-sharded -- rank r owns rows [r T/tp, (r+1) T/tp) -- so the partials are
+REDUCE-SCATTERED, the add + RMSNorm + quant kernel runs on the local rows only, and what is
+ALL-GATHERED in front of the column-parallel Linears is the INT8 codes and their fp32
+per-token scales: 1 byte per element instead of 2, and no replicated glue work.  Per layer
+and rank that moves 2 x (2 + 1) x T x hidden x (tp-1)/tp bytes instead of the 2 x 4 of two
+bf16 all-reduces.  Otherwise (decode, or T not divisible by tp): one NCCL all-reduce per
+row-parallel Linear on replicated activations.
 """
 import math
 from dataclasses import dataclass
@@ -127,6 +134,55 @@ class DecoderLayer(nn.Module):
             torch.distributed.all_reduce(t, group=self.group)
         return t
 
+    def _reduce_scatter(self, t):
+        """Sum [T, H] partials over the ranks; this rank keeps rows [rank T/tp, (rank+1) T/tp)."""
+        dist = torch.distributed
+        tp, rank = self.tp, dist.get_rank(self.group)
+        rows = t.shape[0] // tp
+        if dist.get_backend(self.group) == 'nccl':
+            out = torch.empty((rows, t.shape[1]), dtype=t.dtype, device=t.device)
+            dist.reduce_scatter_tensor(out, t, group=self.group)
+            return out
+        dist.all_reduce(t, group=self.group)                     # backends without reduce-scatter
+        return t[rank * rows:(rank + 1) * rows].contiguous()
+
+    def _addnorm_quant_gather(self, x_loc, gamma, residual_loc):
+        """Local rows -> (codes [T, H] int8, scales [T] fp32 of ALL rows, new local residual)."""
+        dist = torch.distributed
+        tp, rank = self.tp, dist.get_rank(self.group)
+        rows, hid = x_loc.shape
+        q_all = torch.empty((tp * rows, hid), dtype=torch.int8, device=x_loc.device)
+        s_all = torch.empty(tp * rows, dtype=torch.float32, device=x_loc.device)
+        q_loc, s_loc = q_all[rank * rows:(rank + 1) * rows], s_all[rank * rows:(rank + 1) * rows]
+        _, _, h, _ = ops.addnorm_quant_per_token(x_loc, gamma, self.shape.rms_eps, residual=residual_loc, out_q=q_loc, out_scale=s_loc)
+        dist.all_gather_into_tensor(q_all, q_loc, group=self.group)
+        dist.all_gather_into_tensor(s_all, s_loc, group=self.group)
+        return q_all, s_all, (h if h is not None else x_loc)
+
+    def forward_seq_parallel(self, x_loc, cos, sin, branch_loc, b, s):
+        """Prefill with a token-sharded residual stream: x_loc / branch_loc are this rank's
+        [b s / tp, hidden] rows.  Returns (x_loc, branch_loc) like forward() with fused_glue."""
+        shp, lin = self.shape, self.linears
+        if branch_loc is None:
+            q8, ps, x_loc = self._addnorm_quant_gather(x_loc, self.input_norm, None)
+        else:
+            q8, ps, x_loc = self._addnorm_quant_gather(branch_loc, self.input_norm, x_loc)
+        qkv = lin.qkv_proj.forward_quantized(q8, ps).reshape(b, s, -1)
+        ops.rope_inplace(qkv, self.heads + self.kv_heads, shp.head_dim, cos, sin)
+        q, k, v = qkv.split((self.heads * shp.head_dim, self.kv_heads * shp.head_dim, self.kv_heads * shp.head_dim), dim=-1)
+        q = q.reshape(b, s, self.heads, shp.head_dim).transpose(1, 2)
+        k = k.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
+        v = v.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
+        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        attn = attn.transpose(1, 2).reshape(b * s, self.heads * shp.head_dim)
+        o_loc = self._reduce_scatter(lin.o_proj(attn))
+        q8, ps, x_loc = self._addnorm_quant_gather(o_loc, self.post_norm, x_loc)
+        act = lin.gate_up_proj.forward_quantized(q8, ps)
+        if not self.fused_swiglu:
+            gate, up = act.chunk(2, dim=-1)
+            act = F.silu(gate) * up
+        return x_loc, self._reduce_scatter(lin.down_proj(act))
+
     def forward(self, x, cos, sin, kv_cache=None, branch=None):
         """x [B, S, hidden] bf16 (the residual stream).  kv_cache: None (prefill, causal) or (k, v, past)
         with k, v [B, kvh, >= past + S, D] holding `past` keys/values (decode: S new tokens attend to
@@ -191,7 +247,7 @@ class LlamaW8A8(nn.Module):
     """Random-initialised Llama stack; rank `rank` of `tp` holds its shard of every layer."""
 
     def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None, fused_swiglu=True,
-                 fused_glue=True):
+                 fused_glue=True, seq_parallel=True):
         super().__init__()
         if shape.n_kv_heads % tp or shape.n_heads % tp or shape.intermediate % tp:
             raise ValueError(f'tp={tp} does not divide the head / intermediate sizes')
@@ -202,6 +258,8 @@ class LlamaW8A8(nn.Module):
         self.lm_head = torch.empty(shape.vocab, shape.hidden, dtype=torch.bfloat16, device=device).normal_(0, 0.02, generator=shared)
         self.final_norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
         self.fused_glue = fused_glue
+        self.seq_parallel = seq_parallel and fused_glue and tp > 1
+        self.group, self.rank = group, rank
         self.layers = nn.ModuleList(DecoderLayer(shape, tp, group, device, gen, fused_swiglu, fused_glue)
                                     for _ in range(n_layers if n_layers is not None else shape.n_layers))
 
@@ -217,8 +275,38 @@ class LlamaW8A8(nn.Module):
             micro_batches = 2 if (self.tp > 1 and kv_caches is None and b >= 2) else 1
         pos = torch.arange(past_len, past_len + s, device=token_ids.device)
         cos, sin = rotary_tables(self.shape, pos, token_ids.device)
+        sp = self.seq_parallel and kv_caches is None and (b // micro_batches) * s % self.tp == 0 and b % micro_batches == 0
         if micro_batches == 1:
-            x = self._stack(F.embedding(token_ids, self.embed), cos, sin, kv_caches)
+            if sp:
+                x = self._stack_seq_parallel(token_ids, cos, sin)
+            else:
+                x = self._stack(F.embedding(token_ids, self.embed), cos, sin, kv_caches)
+        elif sp:
+            main = torch.cuda.current_stream()
+            if getattr(self, '_streams', None) is None or len(self._streams) != micro_batches:
+                self._streams = [torch.cuda.Stream(device=token_ids.device) for _ in range(micro_batches)]
+            parts = list(token_ids.chunk(micro_batches, dim=0))
+            rows = [p_.numel() // self.tp for p_ in parts]
+            xs, branches = [None] * len(parts), [None] * len(parts)
+            for st in self._streams:
+                st.wait_stream(main)
+            for j, ids in enumerate(parts):
+                with torch.cuda.stream(self._streams[j]):
+                    xs[j] = F.embedding(ids.reshape(-1)[self.rank * rows[j]:(self.rank + 1) * rows[j]], self.embed)
+            for layer in self.layers:
+                for j, ids in enumerate(parts):
+                    with torch.cuda.stream(self._streams[j]):
+                        xs[j], branches[j] = layer.forward_seq_parallel(xs[j], cos, sin, branches[j], ids.shape[0], s)
+            for j, ids in enumerate(parts):
+                with torch.cuda.stream(self._streams[j]):
+                    loc = xs[j] + branches[j]
+                    full = torch.empty((ids.numel(), loc.shape[1]), dtype=loc.dtype, device=loc.device)
+                    torch.distributed.all_gather_into_tensor(full, loc, group=self.group)
+                    xs[j] = full.reshape(ids.shape[0], s, -1)[:, -1:]
+            for j, st in enumerate(self._streams[:len(parts)]):
+                main.wait_stream(st)
+                xs[j].record_stream(main)
+            x = torch.cat(xs, dim=0)
         else:
             main = torch.cuda.current_stream()
             if getattr(self, '_streams', None) is None or len(self._streams) != micro_batches:
@@ -248,6 +336,21 @@ class LlamaW8A8(nn.Module):
             x = torch.cat([t[:, -1:] for t in xs], dim=0)
         x = F.rms_norm(x[:, -1], (self.shape.hidden,), self.final_norm, self.shape.rms_eps)
         return (x @ self.lm_head.t()).float()
+
+    def _stack_seq_parallel(self, token_ids, cos, sin):
+        """Prefill of [b, s] token ids with the residual stream sharded by token rows over the ranks;
+        returns the last position's hidden state [b, 1, hidden] (replicated)."""
+        b, s = token_ids.shape
+        rows = b * s // self.tp
+        ids_loc = token_ids.reshape(-1)[self.rank * rows:(self.rank + 1) * rows]
+        x_loc, branch_loc = F.embedding(ids_loc, self.embed), None
+        for layer in self.layers:
+            x_loc, branch_loc = layer.forward_seq_parallel(x_loc, cos, sin, branch_loc, b, s)
+        if branch_loc is not None:
+            x_loc = x_loc + branch_loc
+        full = torch.empty((b * s, x_loc.shape[1]), dtype=x_loc.dtype, device=x_loc.device)
+        torch.distributed.all_gather_into_tensor(full, x_loc.contiguous(), group=self.group)
+        return full.reshape(b, s, -1)[:, -1:]
 
     def _stack(self, x, cos, sin, kv_caches):
         """All decoder layers on one stream; returns the final residual stream."""

@@ -62,6 +62,60 @@ def test_column_then_row_parallel_w8a8_two_ranks():
             assert err < 3e-2, err          # two chained 8-bit quantizations with per-shard scales vs unsharded
 
 
+def _sp_worker(rank, world, port, ret):
+    """Sequence-parallel dataflow of one decoder block with the oracle as each rank's kernels:
+    local rows -> add + RMSNorm + quant -> all-gather of codes and scales -> column-parallel W8A8
+    -> row-parallel W8A8 partial -> sum over ranks, local rows kept."""
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(1)
+    t, hid, inter = 16, 64, 96
+    x = torch.randn(t, hid, generator=g).to(torch.bfloat16)
+    res = torch.randn(t, hid, generator=g).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(hid, generator=g)).to(torch.bfloat16)
+    w_up = (torch.randn(inter, hid, generator=g) * 0.1).to(torch.bfloat16)
+    w_down = (torch.randn(hid, inter, generator=g) * 0.1).to(torch.bfloat16)
+    rows, n_loc = t // world, inter // world
+    sl = slice(rank * rows, (rank + 1) * rows)
+    # token-sharded glue
+    h_loc, _, q_loc, s_loc = intq.addnorm_dynamic_per_token(x[sl], gamma, 1e-5, res[sl])
+    q_all = torch.empty(t, hid, dtype=torch.int8)
+    s_all = torch.empty(t, dtype=torch.float32)
+    dist.all_gather_into_tensor(q_all, q_loc.contiguous())
+    dist.all_gather_into_tensor(s_all, s_loc.contiguous())
+    # the same on all rows at once (what a replicated rank would compute)
+    h_full, _, q_full, s_full = intq.addnorm_dynamic_per_token(x, gamma, 1e-5, res)
+    ok_gather = torch.equal(q_all, q_full) and torch.equal(s_all, s_full) and torch.equal(h_loc, h_full[sl])
+    # column-parallel then row-parallel Linear on the gathered codes
+    up_loc, down_loc = w_up[rank * n_loc:(rank + 1) * n_loc], w_down[:, rank * n_loc:(rank + 1) * n_loc]
+    sw, _ = intq.weight_scale_offset(up_loc, 'int8', True, 'channel')
+    mid = npu_ops.npu_quant_matmul(q_all, intq.w8a8_weight_codes(up_loc, sw.reshape(-1)).t(), sw.reshape(-1), s_all, None, torch.bfloat16)
+    part, _ = _w8a8(mid, down_loc)
+    total = part.float()
+    dist.all_reduce(total)                                   # gloo has no reduce-scatter: sum, then keep the local rows
+    mine = total[sl]
+    # reference: the replicated (all-reduce) variant gives the same rows
+    ok_rows = mine.shape == (rows, hid)
+    ret[rank] = (ok_gather, ok_rows, mine.clone(), total.clone())
+    dist.destroy_process_group()
+
+
+def test_sequence_parallel_dataflow_two_ranks():
+    world = 2
+    port = 31500 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_sp_worker, args=(world, port, ret), nprocs=world, join=True)
+        full = ret[0][3]
+        for rank in range(world):
+            ok_gather, ok_rows, mine, total = ret[rank]
+            assert ok_gather            # per-token quantization commutes with sharding the token rows: bit-identical
+            assert ok_rows
+            assert torch.equal(total, full)
+            assert torch.equal(mine, full[rank * (16 // world):(rank + 1) * (16 // world)])
+
+
 def test_shard_dims():
     from amct_b200.workloads.llama_tp import shard_dims, LLAMA3_70B
     d1, d8 = shard_dims(LLAMA3_70B, 1), shard_dims(LLAMA3_70B, 8)
