@@ -159,9 +159,10 @@ class DecoderLayer(nn.Module):
         dist.all_gather_into_tensor(s_all, s_loc, group=self.group)
         return q_all, s_all, (h if h is not None else x_loc)
 
-    def forward_seq_parallel(self, x_loc, cos, sin, branch_loc, b, s):
-        """Prefill with a token-sharded residual stream: x_loc / branch_loc are this rank's
-        [b s / tp, hidden] rows.  Returns (x_loc, branch_loc) like forward() with fused_glue."""
+    def sp_attention_half(self, x_loc, cos, sin, branch_loc, b, s):
+        """First half of a token-sharded prefill layer: (previous MLP output + residual) -> norm ->
+        quant -> all-gather -> qkv -> rotary -> attention -> o_proj -> reduce-scatter.
+        x_loc / branch_loc: this rank's [b s / tp, hidden] rows.  Returns (x_loc, o_loc)."""
         shp, lin = self.shape, self.linears
         if branch_loc is None:
             q8, ps, x_loc = self._addnorm_quant_gather(x_loc, self.input_norm, None)
@@ -175,13 +176,24 @@ class DecoderLayer(nn.Module):
         v = v.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b * s, self.heads * shp.head_dim)
-        o_loc = self._reduce_scatter(lin.o_proj(attn))
+        return x_loc, self._reduce_scatter(lin.o_proj(attn))
+
+    def sp_mlp_half(self, x_loc, o_loc):
+        """Second half: (attention output + residual) -> norm -> quant -> all-gather -> gate/up with
+        SwiGLU -> down_proj -> reduce-scatter.  Returns (x_loc, branch_loc)."""
+        lin = self.linears
         q8, ps, x_loc = self._addnorm_quant_gather(o_loc, self.post_norm, x_loc)
         act = lin.gate_up_proj.forward_quantized(q8, ps)
         if not self.fused_swiglu:
             gate, up = act.chunk(2, dim=-1)
             act = F.silu(gate) * up
         return x_loc, self._reduce_scatter(lin.down_proj(act))
+
+    def forward_seq_parallel(self, x_loc, cos, sin, branch_loc, b, s):
+        """Prefill with a token-sharded residual stream: x_loc / branch_loc are this rank's
+        [b s / tp, hidden] rows.  Returns (x_loc, branch_loc) like forward() with fused_glue."""
+        x_loc, o_loc = self.sp_attention_half(x_loc, cos, sin, branch_loc, b, s)
+        return self.sp_mlp_half(x_loc, o_loc)
 
     def forward(self, x, cos, sin, kv_cache=None, branch=None):
         """x [B, S, hidden] bf16 (the residual stream).  kv_cache: None (prefill, causal) or (k, v, past)
@@ -293,10 +305,17 @@ class LlamaW8A8(nn.Module):
             for j, ids in enumerate(parts):
                 with torch.cuda.stream(self._streams[j]):
                     xs[j] = F.embedding(ids.reshape(-1)[self.rank * rows[j]:(self.rank + 1) * rows[j]], self.embed)
+            # ping-pong: the collectives of one micro-batch's half layer are queued right behind that
+            # half's kernels, so on NCCL's in-order stream each one waits only for work issued just
+            # before it, and runs while the other micro-batch computes
+            outs = [None] * len(parts)
             for layer in self.layers:
                 for j, ids in enumerate(parts):
                     with torch.cuda.stream(self._streams[j]):
-                        xs[j], branches[j] = layer.forward_seq_parallel(xs[j], cos, sin, branches[j], ids.shape[0], s)
+                        xs[j], outs[j] = layer.sp_attention_half(xs[j], cos, sin, branches[j], ids.shape[0], s)
+                for j in range(len(parts)):
+                    with torch.cuda.stream(self._streams[j]):
+                        xs[j], branches[j] = layer.sp_mlp_half(xs[j], outs[j])
             for j, ids in enumerate(parts):
                 with torch.cuda.stream(self._streams[j]):
                     loc = xs[j] + branches[j]

@@ -20,6 +20,7 @@ Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
   gpu_launches  launches of this repository's kernels inside the timed region
 """
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -185,7 +186,7 @@ def main():
     import torch.distributed as dist
     group = None
     if world > 1:
-        dist.init_process_group('nccl', device_id=dev)
+        dist.init_process_group('nccl', device_id=dev, timeout=datetime.timedelta(seconds=300))
         group = dist.group.WORLD
 
     from amct_b200.backend import ops
