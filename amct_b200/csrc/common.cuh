@@ -118,6 +118,18 @@ __device__ __forceinline__ float quant_level(float x, float scale, float offset,
   return fminf(fmaxf(t, qmin), qmax);
 }
 
+// Correctly rounded x / s computed from y = rn(1 / s) (__frcp_rn) with two FMA correction steps
+// (Markstein): q0 = rn(x y) is within 2 ulp of the quotient; q1 = rn(q0 + (x - s q0) y) is within
+// one; and for such a q1 and a correctly rounded reciprocal, rn(q1 + (x - s q1) y) IS the correctly
+// rounded quotient, i.e. the value of __fdiv_rn(x, s).  Five FMA-pipe instructions, no branch.
+// Valid for normal, finite s and y and a quotient in the normal range; a quotient that underflows
+// may differ in its last subnormal bits (it rounds to the integer 0 either way).
+__device__ __forceinline__ float div_by_recip(float x, float s, float y) {
+  const float q0 = __fmul_rn(x, y);
+  const float q1 = __fmaf_rn(__fmaf_rn(-s, q0, x), y, q0);
+  return __fmaf_rn(__fmaf_rn(-s, q1, x), y, q1);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace amct

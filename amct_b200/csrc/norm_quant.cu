@@ -22,7 +22,6 @@
 namespace amct {
 
 constexpr float kMagicNQ = 12582912.0f;                  // 1.5 * 2^23
-constexpr float kTieGuardNQ = 0.5f - 2.44140625e-4f;     // within 2^-12 of a tie the IEEE quotient decides
 
 struct NormQuantParams {
   const void* x;
@@ -43,20 +42,12 @@ __device__ __forceinline__ uint32_t nq_pack4(float ra, float rb, float rc, float
   return __byte_perm(w01, w23, 0x5410);
 }
 
-__device__ __noinline__ uint32_t nq_quant4_exact(float a, float b, float c, float d, float s) {
-  const float ra = __fadd_rn(fminf(__fdiv_rn(a, s), 127.f), kMagicNQ), rb = __fadd_rn(fminf(__fdiv_rn(b, s), 127.f), kMagicNQ);
-  const float rc = __fadd_rn(fminf(__fdiv_rn(c, s), 127.f), kMagicNQ), rd = __fadd_rn(fminf(__fdiv_rn(d, s), 127.f), kMagicNQ);
-  return nq_pack4(ra, rb, rc, rd);
-}
-
-// x * rn(1/s) rounded with the magic add; `dist` collects the largest distance from the chosen integer
-__device__ __forceinline__ uint32_t nq_quant4_fast(float a, float b, float c, float d, float y, float& dist) {
-  const float ta = fminf(__fmul_rn(a, y), 127.f), tb = fminf(__fmul_rn(b, y), 127.f);
-  const float tc = fminf(__fmul_rn(c, y), 127.f), td = fminf(__fmul_rn(d, y), 127.f);
-  const float ra = __fadd_rn(ta, kMagicNQ), rb = __fadd_rn(tb, kMagicNQ), rc = __fadd_rn(tc, kMagicNQ), rd = __fadd_rn(td, kMagicNQ);
-  dist = fmaxf(dist, fmaxf(fmaxf(fabsf(__fsub_rn(ta, __fsub_rn(ra, kMagicNQ))), fabsf(__fsub_rn(tb, __fsub_rn(rb, kMagicNQ)))),
-                           fmaxf(fabsf(__fsub_rn(tc, __fsub_rn(rc, kMagicNQ))), fabsf(__fsub_rn(td, __fsub_rn(rd, kMagicNQ))))));
-  return nq_pack4(ra, rb, rc, rd);
+// four quotients by the exact FMA sequence (div_by_recip: the value of the IEEE division), the
+// upper clamp a negative-dominant row needs, round half to even by the magic add
+__device__ __forceinline__ uint32_t nq_quant4(float a, float b, float c, float d, float s, float y) {
+  const float ta = fminf(div_by_recip(a, s, y), 127.f), tb = fminf(div_by_recip(b, s, y), 127.f);
+  const float tc = fminf(div_by_recip(c, s, y), 127.f), td = fminf(div_by_recip(d, s, y), 127.f);
+  return nq_pack4(__fadd_rn(ta, kMagicNQ), __fadd_rn(tb, kMagicNQ), __fadd_rn(tc, kMagicNQ), __fadd_rn(td, kMagicNQ));
 }
 
 // block-wide sum; the caller alternates `part` between rows so one barrier per reduction is enough
@@ -176,11 +167,7 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
         float f[E];
 #pragma unroll
         for (int e = 0; e < E; ++e) f[e] = ElemTraits<T>::to_f(h[j].v[e]);
-        float dist = 0.f;
-        uint32_t w0 = nq_quant4_fast(f[0], f[1], f[2], f[3], y, dist);
-        uint32_t w1 = nq_quant4_fast(f[4], f[5], f[6], f[7], y, dist);
-        if (dist > kTieGuardNQ) { w0 = nq_quant4_exact(f[0], f[1], f[2], f[3], s); w1 = nq_quant4_exact(f[4], f[5], f[6], f[7], s); }
-        *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(w0, w1);
+        *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(nq_quant4(f[0], f[1], f[2], f[3], s, y), nq_quant4(f[4], f[5], f[6], f[7], s, y));
       }
     }
   }

@@ -392,6 +392,11 @@ static int dispatch_rows(int dtype, const RowParams& p, cudaStream_t st) {
   return AMCT_ERR_ARG;
 }
 
+// group-wise kernel of quant_groups.cu; returns 1 when the shape does not fit it
+int quant_groups_try(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld, const void* pre, int pre_op, int compute,
+                     int group, int bits, int symmetric, float* scale, int* offset, int out_mode, void* out, int64_t ld_out,
+                     int* status, cudaStream_t st);
+
 // streaming kernel of quant_token.cu; returns 1 when the shape does not fit it
 int quant_token_try(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, const void* smooth, int8_t* q,
                     int64_t ld_q, float* scale, int* status, cudaStream_t st);
@@ -439,6 +444,12 @@ extern "C" int amct_quant_rows(const void* x, int dtype, int64_t rows, int64_t k
       (pre_op == AMCT_PRE_NONE || pre_op == AMCT_PRE_MUL) && rows > 0 && k > 0) {
     int rc = amct::quant_token_try(x, dtype, rows, k, ld_x, pre_op == AMCT_PRE_MUL ? pre : nullptr,
                                    reinterpret_cast<int8_t*>(out), ld_out, scale, status, (cudaStream_t)stream);
+    if (rc != 1) return rc;
+  }
+  // groups that fit inside a warp: the shuffle-based kernel of quant_groups.cu
+  if (strategy == AMCT_STRATEGY_GROUP && rows > 0 && k > 0) {
+    int rc = amct::quant_groups_try(x, dtype, rows, k, ld_x, pre, pre_op, compute, group, bits, symmetric, scale, offset,
+                                    out_mode, out, ld_out, status, (cudaStream_t)stream);
     if (rc != 1) return rc;
   }
   RowParams p{};

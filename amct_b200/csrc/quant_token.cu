@@ -9,11 +9,11 @@
 //     (cp.async.bulk + mbarrier), several rows ahead of the one being processed;
 //   * 16-bit inputs stay packed in registers; min / max use the packed NaN-propagating
 //     half2 / bfloat162 instructions (one instruction per two elements);
-//   * the quotient x / scale is computed as x * rn(1 / scale); that product is within
-//     |q| * 2^-22 of the correctly rounded quotient, so rint() of it equals rint() of the
-//     IEEE quotient unless it falls within 2^-12 of a rounding tie -- only then (about one
-//     vector in a thousand) the vector is redone with the IEEE division.  Codes are
-//     therefore bit-identical to division everywhere;
+//   * the quotient x / scale is computed from rn(1 / scale) with two FMA correction steps
+//     (div_by_recip in common.cuh), which yields the correctly rounded quotient: the value of
+//     the IEEE division, without its range checks and without a branch.  (A plain
+//     x * rn(1/scale) is not enough: 16-bit inputs make EXACT ties -- x / scale = k + 0.5 --
+//     common, and there the product rounds the wrong way a quarter of the time.)
 //   * rounding uses the add-1.5*2^23 trick (a full-rate FADD whose low mantissa byte is the
 //     two's-complement code) instead of the quarter-rate FRND / F2I conversions; the only
 //     clamp this rule can need is the upper one (a negative-dominant row divides by 128).
@@ -69,28 +69,15 @@ template <> struct Packed<__half> {
 __device__ __forceinline__ float max_nan(float a, float b) { return (a != a || b != b) ? NAN : fmaxf(a, b); }
 __device__ __forceinline__ float min_nan(float a, float b) { return (a != a || b != b) ? NAN : fminf(a, b); }
 
-// exact quotients for a vector whose fast-path quotients came too close to a tie (rare; kept
-// out of line so the hot loop stays small)
-__device__ __noinline__ uint32_t quant4_exact(float a, float b, float c, float d, float s) {
-  const float ra = __fadd_rn(fminf(__fdiv_rn(a, s), 127.f), kMagic), rb = __fadd_rn(fminf(__fdiv_rn(b, s), 127.f), kMagic);
-  const float rc = __fadd_rn(fminf(__fdiv_rn(c, s), 127.f), kMagic), rd = __fadd_rn(fminf(__fdiv_rn(d, s), 127.f), kMagic);
-  return pack4_s8(ra, rb, rc, rd);
-}
-
-// fast path for 4 values: quotient by reciprocal, rounded with the magic add; returns the packed
-// codes and raises `dist` to the largest distance of a quotient from the integer it rounded to
+// four quotients -> four codes: x / scale by the FMA sequence of div_by_recip (bit-identical to the
+// IEEE division), rounded half to even by the magic add
 template <bool CLAMP>
-__device__ __forceinline__ uint32_t quant4_fast(float a, float b, float c, float d, float y, float& dist) {
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float s, float y) {
   // only a negative-dominant row (divisor 128) can produce a quotient above 127.5
-  float ta = __fmul_rn(a, y), tb = __fmul_rn(b, y), tc = __fmul_rn(c, y), td = __fmul_rn(d, y);
+  float ta = div_by_recip(a, s, y), tb = div_by_recip(b, s, y), tc = div_by_recip(c, s, y), td = div_by_recip(d, s, y);
   if (CLAMP) { ta = fminf(ta, 127.f); tb = fminf(tb, 127.f); tc = fminf(tc, 127.f); td = fminf(td, 127.f); }
-  const float ra = __fadd_rn(ta, kMagic), rb = __fadd_rn(tb, kMagic), rc = __fadd_rn(tc, kMagic), rd = __fadd_rn(td, kMagic);
-  dist = fmaxf(dist, fmaxf(fmaxf(fabsf(__fsub_rn(ta, __fsub_rn(ra, kMagic))), fabsf(__fsub_rn(tb, __fsub_rn(rb, kMagic)))),
-                           fmaxf(fabsf(__fsub_rn(tc, __fsub_rn(rc, kMagic))), fabsf(__fsub_rn(td, __fsub_rn(rd, kMagic))))));
-  return pack4_s8(ra, rb, rc, rd);
+  return pack4_s8(__fadd_rn(ta, kMagic), __fadd_rn(tb, kMagic), __fadd_rn(tc, kMagic), __fadd_rn(td, kMagic));
 }
-
-constexpr float kTieGuard = 0.5f - 2.44140625e-4f;   // within 2^-12 of a tie the exact quotient decides
 
 // second pass over the row held in shared memory: quantize and store
 template <typename T, bool CLAMP>
@@ -98,21 +85,15 @@ __device__ __forceinline__ void quantize_row(const uint4* src, int8_t* qrow, int
 #pragma unroll 2
   for (int v = tid; v < nvec; v += nthr) {
     const uint4 raw = src[v];
-    float dist = 0.f;
     if constexpr (sizeof(T) == 2) {
       using P = Packed<T>;
       const typename P::V2* h = reinterpret_cast<const typename P::V2*>(&raw);
       const float f0 = P::lo(h[0]), f1 = P::hi(h[0]), f2 = P::lo(h[1]), f3 = P::hi(h[1]);
       const float f4 = P::lo(h[2]), f5 = P::hi(h[2]), f6 = P::lo(h[3]), f7 = P::hi(h[3]);
-      uint32_t w0 = quant4_fast<CLAMP>(f0, f1, f2, f3, y, dist);
-      uint32_t w1 = quant4_fast<CLAMP>(f4, f5, f6, f7, y, dist);
-      if (dist > kTieGuard) { w0 = quant4_exact(f0, f1, f2, f3, s); w1 = quant4_exact(f4, f5, f6, f7, s); }
-      *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(w0, w1);
+      *reinterpret_cast<uint2*>(qrow + (int64_t)v * 8) = make_uint2(quant4<CLAMP>(f0, f1, f2, f3, s, y), quant4<CLAMP>(f4, f5, f6, f7, s, y));
     } else {
       const float* f = reinterpret_cast<const float*>(&raw);
-      uint32_t w0 = quant4_fast<CLAMP>(f[0], f[1], f[2], f[3], y, dist);
-      if (dist > kTieGuard) w0 = quant4_exact(f[0], f[1], f[2], f[3], s);
-      *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = w0;
+      *reinterpret_cast<uint32_t*>(qrow + (int64_t)v * 4) = quant4<CLAMP>(f[0], f[1], f[2], f[3], s, y);
     }
   }
 }

@@ -164,6 +164,19 @@ def cases():
     yield ('fake_quant i4 g128 asym [11008x4096] bf16', lambda: randn(11008, 4096, torch.bfloat16, 0.02),
            lambda w: (lambda: ops.quant_rows(w, 'int4', False, 'group', 128, out='fake', check=False)),
            dict(nbytes=11008 * 4096 * 4 + 11008 * 32 * 8))
+    yield ('weight_quant_i4 g128 asym pack c5 gate/up [57344x8192] bf16', lambda: randn(57344, 8192, torch.bfloat16, 0.02),
+           lambda w: (lambda: ops.quant_rows(w, 'int4', False, 'group', 128, out='pack4', check=False)),
+           dict(nbytes=57344 * 8192 * 2 + 57344 * 8192 // 2 + 57344 * 64 * 8))
+    def setup_given():
+        w = randn(57344, 8192, torch.bfloat16, 0.02)
+        sc, off, _ = ops.quant_rows(w, 'int4', False, 'group', 128, out='none', check=False)
+        return w, sc, off
+    yield ('weight_codes_i4 g128 asym pack, given scales, c5 gate/up [57344x8192] bf16', setup_given,
+           lambda t: (lambda: ops.quant_rows(t[0], 'int4', False, 'group', 128, scale=t[1], offset=t[2], out='pack4', check=False)),
+           dict(nbytes=57344 * 8192 * 2 + 57344 * 8192 // 2 + 57344 * 64 * 8))
+    yield ('fake_quant_awq i4 g128 asym c5 gate/up [57344x8192] bf16', lambda: randn(57344, 8192, torch.bfloat16, 0.02),
+           lambda w: (lambda: ops.quant_rows(w, 'int4', False, 'group', 128, out='fake_awq', check=False)),
+           dict(nbytes=57344 * 8192 * 4 + 57344 * 64 * 8))
     # ---- observers
     yield ('minmax column [65536x8192] bf16', lambda: randn(65536, 8192, torch.bfloat16),
            lambda x: (lambda: ops.minmax(x, 'column')), dict(nbytes=65536 * 8192 * 2))

@@ -260,3 +260,55 @@ def test_channel_int8_weight_quant_streaming_path(dtype, smooth):
     q_ref = intq.weight_codes(ws, 'int8', s_ref)
     s, o, q = ops().quant_rows(w.cuda(), 'int8', True, 'channel', out='i8', pre=dev(f), pre_op='mul' if smooth else 'none')
     assert o is None and bits_equal(s.reshape(-1, 1), s_ref) and bits_equal(q, q_ref)
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize('qt,sym', [('int4', False), ('int4', True), ('int8', False)])
+@pytest.mark.parametrize('rows,k,gs', [(37, 1024, 128), (300, 4096, 32), (64, 2048, 256), (5, 512, 64), (16, 96, 48)])
+def test_group_weight_quant_oracle(dtype, qt, sym, rows, k, gs):
+    """Group-wise weight quantization (warp-shuffle kernel where the group fits a warp, row kernel
+    otherwise) against the oracle: factors, codes, packed nibbles and both fake-quant variants,
+    with and without an AWQ-style pre-division."""
+    g = torch.Generator().manual_seed(rows + k + gs)
+    w = (torch.randn(rows, k, generator=g) * 0.05).to(dtype)
+    w[0, :gs] = 0                                            # an all-zero group: scale becomes 1
+    w[1 % rows, gs:2 * gs] = w[1 % rows, gs:2 * gs].abs() * -1       # a negative-only group
+    pre = (torch.rand(k, generator=g) + 0.5).to(dtype)
+    for pre_t, pre_op in ((None, 'none'), (pre, 'div')):
+        wp = w if pre_t is None else w / pre_t
+        s, o = intq.weight_scale_offset(wp, qt, sym, 'group', gs)
+        kw = dict(pre=None if pre_t is None else pre_t.cuda(), pre_op=pre_op)
+        s2, o2, codes = ops().quant_rows(w.cuda(), qt, sym, 'group', gs, out='i32', **kw)
+        assert bits_equal(s2.reshape(s.shape), s)
+        if not sym:
+            assert bits_equal(o2.reshape(o.shape), o.to(torch.int32))
+        want = intq.crop_groups(intq.weight_codes(wp, qt, s, o, gs), w.shape).to(torch.int32)
+        assert bits_equal(codes, want.contiguous())
+        # given factors (the deploy path), int8 codes
+        _, _, c8 = ops().quant_rows(w.cuda(), qt, sym, 'group', gs, scale=s.cuda(), offset=dev(o), out='i8', **kw)
+        assert bits_equal(c8, want.to(torch.int8).contiguous())
+        if qt == 'int4':
+            _, _, packed = ops().quant_rows(w.cuda(), qt, sym, 'group', gs, scale=s.cuda(), offset=dev(o), out='pack4', **kw)
+            nib = (want + 8).to(torch.uint8)
+            assert bits_equal(packed, (nib[:, 0::2] | (nib[:, 1::2] << 4)).contiguous())
+        _, _, fake = ops().quant_rows(w.cuda(), qt, sym, 'group', gs, scale=s.cuda(), offset=dev(o), out='fake', **kw)
+        assert bits_equal(fake, intq.fake_quant(wp, qt, s, o, gs))
+        _, _, fake_awq = ops().quant_rows(w.cuda(), qt, sym, 'group', gs, scale=s.cuda(), offset=dev(o), out='fake_awq', **kw)
+        assert bits_equal(fake_awq, intq.fake_quant_awq(wp, qt, s, o, gs))
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_group_weight_quant_rounding_ties(dtype):
+    """Weights that are exact multiples of half a quantization step: every quotient is an integer or
+    a tie, where a reciprocal-multiply shortcut and the IEEE division may disagree."""
+    g = torch.Generator().manual_seed(9)
+    rows, k, gs = 64, 1024, 128
+    steps = torch.randint(-15, 16, (rows, k), generator=g).float() * 0.5          # multiples of 0.5 in [-7.5, 7.5]
+    scale = torch.tensor([0.0078125, 0.013671875, 0.1, 0.3]).repeat(rows * k // gs // 4 + 1)[:rows * k // gs].reshape(rows, k // gs, 1)
+    w = (steps.reshape(rows, k // gs, gs) * scale).reshape(rows, k).to(dtype)
+    for off in (None, torch.randint(-3, 4, (rows, k // gs, 1), generator=g).to(torch.int32)):
+        want = intq.crop_groups(intq.weight_codes(w, 'int4', scale, off, gs), w.shape).to(torch.int32)
+        _, _, codes = ops().quant_rows(w.cuda(), 'int4', off is None, 'group', gs, scale=scale.cuda(), offset=dev(off), out='i32')
+        assert bits_equal(codes, want.contiguous())
+        _, _, fake_awq = ops().quant_rows(w.cuda(), 'int4', off is None, 'group', gs, scale=scale.cuda(), offset=dev(off), out='fake_awq')
+        assert bits_equal(fake_awq, intq.fake_quant_awq(w, 'int4', scale, off, gs))
