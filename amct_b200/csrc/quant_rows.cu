@@ -61,22 +61,42 @@ __device__ __forceinline__ float apply_pre(float x, const T* pre, int64_t j, int
 struct UnitQ {
   float scale, offset;
   bool has_offset;
+  float recip;                 // rn(1 / scale) when the FMA division applies, else 0
 };
+
+// the FMA division of common.cuh needs a normal scale and a normal reciprocal
+__device__ __forceinline__ float usable_recip(float s) {
+  const float y = __frcp_rn(s);
+  const bool ok = fabsf(s) >= 1.17549435e-38f && fabsf(y) >= 1.17549435e-38f && isfinite(y) && isfinite(s);
+  return ok ? y : 0.f;
+}
+
+// x / scale as the reference's torch division gives it: the branch-free FMA sequence where it is
+// valid (and the result is finite), the IEEE division otherwise
+__device__ __forceinline__ float quotient(float x, const UnitQ& u) {
+  if (u.recip != 0.f) {
+    const float q = div_by_recip(x, u.scale, u.recip);
+    if (fabsf(q) <= 3.0e38f) return q;
+  }
+  return __fdiv_rn(x, u.scale);
+}
 
 template <typename T>
 __device__ __forceinline__ float level_of(float x, const UnitQ& u, const RowParams& p, float qmin, float qmax) {
   if (p.rule == AMCT_RULE_EXPERIMENTAL) {
     // division carried out in the input dtype (node.py:39-43 on T tensors)
-    float t = round_to<T>(__fdiv_rn(x, u.scale));
+    float t = round_to<T>(quotient(x, u));
     return fminf(fmaxf(rintf(t), qmin), qmax);
   }
   if (p.out_mode == AMCT_OUT_FAKE_AWQ) {
-    float t = __fdiv_rn(x, u.scale);
+    float t = quotient(x, u);
     if (u.has_offset) t = __fadd_rn(t, u.offset);
     t = round_to<T>(t);                               // awq.py:149 casts before rounding
     return fminf(fmaxf(rintf(t), qmin), qmax);
   }
-  return quant_level(x, u.scale, u.offset, u.has_offset, qmin, qmax);
+  float t = quotient(x, u);
+  if (u.has_offset) t = __fadd_rn(t, u.offset);
+  return fminf(fmaxf(rintf(t), qmin), qmax);
 }
 
 template <typename T>
@@ -208,7 +228,7 @@ __global__ void __launch_bounds__(512) quant_rows_vec_kernel(RowParams p) {
     if (v >= nvec) continue;
     const int64_t j0 = (int64_t)v * E;
     const int u = p.strategy == AMCT_STRATEGY_GROUP ? (int)(j0 / p.group) : 0;
-    UnitQ uq{s_scale[u], s_off[u], has_off};
+    UnitQ uq{s_scale[u], s_off[u], has_off, usable_recip(s_scale[u])};
     float lv[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) lv[e] = level_of<T>(val[i][e], uq, p, qmin, qmax);
@@ -319,7 +339,7 @@ __global__ void __launch_bounds__(256) quant_rows_generic_kernel(RowParams p) {
         if (j < p.k) {
           float f = apply_pre<T>(ElemTraits<T>::to_f(xrow[j]), pre, j, p.pre_op);
           int u = (int)(j / gsz);
-          UnitQ uq{s_scale[u], s_off[u], has_off};
+          UnitQ uq{s_scale[u], s_off[u], has_off, 0.f};
           q = (int)level_of<T>(f, uq, p, qmin, qmax);
         }
         byte |= (uint32_t)((q + 8) & 0xF) << (4 * h);
@@ -331,7 +351,7 @@ __global__ void __launch_bounds__(256) quant_rows_generic_kernel(RowParams p) {
   for (int64_t j = tid; j < p.k; j += nthr) {
     float f = apply_pre<T>(ElemTraits<T>::to_f(xrow[j]), pre, j, p.pre_op);
     int u = (int)(j / gsz);
-    UnitQ uq{s_scale[u], s_off[u], has_off};
+    UnitQ uq{s_scale[u], s_off[u], has_off, 0.f};
     float lv = level_of<T>(f, uq, p, qmin, qmax);
     if (p.out_mode == AMCT_OUT_I8) reinterpret_cast<int8_t*>(p.out)[row * p.ld_out + j] = (int8_t)(int)lv;
     else if (p.out_mode == AMCT_OUT_I32) reinterpret_cast<int*>(p.out)[row * p.ld_out + j] = (int)lv;
