@@ -80,30 +80,97 @@ __global__ void __launch_bounds__(256) minmax_tensor_final_kernel(const float* p
   }
 }
 
-// grid (column blocks, row chunks); each thread owns E adjacent columns.
+// packed NaN-propagating min / max of two 16-bit values per instruction
+__device__ __forceinline__ __nv_bfloat162 pmax2(__nv_bfloat162 a, __nv_bfloat162 b) { return __hmax2_nan(a, b); }
+__device__ __forceinline__ __nv_bfloat162 pmin2(__nv_bfloat162 a, __nv_bfloat162 b) { return __hmin2_nan(a, b); }
+__device__ __forceinline__ __half2 pmax2(__half2 a, __half2 b) { return __hmax2_nan(a, b); }
+__device__ __forceinline__ __half2 pmin2(__half2 a, __half2 b) { return __hmin2_nan(a, b); }
+template <typename T> struct Pair2;
+template <> struct Pair2<__nv_bfloat16> { using type = __nv_bfloat162; };
+template <> struct Pair2<__half> { using type = __half2; };
+
+// grid (column blocks, row chunks); each thread owns E adjacent columns and walks its row chunk
+// four rows at a time (four independent 16-byte loads in flight).  16-bit inputs stay packed: one
+// NaN-propagating min and max instruction per two elements, a NaN shows in the result.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(128) minmax_column_kernel(const T* x, int64_t rows, int64_t k, int64_t ld,
                                                             float* part, int* status) {
   constexpr int E = VEC ? ElemTraits<T>::kPerVec : 1;
+  constexpr int U = 4;
   const int64_t c0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * E;
   if (c0 >= k) return;
   const int64_t per = (rows + gridDim.y - 1) / gridDim.y;
   const int64_t r0 = blockIdx.y * per, r1 = min(rows, r0 + per);
   float mn[E], mx[E];
   bool nan = false;
+  if constexpr (VEC && sizeof(T) == 2) {
+    using P2 = typename Pair2<T>::type;
+    P2 pmn[E / 2], pmx[E / 2];
+    {
+      const Vec16<T> first = ld_vec(x + (r0 < r1 ? r0 : 0) * ld + c0);       // seed with a real row
+      const P2* h = reinterpret_cast<const P2*>(&first);
 #pragma unroll
-  for (int e = 0; e < E; ++e) { mn[e] = INFINITY; mx[e] = -INFINITY; }
-  for (int64_t r = r0; r < r1; ++r) {
-    if constexpr (VEC) {
-      Vec16<T> raw = ld_vec_stream(x + r * ld + c0);
+      for (int e = 0; e < E / 2; ++e) { pmn[e] = h[e]; pmx[e] = h[e]; }
+    }
+    int64_t r = r0;
+    for (; r + U <= r1; r += U) {
+      Vec16<T> raw[U];
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        float f = ElemTraits<T>::to_f(raw.v[e]);
-        mn[e] = fminf(mn[e], f); mx[e] = fmaxf(mx[e], f); nan |= (f != f);
+      for (int u = 0; u < U; ++u) raw[u] = ld_vec_stream(x + (r + u) * ld + c0);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const P2* h = reinterpret_cast<const P2*>(&raw[u]);
+#pragma unroll
+        for (int e = 0; e < E / 2; ++e) { pmn[e] = pmin2(pmn[e], h[e]); pmx[e] = pmax2(pmx[e], h[e]); }
       }
-    } else {
-      float f = ElemTraits<T>::to_f(x[r * ld + c0]);
-      mn[0] = fminf(mn[0], f); mx[0] = fmaxf(mx[0], f); nan |= (f != f);
+    }
+    for (; r < r1; ++r) {
+      const Vec16<T> raw = ld_vec_stream(x + r * ld + c0);
+      const P2* h = reinterpret_cast<const P2*>(&raw);
+#pragma unroll
+      for (int e = 0; e < E / 2; ++e) { pmn[e] = pmin2(pmn[e], h[e]); pmx[e] = pmax2(pmx[e], h[e]); }
+    }
+#pragma unroll
+    for (int e = 0; e < E / 2; ++e) {
+      mn[2 * e] = __low2float(pmn[e]); mn[2 * e + 1] = __high2float(pmn[e]);
+      mx[2 * e] = __low2float(pmx[e]); mx[2 * e + 1] = __high2float(pmx[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      nan |= (mn[e] != mn[e]) || (mx[e] != mx[e]);
+      if (r0 >= r1) { mn[e] = INFINITY; mx[e] = -INFINITY; }               // empty chunk
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < E; ++e) { mn[e] = INFINITY; mx[e] = -INFINITY; }
+    int64_t r = r0;
+    if constexpr (VEC) {
+      for (; r + U <= r1; r += U) {
+        Vec16<T> raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) raw[u] = ld_vec_stream(x + (r + u) * ld + c0);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            const float f = ElemTraits<T>::to_f(raw[u].v[e]);
+            mn[e] = fminf(mn[e], f); mx[e] = fmaxf(mx[e], f); nan |= (f != f);
+          }
+        }
+      }
+    }
+    for (; r < r1; ++r) {
+      if constexpr (VEC) {
+        const Vec16<T> raw = ld_vec_stream(x + r * ld + c0);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float f = ElemTraits<T>::to_f(raw.v[e]);
+          mn[e] = fminf(mn[e], f); mx[e] = fmaxf(mx[e], f); nan |= (f != f);
+        }
+      } else {
+        const float f = ElemTraits<T>::to_f(x[r * ld + c0]);
+        mn[0] = fminf(mn[0], f); mx[0] = fmaxf(mx[0], f); nan |= (f != f);
+      }
     }
   }
   if (nan && status) atomicOr(status, 1);

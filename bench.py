@@ -286,6 +286,17 @@ def main():
     value = tokens * args.steps / (ms_total / 1e3)
     achieved = gemm_ops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
     peak = 2 * bf16_sus
+    # DRAM traffic of the dominant launch (the gate/up GEMM, 57344 x 8192 weights): ncu measured
+    # dram__bytes_read + dram__bytes_write = 2.865 GB for 8192 token rows (profiles/gemm_pair_vs_single_steady_state.md);
+    # the B operand is re-streamed once per 2048-row group and A / C grow with the rows, so a launch's
+    # traffic is proportional to its rows.  Only quoted for the unsharded prefill shape it was captured on.
+    traffic, traffic_note = None, None
+    if world == 1 and args.mode == 'prefill':
+        rows = args.batch * args.seq
+        # captured with a plain bf16 epilogue (1.949 GB read, 0.916 GB written); the SwiGLU epilogue writes half the columns
+        traffic = (1.949e9 + 0.916e9 / 2) * rows / 8192.0
+        traffic_note = ('bytes per gate/up GEMM launch: ncu dram read + write of the 8192-row case scaled by rows; '
+                        'algorithmic A + B + C of that launch is %.3g' % (rows * 8192.0 + 57344 * 8192.0 + rows * 28672 * 2.0))
     line = {
         'metric': METRIC if args.mode == 'prefill' else METRIC.replace('prefill', 'decode'), 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
         'ms_per_step': ms_total / args.steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
@@ -299,8 +310,8 @@ def main():
                 'd2h_bytes_per_step': logits_host.numel() * logits_host.element_size()},
         'gpu_launches': launches,
         'roofline': {'bound': 'tensor', 'kernel': 'gemm_tcgen05_kernel (kind::i8)', 'achieved': achieved, 'peak': peak,
-                     'unit': 'TOP/s', 'frac': (achieved / peak) if achieved else None, 'traffic': None,
-                     'launches_per_step': n_gemm, 'gemm_ms_per_step': gemm_ms,
+                     'unit': 'TOP/s', 'frac': (achieved / peak) if achieved else None, 'traffic': traffic,
+                     'traffic_note': traffic_note, 'launches_per_step': n_gemm, 'gemm_ms_per_step': gemm_ms,
                      'peak_source': f'2 x bf16_tflops_sustained ({bf16_sus}) of {src}; no direct INT8 peak measurement'},
         'clocks': clocks,
     }
