@@ -376,6 +376,75 @@ def dequant_weight(codes_nk, bits, scale_gn, offset_gn, group, out=None):
     return out
 
 
+def gemm_w4a16(x, codes_nk, bits, scale_gn, offset_gn, group, bias=None, out_dtype=None, out=None, status=None):
+    """x [M, K] (fp16 / bf16) times the group-dequantized weight, one kernel (dequant in shared
+    memory ahead of the MMA).  Returns None when the shape is outside what the fused kernel takes
+    (the caller then uses dequant_weight + gemm_f16)."""
+    _need_cuda(x, codes_nk, scale_gn, offset_gn, bias)
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise _l.BackendError('gemm_w4a16: float16 / bfloat16 activations only')
+    x = _kmajor(x)
+    m, k = x.shape
+    n = codes_nk.shape[0]
+    assert codes_nk.stride(1) == 1 and codes_nk.shape[1] * (2 if bits == 4 else 1) == k
+    scale_gn = scale_gn.to(x.dtype).contiguous()
+    if offset_gn is not None:
+        offset_gn = offset_gn.to(x.dtype).contiguous()
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    bk = 0
+    if bias is not None:
+        bias = bias.reshape(-1).contiguous()
+        bk = _BIAS_KIND[bias.dtype]
+    prof = _prof_begin()
+    rc = _l.load().amct_gemm_w4a16(
+        _p(x), c_int(_dt(x)), _p(codes_nk), c_int(bits), c_int64(m), c_int64(n), c_int64(k), c_int64(x.stride(0)),
+        c_int64(codes_nk.stride(0)), _p(scale_gn), _p(offset_gn), c_int(group or 0), _p(bias), c_int(bk), _p(out),
+        c_int(_OUT_KIND[out.dtype]), c_int64(out.stride(0)), _p(status) if status is not None else c_void_p(0), _stream())
+    if rc in (-4, -2):            # AMCT_ERR_UNSUPPORTED, AMCT_ERR_ALIGN: the caller takes the two-kernel route
+        return None
+    _l.check(rc, 'amct_gemm_w4a16')
+    COUNTERS['launches'] += 1
+    _prof_end(prof, 2 * m * n * k)
+    return out
+
+
+_HIF8_LUT = {}
+
+
+def gemm_hif8_weight(x, codes_nk, bias=None, out_dtype=None, out=None, status=None):
+    """x [M, K] (fp16 / bf16) times HiFloat8 weight codes [N, K], decoded exactly in shared memory
+    ahead of the MMA.  Returns None for shapes the fused kernel does not take."""
+    _need_cuda(x, codes_nk, bias)
+    x = _kmajor(x)
+    m, k = x.shape
+    n = codes_nk.shape[0]
+    assert codes_nk.dtype == torch.uint8 and codes_nk.stride(1) == 1 and codes_nk.shape[1] == k
+    key = (x.device, x.dtype)
+    if key not in _HIF8_LUT:
+        _HIF8_LUT[key] = hif8_decode(torch.arange(256, dtype=torch.uint8, device=x.device), dtype=x.dtype)
+    lut = _HIF8_LUT[key]
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    bk = 0
+    if bias is not None:
+        bias = bias.reshape(-1).contiguous()
+        bk = _BIAS_KIND[bias.dtype]
+    prof = _prof_begin()
+    rc = _l.load().amct_gemm_lut8(
+        _p(x), c_int(_dt(x)), _p(codes_nk), _p(lut), c_int64(m), c_int64(n), c_int64(k), c_int64(x.stride(0)),
+        c_int64(codes_nk.stride(0)), _p(bias), c_int(bk), _p(out), c_int(_OUT_KIND[out.dtype]), c_int64(out.stride(0)),
+        _p(status) if status is not None else c_void_p(0), _stream())
+    if rc in (-4, -2):
+        return None
+    _l.check(rc, 'amct_gemm_lut8')
+    COUNTERS['launches'] += 1
+    _prof_end(prof, 2 * m * n * k)
+    return out
+
+
 def minmax_noalloc(x, axis, out_min, out_max, merge=False):
     """amct_minmax without a workspace and without any allocation: the caller passes the
     input and both outputs (in x's dtype; 1 element for axis 'tensor', K for 'column').

@@ -104,13 +104,38 @@ __device__ __forceinline__ uint32_t hif8_lookup(const uint8_t* tab, float x) {
   return abits > 0x7f800000u ? 0x80u : t;
 }
 
+// The two tables, built once per device by hif8_init_tables and copied into shared memory by every
+// CTA (building the 4096 entries in each CTA cost as much as the encoding itself).
+static __device__ __align__(16) uint8_t g_hif8_tab[4096];
+static __device__ __align__(16) float g_hif8_dec[256];
+
+__global__ void hif8_init_tables() {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < 4096) g_hif8_tab[i] = (uint8_t)hif8_encode(__uint_as_float((uint32_t)i << 19));
+  if (i < 256) g_hif8_dec[i] = hif8_decode(i);
+}
+
+// Launch-ordered on `st` before the first use on each device; repeating it is harmless.
+static int ensure_tables(cudaStream_t st) {
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return AMCT_ERR_CUDA;
+  if (dev >= 0 && dev < 64 && done[dev]) return AMCT_OK;
+  // the tables must be complete before any later kernel on any stream reads them
+  hif8_init_tables<<<16, 256, 0, st>>>();
+  AMCT_CHECK_LAUNCH();
+  if (cudaStreamSynchronize(st) != cudaSuccess) return AMCT_ERR_CUDA;
+  if (dev >= 0 && dev < 64) done[dev] = true;
+  return AMCT_OK;
+}
+
 // mode 0: encode x -> codes;  mode 1: fake-quantize x -> decode(encode(x)) in T
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) hif8_encode_kernel(const T* x, int64_t n, uint8_t* codes, T* fake) {
-  __shared__ uint8_t tab[4096];
+  __shared__ __align__(16) uint8_t tab[4096];
   __shared__ float dec[256];
-  for (int i = threadIdx.x; i < 4096; i += blockDim.x) tab[i] = (uint8_t)hif8_encode(__uint_as_float((uint32_t)i << 19));
-  if (MODE == 1) dec[threadIdx.x] = hif8_decode(threadIdx.x);
+  reinterpret_cast<uint4*>(tab)[threadIdx.x] = reinterpret_cast<const uint4*>(g_hif8_tab)[threadIdx.x];
+  if (MODE == 1) dec[threadIdx.x] = g_hif8_dec[threadIdx.x];
   __syncthreads();
   constexpr int U = 2;
   const int64_t nv = n / 8;
@@ -162,7 +187,7 @@ __global__ void __launch_bounds__(256) hif8_encode_kernel(const T* x, int64_t n,
 template <typename T>
 __global__ void __launch_bounds__(256) hif8_decode_kernel(const uint8_t* codes, int64_t n, T* out) {
   __shared__ float table[256];
-  table[threadIdx.x] = hif8_decode(threadIdx.x);
+  table[threadIdx.x] = g_hif8_dec[threadIdx.x];
   __syncthreads();
   const int64_t nv = n / 8;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -188,6 +213,8 @@ static unsigned grid_for(int64_t n) {
 
 template <typename T>
 static int run_encode(const T* x, int64_t n, uint8_t* codes, T* fake, cudaStream_t st) {
+  const int rc = ensure_tables(st);
+  if (rc != AMCT_OK) return rc;
   if (codes) hif8_encode_kernel<T, 0><<<grid_for(n), 256, 0, st>>>(x, n, codes, nullptr);
   else hif8_encode_kernel<T, 1><<<grid_for(n), 256, 0, st>>>(x, n, nullptr, fake);
   AMCT_CHECK_LAUNCH();
@@ -220,6 +247,8 @@ extern "C" int amct_hif8_decode(const void* codes, int64_t n, int dtype, void* o
   if (reinterpret_cast<uintptr_t>(codes) % 8 || !amct::aligned16(out)) return AMCT_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
   const uint8_t* c = reinterpret_cast<const uint8_t*>(codes);
+  const int rc = amct::ensure_tables(st);
+  if (rc != AMCT_OK) return rc;
   const unsigned grid = amct::grid_for(n);
   switch (dtype) {
     case AMCT_DTYPE_F32: amct::hif8_decode_kernel<float><<<grid, 256, 0, st>>>(c, n, (float*)out); break;

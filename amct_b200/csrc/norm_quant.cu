@@ -63,11 +63,25 @@ __device__ __forceinline__ float block_sum(float v, float* part, int warp, int l
   return t;
 }
 
-// 16-bit T only; NV 16-byte vectors (8 elements each) per thread, NT threads per row.
+template <typename T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  __device__ static type from_floats(float a, float b) { return __floats2bfloat162_rn(a, b); }
+};
+template <> struct Pack2<__half> {
+  using type = __half2;
+  __device__ static type from_floats(float a, float b) { return __floats2half2_rn(a, b); }
+};
+
+// 16-bit T only; NV 16-byte vectors (8 elements each) per thread, NT threads per row.  Values stay
+// packed two to a register wherever the arithmetic allows: the residual add is the packed add (the
+// exact sum of two 16-bit floats rounded once, which is what an fp32 add followed by the rounding to
+// T gives as well), min / max use the packed NaN-propagating instructions, conversions go pairwise.
 template <typename T, int NV, int NT>
 __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
   constexpr int E = 8;
   constexpr int NW = NT / 32;
+  using P2 = typename Pack2<T>::type;
   __shared__ float part_sum[2][NW];
   __shared__ float part_mx[2][NW], part_mn[2][NW];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -94,51 +108,61 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
       for (int j = 0; j < NV; ++j) {
         const int v = tid + j * NT;
         if (v < nvec) {
+          P2* hp = reinterpret_cast<P2*>(&h[j]);
+          const P2* rp = reinterpret_cast<const P2*>(&r[j]);
 #pragma unroll
-          for (int e = 0; e < E; ++e)
-            h[j].v[e] = ElemTraits<T>::from_f(__fadd_rn(ElemTraits<T>::to_f(h[j].v[e]), ElemTraits<T>::to_f(r[j].v[e])));
+          for (int e = 0; e < E / 2; ++e) hp[e] = __hadd2(hp[e], rp[e]);
           if (p.residual_out)
             *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.residual_out) + row * p.ld_res_out + v * E) =
                 *reinterpret_cast<const uint4*>(&h[j]);
         }
       }
     }
-    // ---- mean of squares (fp32)
+    // ---- mean of squares (fp32); the unpacked values are kept for the normalisation
+    float f[NV][E];
     float ssq = 0.f;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       if (tid + j * NT < nvec) {
+        const P2* hp = reinterpret_cast<const P2*>(&h[j]);
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float f = ElemTraits<T>::to_f(h[j].v[e]);
-          ssq = __fmaf_rn(f, f, ssq);
+        for (int e = 0; e < E / 2; ++e) {
+          f[j][2 * e] = __low2float(hp[e]);
+          f[j][2 * e + 1] = __high2float(hp[e]);
+          ssq = __fmaf_rn(f[j][2 * e], f[j][2 * e], ssq);
+          ssq = __fmaf_rn(f[j][2 * e + 1], f[j][2 * e + 1], ssq);
         }
       }
     }
     const float total = block_sum<NW>(ssq, part_sum[it], warp, lane);
     const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)p.k), p.eps));
-    // ---- normalise, round to T, min / max
-    float mx = -INFINITY, mn = INFINITY;
-    bool bad = false;
+    // ---- normalise, round to T (pairwise), packed min / max
+    P2 vmx = Pack2<T>::from_floats(-INFINITY, -INFINITY), vmn = Pack2<T>::from_floats(INFINITY, INFINITY);
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int v = tid + j * NT;
       if (v < nvec) {
         const Vec16<T> g = ld_vec(gamma + v * E);
+        const P2* gp = reinterpret_cast<const P2*>(&g);
+        P2* hp = reinterpret_cast<P2*>(&h[j]);
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const T n = ElemTraits<T>::from_f(__fmul_rn(__fmul_rn(ElemTraits<T>::to_f(h[j].v[e]), rstd), ElemTraits<T>::to_f(g.v[e])));
-          h[j].v[e] = n;
-          const float f = ElemTraits<T>::to_f(n);
-          mx = fmaxf(mx, f);
-          mn = fminf(mn, f);
-          bad |= (f != f);
+        for (int e = 0; e < E / 2; ++e) {
+          hp[e] = Pack2<T>::from_floats(__fmul_rn(__fmul_rn(f[j][2 * e], rstd), __low2float(gp[e])),
+                                        __fmul_rn(__fmul_rn(f[j][2 * e + 1], rstd), __high2float(gp[e])));
+          vmx = __hmax2_nan(vmx, hp[e]);
+          vmn = __hmin2_nan(vmn, hp[e]);
         }
         if (p.norm_out)
           *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.norm_out) + row * p.ld_norm + v * E) = *reinterpret_cast<const uint4*>(&h[j]);
       }
     }
-    if (bad) { mx = INFINITY; mn = 0.f; }           // a NaN in the row: infinite scale, row flagged
+    float mx, mn;
+    {
+      const float a0 = __low2float(vmx), a1 = __high2float(vmx), b0 = __low2float(vmn), b1 = __high2float(vmn);
+      // a NaN in the row: infinite scale, row flagged
+      if (a0 != a0 || a1 != a1 || b0 != b0 || b1 != b1) { mx = INFINITY; mn = 0.f; }
+      else { mx = fmaxf(a0, a1); mn = fminf(b0, b1); }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -164,10 +188,10 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
     for (int j = 0; j < NV; ++j) {
       const int v = tid + j * NT;
       if (v < nvec) {
-        float f[E];
-#pragma unroll
-        for (int e = 0; e < E; ++e) f[e] = ElemTraits<T>::to_f(h[j].v[e]);
-        *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(nq_quant4(f[0], f[1], f[2], f[3], s, y), nq_quant4(f[4], f[5], f[6], f[7], s, y));
+        const P2* hp = reinterpret_cast<const P2*>(&h[j]);
+        const uint32_t w0 = nq_quant4(__low2float(hp[0]), __high2float(hp[0]), __low2float(hp[1]), __high2float(hp[1]), s, y);
+        const uint32_t w1 = nq_quant4(__low2float(hp[2]), __high2float(hp[2]), __low2float(hp[3]), __high2float(hp[3]), s, y);
+        *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(w0, w1);
       }
     }
   }

@@ -10,8 +10,8 @@ class HiFloat8Linear(torch.nn.Module):
     K-contiguous [N, K] storage), ``scale_factor`` [1, K] reciprocal smoothing factor (only
     when the calibration produced one), ``bias``.  forward(): activations are multiplied by
     scale_factor, rounded to HiFloat8 and back in one pass; the weight codes are decoded
-    (exactly) to the activation dtype and the product runs on the tensor cores with fp32
-    accumulation.  B200 has no HiFloat8 MMA, so the 16-bit MMA on exactly decoded operands
+    (exactly) to the activation dtype -- in shared memory, ahead of the MMA, inside the GEMM
+    kernel -- and the product runs on the tensor cores with fp32 accumulation.  B200 has no HiFloat8 MMA, so the 16-bit MMA on exactly decoded operands
     is the arithmetic definition of this layer.
     """
 
@@ -42,6 +42,11 @@ class HiFloat8Linear(torch.nn.Module):
             x2 = x2 * self.scale_factor
         xq = ops.hif8_fake_quant(x2)
         w = self._decoded
+        if w is None and x.dtype in (torch.float16, torch.bfloat16):
+            # one kernel: the weight codes are decoded in shared memory ahead of the MMA
+            out = ops.gemm_hif8_weight(xq, self.quantized_weight.t(), bias=self.bias, out_dtype=x.dtype)
+            if out is not None:
+                return out.reshape(*x.shape[:-1], -1)
         if w is None:
             w = ops.hif8_decode(self.quantized_weight.t(), dtype=x.dtype)
             if self.cache_decoded_weight:

@@ -39,10 +39,15 @@ def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=No
     """x [M, K] (fp16/bf16) times the dequantized weight; weight is int8 [K, N] or packed
     uint8 [K/2, N] as produced by npu_convert_weight_to_int4pack."""
     bits = 4 if weight.dtype == torch.uint8 else 8
-    w = ops.dequant_weight(_as_nk(weight), bits, antiquant_scale.to(x.dtype), antiquant_offset,
-                           antiquant_group_size)
     k = x.shape[-1]
-    out = ops.gemm_f16(x.reshape(-1, k), w, bias=bias, out_dtype=x.dtype)
+    codes_nk = _as_nk(weight)
+    # one kernel: codes dequantized in shared memory ahead of the MMA; shapes it does not take go
+    # through the two-kernel route (dequantize to HBM, then the 16-bit GEMM)
+    out = ops.gemm_w4a16(x.reshape(-1, k), codes_nk, bits, antiquant_scale, antiquant_offset, antiquant_group_size,
+                         bias=bias, out_dtype=x.dtype)
+    if out is None:
+        w = ops.dequant_weight(codes_nk, bits, antiquant_scale.to(x.dtype), antiquant_offset, antiquant_group_size)
+        out = ops.gemm_f16(x.reshape(-1, k), w, bias=bias, out_dtype=x.dtype)
     return out.reshape(*x.shape[:-1], -1)
 
 

@@ -192,15 +192,29 @@ def cases():
             b = torch.randint(-128, 128, (n, k), device='cuda', dtype=torch.int8)
             return (a, b, torch.rand(n, device='cuda') * 1e-3, torch.rand(m, device='cuda'),
                     torch.empty(m, n, device='cuda', dtype=od))
+        # M <= 128 streams the weight once: that launch is bound by HBM, not by the tensor cores
+        kw = dict(nops=2 * m * n * k, peak_mult=2.0) if m > 128 else dict(nbytes=n * k + m * k + m * n * (4 if od == torch.float32 else 2))
         yield (f'gemm_w8a8 {tag} {m}x{n}x{k} -> {str(od)[6:]}', setup,
-               lambda t: (lambda: ops.gemm_w8a8(t[0], t[1], t[2], t[3], None, out=t[4])), dict(nops=2 * m * n * k, peak_mult=2.0))
+               lambda t: (lambda: ops.gemm_w8a8(t[0], t[1], t[2], t[3], None, out=t[4])), kw)
     # ---- 16-bit GEMM
     for m, n, k, tag in ((8192, 8192, 8192, 'square'), (4096, 11008, 4096, 'c2 M=4096'), (128, 11008, 4096, 'c2 M=128'),
                          (16384, 14336, 4096, 'c4 gate')):
         def setup16(m=m, n=n, k=k):
             return (randn(m, k, torch.bfloat16), randn(n, k, torch.bfloat16, 0.02), torch.empty(m, n, device='cuda', dtype=torch.bfloat16))
-        yield (f'gemm_f16 bf16 {tag} {m}x{n}x{k}', setup16, lambda t: (lambda: ops.gemm_f16(t[0], t[1], out=t[2])),
-               dict(nops=2 * m * n * k, peak_mult=1.0))
+        kw = dict(nops=2 * m * n * k, peak_mult=1.0) if m > 128 else dict(nbytes=2 * (n * k + m * k + m * n))
+        yield (f'gemm_f16 bf16 {tag} {m}x{n}x{k}', setup16, lambda t: (lambda: ops.gemm_f16(t[0], t[1], out=t[2])), kw)
+    # ---- W4A16 Linear, one kernel (dequant in shared memory ahead of the MMA): config 2 sweep over M
+    for m in (1, 16, 128, 1024, 4096):
+        def setup_w4(m=m):
+            n, k = 11008, 4096
+            codes = torch.randint(0, 256, (n, k // 2), device='cuda', dtype=torch.uint8)
+            sc = (torch.rand(k // 128, n, device='cuda') * 0.01 + 0.002).to(torch.bfloat16)
+            off = torch.randint(-8, 8, (k // 128, n), device='cuda').to(torch.bfloat16)
+            return randn(m, k, torch.bfloat16), codes, sc, off, torch.empty(m, n, device='cuda', dtype=torch.bfloat16)
+        nbytes = 11008 * 2048 + 2 * 32 * 11008 * 2 + m * 4096 * 2 + m * 11008 * 2
+        kw = dict(nbytes=nbytes) if m <= 128 else dict(nops=2 * m * 11008 * 4096, peak_mult=1.0)
+        yield (f'gemm_w4a16 fused c2 M={m} {m}x11008x4096 g128 bf16', setup_w4,
+               lambda t: (lambda: ops.gemm_w4a16(t[0], t[1], 4, t[2], t[3], 128, out=t[4])), kw)
     # ---- MX quantization and block-scaled GEMM (config 3 shapes)
     for fmt, pb in (('fp8', 1.0), ('fp4', 0.5)):
         for r, k, opnd, tag in ((8192, 8192, 'a', 'c3 act'), (28672, 8192, 'b', 'c3 weight')):

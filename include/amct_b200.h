@@ -191,6 +191,27 @@ int amct_dequant_weight(const void* codes, int bits, int64_t n_rows, int64_t k, 
                         const void* scale, const void* offset, int group, int dtype, void* out,
                         int64_t ld_out, void* stream);
 
+/* The weight-only quantized Linear in one kernel:
+ *   out[m, n] = sum_k x[m, k] * w[n, k] + bias[n],  w[n, k] = (code[n, k] + offset[g(k), n]) * scale[g(k), n]
+ * with w rounded to `dtype` exactly as amct_dequant_weight rounds it, dequantized in shared memory
+ * ahead of the tcgen05 MMA (the 16-bit weight is never written to HBM).  Replaces
+ * torch_npu.npu_weight_quant_batchmatmul (amct_pytorch/deploy_op/weight_npu_quant_module.py:116-117).
+ * x [m, k] in `dtype` (F16 / BF16), codes / scale / offset / group as for amct_dequant_weight;
+ * bias_kind: AMCT_BIAS_NONE / F32 / F16 / BF16; out_kind: AMCT_GEMM_OUT_F32 / F16 / BF16.
+ * k % 64 == 0, group % 64 == 0 (or 0), k % group == 0; other shapes: AMCT_ERR_UNSUPPORTED (use
+ * amct_dequant_weight + amct_gemm_f16).  *status bit 1: a bounded wait expired. */
+int amct_gemm_w4a16(const void* x, int dtype, const void* codes, int bits, int64_t m, int64_t n, int64_t k,
+                    int64_t ld_x, int64_t ld_codes, const void* scale, const void* offset, int group,
+                    const void* bias, int bias_kind, void* out, int out_kind, int64_t ld_out, int* status,
+                    void* stream);
+
+/* Same kernel with a table instead of the integer rule: one code byte per weight, w[n, k] = lut[code[n, k]],
+ * lut = 256 values in `dtype`.  Used for HiFloat8 weights (lut = the exact decode of every code; no counterpart
+ * in the reference).  codes [n, k] uint8, K contiguous; k % 64 == 0. */
+int amct_gemm_lut8(const void* x, int dtype, const void* codes, const void* lut, int64_t m, int64_t n, int64_t k,
+                   int64_t ld_x, int64_t ld_codes, const void* bias, int bias_kind, void* out, int out_kind,
+                   int64_t ld_out, int* status, void* stream);
+
 /* ---- MX formats (no counterpart in the reference: amct_pytorch/utils/vars.py:19-20
  * admits int8 / int4 only; the rule is the public OCP Microscaling v1.0 conversion) ---- */
 
