@@ -18,7 +18,8 @@
 //   warp 6     TMA of the x tile (BN x 128 bytes) of each 64-element K step;
 //   warp 1     TMEM allocation; one elected lane issues tcgen05.mma (M128 x N BN x K16, kind::f16);
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator (lane = output channel n), bias, transposed store;
-//   warps 7-22 dequant: four threads per weight row turn the raw codes of a K step into 16-bit values
+//   warps 7-22 dequant, four groups of four warps, group g on the K steps g (mod 4): one thread per weight row turns
+//              the raw codes of a K step into 16-bit values
 //              and write them into the stage's A tile in the swizzled layout the MMA descriptor
 //              expects (packed arithmetic for INT4: nibble | 0x4300 is the bf16 number 128 + nibble),
 //              then fence.proxy.async and arrive on the stage's `ready` barrier.
@@ -109,7 +110,12 @@ __global__ void __launch_bounds__(kDqThreads, 1)
 gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __grid_constant__ CUtensorMap tma_x, DqParams p) {
   constexpr int SUB = BITS == 4 ? 4 : 2;                           // MMA stages (64 K elements) per raw slot
   constexpr int SUBB = kDqRawRowBytes / SUB;                       // raw bytes per row and MMA stage: 32 or 64
-  constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  // MMAs that accumulate into the same TMEM tile are serialised by that dependency, and with BN this small one MMA is
+  // far shorter than the pipeline's latency: the four K-16 MMAs of a stage go to NACC separate accumulators instead,
+  // which the epilogue adds up (fp32).
+  constexpr int NACC = BN <= 64 ? 4 : 2;
+  constexpr int kAccCols = NACC * BN;                              // columns of one (double-buffered) accumulator set
+  constexpr int kTmemCols = 2 * kAccCols;                          // 256 or 512: a power of two
   using Smem = DqSmem<BN, STAGES, XSLOTS, RSLOTS>;
   extern __shared__ uint8_t smem_raw[];
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -122,7 +128,7 @@ gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __gr
   if (threadIdx.x == 0) {
     s.abort_flag = 0;
     for (int i = 0; i < STAGES; ++i) {
-      tc05::mbar_init(tc05::smem_u32(&s.ready[i]), kDqWarpsDequant);
+      tc05::mbar_init(tc05::smem_u32(&s.ready[i]), kDqWarpsDequant / 4);     // the four warps of one dequant group
       tc05::mbar_init(tc05::smem_u32(&s.empty[i]), 1);
     }
     for (int i = 0; i < XSLOTS; ++i) {
@@ -131,7 +137,7 @@ gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __gr
     }
     for (int i = 0; i < RSLOTS; ++i) {
       tc05::mbar_init(tc05::smem_u32(&s.full_raw[i]), 1);
-      tc05::mbar_init(tc05::smem_u32(&s.empty_raw[i]), kDqWarpsDequant);
+      tc05::mbar_init(tc05::smem_u32(&s.empty_raw[i]), (kDqWarpsDequant / 4) * SUB);   // each of the slot's SUB steps is one group's
     }
     for (int i = 0; i < 2; ++i) { tc05::mbar_init(tc05::smem_u32(&s.tmem_full[i]), 1); tc05::mbar_init(tc05::smem_u32(&s.tmem_empty[i]), 4); }
     tc05::fence_barrier_init();
@@ -191,7 +197,7 @@ gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __gr
       for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_empty[acc]), acc_phase ^ 1, abort_flag)) break;
         tc05::fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * kAccCols;
         for (int64_t kb = 0; kb < num_kb; ++kb) {
           if (!tc05::mbar_wait(tc05::smem_u32(&s.full_x[xs]), xphase, abort_flag) ||
               !tc05::mbar_wait(tc05::smem_u32(&s.ready[stage]), phase, abort_flag)) { alive = false; break; }
@@ -202,7 +208,8 @@ gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __gr
           for (int ks = 0; ks < kBKBytes / 32; ++ks) {
             const uint64_t adesc = tc05::smem_desc_sw128(a0 + ks * 32);
             const uint64_t bdesc = tc05::smem_desc_sw128(b0 + ks * 32);
-            tc05::umma_f16(d_tmem, adesc, bdesc, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            // K-16 step ks of every stage goes to accumulator ks % NACC; its first use overwrites
+            tc05::umma_f16(d_tmem + (ks % NACC) * BN, adesc, bdesc, idesc, (kb > 0 || ks >= NACC) ? 1u : 0u);
           }
           tc05::umma_commit(tc05::smem_u32(&s.empty[stage]));        // the A tile may be overwritten
           tc05::umma_commit(tc05::smem_u32(&s.empty_x[xs]));         // and the x slot refilled
@@ -225,12 +232,20 @@ gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __gr
       const float bias = (p.bias_kind != BIAS_NONE && n < p.n) ? bias_at(p.bias, p.bias_kind, n) : 0.f;
       if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_full[acc]), acc_phase, abort_flag)) break;
       tc05::fence_after_sync();
-      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kAccCols;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         tc05::tmem_ld_32x32(t_row + c0, r);
         tc05::tmem_ld_wait();
+#pragma unroll 1
+        for (int a = 1; a < NACC; ++a) {                             // add the other partial accumulators
+          uint32_t r2[32];
+          tc05::tmem_ld_32x32(t_row + a * BN + c0, r2);
+          tc05::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(r2[j])));
+        }
         if (n < p.n) {
           // a warp writes 32 adjacent channels of one token per store
           const int64_t mleft = p.m - (m0 + c0);
@@ -259,35 +274,41 @@ gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __gr
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   } else {
-    // ------------------------------------------------------------ dequant (warps 7..): four threads per weight row
+    // ------------------------------------------------------------ dequant (warps 7..): four groups of four warps.  Group g
+    // owns the K steps kb = g (mod 4) and one thread of it owns one weight row (64 values per step): a step costs a warp
+    // several hundred cycles of latency (shared-memory round trips, the barrier hand-offs), and four groups working on
+    // four consecutive steps at once hide that.
     const int dt = threadIdx.x - 7 * 32;
-    const int row = dt >> 2, qtr = dt & 3;                         // qtr: elements [16 qtr, 16 qtr + 16) of the 64-element K step
+    const int grp = dt >> 7, row = dt & 127;
     const int steps_per_group = p.group ? p.group / kDqBK : 0;
-    uint32_t stage = 0, phase = 0, rslot = 0, rphase = 0;
+    const uint32_t kb_pad = (uint32_t)((num_kb + SUB - 1) / SUB * SUB);     // K steps rounded up to whole raw slots
+    const uint32_t slots_per_tile = kb_pad / SUB;
+    uint32_t t_ord = 0;                                             // tiles this CTA has started
     bool alive = true;
-    for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+    for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++t_ord) {
       const int64_t tw = tile % tiles_w;
       const int64_t n = tw * kBM + row;
       const bool valid = n < p.n;
-      int64_t g = 0;
-      int left_in_group = 0;                                       // K steps until the next group's scale is needed
+      int64_t cur_g = -1;
       uint32_t addc = 0, scl = 0;                                  // packed (offset constant, scale), both halves equal
       float fs = 0.f, fo = 0.f;
-      // the scale / offset of the NEXT group are fetched while the current group is being processed: the load's
-      // latency (an L2 round trip) would otherwise sit on every group boundary of this thread's critical path
-      uint16_t sb_next = 0, ob_next = 0;
-      const int64_t num_groups = steps_per_group ? (num_kb + steps_per_group - 1) / steps_per_group : 1;
-      if (valid && BITS != 1) {
-        sb_next = reinterpret_cast<const uint16_t*>(p.scale)[n];
-        if (p.offset) ob_next = reinterpret_cast<const uint16_t*>(p.offset)[n];
-      }
-      for (int64_t kb = 0; kb < num_kb; ++kb) {
-        if (left_in_group == 0 && (kb == 0 || steps_per_group)) {  // this row's next group begins
-          const uint16_t sb = sb_next, ob = ob_next;
-          ++g;
-          if (valid && BITS != 1 && g < num_groups) {
-            sb_next = reinterpret_cast<const uint16_t*>(p.scale)[g * p.n + n];
-            if (p.offset) ob_next = reinterpret_cast<const uint16_t*>(p.offset)[g * p.n + n];
+      for (uint32_t kb = grp; kb < kb_pad; kb += 4) {
+        const uint32_t slot_seq = t_ord * slots_per_tile + kb / SUB;
+        const uint32_t rslot = slot_seq % RSLOTS, rphase = (slot_seq / RSLOTS) & 1;
+        if (kb >= (uint32_t)num_kb) {                              // padding step of the last raw slot: only release it
+          __syncwarp();
+          if (lane == 0) tc05::mbar_arrive(tc05::smem_u32(&s.empty_raw[rslot]));
+          continue;
+        }
+        const uint32_t seq = t_ord * (uint32_t)num_kb + kb;
+        const uint32_t stage = seq % STAGES, phase = (seq / STAGES) & 1;
+        const int64_t g = steps_per_group ? kb / steps_per_group : 0;
+        if (g != cur_g) {                                          // this row's scale / offset for the group of this step
+          cur_g = g;
+          uint16_t sb = 0, ob = 0;
+          if (valid && BITS != 1) {
+            sb = reinterpret_cast<const uint16_t*>(p.scale)[g * p.n + n];
+            if (p.offset) ob = reinterpret_cast<const uint16_t*>(p.offset)[g * p.n + n];
           }
           fs = p.f16 ? dq_to_f<true>(sb) : dq_to_f<false>(sb);
           fo = p.f16 ? dq_to_f<true>(ob) : dq_to_f<false>(ob);
@@ -295,48 +316,51 @@ gemm_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_codes, const __gr
           const float c = fo - 8.f - (p.f16 ? 1024.f : 128.f);
           addc = p.f16 ? dq_pack2<true>(c, c) : dq_pack2<false>(c, c);
           scl = (uint32_t)sb | ((uint32_t)sb << 16);
-          left_in_group = steps_per_group;
         }
-        --left_in_group;
-        const int sub = (int)(kb % SUB);
-        if (sub == 0 && !tc05::mbar_wait(tc05::smem_u32(&s.full_raw[rslot]), rphase, abort_flag)) { alive = false; break; }
+        if (!tc05::mbar_wait(tc05::smem_u32(&s.full_raw[rslot]), rphase, abort_flag)) { alive = false; break; }
         // the MMAs that read this stage's previous contents are done
         if (!tc05::mbar_wait(tc05::smem_u32(&s.empty[stage]), phase ^ 1, abort_flag)) { alive = false; break; }
         const uint8_t* rawp = &s.raw[rslot][0];
         uint8_t* a_tile = &s.a_tile[stage][0];
-        uint32_t o[8];                                             // 16 values = two 16-byte chunks
+        const int sub = (int)(kb % SUB);
         if constexpr (BITS == 4) {
-          const uint2 raw = *reinterpret_cast<const uint2*>(rawp + sw128(row, sub * SUBB + qtr * 8));
-          uint32_t o0[4], o1[4];
-          if (p.f16) { dq_int4_word<true>(raw.x, addc, scl, o0); dq_int4_word<true>(raw.y, addc, scl, o1); }
-          else { dq_int4_word<false>(raw.x, addc, scl, o0); dq_int4_word<false>(raw.y, addc, scl, o1); }
+          const uint4 r0 = *reinterpret_cast<const uint4*>(rawp + sw128(row, sub * SUBB));
+          const uint4 r1 = *reinterpret_cast<const uint4*>(rawp + sw128(row, sub * SUBB + 16));
+          const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { o[j] = o0[j]; o[4 + j] = o1[j]; }
+          for (int c = 0; c < 8; ++c) {                            // word c = 8 nibbles = 16-byte chunk c of the A row
+            uint32_t o[4];
+            if (p.f16) dq_int4_word<true>(w[c], addc, scl, o);
+            else dq_int4_word<false>(w[c], addc, scl, o);
+            *reinterpret_cast<uint4*>(a_tile + sw128(row, c * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
         } else {
-          const uint4 raw = *reinterpret_cast<const uint4*>(rawp + sw128(row, sub * SUBB + qtr * 16));
-          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {                            // two code bytes -> two values
-            const uint32_t ww = w[j >> 1] >> (16 * (j & 1));
-            if constexpr (BITS == 1) {
-              o[j] = (uint32_t)s.lut[ww & 0xFF] | ((uint32_t)s.lut[(ww >> 8) & 0xFF] << 16);
-            } else {                                               // (q + aoff) * scale, rounded once
-              const float q0 = (float)(int)(int8_t)(ww & 0xFF), q1 = (float)(int)(int8_t)((ww >> 8) & 0xFF);
-              const float v0 = __fmul_rn(__fadd_rn(q0, fo), fs), v1 = __fmul_rn(__fadd_rn(q1, fo), fs);
-              o[j] = p.f16 ? dq_pack2<true>(v0, v1) : dq_pack2<false>(v0, v1);
+          for (int h = 0; h < 4; ++h) {                            // 16 code bytes -> two 16-byte chunks
+            const uint4 raw = *reinterpret_cast<const uint4*>(rawp + sw128(row, sub * SUBB + h * 16));
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {                          // two code bytes -> two values
+              const uint32_t ww = w[j >> 1] >> (16 * (j & 1));
+              if constexpr (BITS == 1) {
+                o[j] = (uint32_t)s.lut[ww & 0xFF] | ((uint32_t)s.lut[(ww >> 8) & 0xFF] << 16);
+              } else {                                             // (q + aoff) * scale, rounded once
+                const float q0 = (float)(int)(int8_t)(ww & 0xFF), q1 = (float)(int)(int8_t)((ww >> 8) & 0xFF);
+                const float v0 = __fmul_rn(__fadd_rn(q0, fo), fs), v1 = __fmul_rn(__fadd_rn(q1, fo), fs);
+                o[j] = p.f16 ? dq_pack2<true>(v0, v1) : dq_pack2<false>(v0, v1);
+              }
             }
+            *reinterpret_cast<uint4*>(a_tile + sw128(row, h * 32)) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(a_tile + sw128(row, h * 32 + 16)) = make_uint4(o[4], o[5], o[6], o[7]);
           }
         }
-        *reinterpret_cast<uint4*>(a_tile + sw128(row, qtr * 32)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4*>(a_tile + sw128(row, qtr * 32 + 16)) = make_uint4(o[4], o[5], o[6], o[7]);
         tc05::fence_proxy_async();                                 // these generic-proxy stores are read by the MMA (async proxy)
         __syncwarp();
         if (lane == 0) {
           tc05::mbar_arrive(tc05::smem_u32(&s.ready[stage]));
-          if (sub == SUB - 1 || kb == num_kb - 1) tc05::mbar_arrive(tc05::smem_u32(&s.empty_raw[rslot]));
+          tc05::mbar_arrive(tc05::smem_u32(&s.empty_raw[rslot]));
         }
-        if (sub == SUB - 1 || kb == num_kb - 1) { if (++rslot == RSLOTS) { rslot = 0; rphase ^= 1; } }
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   }

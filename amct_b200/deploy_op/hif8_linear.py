@@ -42,7 +42,7 @@ class HiFloat8Linear(torch.nn.Module):
             x2 = x2 * self.scale_factor
         xq = ops.hif8_fake_quant(x2)
         w = self._decoded
-        if w is None and x.dtype in (torch.float16, torch.bfloat16):
+        if w is None and x.dtype in (torch.float16, torch.bfloat16) and x2.shape[0] <= 512:
             # one kernel: the weight codes are decoded in shared memory ahead of the MMA
             out = ops.gemm_hif8_weight(xq, self.quantized_weight.t(), bias=self.bias, out_dtype=x.dtype)
             if out is not None:

@@ -34,6 +34,9 @@ def npu_quant_matmul(x1, x2, scale, offset=None, bias=None, pertoken_scale=None,
     return out.reshape(*x1.shape[:-1], -1)
 
 
+FUSED_MAX_TOKENS = 512
+
+
 def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, quant_scale=None,
                                  quant_offset=None, bias=None, antiquant_group_size=0, **_):
     """x [M, K] (fp16/bf16) times the dequantized weight; weight is int8 [K, N] or packed
@@ -41,10 +44,14 @@ def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=No
     bits = 4 if weight.dtype == torch.uint8 else 8
     k = x.shape[-1]
     codes_nk = _as_nk(weight)
-    # one kernel: codes dequantized in shared memory ahead of the MMA; shapes it does not take go
-    # through the two-kernel route (dequantize to HBM, then the 16-bit GEMM)
-    out = ops.gemm_w4a16(x.reshape(-1, k), codes_nk, bits, antiquant_scale, antiquant_offset, antiquant_group_size,
-                         bias=bias, out_dtype=x.dtype)
+    # up to FUSED_MAX_TOKENS rows: one kernel, codes dequantized in shared memory ahead of the MMA (the weight is
+    # streamed once, in its packed form).  More rows, or shapes that kernel does not take: dequantize to HBM once and
+    # run the 16-bit GEMM, whose larger tiles win once the work is tensor-bound (measured cross-over 512-1024 rows).
+    x2 = x.reshape(-1, k)
+    out = None
+    if x2.shape[0] <= FUSED_MAX_TOKENS:
+        out = ops.gemm_w4a16(x2, codes_nk, bits, antiquant_scale, antiquant_offset, antiquant_group_size,
+                             bias=bias, out_dtype=x.dtype)
     if out is None:
         w = ops.dequant_weight(codes_nk, bits, antiquant_scale.to(x.dtype), antiquant_offset, antiquant_group_size)
         out = ops.gemm_f16(x.reshape(-1, k), w, bias=bias, out_dtype=x.dtype)
