@@ -455,20 +455,21 @@ static int run_dq(const void* x, int dtype, const void* codes, int bits, int64_t
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t tiles = ((n + kBM - 1) / kBM) * ((m + bn - 1) / bn);
   const int grid = (int)(tiles < sms ? tiles : sms);
-  // shared memory: STAGES x 16 KB (A) + XSLOTS x BN x 128 B (x) + RSLOTS x 16 KB (codes)
+  // shared memory: STAGES x 16 KB (A) + XSLOTS x BN x 128 B (x) + RSLOTS x 16 KB (codes).  Each of the four dequant
+  // groups needs two A slots of its own (it fills one while the MMAs read the other): STAGES = 8 where that fits.
   if (bits == 4) {
-    if (bn == 32) return launch_dq<32, 4, 16, 4, 4>(mc, mx, p, grid, st);
-    if (bn == 64) return launch_dq<64, 4, 10, 4, 4>(mc, mx, p, grid, st);
-    return launch_dq<128, 4, 6, 3, 4>(mc, mx, p, grid, st);
+    if (bn == 32) return launch_dq<32, 8, 8, 2, 4>(mc, mx, p, grid, st);
+    if (bn == 64) return launch_dq<64, 8, 6, 2, 4>(mc, mx, p, grid, st);
+    return launch_dq<128, 6, 4, 2, 4>(mc, mx, p, grid, st);
   }
   if (bits == 8) {
-    if (bn == 32) return launch_dq<32, 4, 16, 4, 8>(mc, mx, p, grid, st);
-    if (bn == 64) return launch_dq<64, 4, 10, 4, 8>(mc, mx, p, grid, st);
-    return launch_dq<128, 4, 6, 3, 8>(mc, mx, p, grid, st);
+    if (bn == 32) return launch_dq<32, 8, 8, 2, 8>(mc, mx, p, grid, st);
+    if (bn == 64) return launch_dq<64, 8, 6, 2, 8>(mc, mx, p, grid, st);
+    return launch_dq<128, 6, 4, 2, 8>(mc, mx, p, grid, st);
   }
-  if (bn == 32) return launch_dq<32, 4, 16, 4, 1>(mc, mx, p, grid, st);
-  if (bn == 64) return launch_dq<64, 4, 10, 4, 1>(mc, mx, p, grid, st);
-  return launch_dq<128, 4, 6, 3, 1>(mc, mx, p, grid, st);
+  if (bn == 32) return launch_dq<32, 8, 8, 2, 1>(mc, mx, p, grid, st);
+  if (bn == 64) return launch_dq<64, 8, 6, 2, 1>(mc, mx, p, grid, st);
+  return launch_dq<128, 6, 4, 2, 1>(mc, mx, p, grid, st);
 }
 
 extern "C" int amct_gemm_w4a16(const void* x, int dtype, const void* codes, int bits, int64_t m, int64_t n, int64_t k,
