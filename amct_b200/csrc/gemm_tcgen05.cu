@@ -210,15 +210,24 @@ static int make_map(CUtensorMap* map, const void* base, int esize, int64_t rows,
   return r == CUDA_SUCCESS ? AMCT_OK : AMCT_ERR_CUDA;
 }
 
-static int sm_count() {
+// Number of persistent CTAs: one per SM, or fewer when AMCT_GEMM_MAX_CTAS is set.  A job that runs collectives next to
+// its GEMMs (tensor parallelism) leaves a few SMs to the communication kernels that way: a persistent CTA that cannot be
+// placed until a communication kernel has left its SM would delay its whole statically assigned share of the tiles.
+int gemm_cta_budget() {
   static int n = 0;
   if (!n) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
   }
+  const char* e = getenv("AMCT_GEMM_MAX_CTAS");
+  if (e) {
+    const int cap = atoi(e);
+    if (cap >= 2 && cap < n) return cap & ~1;        // even: the pair kernel launches clusters of two
+  }
   return n;
 }
+static int sm_count() { return gemm_cta_budget(); }
 
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st);
 

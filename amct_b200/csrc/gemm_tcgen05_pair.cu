@@ -185,15 +185,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   }
 }
 
+int gemm_cta_budget();        // gemm_tcgen05.cu: SM count, or the AMCT_GEMM_MAX_CTAS cap
+
 static int max_pairs() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    n = sms / 2 > 0 ? sms / 2 : 1;
-  }
-  return n;
+  const int n = gemm_cta_budget() / 2;
+  return n > 0 ? n : 1;
 }
 
 // tma_a: box of 128 rows of A; tma_b: box of 128 rows of B (half a tile).

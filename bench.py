@@ -56,6 +56,8 @@ def parse():
     ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (2 streams when N > 1)')
     ap.add_argument('--no-seq-parallel', action='store_true',
                     help='A/B only: replicated activations + all-reduce instead of the token-sharded residual stream')
+    ap.add_argument('--gemm-ctas', type=int, default=0,
+                    help='A/B only: cap the persistent GEMM CTAs (AMCT_GEMM_MAX_CTAS), leaving SMs to the NCCL kernels')
     ap.add_argument('--torch-glue', action='store_true',
                     help='A/B only: RMSNorm, residual adds and rotary embedding as torch ops instead of the fused kernels')
     return ap.parse_args()
@@ -175,6 +177,8 @@ def main():
     args = parse()
     if args.impl == 'reference':
         return run_reference(args)
+    if args.gemm_ctas:
+        os.environ['AMCT_GEMM_MAX_CTAS'] = str(args.gemm_ctas)
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
