@@ -56,6 +56,9 @@ def parse():
     ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (2 streams when N > 1)')
     ap.add_argument('--no-seq-parallel', action='store_true',
                     help='A/B only: replicated activations + all-reduce instead of the token-sharded residual stream')
+    ap.add_argument('--torch-profile', default='',
+                    help='diagnostic: after the timed runs, profile one more step with torch.profiler on rank 0 and write the '
+                         'per-kernel totals (text) to this file')
     ap.add_argument('--gemm-ctas', type=int, default=0,
                     help='A/B only: cap the persistent GEMM CTAs (AMCT_GEMM_MAX_CTAS), leaving SMs to the NCCL kernels')
     ap.add_argument('--torch-glue', action='store_true',
@@ -272,6 +275,16 @@ def main():
     launches = ops.COUNTERS['launches'] if graph is None else launches_per_replay * args.steps
     clocks = sampler.stop() if sampler else None
     ms_e2e = timed(step_e2e, args.steps)
+    if args.torch_profile:
+        from torch.profiler import profile, ProfilerActivity
+        if world > 1:
+            dist.barrier()
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            step_resident()
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.torch_profile, 'w') as f:
+                f.write(prof.key_averages().table(sort_by='cuda_time_total', row_limit=40, max_name_column_width=70))
 
     # roofline of the dominant kernel: one more step with CUDA events around every GEMM launch
     ops.GEMM_PROFILE = []
