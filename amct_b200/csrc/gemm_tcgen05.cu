@@ -238,6 +238,8 @@ constexpr int64_t kPairMaxBBytes = 96LL << 20;
 static bool use_pair_kernel(const GemmParams& p, int esize) {
   if (p.m <= 128) return false;
   const char* e = getenv("AMCT_GEMM_VARIANT");
+  const char* sm = getenv("AMCT_GEMM_SMEM");
+  if (sm && sm[0] == 's') return false;            // the small-footprint mode exists for the one-CTA kernel only
   if (e && e[0] == 's') return false;
   if (e && e[0] == 'p') return true;
   return p.n * p.k * esize <= kPairMaxBBytes;
@@ -273,14 +275,28 @@ static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b,
     }
     gemm_tcgen05_kernel<kBNSmall, kStagesSmall><<<grid, kThreads, smem, st>>>(ma, mb, p);
   } else {
-    const size_t smem = sizeof(GemmSmem<kBNLarge, kStagesLarge>) + 1024;
-    static bool attr_large = false;
-    if (!attr_large) {
-      if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNLarge, kStagesLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return AMCT_ERR_CUDA;
-      attr_large = true;
+    // AMCT_GEMM_SMEM=small: a three-stage ring (153 KB instead of 201 KB of shared memory per SM), so that the CTAs of a
+    // communication kernel running next to the GEMM fit on the same SMs
+    const char* e = getenv("AMCT_GEMM_SMEM");
+    if (e && e[0] == 's') {
+      const size_t smem = sizeof(GemmSmem<kBNLarge, 3>) + 1024;
+      static bool attr_small3 = false;
+      if (!attr_small3) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNLarge, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+          return AMCT_ERR_CUDA;
+        attr_small3 = true;
+      }
+      gemm_tcgen05_kernel<kBNLarge, 3><<<grid, kThreads, smem, st>>>(ma, mb, p);
+    } else {
+      const size_t smem = sizeof(GemmSmem<kBNLarge, kStagesLarge>) + 1024;
+      static bool attr_large = false;
+      if (!attr_large) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNLarge, kStagesLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+          return AMCT_ERR_CUDA;
+        attr_large = true;
+      }
+      gemm_tcgen05_kernel<kBNLarge, kStagesLarge><<<grid, kThreads, smem, st>>>(ma, mb, p);
     }
-    gemm_tcgen05_kernel<kBNLarge, kStagesLarge><<<grid, kThreads, smem, st>>>(ma, mb, p);
   }
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;

@@ -59,6 +59,8 @@ def parse():
     ap.add_argument('--torch-profile', default='',
                     help='diagnostic: after the timed runs, profile one more step with torch.profiler on rank 0 and write the '
                          'per-kernel totals (text) to this file')
+    ap.add_argument('--gemm-small-smem', action='store_true',
+                    help='A/B only: three-stage GEMM ring, leaving shared memory to communication kernels on the same SMs')
     ap.add_argument('--gemm-ctas', type=int, default=0,
                     help='A/B only: cap the persistent GEMM CTAs (AMCT_GEMM_MAX_CTAS), leaving SMs to the NCCL kernels')
     ap.add_argument('--torch-glue', action='store_true',
@@ -182,6 +184,8 @@ def main():
         return run_reference(args)
     if args.gemm_ctas:
         os.environ['AMCT_GEMM_MAX_CTAS'] = str(args.gemm_ctas)
+    if args.gemm_small_smem:
+        os.environ['AMCT_GEMM_SMEM'] = 'small'
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
