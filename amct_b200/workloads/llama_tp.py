@@ -37,6 +37,11 @@ import torch.nn.functional as F
 import amct_b200 as amct
 from amct_b200.backend import ops
 
+import os
+
+# how the INT8 codes are handed to the all-gather: as bytes, or (same memory) as 32-bit words
+GATHER_CODES_AS_WORDS = os.environ.get('AMCT_GATHER_WORDS', '0') == '1'
+
 W8A8_DYNAMIC_CFG = {
     'batch_num': 1,
     'quant_cfg': {
@@ -155,7 +160,11 @@ class DecoderLayer(nn.Module):
         s_all = torch.empty(tp * rows, dtype=torch.float32, device=x_loc.device)
         q_loc, s_loc = q_all[rank * rows:(rank + 1) * rows], s_all[rank * rows:(rank + 1) * rows]
         _, _, h, _ = ops.addnorm_quant_per_token(x_loc, gamma, self.shape.rms_eps, residual=residual_loc, out_q=q_loc, out_scale=s_loc)
-        dist.all_gather_into_tensor(q_all, q_loc, group=self.group)
+        if GATHER_CODES_AS_WORDS and hid % 4 == 0:
+            # same bytes, gathered as 32-bit words
+            dist.all_gather_into_tensor(q_all.view(torch.int32), q_loc.view(torch.int32), group=self.group)
+        else:
+            dist.all_gather_into_tensor(q_all, q_loc, group=self.group)
         dist.all_gather_into_tensor(s_all, s_loc, group=self.group)
         return q_all, s_all, (h if h is not None else x_loc)
 
