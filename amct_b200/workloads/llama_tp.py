@@ -288,12 +288,14 @@ class LlamaW8A8(nn.Module):
     def forward(self, token_ids, kv_caches=None, past_len=0, micro_batches=None):
         """token_ids [B, S] -> logits of the last position [B, vocab] (fp32).
 
-        With tp > 1 the batch is cut into micro-batches that run on separate CUDA streams,
-        layer by layer: while one micro-batch waits for its all-reduce the other one's
-        kernels run, so the NVLink transfer overlaps the GEMMs."""
+        micro_batches > 1 (tp > 1) cuts the batch into micro-batches that run on separate CUDA
+        streams, half layer by half layer, so that one micro-batch's collective can run while
+        the other one computes."""
         b, s = token_ids.shape
         if micro_batches is None:
-            micro_batches = 2 if (self.tp > 1 and kv_caches is None and b >= 2) else 1
+            # one micro-batch by default: with two (two CUDA streams, ping-pong order) the collectives of one ran next to
+            # the GEMMs of the other only on paper -- measured 27.4 vs 27.9 k tokens/s at 2 GPUs, 68.0 vs 69.8 k at 8
+            micro_batches = 1
         pos = torch.arange(past_len, past_len + s, device=token_ids.device)
         cos, sin = rotary_tables(self.shape, pos, token_ids.device)
         sp = self.seq_parallel and kv_caches is None and (b // micro_batches) * s % self.tp == 0 and b % micro_batches == 0
