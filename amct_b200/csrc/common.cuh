@@ -1,9 +1,9 @@
 // Shared device helpers for the quantization kernels (sm_100a).
 //
 // Numerics contract shared by every kernel in this directory: fp32 arithmetic,
-// IEEE division (__fdiv_rn), round-half-to-even (rintf), no FMA contraction
-// (explicit __fmul_rn/__fadd_rn; the quant files are also compiled with
-// -fmad=false).  These choices make integer codes bit-identical to the
+// correctly rounded division (__fdiv_rn, or div_by_recip below, which returns the
+// same value), round-half-to-even, no FMA contraction of x*s+z (explicit
+// __fmul_rn/__fadd_rn; the quant files are also compiled with -fmad=false).  These choices make integer codes bit-identical to the
 // reference's torch arithmetic (amct_pytorch/utils/quant_util.py:57-93).
 #pragma once
 #include <cuda_runtime.h>
@@ -107,15 +107,6 @@ __device__ __forceinline__ bool qparams_from_minmax(float mx, float mn, int bits
   *scale = s;
   *offset = (int)o;
   return isfinite(s) && isfinite(o);
-}
-
-// One element through the integer quantizer: clamp(rne(x/scale + offset)).
-__device__ __forceinline__ float quant_level(float x, float scale, float offset, bool has_offset,
-                                             float qmin, float qmax) {
-  float t = __fdiv_rn(x, scale);
-  if (has_offset) t = __fadd_rn(t, offset);
-  t = rintf(t);
-  return fminf(fmaxf(t, qmin), qmax);
 }
 
 // Correctly rounded x / s computed from y = rn(1 / s) (__frcp_rn) with two FMA correction steps

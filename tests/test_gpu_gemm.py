@@ -28,13 +28,18 @@ def status():
     return torch.zeros(1, dtype=torch.int32, device='cuda')
 
 
-@pytest.fixture(params=['auto', 'single', 'pair'])
+@pytest.fixture(params=['auto', 'single', 'pair', 'small_smem', 'capped'])
 def variant(request, monkeypatch):
-    """Which kernel takes M > 128: the size rule, the one-CTA kernel, or the CTA-pair kernel."""
-    if request.param != 'auto':
+    """Which kernel takes M > 128: the size rule, the one-CTA kernel, the CTA-pair kernel, the one-CTA kernel
+    with the three-stage ring, or either with the number of persistent CTAs capped."""
+    for name in ('AMCT_GEMM_VARIANT', 'AMCT_GEMM_SMEM', 'AMCT_GEMM_MAX_CTAS'):
+        monkeypatch.delenv(name, raising=False)
+    if request.param in ('single', 'pair'):
         monkeypatch.setenv('AMCT_GEMM_VARIANT', request.param)
-    else:
-        monkeypatch.delenv('AMCT_GEMM_VARIANT', raising=False)
+    elif request.param == 'small_smem':
+        monkeypatch.setenv('AMCT_GEMM_SMEM', 'small')
+    elif request.param == 'capped':
+        monkeypatch.setenv('AMCT_GEMM_MAX_CTAS', '6')
     return request.param
 
 
