@@ -98,7 +98,9 @@ class NpuQuantizationLinear(torch.nn.Module):
             self.bias = self.offset_bias
 
     @torch.no_grad()
-    def forward(self, x):
+    def forward(self, x, out=None):
+        """`out` (optional, not in the reference): a preallocated [rows, N] tensor the GEMM writes into, e.g. a
+        peer-mapped buffer the other ranks read the partial result from."""
         smooth = getattr(self, 'scale_factor', None)
         k = x.shape[-1]
         wq_nk = self.quantized_weight.t()
@@ -109,16 +111,16 @@ class NpuQuantizationLinear(torch.nn.Module):
             pertoken = self.pertoken_scale
             if pertoken is not None and x.dim() > 2:
                 pertoken = pertoken.repeat(x.numel() // (x.shape[-2] * k))
-        return self._gemm(q, pertoken)
+        return self._gemm(q, pertoken, out)
 
-    def _gemm(self, q, pertoken):
+    def _gemm(self, q, pertoken, out=None):
         k = q.shape[-1]
         wq_nk = self.quantized_weight.t()
         if self.fused_act == 'swiglu':
-            out = ops.gemm_w8a8_swiglu(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias)
-            return out.reshape(*q.shape[:-1], -1)
-        out = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out_dtype=self.output_dtype)
-        return out.reshape(*q.shape[:-1], -1)
+            res = ops.gemm_w8a8_swiglu(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out=out)
+            return res.reshape(*q.shape[:-1], -1)
+        res = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out_dtype=self.output_dtype, out=out)
+        return res.reshape(*q.shape[:-1], -1)
 
     @torch.no_grad()
     def forward_quantized(self, q, pertoken_scale):

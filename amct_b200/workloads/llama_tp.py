@@ -117,6 +117,56 @@ def apply_rotary(x, cos, sin):
     return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s), dim=-1)
 
 
+class PeerBuffers:
+    """Collectives of the token-sharded prefill done by the copy engines over peer-mapped (symmetric) buffers, so that
+    no communication kernel competes with the GEMMs for SMs: every rank writes its slice / partial into its own
+    buffer, a barrier, every rank PULLS what it needs from the peers' buffers with plain device-to-device copies, a
+    second barrier (the buffers may be overwritten), and a local sum for the reduce-scatter.  One instance per
+    micro-batch stream; all ranks call its methods in the same order."""
+
+    TIMEOUT_MS = 60000          # of one barrier: a rank that never arrives ends the wait instead of hanging the GPU
+
+    def __init__(self, group, rows_total, hidden, device):
+        import os
+        os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')      # plain peer mappings only: nothing here uses multimem
+        import torch.distributed._symmetric_memory as symm
+        dist = torch.distributed
+        self.tp, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.rows = rows_total // self.tp
+        self.codes = symm.empty((rows_total, hidden), dtype=torch.int8, device=device)
+        self.scales = symm.empty((rows_total,), dtype=torch.float32, device=device)
+        self.partial = symm.empty((rows_total, hidden), dtype=torch.bfloat16, device=device)
+        self.h_codes = symm.rendezvous(self.codes, group)
+        self.h_scales = symm.rendezvous(self.scales, group)
+        self.h_partial = symm.rendezvous(self.partial, group)
+
+    def local_slices(self):
+        sl = slice(self.rank * self.rows, (self.rank + 1) * self.rows)
+        return self.codes[sl], self.scales[sl]
+
+    def gather_codes(self):
+        """The local slices of codes / scales have been written: fetch everybody else's."""
+        self.h_codes.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+        for step in range(1, self.tp):
+            r = (self.rank - step) % self.tp
+            sl = slice(r * self.rows, (r + 1) * self.rows)
+            self.codes[sl].copy_(self.h_codes.get_buffer(r, tuple(self.codes.shape), torch.int8)[sl])
+            self.scales[sl].copy_(self.h_scales.get_buffer(r, tuple(self.scales.shape), torch.float32)[sl])
+        self.h_codes.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+        return self.codes, self.scales
+
+    def reduce_scatter_partial(self):
+        """self.partial holds this rank's [T, H] partial sums: return the sum over ranks of rows [rank T/tp, ...)."""
+        self.h_partial.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+        mine = slice(self.rank * self.rows, (self.rank + 1) * self.rows)
+        staging = torch.empty((self.tp, self.rows, self.partial.shape[1]), dtype=self.partial.dtype, device=self.partial.device)
+        for step in range(self.tp):
+            r = (self.rank - step) % self.tp
+            staging[r].copy_(self.h_partial.get_buffer(r, tuple(self.partial.shape), self.partial.dtype)[mine])
+        self.h_partial.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+        return staging.sum(dim=0)
+
+
 class DecoderLayer(nn.Module):
     def __init__(self, shape, tp, group, device, gen, fused_swiglu=True, fused_glue=True):
         super().__init__()
@@ -151,8 +201,13 @@ class DecoderLayer(nn.Module):
         dist.all_reduce(t, group=self.group)                     # backends without reduce-scatter
         return t[rank * rows:(rank + 1) * rows].contiguous()
 
-    def _addnorm_quant_gather(self, x_loc, gamma, residual_loc):
+    def _addnorm_quant_gather(self, x_loc, gamma, residual_loc, peers=None):
         """Local rows -> (codes [T, H] int8, scales [T] fp32 of ALL rows, new local residual)."""
+        if peers is not None:
+            q_loc, s_loc = peers.local_slices()
+            _, _, h, _ = ops.addnorm_quant_per_token(x_loc, gamma, self.shape.rms_eps, residual=residual_loc, out_q=q_loc, out_scale=s_loc)
+            q_all, s_all = peers.gather_codes()
+            return q_all, s_all, (h if h is not None else x_loc)
         dist = torch.distributed
         tp, rank = self.tp, dist.get_rank(self.group)
         rows, hid = x_loc.shape
@@ -168,15 +223,22 @@ class DecoderLayer(nn.Module):
         dist.all_gather_into_tensor(s_all, s_loc, group=self.group)
         return q_all, s_all, (h if h is not None else x_loc)
 
-    def sp_attention_half(self, x_loc, cos, sin, branch_loc, b, s):
+    def _row_parallel(self, linear, x, peers):
+        """A row-parallel Linear followed by the sum over ranks, local rows kept."""
+        if peers is None:
+            return self._reduce_scatter(linear(x))
+        linear(x, out=peers.partial)
+        return peers.reduce_scatter_partial()
+
+    def sp_attention_half(self, x_loc, cos, sin, branch_loc, b, s, peers=None):
         """First half of a token-sharded prefill layer: (previous MLP output + residual) -> norm ->
         quant -> all-gather -> qkv -> rotary -> attention -> o_proj -> reduce-scatter.
         x_loc / branch_loc: this rank's [b s / tp, hidden] rows.  Returns (x_loc, o_loc)."""
         shp, lin = self.shape, self.linears
         if branch_loc is None:
-            q8, ps, x_loc = self._addnorm_quant_gather(x_loc, self.input_norm, None)
+            q8, ps, x_loc = self._addnorm_quant_gather(x_loc, self.input_norm, None, peers)
         else:
-            q8, ps, x_loc = self._addnorm_quant_gather(branch_loc, self.input_norm, x_loc)
+            q8, ps, x_loc = self._addnorm_quant_gather(branch_loc, self.input_norm, x_loc, peers)
         qkv = lin.qkv_proj.forward_quantized(q8, ps).reshape(b, s, -1)
         ops.rope_inplace(qkv, self.heads + self.kv_heads, shp.head_dim, cos, sin)
         q, k, v = qkv.split((self.heads * shp.head_dim, self.kv_heads * shp.head_dim, self.kv_heads * shp.head_dim), dim=-1)
@@ -185,24 +247,24 @@ class DecoderLayer(nn.Module):
         v = v.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b * s, self.heads * shp.head_dim)
-        return x_loc, self._reduce_scatter(lin.o_proj(attn))
+        return x_loc, self._row_parallel(lin.o_proj, attn, peers)
 
-    def sp_mlp_half(self, x_loc, o_loc):
+    def sp_mlp_half(self, x_loc, o_loc, peers=None):
         """Second half: (attention output + residual) -> norm -> quant -> all-gather -> gate/up with
         SwiGLU -> down_proj -> reduce-scatter.  Returns (x_loc, branch_loc)."""
         lin = self.linears
-        q8, ps, x_loc = self._addnorm_quant_gather(o_loc, self.post_norm, x_loc)
+        q8, ps, x_loc = self._addnorm_quant_gather(o_loc, self.post_norm, x_loc, peers)
         act = lin.gate_up_proj.forward_quantized(q8, ps)
         if not self.fused_swiglu:
             gate, up = act.chunk(2, dim=-1)
             act = F.silu(gate) * up
-        return x_loc, self._reduce_scatter(lin.down_proj(act))
+        return x_loc, self._row_parallel(lin.down_proj, act, peers)
 
-    def forward_seq_parallel(self, x_loc, cos, sin, branch_loc, b, s):
+    def forward_seq_parallel(self, x_loc, cos, sin, branch_loc, b, s, peers=None):
         """Prefill with a token-sharded residual stream: x_loc / branch_loc are this rank's
         [b s / tp, hidden] rows.  Returns (x_loc, branch_loc) like forward() with fused_glue."""
-        x_loc, o_loc = self.sp_attention_half(x_loc, cos, sin, branch_loc, b, s)
-        return self.sp_mlp_half(x_loc, o_loc)
+        x_loc, o_loc = self.sp_attention_half(x_loc, cos, sin, branch_loc, b, s, peers)
+        return self.sp_mlp_half(x_loc, o_loc, peers)
 
     def forward(self, x, cos, sin, kv_cache=None, branch=None):
         """x [B, S, hidden] bf16 (the residual stream).  kv_cache: None (prefill, causal) or (k, v, past)
@@ -268,8 +330,13 @@ class LlamaW8A8(nn.Module):
     """Random-initialised Llama stack; rank `rank` of `tp` holds its shard of every layer."""
 
     def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None, fused_swiglu=True,
-                 fused_glue=True, seq_parallel=True):
+                 fused_glue=True, seq_parallel=True, comm='nccl'):
+        """comm: 'nccl' (reduce-scatter / all-gather kernels) or 'ce' (copy-engine pulls over peer-mapped buffers, see
+        PeerBuffers; meant for micro_batches >= 2, where one micro-batch's copies run beside the other one's GEMMs)."""
         super().__init__()
+        if comm not in ('nccl', 'ce'):
+            raise ValueError(f'comm={comm!r}')
+        self.comm, self._peers = comm, {}
         if shape.n_kv_heads % tp or shape.n_heads % tp or shape.intermediate % tp:
             raise ValueError(f'tp={tp} does not divide the head / intermediate sizes')
         self.shape, self.tp = shape, tp
@@ -283,6 +350,14 @@ class LlamaW8A8(nn.Module):
         self.group, self.rank = group, rank
         self.layers = nn.ModuleList(DecoderLayer(shape, tp, group, device, gen, fused_swiglu, fused_glue)
                                     for _ in range(n_layers if n_layers is not None else shape.n_layers))
+
+    def _peer_buffers(self, j, rows_total, device):
+        if self.comm != 'ce':
+            return None
+        key = (j, rows_total)
+        if key not in self._peers:
+            self._peers[key] = PeerBuffers(self.group, rows_total, self.shape.hidden, device)
+        return self._peers[key]
 
     @torch.no_grad()
     def forward(self, token_ids, kv_caches=None, past_len=0, micro_batches=None):
@@ -320,13 +395,14 @@ class LlamaW8A8(nn.Module):
             # half's kernels, so on NCCL's in-order stream each one waits only for work issued just
             # before it, and runs while the other micro-batch computes
             outs = [None] * len(parts)
+            peers = [self._peer_buffers(j, ids.numel(), token_ids.device) for j, ids in enumerate(parts)]
             for layer in self.layers:
                 for j, ids in enumerate(parts):
                     with torch.cuda.stream(self._streams[j]):
-                        xs[j], outs[j] = layer.sp_attention_half(xs[j], cos, sin, branches[j], ids.shape[0], s)
+                        xs[j], outs[j] = layer.sp_attention_half(xs[j], cos, sin, branches[j], ids.shape[0], s, peers[j])
                 for j in range(len(parts)):
                     with torch.cuda.stream(self._streams[j]):
-                        xs[j], branches[j] = layer.sp_mlp_half(xs[j], outs[j])
+                        xs[j], branches[j] = layer.sp_mlp_half(xs[j], outs[j], peers[j])
             for j, ids in enumerate(parts):
                 with torch.cuda.stream(self._streams[j]):
                     loc = xs[j] + branches[j]
@@ -374,8 +450,9 @@ class LlamaW8A8(nn.Module):
         rows = b * s // self.tp
         ids_loc = token_ids.reshape(-1)[self.rank * rows:(self.rank + 1) * rows]
         x_loc, branch_loc = F.embedding(ids_loc, self.embed), None
+        peers = self._peer_buffers(0, b * s, token_ids.device)
         for layer in self.layers:
-            x_loc, branch_loc = layer.forward_seq_parallel(x_loc, cos, sin, branch_loc, b, s)
+            x_loc, branch_loc = layer.forward_seq_parallel(x_loc, cos, sin, branch_loc, b, s, peers)
         if branch_loc is not None:
             x_loc = x_loc + branch_loc
         full = torch.empty((b * s, x_loc.shape[1]), dtype=x_loc.dtype, device=x_loc.device)

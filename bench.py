@@ -53,6 +53,8 @@ def parse():
     ap.add_argument('--mode', default='prefill', choices=['prefill', 'decode'],
                     help='decode: one new token for 64 sequences against a 2048-token KV cache (not the headline metric)')
     ap.add_argument('--no-cuda-graph', action='store_true')
+    ap.add_argument('--comm', choices=('nccl', 'ce'), default='nccl',
+                    help="collectives of the token-sharded prefill: NCCL kernels, or copy-engine pulls over peer-mapped buffers")
     ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (2 streams when N > 1)')
     ap.add_argument('--no-seq-parallel', action='store_true',
                     help='A/B only: replicated activations + all-reduce instead of the token-sharded residual stream')
@@ -205,7 +207,7 @@ def main():
 
     t_build = time.time()
     model = LlamaW8A8(LLAMA3_70B, tp=world, rank=rank, group=group, device=dev, seed=SEED, n_layers=args.layers,
-                      fused_glue=not args.torch_glue, seq_parallel=not args.no_seq_parallel)
+                      fused_glue=not args.torch_glue, seq_parallel=not args.no_seq_parallel, comm=args.comm)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
 

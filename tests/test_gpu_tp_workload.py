@@ -18,7 +18,7 @@ def _worker(rank, world, port, ret):
     shape = LlamaShape(hidden=1024, n_heads=8, n_kv_heads=2, head_dim=128, intermediate=2048, n_layers=2, vocab=512)
     ids = torch.randint(0, 512, (4, 32), generator=torch.Generator().manual_seed(3)).cuda()
     out = {}
-    for name, kw in {'sp': dict(seq_parallel=True), 'ar': dict(seq_parallel=False)}.items():
+    for name, kw in {'sp': dict(seq_parallel=True), 'ar': dict(seq_parallel=False), 'ce': dict(seq_parallel=True, comm='ce')}.items():
         m = LlamaW8A8(shape, tp=world, rank=rank, group=dist.group.WORLD, device=f'cuda:{rank}', seed=11, **kw)
         out[name] = m(ids, micro_batches=1).cpu()
         out[name + '_mb2'] = m(ids, micro_batches=2).cpu()
@@ -43,4 +43,6 @@ def test_seq_parallel_prefill_matches_all_reduce_prefill():
         # activations up to the one-ulp freedom of the normalisation's fp32 sum
         for key in ('sp', 'sp_mb2', 'ar_mb2'):
             assert float((r0[key] - ref).abs().max() / scale) < 2e-2, key
+        # copy-engine collectives: the sum of two bf16 partials rounds once whichever way it is formed
+        assert torch.equal(r0['ce'], r0['sp']) and torch.equal(r0['ce_mb2'], r0['sp_mb2'])
         assert r0['sp'].shape == (4, 512)
