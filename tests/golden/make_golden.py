@@ -22,7 +22,7 @@ import itertools
 import numpy as np
 import torch
 
-REF = os.environ.get('AMCT_REFERENCE', '/root/reference')
+REF = os.environ.get('AMCT_REFERENCE') or sys.exit('set AMCT_REFERENCE to a checkout of the reference (read only)')
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 DT = {'fp32': torch.float32, 'bf16': torch.bfloat16, 'fp16': torch.float16}
