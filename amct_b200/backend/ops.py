@@ -641,3 +641,13 @@ def rope_inplace(x, heads, head_dim, cos, sin):
     _l.check(rc, 'amct_rope_inplace')
     COUNTERS['launches'] += 1
     return x
+
+
+def peer_barrier(flag_ptrs, rank, seq, status=None):
+    """Barrier number `seq` between the ranks whose flag arrays (device addresses, one per rank, every one mapped
+    into this process) are `flag_ptrs`, enqueued on the current stream; a wait that runs out sets bit 1 of `status`."""
+    import ctypes
+    arr = (ctypes.c_void_p * len(flag_ptrs))(*[int(p_) for p_ in flag_ptrs])
+    rc = _l.load().amct_peer_barrier(arr, c_int(len(flag_ptrs)), c_int(rank), ctypes.c_uint32(seq & 0xFFFFFFFF), _p(status), _stream())
+    _l.check(rc, 'amct_peer_barrier')
+    COUNTERS['launches'] += 1

@@ -121,10 +121,9 @@ class PeerBuffers:
     """Collectives of the token-sharded prefill done by the copy engines over peer-mapped (symmetric) buffers, so that
     no communication kernel competes with the GEMMs for SMs: every rank writes its slice / partial into its own
     buffer, a barrier, every rank PULLS what it needs from the peers' buffers with plain device-to-device copies, a
-    second barrier (the buffers may be overwritten), and a local sum for the reduce-scatter.  One instance per
-    micro-batch stream; all ranks call its methods in the same order."""
-
-    TIMEOUT_MS = 60000          # of one barrier: a rank that never arrives ends the wait instead of hanging the GPU
+    second barrier (the buffers may be overwritten), and a local sum for the reduce-scatter.  The barrier is this
+    library's one-block kernel over peer-mapped flag words (bounded wait, status bit 1 on time-out).  One instance
+    per micro-batch stream; all ranks call its methods in the same order."""
 
     def __init__(self, group, rows_total, hidden, device):
         import os
@@ -136,9 +135,27 @@ class PeerBuffers:
         self.codes = symm.empty((rows_total, hidden), dtype=torch.int8, device=device)
         self.scales = symm.empty((rows_total,), dtype=torch.float32, device=device)
         self.partial = symm.empty((rows_total, hidden), dtype=torch.bfloat16, device=device)
-        self.h_codes = symm.rendezvous(self.codes, group)
-        self.h_scales = symm.rendezvous(self.scales, group)
-        self.h_partial = symm.rendezvous(self.partial, group)
+        self.flags = symm.empty((self.tp,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        shape = lambda t: tuple(t.shape)
+        handles = {name: symm.rendezvous(getattr(self, name), group) for name in ('codes', 'scales', 'partial', 'flags')}
+        # views of every rank's buffers through this process's mappings of them
+        self.peer_codes = [handles['codes'].get_buffer(r, shape(self.codes), torch.int8) for r in range(self.tp)]
+        self.peer_scales = [handles['scales'].get_buffer(r, shape(self.scales), torch.float32) for r in range(self.tp)]
+        self.peer_partial = [handles['partial'].get_buffer(r, shape(self.partial), torch.bfloat16) for r in range(self.tp)]
+        self.flag_ptrs = [int(p_) for p_ in handles['flags'].buffer_ptrs]
+        self._handles, self.seq = handles, 0
+        dist.barrier(group)                                                   # every rank's flags are zero before anyone signals
+
+    def _barrier(self):
+        self.seq += 1
+        ops.peer_barrier(self.flag_ptrs, self.rank, self.seq, self.status)
+
+    def check(self):
+        """Raise if a barrier of this instance ever gave up waiting (synchronizes the device)."""
+        ops.raise_if_timed_out(self.status)
 
     def local_slices(self):
         sl = slice(self.rank * self.rows, (self.rank + 1) * self.rows)
@@ -146,24 +163,24 @@ class PeerBuffers:
 
     def gather_codes(self):
         """The local slices of codes / scales have been written: fetch everybody else's."""
-        self.h_codes.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+        self._barrier()
         for step in range(1, self.tp):
             r = (self.rank - step) % self.tp
             sl = slice(r * self.rows, (r + 1) * self.rows)
-            self.codes[sl].copy_(self.h_codes.get_buffer(r, tuple(self.codes.shape), torch.int8)[sl])
-            self.scales[sl].copy_(self.h_scales.get_buffer(r, tuple(self.scales.shape), torch.float32)[sl])
-        self.h_codes.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+            self.codes[sl].copy_(self.peer_codes[r][sl])
+            self.scales[sl].copy_(self.peer_scales[r][sl])
+        self._barrier()
         return self.codes, self.scales
 
     def reduce_scatter_partial(self):
         """self.partial holds this rank's [T, H] partial sums: return the sum over ranks of rows [rank T/tp, ...)."""
-        self.h_partial.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+        self._barrier()
         mine = slice(self.rank * self.rows, (self.rank + 1) * self.rows)
         staging = torch.empty((self.tp, self.rows, self.partial.shape[1]), dtype=self.partial.dtype, device=self.partial.device)
         for step in range(self.tp):
             r = (self.rank - step) % self.tp
-            staging[r].copy_(self.h_partial.get_buffer(r, tuple(self.partial.shape), self.partial.dtype)[mine])
-        self.h_partial.barrier(channel=0, timeout_ms=self.TIMEOUT_MS)
+            staging[r].copy_(self.peer_partial[r][mine])
+        self._barrier()
         return staging.sum(dim=0)
 
 
@@ -358,6 +375,11 @@ class LlamaW8A8(nn.Module):
         if key not in self._peers:
             self._peers[key] = PeerBuffers(self.group, rows_total, self.shape.hidden, device)
         return self._peers[key]
+
+    def check_comm(self):
+        """Raise if any barrier of the copy-engine collectives timed out since the model was built (synchronizes)."""
+        for peers in self._peers.values():
+            peers.check()
 
     @torch.no_grad()
     def forward(self, token_ids, kv_caches=None, past_len=0, micro_batches=None):

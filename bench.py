@@ -281,6 +281,7 @@ def main():
     launches = ops.COUNTERS['launches'] if graph is None else launches_per_replay * args.steps
     clocks = sampler.stop() if sampler else None
     ms_e2e = timed(step_e2e, args.steps)
+    model.check_comm()
     if args.torch_profile:
         from torch.profiler import profile, ProfilerActivity
         if world > 1:
@@ -326,7 +327,7 @@ def main():
         'dtype': 'int8', 'data': 'synthetic',
         'config': {'workload': f'llama3-70b W8A8 {args.mode}, batch {args.batch} x seq {args.seq}, {args.layers} layers, '
                                'per-channel INT8 weights, dynamic per-token INT8 activations',
-                   'parallelism': f'tp{world}', 'l2': 'per-step working set (>70 GB of weights) exceeds L2; no flush needed',
+                   'parallelism': f'tp{world}', 'collectives': args.comm if world > 1 else None, 'l2': 'per-step working set (>70 GB of weights) exceeds L2; no flush needed',
                    'build_s': round(t_build, 1)},
         'e2e': {'value': tokens * args.steps / (ms_e2e / 1e3), 'unit': UNIT,
                 'h2d_bytes_per_step': ids_host.numel() * ids_host.element_size(),

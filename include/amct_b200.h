@@ -272,6 +272,14 @@ int amct_addnorm_quant_pertoken(const void* x, const void* residual, int dtype, 
 int amct_rope_inplace(void* x, int dtype, int64_t tokens, int64_t ld, int heads, int head_dim,
                       const void* cos_table, const void* sin_table, int64_t seq, void* stream);
 
+/* Barrier number `seq` between the `world` ranks of one node, in stream order, for collectives made of plain
+ * device-to-device copies: flag_arrays[r] is rank r's array of `world` zero-initialised 32-bit words in memory every
+ * rank has mapped (host array of device pointers, r = 0 .. world-1; world <= 16).  Callers count seq 1, 2, 3 ... the
+ * same on every rank.  One 32-thread block; a peer that has not arrived within two seconds sets bit 1 of *status and
+ * the kernel returns.  No counterpart in the reference (it has no multi-device path); serves the tensor-parallel
+ * workload around NpuQuantizationLinear. */
+int amct_peer_barrier(void* const* flag_arrays, int world, int rank, uint32_t seq, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,6 +22,7 @@ def _worker(rank, world, port, ret):
         m = LlamaW8A8(shape, tp=world, rank=rank, group=dist.group.WORLD, device=f'cuda:{rank}', seed=11, **kw)
         out[name] = m(ids, micro_batches=1).cpu()
         out[name + '_mb2'] = m(ids, micro_batches=2).cpu()
+        m.check_comm()
     ret[rank] = out
     dist.barrier()
     dist.destroy_process_group()
