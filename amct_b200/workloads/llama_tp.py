@@ -392,7 +392,11 @@ class LlamaW8A8(nn.Module):
         if micro_batches is None:
             # one micro-batch by default: with two (two CUDA streams, ping-pong order) the collectives of one ran next to
             # the GEMMs of the other only on paper -- measured 27.4 vs 27.9 k tokens/s at 2 GPUs, 68.0 vs 69.8 k at 8
-            micro_batches = 1
+            # ... with NCCL.  Copy-engine collectives exist to run beside the other micro-batch's GEMMs: two by default
+            micro_batches = 2 if (self.comm == 'ce' and self.seq_parallel and kv_caches is None and b % 2 == 0) else 1
+        if self.comm == 'ce' and micro_batches > 2:
+            # four streams stalled at 8 GPUs (every barrier ran into its time limit); two are what has been measured
+            raise ValueError("comm='ce' runs at most two micro-batch streams")
         pos = torch.arange(past_len, past_len + s, device=token_ids.device)
         cos, sin = rotary_tables(self.shape, pos, token_ids.device)
         sp = self.seq_parallel and kv_caches is None and (b // micro_batches) * s % self.tp == 0 and b % micro_batches == 0

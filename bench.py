@@ -53,8 +53,9 @@ def parse():
     ap.add_argument('--mode', default='prefill', choices=['prefill', 'decode'],
                     help='decode: one new token for 64 sequences against a 2048-token KV cache (not the headline metric)')
     ap.add_argument('--no-cuda-graph', action='store_true')
-    ap.add_argument('--comm', choices=('nccl', 'ce'), default='nccl',
-                    help="collectives of the token-sharded prefill: NCCL kernels, or copy-engine pulls over peer-mapped buffers")
+    ap.add_argument('--comm', choices=('auto', 'nccl', 'ce'), default='auto',
+                    help="collectives of the token-sharded prefill: NCCL kernels, or copy-engine pulls over peer-mapped buffers "
+                         "beside two micro-batch streams (auto: the latter when N > 1, NCCL if one of its barriers times out)")
     ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (2 streams when N > 1)')
     ap.add_argument('--no-seq-parallel', action='store_true',
                     help='A/B only: replicated activations + all-reduce instead of the token-sharded residual stream')
@@ -205,9 +206,13 @@ def main():
     from amct_b200.backend import ops
     from amct_b200.workloads.llama_tp import LlamaW8A8, LLAMA3_70B
 
+    comm = args.comm
+    if comm == 'auto':
+        sharded_prefill = world > 1 and args.mode == 'prefill' and not args.no_seq_parallel and not args.torch_glue
+        comm = 'ce' if sharded_prefill else 'nccl'
     t_build = time.time()
     model = LlamaW8A8(LLAMA3_70B, tp=world, rank=rank, group=group, device=dev, seed=SEED, n_layers=args.layers,
-                      fused_glue=not args.torch_glue, seq_parallel=not args.no_seq_parallel, comm=args.comm)
+                      fused_glue=not args.torch_glue, seq_parallel=not args.no_seq_parallel, comm=comm)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
 
@@ -243,7 +248,29 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    mb = args.micro_batches or None
+    mb = args.micro_batches or (2 if comm == 'ce' else None)
+
+    def comm_failed():
+        """True on every rank if a barrier of the copy-engine collectives gave up waiting on any rank."""
+        if world == 1 or model.comm != 'ce':
+            return False
+        try:
+            model.check_comm()
+            bad = 0
+        except RuntimeError:
+            bad = 1
+        flag = torch.tensor([bad], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        return bool(flag.item())
+
+    def fall_back(when):
+        nonlocal mb
+        if rank == 0:
+            print(f'bench.py: a barrier of the copy-engine collectives timed out {when}; measuring with NCCL instead',
+                  file=sys.stderr, flush=True)
+        model.comm, mb = 'nccl', (args.micro_batches or None)
+        for _ in range(args.warmup):
+            step_resident()
 
     def step_resident():
         return model(ids_dev, kv_caches=kv_caches, past_len=2048 if kv_caches else 0, micro_batches=mb)
@@ -254,6 +281,8 @@ def main():
 
     for _ in range(args.warmup):
         step_resident()
+    if comm_failed():
+        fall_back('during warm-up')
     graph = None
     if args.mode == 'decode' and not args.no_cuda_graph:
         # the decode step is launch-bound (hundreds of small kernels): replay it as one CUDA graph
@@ -275,13 +304,19 @@ def main():
             logits_host.copy_(graph_logits, non_blocking=True)
         for _ in range(2):
             step_resident()
-    sampler = ClockSampler(local) if rank == 0 else None
-    ops.COUNTERS['launches'] = 0
-    ms_total = timed(step_resident, args.steps)
-    launches = ops.COUNTERS['launches'] if graph is None else launches_per_replay * args.steps
-    clocks = sampler.stop() if sampler else None
-    ms_e2e = timed(step_e2e, args.steps)
-    model.check_comm()
+
+    def measure():
+        sampler = ClockSampler(local) if rank == 0 else None
+        ops.COUNTERS['launches'] = 0
+        ms = timed(step_resident, args.steps)
+        n_launch = ops.COUNTERS['launches'] if graph is None else launches_per_replay * args.steps
+        clk = sampler.stop() if sampler else None
+        return ms, n_launch, clk, timed(step_e2e, args.steps)
+
+    ms_total, launches, clocks, ms_e2e = measure()
+    if comm_failed():
+        fall_back('in the timed region')
+        ms_total, launches, clocks, ms_e2e = measure()
     if args.torch_profile:
         from torch.profiler import profile, ProfilerActivity
         if world > 1:
@@ -327,7 +362,7 @@ def main():
         'dtype': 'int8', 'data': 'synthetic',
         'config': {'workload': f'llama3-70b W8A8 {args.mode}, batch {args.batch} x seq {args.seq}, {args.layers} layers, '
                                'per-channel INT8 weights, dynamic per-token INT8 activations',
-                   'parallelism': f'tp{world}', 'collectives': args.comm if world > 1 else None, 'l2': 'per-step working set (>70 GB of weights) exceeds L2; no flush needed',
+                   'parallelism': f'tp{world}', 'collectives': model.comm if world > 1 else None, 'micro_batches': mb or 1, 'l2': 'per-step working set (>70 GB of weights) exceeds L2; no flush needed',
                    'build_s': round(t_build, 1)},
         'e2e': {'value': tokens * args.steps / (ms_e2e / 1e3), 'unit': UNIT,
                 'h2d_bytes_per_step': ids_host.numel() * ids_host.element_size(),

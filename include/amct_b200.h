@@ -276,8 +276,8 @@ int amct_rope_inplace(void* x, int dtype, int64_t tokens, int64_t ld, int heads,
  * device-to-device copies: flag_arrays[r] is rank r's array of `world` zero-initialised 32-bit words in memory every
  * rank has mapped (host array of device pointers, r = 0 .. world-1; world <= 16).  Callers count seq 1, 2, 3 ... the
  * same on every rank.  One 32-thread block; a peer that has not arrived within two seconds sets bit 1 of *status and
- * the kernel returns.  No counterpart in the reference (it has no multi-device path); serves the tensor-parallel
- * workload around NpuQuantizationLinear. */
+ * the kernel returns; with that bit already set the barrier returns at once.  No counterpart in the reference (it
+ * has no multi-device path); serves the tensor-parallel workload around NpuQuantizationLinear. */
 int amct_peer_barrier(void* const* flag_arrays, int world, int rank, uint32_t seq, int* status, void* stream);
 
 #ifdef __cplusplus
