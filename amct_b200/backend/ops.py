@@ -651,3 +651,95 @@ def peer_barrier(flag_ptrs, rank, seq, status=None):
     rc = _l.load().amct_peer_barrier(arr, c_int(len(flag_ptrs)), c_int(rank), ctypes.c_uint32(seq & 0xFFFFFFFF), _p(status), _stream())
     _l.check(rc, 'amct_peer_barrier')
     COUNTERS['launches'] += 1
+
+
+# ---------------------------------------------------------------------------
+# offline checkpoint formats (amct_pytorch/experimental/quantization/DeepSeekV3.2/deploy.py)
+def ckpt_block_dequant(weight_fp8, scale, block_size=128, out_dtype=torch.bfloat16):
+    """E4M3 weight [M, N] times one fp32 scale per block_size x block_size tile -> out_dtype [M, N]."""
+    _need_cuda(weight_fp8, scale)
+    if weight_fp8.dim() != 2 or weight_fp8.element_size() != 1:
+        raise ValueError('weight must be a 2-D tensor of one-byte E4M3 values')
+    m, n = weight_fp8.shape
+    if tuple(scale.shape) != ((m + block_size - 1) // block_size, (n + block_size - 1) // block_size):
+        raise AssertionError('Mismatch in scale shape and weight shape.')          # deploy.py:70-73
+    w = weight_fp8.contiguous().view(torch.uint8)
+    s = scale.to(torch.float32).contiguous()
+    out = torch.empty((m, n), dtype=out_dtype, device=w.device)
+    rc = _l.load().amct_ckpt_block_dequant(_p(w), c_int64(m), c_int64(n), c_int64(n), _p(s), c_int64(s.shape[1]),
+                                           c_int(block_size), _p(out), c_int(_DT[out_dtype]), c_int64(n), _stream())
+    _l.check(rc, 'amct_ckpt_block_dequant')
+    COUNTERS['launches'] += 1
+    return out
+
+
+def ckpt_rowquant(weight, bits=8, clip_factor=None):
+    """Per-row symmetric codes in the weight's dtype.  bits=8 -> (int8 [N, K], fp32 [N, 1], None);
+    bits=4 -> (packed int8 [N / 2, K], uint64 [N, 1], fp32 bias [N])."""
+    _need_cuda(weight)
+    if weight.dim() != 2:
+        raise AssertionError('weight must be 2-D')                                   # deploy.py:129
+    if bits not in (8, 4):
+        raise ValueError('bits must be 8 or 4')
+    w2, rows, k, ld = _rows2d(weight)
+    if bits == 4 and rows % 2:
+        raise ValueError('INT4 packing pairs output channels: the row count must be even')
+    dev = weight.device
+    codes = torch.empty((rows if bits == 8 else rows // 2, k), dtype=torch.int8, device=dev)
+    scale = torch.empty((rows, 1), dtype=torch.float32 if bits == 8 else torch.int64, device=dev)
+    bias = torch.empty(rows, dtype=torch.float32, device=dev) if bits == 4 else None
+    use_clip = clip_factor is not None
+    rc = _l.load().amct_ckpt_rowquant(_p(w2), c_int(_dt(w2)), c_int64(rows), c_int64(k), c_int64(ld), c_int(bits),
+                                      c_int(int(use_clip)), ctypes.c_float(float(clip_factor) if use_clip else 1.0),
+                                      _p(codes), c_int64(k), _p(scale), _p(bias), _stream())
+    _l.check(rc, 'amct_ckpt_rowquant')
+    COUNTERS['launches'] += 1
+    if bits == 4:
+        scale = scale.view(torch.uint64)
+    return codes, scale, bias
+
+
+def ckpt_pack4_rows(codes):
+    """int8 [N, K] of 4-bit values, N even -> int8 [N / 2, K] (row 2j low nibble, row 2j + 1 high nibble)."""
+    _need_cuda(codes)
+    assert codes.dtype == torch.int8 and codes.dim() == 2                           # deploy.py:113
+    if codes.shape[0] % 2:
+        raise ValueError('INT4 packing pairs output channels: the row count must be even')
+    c = codes.contiguous()
+    rows, k = c.shape
+    out = torch.empty((rows // 2, k), dtype=torch.int8, device=c.device)
+    rc = _l.load().amct_ckpt_pack4_rows(_p(c), c_int64(rows), c_int64(k), c_int64(k), _p(out), c_int64(k), _stream())
+    _l.check(rc, 'amct_ckpt_pack4_rows')
+    COUNTERS['launches'] += 1
+    return out
+
+
+def ckpt_int4_bias(codes, scale):
+    """fp32 [N]: sum over a row of scale * code * 8 with every product rounded to scale's dtype."""
+    _need_cuda(codes, scale)
+    assert codes.dtype == torch.int8 and codes.dim() == 2 and scale.dim() == 2 and scale.shape[0] == codes.shape[0]
+    c = codes.contiguous()
+    s = scale.contiguous()
+    rows, k = c.shape
+    groups = s.shape[1]
+    if groups == 0 or k % groups:
+        raise ValueError('the scale columns must divide the code columns')
+    bias = torch.empty(rows, dtype=torch.float32, device=c.device)
+    rc = _l.load().amct_ckpt_int4_bias(_p(c), c_int64(rows), c_int64(k), c_int64(k), _p(s), c_int(_dt(s)),
+                                       c_int64(groups), _p(bias), _stream())
+    _l.check(rc, 'amct_ckpt_int4_bias')
+    COUNTERS['launches'] += 1
+    return bias
+
+
+def hadamard_pow2(n, norm=True, dtype=torch.bfloat16, device='cuda'):
+    """Sylvester Hadamard matrix [n, n]; with norm, log2(n) divisions by sqrt(2) each rounded to dtype."""
+    if n <= 0 or n & (n - 1):
+        raise ValueError(f'n must be a positive power of 2, got{n}')                 # deploy.py:37-38
+    out = torch.empty((n, n), dtype=dtype, device=device)
+    _need_cuda(out)
+    with torch.cuda.device(out.device):
+        rc = _l.load().amct_hadamard_pow2(c_int(n), c_int(int(bool(norm))), c_int(_DT[dtype]), _p(out), _stream())
+    _l.check(rc, 'amct_hadamard_pow2')
+    COUNTERS['launches'] += 1
+    return out

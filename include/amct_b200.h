@@ -251,6 +251,43 @@ int amct_hif8_encode(const void* x, int dtype, int64_t n, void* codes, void* fak
 /* HiF8 codes uint8 [n] -> values in `dtype` (exact in fp16, bf16 and fp32). */
 int amct_hif8_decode(const void* codes, int64_t n, int dtype, void* out, void* stream);
 
+/* ---- Offline checkpoint formats
+ * (amct_pytorch/experimental/quantization/DeepSeekV3.2/deploy.py, "deploy.py" below) ---- */
+
+/* E4M3 weight [rows, cols] (uint8 bit patterns, ld_w) times one fp32 scale per block x block tile ->
+ * out [rows, cols] in out_dtype (ld_out).  scale is [ceil(rows / block), ceil(cols / block)] with row stride
+ * ld_scale; ragged edges use the last tile's scale.  The product is formed in fp32 and rounded once.
+ * Replaces weight_dequant (deploy.py:48-90; block = 128, out_dtype = the default dtype, bf16 in its main). */
+int amct_ckpt_block_dequant(const void* w_fp8, int64_t rows, int64_t cols, int64_t ld_w, const float* scale,
+                            int64_t ld_scale, int block, void* out, int out_dtype, int64_t ld_out, void* stream);
+
+/* Symmetric per-row (per output channel) quantization of w [rows, k] (ld) carried out in w's own dtype T:
+ * scale = T(T(max|w| [* clip_factor]) / qmax), code = clamp(round(T(w / scale)), -qmax, qmax), qmax = 2^(bits-1) - 1.
+ * bits = 8: codes int8 [rows, k] (ld_codes), scale fp32 [rows], bias unused (may be NULL).
+ * bits = 4: rows must be even; codes int8 [rows / 2, k], byte [j, c] = (code[2j, c] & 15) | (code[2j+1, c] << 4)
+ *           (pack_4bit, deploy.py:109-125); scale uint64 [rows], low word = the fp32 bit pattern
+ *           (scale_fp32_to_u64, deploy.py:93-106); bias fp32 [rows] = T(sum_c T(T(scale * code) * 8))
+ *           (int4_assistance_bias, deploy.py:149-157; the sum is exact, hence order independent, for bf16 with
+ *           k < 8192 and fp16 with k < 1024, and an fp32 sum in this kernel's own order otherwise).
+ * use_clip != 0 applies clip_factor (a host value, sigmoid of the stored clip parameter).  An all-zero row gives
+ * scale 0 and codes 0.  Replaces int_weight_quant (deploy.py:128-146). */
+int amct_ckpt_rowquant(const void* w, int dtype, int64_t rows, int64_t k, int64_t ld, int bits, int use_clip,
+                       float clip_factor, int8_t* codes, int64_t ld_codes, void* scale, float* bias, void* stream);
+
+/* pack_4bit alone (deploy.py:109-125): codes int8 [rows, k] (ld), rows even -> out int8 [rows / 2, k] (ld_out). */
+int amct_ckpt_pack4_rows(const int8_t* codes, int64_t rows, int64_t k, int64_t ld, int8_t* out, int64_t ld_out,
+                         void* stream);
+
+/* int4_assistance_bias alone (deploy.py:149-157): codes int8 [rows, k] (ld), scale [rows, groups] contiguous in
+ * `dtype` with k % groups == 0 (each scale covers k / groups consecutive codes) -> bias fp32 [rows]. */
+int amct_ckpt_int4_bias(const int8_t* codes, int64_t rows, int64_t k, int64_t ld, const void* scale, int dtype,
+                        int64_t groups, float* bias, void* stream);
+
+/* Sylvester Hadamard matrix out [n, n] in `dtype`, n a power of two <= 32768.  norm != 0: every doubling divides
+ * by fp32 sqrt(2) and rounds to dtype, as the reference does on a tensor of its default dtype, so the magnitude is
+ * that chain of log2(n) rounded divisions.  Replaces get_had_pow2 (deploy.py:32-45). */
+int amct_hadamard_pow2(int n, int norm, int dtype, void* out, void* stream);
+
 /* ---- Glue of the sharded deploy workload (no counterpart in the reference) ---- */
 
 /* h = x + residual (rounded to dtype; residual may be NULL: h = x); n = round(h * rstd * gamma) with

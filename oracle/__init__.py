@@ -16,6 +16,10 @@ npu_ops  the four external ``torch_npu`` ops the deploy modules call.  The
          documented formula and the operand construction at the call sites.
 mx       MXFP8-E4M3 / MXFP4-E2M1 with E8M0 block scales.  Absent from the
          reference: PARITY UNPINNED, restated from the public OCP MX v1.0 rules.
+ckpt     the offline checkpoint formats of the reference's DeepSeek-V3.2 export script (FP8 block dequant,
+         per-channel INT8 / INT4 with nibble packing, uint64 scale words, INT4 assistance bias, Hadamard
+         matrix).  PINNED: checked against outputs of the imported reference script, committed as
+         ``tests/golden/ckpt_golden.*`` (``tests/golden/make_ckpt_golden.py``).
 hif8     HiFloat8 encode/decode.  Absent from the reference: PARITY UNPINNED,
          restated from the published format description.
 """

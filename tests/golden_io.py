@@ -1,11 +1,13 @@
-"""Loader for the golden fixtures written by tests/golden/make_golden.py."""
+"""Loader for the golden fixtures written by tests/golden/make_golden.py and tests/golden/make_ckpt_golden.py."""
 import os
 
 import numpy as np
 import torch
 
 _PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden', 'intq_golden.npz')
-_TAGS = {'bf16': torch.bfloat16, 'fp16': torch.float16}
+CKPT_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden', 'ckpt_golden.npz')
+CKPT_JSON = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden', 'ckpt_golden.json')
+_TAGS = {'bf16': torch.bfloat16, 'fp16': torch.float16, 'fp8': torch.float8_e4m3fn, 'u64': torch.uint64}
 
 
 class Golden:
@@ -39,6 +41,8 @@ def bits_equal(a, b):
         return False
     a = a.detach().cpu().contiguous()
     b = b.detach().cpu().contiguous()
+    if a.dtype == torch.uint64:
+        return bool((a.view(torch.int64) == b.view(torch.int64)).all())
     if a.dtype.is_floating_point:
         w = {2: torch.int16, 4: torch.int32, 8: torch.int64, 1: torch.uint8}[a.element_size()]
         return bool((a.view(w) == b.view(w)).all())
