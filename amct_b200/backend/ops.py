@@ -743,3 +743,28 @@ def hadamard_pow2(n, norm=True, dtype=torch.bfloat16, device='cuda'):
     _l.check(rc, 'amct_hadamard_pow2')
     COUNTERS['launches'] += 1
     return out
+
+
+# ---------------------------------------------------------------------------
+# KV-cache / indexer activations (amct_pytorch/experimental/quantization/DeepSeekV3.2/cores)
+def dsa_rotate_fakequant(x, rotate=False, out_dtype=None, bits=8, symmetric=True, clip_max_sigmoid=None,
+                         clip_min_sigmoid=None):
+    """Optional Hadamard rotation of the last axis, optional cast, per-token dynamic fake quantization (bits=16:
+    none) in one pass.  Learned clipping is on when clip_max_sigmoid is given (then fp32 arithmetic, as torch
+    promotes); the asymmetric rule also needs clip_min_sigmoid."""
+    _need_cuda(x)
+    out_dtype = out_dtype or x.dtype
+    x2, rows, k, ld = _rows2d(x)
+    out = torch.empty((rows, k), dtype=out_dtype, device=x.device)
+    lac = clip_max_sigmoid is not None
+    if lac and not symmetric and clip_min_sigmoid is None:
+        raise ValueError('the asymmetric rule with learned clipping needs both sigmoids')
+    rc = _l.load().amct_dsa_rotate_fakequant(
+        _p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), c_int(int(bool(rotate))), c_int(_DT[out_dtype]),
+        c_int(bits), c_int(int(bool(symmetric))), c_int(int(lac)),
+        ctypes.c_float(float(clip_max_sigmoid) if lac else 1.0),
+        ctypes.c_float(float(clip_min_sigmoid) if clip_min_sigmoid is not None else 1.0),
+        _p(out), c_int64(k), _stream())
+    _l.check(rc, 'amct_dsa_rotate_fakequant')
+    COUNTERS['launches'] += 1
+    return out.reshape(x.shape)

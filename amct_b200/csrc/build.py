@@ -18,7 +18,7 @@ INCLUDE = os.path.join(os.path.dirname(os.path.dirname(HERE)), 'include')
 
 # numerics-critical files: no FMA contraction so that x*s+z rounds twice like torch
 STRICT = {'quant_rows.cu', 'quant_token.cu', 'quant_static.cu', 'reduce.cu', 'mx_quant.cu', 'hif8.cu', 'norm_quant.cu',
-          'rope.cu', 'quant_groups.cu', 'ckpt_formats.cu'}
+          'rope.cu', 'quant_groups.cu', 'ckpt_formats.cu', 'kv_quant.cu'}
 
 
 def sources():

@@ -1,0 +1,272 @@
+// KV-cache / indexer activation path of the reference's DeepSeek-V3.2 tree
+// (amct_pytorch/experimental/quantization/DeepSeekV3.2/cores/...):
+//   * rotate_activation: x @ (H / sqrt(d)) over the last axis in fp32, H the Sylvester Hadamard matrix
+//     (models/deepseek_v3_2/indexer.py:140-151), here a fast Walsh-Hadamard transform inside one warp;
+//   * ActivationQuantizer.fake_quant, per token, dynamic (quantization/node.py:140-215 with :39-66):
+//     symmetric without learned clipping (the attention module's afq1 / afq2 / afq_rot_q / afq_rot_k,
+//     models/deepseek_v3_2/quant_dsa.py:46-49, :121-124), symmetric or asymmetric with it (k_cache_quantizer,
+//     quant_dsa.py:118-119);
+//   * the indexer's chain rotate -> .half() -> fake_quant (quant_dsa.py:75-82) in one pass over the row.
+//
+// One warp owns one row (a token, or a token-head of the indexer).  Arithmetic follows torch's dtypes: without
+// learned clipping every step is rounded to the activation dtype; with it the fp32 clip parameter promotes the
+// bounds and all later steps to fp32 and only the result is cast back.  round_ste(t) = (round(t) - t) + t is
+// exact except that it turns a zero into +0, which the symmetric path reproduces.  NaN inputs are not handled
+// like torch.clamp (which propagates them).  Compiled without FMA contraction.
+//
+// Algorithmic HBM bytes per element: sizeof(in) read + sizeof(out) written.
+#include "common.cuh"
+
+namespace amct {
+
+struct DsaParams {
+  const void* x;
+  int64_t rows, k, ld_x;
+  int bits;            // 16: no quantization (rotation / cast only)
+  int symmetric;
+  int learned_clip;    // 1: bounds times the sigmoids below, computation in fp32
+  float sig_max, sig_min;
+  float had_entry;     // fl32(1 / fl32(sqrt(k))) when rotating
+  void* out;
+  int64_t ld_out;
+};
+
+struct DsaRow {
+  float scale, recip, zero, qlo, qhi;
+};
+
+// rounding to the dtype torch computes in: fp32 with learned clipping, else the output dtype
+template <typename T>
+__device__ __forceinline__ float round_c(float v, bool fp32_math) {
+  return fp32_math ? v : round_to<T>(v);
+}
+
+// row bounds (values of the output dtype) -> scale, zero point and code range          node.py:181-215
+template <typename T>
+__device__ __forceinline__ DsaRow dsa_row_params(float row_max, float row_min, const DsaParams& p) {
+  const bool f32 = p.learned_clip != 0;
+  float hi = fmaxf(row_max, 0.f), lo = fminf(row_min, 0.f);
+  DsaRow r;
+  if (p.symmetric) {
+    const float qmax = (float)((1 << (p.bits - 1)) - 1);
+    const float bound = f32 ? __fmul_rn(fmaxf(fabsf(lo), hi), p.sig_max) : hi;
+    r.scale = round_c<T>(__fdiv_rn(bound, qmax), f32);
+    if (bound == 0.f) r.scale = 1.f;
+    r.zero = 0.f;
+    r.qlo = -(qmax + 1.f);
+    r.qhi = qmax;
+  } else {
+    const float qmax = (float)((1 << p.bits) - 1);
+    if (f32) {
+      hi = __fmul_rn(hi, p.sig_max);
+      lo = __fmul_rn(lo, p.sig_min);
+    }
+    if (hi == 0.f && lo == 0.f) {
+      hi = 1.f;
+      lo = -1.f;
+    }
+    r.scale = round_c<T>(__fdiv_rn(round_c<T>(__fsub_rn(hi, lo), f32), qmax), f32);
+    r.zero = rintf(round_c<T>(__fdiv_rn(-lo, r.scale), f32));
+    r.qlo = 0.f;
+    r.qhi = qmax;
+  }
+  const float y = __frcp_rn(r.scale);
+  const bool ok = fabsf(r.scale) >= 1.17549435e-38f && fabsf(y) >= 1.17549435e-38f && isfinite(y) && isfinite(r.scale);
+  r.recip = ok ? y : 0.f;
+  return r;
+}
+
+// one value of the output dtype -> its fake-quantized value (as fp32, representable in T)   node.py:39-66
+template <typename T>
+__device__ __forceinline__ float dsa_fake_quant(float v, const DsaRow& r, const DsaParams& p) {
+  const bool f32 = p.learned_clip != 0;
+  float q;
+  if (r.recip != 0.f) {
+    q = div_by_recip(v, r.scale, r.recip);
+    if (!(fabsf(q) <= 3.0e38f)) q = __fdiv_rn(v, r.scale);
+  } else {
+    q = __fdiv_rn(v, r.scale);
+  }
+  float level = rintf(round_c<T>(q, f32));
+  if (p.symmetric) {
+    level = fminf(fmaxf(__fadd_rn(level, 0.f), r.qlo), r.qhi);           // -0 -> +0 like round_ste
+    return round_to<T>(round_c<T>(__fmul_rn(r.scale, level), f32));
+  }
+  level = fminf(fmaxf(round_c<T>(__fadd_rn(level, r.zero), f32), r.qlo), r.qhi);
+  return round_to<T>(round_c<T>(__fmul_rn(r.scale, round_c<T>(__fsub_rn(level, r.zero), f32)), f32));
+}
+
+constexpr int kDsaWarps = 4;
+
+// Rotation (+ cast + fake quantization): k = 32 * EPL, lane l holds elements l, 32 + l, 64 + l, ...
+template <typename TIN, typename TOUT, int EPL>
+__global__ void __launch_bounds__(kDsaWarps * 32) dsa_rotate_quant_kernel(DsaParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kDsaWarps + (threadIdx.x >> 5);
+  if (row >= p.rows) return;                                  // whole warps leave together
+  const TIN* x = reinterpret_cast<const TIN*>(p.x) + row * p.ld_x;
+  float v[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) v[e] = ElemTraits<TIN>::to_f(x[e * 32 + lane]);
+
+  // butterflies over the index bits held in the lane number ...
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
+      v[e] = (lane & m) ? __fsub_rn(other, v[e]) : __fadd_rn(v[e], other);
+    }
+  }
+  // ... and over the bits held in the register number
+#pragma unroll
+  for (int m = 1; m < EPL; m <<= 1) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      if ((e & m) == 0) {
+        const float a = v[e], c = v[e | m];
+        v[e] = __fadd_rn(a, c);
+        v[e | m] = __fsub_rn(a, c);
+      }
+    }
+  }
+  // scale, round to the input dtype (the rotation's result), then to the output dtype (.half() of the caller)
+  float hi = -INFINITY, lo = INFINITY;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    v[e] = round_to<TOUT>(round_to<TIN>(__fmul_rn(v[e], p.had_entry)));
+    hi = fmaxf(hi, v[e]);
+    lo = fminf(lo, v[e]);
+  }
+  TOUT* out = reinterpret_cast<TOUT*>(p.out) + row * p.ld_out;
+  if (p.bits == 16) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) out[e * 32 + lane] = ElemTraits<TOUT>::from_f(v[e]);
+    return;
+  }
+  const DsaRow r = dsa_row_params<TOUT>(warp_max(hi), warp_min(lo), p);
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) out[e * 32 + lane] = ElemTraits<TOUT>::from_f(dsa_fake_quant<TOUT>(v[e], r, p));
+}
+
+// Fake quantization alone (any k): pass 1 takes the bounds, pass 2 re-reads the row (an L1 / L2 hit).
+// VEC: 16-byte loads and stores, possible when input and output elements have the same size.
+template <typename TIN, typename TOUT, bool VEC>
+__global__ void __launch_bounds__(kDsaWarps * 32) dsa_fakequant_kernel(DsaParams p) {
+  constexpr int E = ElemTraits<TIN>::kPerVec;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kDsaWarps + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const TIN* x = reinterpret_cast<const TIN*>(p.x) + row * p.ld_x;
+  TOUT* out = reinterpret_cast<TOUT*>(p.out) + row * p.ld_out;
+  const int64_t nvec = VEC ? p.k / E : 0;
+
+  float hi = -INFINITY, lo = INFINITY;
+  if (VEC) {
+    for (int64_t i = lane; i < nvec; i += 32) {
+      const Vec16<TIN> raw = ld_vec(x + i * E);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float f = round_to<TOUT>(ElemTraits<TIN>::to_f(raw.v[e]));
+        hi = fmaxf(hi, f);
+        lo = fminf(lo, f);
+      }
+    }
+  } else {
+    for (int64_t j = lane; j < p.k; j += 32) {
+      const float f = round_to<TOUT>(ElemTraits<TIN>::to_f(x[j]));
+      hi = fmaxf(hi, f);
+      lo = fminf(lo, f);
+    }
+  }
+  const DsaRow r = dsa_row_params<TOUT>(warp_max(hi), warp_min(lo), p);
+
+  if (VEC) {
+    for (int64_t i = lane; i < nvec; i += 32) {
+      const Vec16<TIN> raw = ld_vec_stream(x + i * E);
+      Vec16<TOUT> o;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float f = round_to<TOUT>(ElemTraits<TIN>::to_f(raw.v[e]));
+        o.v[e] = ElemTraits<TOUT>::from_f(dsa_fake_quant<TOUT>(f, r, p));
+      }
+      *reinterpret_cast<uint4*>(out + i * E) = *reinterpret_cast<const uint4*>(&o);
+    }
+  } else {
+    for (int64_t j = lane; j < p.k; j += 32) {
+      const float f = round_to<TOUT>(ElemTraits<TIN>::to_f(x[j]));
+      out[j] = ElemTraits<TOUT>::from_f(dsa_fake_quant<TOUT>(f, r, p));
+    }
+  }
+}
+
+template <typename TIN, typename TOUT>
+static int launch_dsa(const DsaParams& p, int rotate, cudaStream_t st) {
+  const unsigned grid = (unsigned)((p.rows + kDsaWarps - 1) / kDsaWarps);
+  const int threads = kDsaWarps * 32;
+  if (rotate) {
+    switch (p.k) {
+      case 32: dsa_rotate_quant_kernel<TIN, TOUT, 1><<<grid, threads, 0, st>>>(p); break;
+      case 64: dsa_rotate_quant_kernel<TIN, TOUT, 2><<<grid, threads, 0, st>>>(p); break;
+      case 128: dsa_rotate_quant_kernel<TIN, TOUT, 4><<<grid, threads, 0, st>>>(p); break;
+      case 256: dsa_rotate_quant_kernel<TIN, TOUT, 8><<<grid, threads, 0, st>>>(p); break;
+      case 512: dsa_rotate_quant_kernel<TIN, TOUT, 16><<<grid, threads, 0, st>>>(p); break;
+      default: return AMCT_ERR_UNSUPPORTED;
+    }
+  } else {
+    constexpr int E = ElemTraits<TIN>::kPerVec;
+    const bool vec = sizeof(TIN) == sizeof(TOUT) && p.k % E == 0 && aligned16(p.x) && aligned16(p.out) &&
+                     (p.ld_x * (int64_t)sizeof(TIN)) % 16 == 0 && (p.ld_out * (int64_t)sizeof(TOUT)) % 16 == 0;
+    if (vec) dsa_fakequant_kernel<TIN, TOUT, sizeof(TIN) == sizeof(TOUT)><<<grid, threads, 0, st>>>(p);
+    else dsa_fakequant_kernel<TIN, TOUT, false><<<grid, threads, 0, st>>>(p);
+  }
+  AMCT_CHECK_LAUNCH();
+  return AMCT_OK;
+}
+
+template <typename TIN>
+static int dispatch_dsa_out(const DsaParams& p, int rotate, int out_dtype, cudaStream_t st) {
+  switch (out_dtype) {
+    case AMCT_DTYPE_F32: return launch_dsa<TIN, float>(p, rotate, st);
+    case AMCT_DTYPE_F16: return launch_dsa<TIN, __half>(p, rotate, st);
+    case AMCT_DTYPE_BF16: return launch_dsa<TIN, __nv_bfloat16>(p, rotate, st);
+  }
+  return AMCT_ERR_ARG;
+}
+
+}  // namespace amct
+
+using namespace amct;
+
+extern "C" int amct_dsa_rotate_fakequant(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int rotate,
+                                         int out_dtype, int bits, int symmetric, int learned_clip,
+                                         float clip_max_sigmoid, float clip_min_sigmoid, void* out, int64_t ld_out,
+                                         void* stream) {
+  if (rows < 0 || k <= 0 || ld_x < k || ld_out < k) return AMCT_ERR_ARG;
+  if (bits != 16 && (bits < 2 || bits > 8)) return AMCT_ERR_ARG;
+  if (rotate && (k & (k - 1)) != 0) return AMCT_ERR_ARG;
+  if (rotate && (k < 32 || k > 512)) return AMCT_ERR_UNSUPPORTED;
+  if (rows == 0) return AMCT_OK;
+  if (!x || !out) return AMCT_ERR_ARG;
+  if ((rows + kDsaWarps - 1) / kDsaWarps > 0x7fffffff) return AMCT_ERR_UNSUPPORTED;
+  DsaParams p;
+  p.x = x;
+  p.rows = rows;
+  p.k = k;
+  p.ld_x = ld_x;
+  p.bits = bits;
+  p.symmetric = symmetric ? 1 : 0;
+  p.learned_clip = learned_clip ? 1 : 0;
+  p.sig_max = clip_max_sigmoid;
+  p.sig_min = clip_min_sigmoid;
+  p.had_entry = rotate ? 1.0f / sqrtf((float)k) : 1.0f;
+  p.out = out;
+  p.ld_out = ld_out;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case AMCT_DTYPE_F32: return dispatch_dsa_out<float>(p, rotate, out_dtype, st);
+    case AMCT_DTYPE_F16: return dispatch_dsa_out<__half>(p, rotate, out_dtype, st);
+    case AMCT_DTYPE_BF16: return dispatch_dsa_out<__nv_bfloat16>(p, rotate, out_dtype, st);
+  }
+  return AMCT_ERR_ARG;
+}

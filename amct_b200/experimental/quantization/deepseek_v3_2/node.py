@@ -1,0 +1,79 @@
+"""Activation quantizer of the reference's DeepSeek-V3.2 tree on the CUDA kernel.
+
+Drop-in for ``ActivationQuantizer`` of amct_pytorch/experimental/quantization/DeepSeekV3.2/cores/quantization/node.py
+("node.py" below) in the configuration its attention module uses (cores/models/deepseek_v3_2/quant_dsa.py:46-49,
+:113-124): dynamic per-token fake quantization, symmetric without learned clipping, symmetric or asymmetric with
+it.  Same constructor arguments, parameter and buffer names (``clip_factor_a_max``, ``clip_factor_a_min``,
+``maxval``, ``minval``, ``scale``, ``zero``), observe mode and bits=16 pass-through.  The quantization itself is
+``amct_dsa_rotate_fakequant`` (``amct_b200/csrc/kv_quant.cu``); it is an inference-time path: the kernel has no
+backward, so the learned clip factors are read, not trained, here.  Not covered: ``per_tensor=True`` (static
+scale) and ``clip_ratio`` -- both raise NotImplementedError rather than fall back to torch arithmetic.
+"""
+import torch
+
+from ....backend import ops as _ops
+
+
+def get_qmin_qmax(bits, sym):
+    """(q_max, q_min) as node.py:30-36."""
+    if sym:
+        q_max = torch.tensor(2 ** (bits - 1) - 1)
+        return q_max, -q_max - 1
+    return torch.tensor(2 ** bits - 1), 0
+
+
+class ActivationQuantizer(torch.nn.Module):
+    """Per-token (last axis) dynamic activation fake quantizer (node.py:85-215)."""
+
+    def __init__(self, bits, sym=False, lac=False, groupsize=-1, clip_ratio=None, per_tensor=False, head_num=-1):
+        super().__init__()
+        if groupsize > 0:
+            raise NotImplementedError('Not support per-group quantization for activation yet.')       # node.py:98-99
+        if per_tensor:
+            raise NotImplementedError('per_tensor=True (a static scale) is not built on the CUDA path')
+        if clip_ratio is not None:
+            raise NotImplementedError('clip_ratio is not built on the CUDA path')
+        self.bits, self.sym, self.lac, self.groupsize = bits, sym, lac, groupsize
+        self.q_max, self.q_min = get_qmin_qmax(bits, sym)
+        self._clip_ratio = clip_ratio
+        if lac:
+            self.sigmoid = torch.nn.Sigmoid()
+            self.clip_factor_a_max = torch.nn.Parameter(torch.ones((1,)) * 4.0, requires_grad=True)
+            self.clip_factor_a_min = torch.nn.Parameter(torch.ones((1,)) * 4.0, requires_grad=True)
+        self.enable = True
+        self.register_buffer('maxval', torch.zeros(1))
+        self.register_buffer('minval', torch.zeros(1))
+        self.register_buffer('scale', torch.ones(1))
+        self.register_buffer('zero', torch.zeros(1))
+        self.is_observe = False
+        self.is_deploy = False
+        self.is_per_tensor = per_tensor
+        self.cnt = 0
+
+    def forward(self, x):
+        if self.bits == 16:
+            return x
+        if self.is_observe:                                                    # node.py:121-128
+            hi, lo = x.max(), x.min()
+            if hi > self.maxval.to(x.device):
+                self.maxval.data = hi
+            if lo < self.minval.to(x.device):
+                self.minval.data = lo
+            return x
+        return self.fake_quant(x)
+
+    def _sigmoids(self):
+        if not self.lac:
+            return None, None
+        if self.clip_factor_a_max.dtype != torch.float32:
+            raise NotImplementedError('the kernel follows torch promotion for fp32 clip parameters only')
+        with torch.no_grad():
+            return (float(torch.sigmoid(self.clip_factor_a_max.float())),
+                    float(torch.sigmoid(self.clip_factor_a_min.float())))
+
+    def fake_quant(self, x):
+        sig_max, sig_min = self._sigmoids()
+        if self.sym:
+            self.cnt += 1
+        return _ops.dsa_rotate_fakequant(x, rotate=False, bits=self.bits, symmetric=self.sym,
+                                         clip_max_sigmoid=sig_max, clip_min_sigmoid=sig_min)

@@ -288,6 +288,27 @@ int amct_ckpt_int4_bias(const int8_t* codes, int64_t rows, int64_t k, int64_t ld
  * that chain of log2(n) rounded divisions.  Replaces get_had_pow2 (deploy.py:32-45). */
 int amct_hadamard_pow2(int n, int norm, int dtype, void* out, void* stream);
 
+/* ---- KV-cache / indexer activation path
+ * (amct_pytorch/experimental/quantization/DeepSeekV3.2/cores, "cores" below) ---- */
+
+/* Per row of x [rows, k] (ld_x), in this order:
+ *   rotate != 0: r = dtype(x @ (H / sqrt(k))) in fp32, H the k x k Sylvester Hadamard matrix, k a power of two in
+ *                32 .. 512 (rotate_activation, cores/models/deepseek_v3_2/indexer.py:140-151); else r = x;
+ *   y = out_dtype(r) (the `.half()` of cores/models/deepseek_v3_2/quant_dsa.py:78-79 when out_dtype differs);
+ *   bits == 16: out = y.  Otherwise out = the per-token dynamic fake quantization of y, any k
+ *   (ActivationQuantizer.fake_quant with per_tensor=False, cores/quantization/node.py:140-215 and :39-66):
+ *     bounds hi = max(row max, 0), lo = min(row min, 0);
+ *     symmetric, learned_clip = 0: scale = hi / qmax (the negative side does not widen it; 1 when hi == 0),
+ *       codes in [-(qmax + 1), qmax], qmax = 2^(bits-1) - 1, every step rounded to out_dtype;
+ *     symmetric, learned_clip = 1: scale = max(|lo|, hi) * clip_max_sigmoid / qmax in fp32, all steps in fp32;
+ *     asymmetric: hi *= clip_max_sigmoid, lo *= clip_min_sigmoid when learned_clip (fp32 steps), a row of zeros uses
+ *       [-1, 1], scale = (hi - lo) / qmax, zero = round(-lo / scale), codes in [0, qmax], qmax = 2^bits - 1.
+ *   clip_*_sigmoid are host values: the sigmoid of the module's clip_factor_a_max / clip_factor_a_min parameters.
+ * out [rows, k] in out_dtype (ld_out).  One warp per row; one pass over HBM. */
+int amct_dsa_rotate_fakequant(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int rotate, int out_dtype,
+                              int bits, int symmetric, int learned_clip, float clip_max_sigmoid, float clip_min_sigmoid,
+                              void* out, int64_t ld_out, void* stream);
+
 /* ---- Glue of the sharded deploy workload (no counterpart in the reference) ---- */
 
 /* h = x + residual (rounded to dtype; residual may be NULL: h = x); n = round(h * rstd * gamma) with

@@ -20,6 +20,9 @@ ckpt     the offline checkpoint formats of the reference's DeepSeek-V3.2 export 
          per-channel INT8 / INT4 with nibble packing, uint64 scale words, INT4 assistance bias, Hadamard
          matrix).  PINNED: checked against outputs of the imported reference script, committed as
          ``tests/golden/ckpt_golden.*`` (``tests/golden/make_ckpt_golden.py``).
+dsa      the KV-cache / indexer activation path of the same tree: per-token dynamic fake quantization
+         (ActivationQuantizer) and the Hadamard rotation.  PINNED: checked against outputs of the imported
+         reference modules, committed as ``tests/golden/dsa_golden.npz`` (``tests/golden/make_dsa_golden.py``).
 hif8     HiFloat8 encode/decode.  Absent from the reference: PARITY UNPINNED,
          restated from the published format description.
 """

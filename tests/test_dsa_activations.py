@@ -1,0 +1,67 @@
+"""KV-cache / indexer activation path on the CPU: the oracle against the reference's outputs
+(tests/golden/dsa_golden.npz) and the host side of the drop-in modules (names, refusals)."""
+import os
+
+import pytest
+import torch
+
+from golden_io import Golden, bits_equal
+from oracle import dsa as O
+
+GOLD = Golden(os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden', 'dsa_golden.npz'))
+CLIP_MAX, CLIP_MIN = float(GOLD.get('fq.clip_max_raw')), float(GOLD.get('fq.clip_min_raw'))
+
+
+@pytest.mark.parametrize('dtype', ['fp16', 'bf16', 'fp32'])
+@pytest.mark.parametrize('k', [128, 512, 200])
+def test_oracle_fake_quant(dtype, k):
+    x = GOLD.get(f'fq.{dtype}.{k}.x')
+    assert bits_equal(O.activation_fake_quant(x), GOLD.get(f'fq.{dtype}.{k}.sym'))
+    assert bits_equal(O.activation_fake_quant(x, 8, True, True, CLIP_MAX, CLIP_MIN), GOLD.get(f'fq.{dtype}.{k}.lac.sym'))
+    assert bits_equal(O.activation_fake_quant(x, 8, False, True, CLIP_MAX, CLIP_MIN), GOLD.get(f'fq.{dtype}.{k}.lac.asym'))
+    assert O.activation_fake_quant(x, bits=16) is x
+
+
+@pytest.mark.parametrize('dtype', ['bf16', 'fp16', 'fp32'])
+@pytest.mark.parametrize('d', [128, 64])
+def test_oracle_rotation(dtype, d):
+    """Bit-equal here because the oracle's matmul and the reference's ran on the same BLAS; one unit in the last place
+    is what the contract promises."""
+    x = GOLD.get(f'rot.{dtype}.{d}.x')
+    got, want = O.rotate_activation(x), GOLD.get(f'rot.{dtype}.{d}.out')
+    assert got.dtype == want.dtype
+    ulp = torch.finfo(x.dtype).eps * want.float().abs().clamp_min(float(torch.finfo(x.dtype).tiny))
+    assert bool(((got.float() - want.float()).abs() <= ulp).all())
+
+
+def test_oracle_indexer_chain():
+    r = O.rotate_activation(GOLD.get('chain.x'))
+    assert bits_equal(O.activation_fake_quant(GOLD.get('chain.rotated').half()), GOLD.get('chain.out'))
+    assert bits_equal(r, GOLD.get('chain.rotated'))
+
+
+def test_rotation_is_orthonormal_and_rejects_other_widths():
+    x = torch.randn(5, 256, generator=torch.Generator().manual_seed(1))
+    y = O.rotate_activation(O.rotate_activation(x))
+    assert torch.allclose(x, y, atol=1e-5)
+    with pytest.raises(ValueError):
+        O.rotate_activation(torch.zeros(2, 48))
+
+
+def test_module_mirror_names_and_refusals():
+    from amct_b200.experimental.quantization.deepseek_v3_2.node import ActivationQuantizer, get_qmin_qmax
+    q = ActivationQuantizer(bits=8, sym=True, lac=True, groupsize=-1, per_tensor=False)
+    assert sorted(q.state_dict()) == ['clip_factor_a_max', 'clip_factor_a_min', 'maxval', 'minval', 'scale', 'zero']
+    assert float(q.clip_factor_a_max) == 4.0 and int(q.q_max) == 127 and int(q.q_min) == -128
+    assert [int(v) for v in get_qmin_qmax(8, False)] == [255, 0]
+    x = torch.randn(3, 8)
+    assert ActivationQuantizer(bits=16)(x) is x                                # pass-through needs no kernel
+    obs = ActivationQuantizer(bits=8, sym=True)
+    obs.is_observe = True
+    assert obs(x) is x and float(obs.maxval) == float(x.max()) and float(obs.minval) == float(x.min())
+    for kwargs in ({'groupsize': 64}, {'per_tensor': True}, {'clip_ratio': 0.9}):
+        with pytest.raises(NotImplementedError):
+            ActivationQuantizer(bits=8, sym=True, **kwargs)
+    from amct_b200.backend.lib import BackendError
+    with pytest.raises(BackendError):                                          # no CPU fallback
+        ActivationQuantizer(bits=8, sym=True)(x)
