@@ -247,6 +247,25 @@ def cases():
     yield ('dequant_weight i4 g128 c2 [11008x4096] -> bf16', setup_dq,
            lambda t: (lambda: ops.dequant_weight(t[0], 4, t[1], t[2], 128, out=t[3])),
            dict(nbytes=11008 * 2048 + 11008 * 4096 * 2 + 2 * 32 * 11008 * 2))
+    # ---- offline checkpoint formats: 64 routed experts' up projections of a DeepSeek-V3-sized MoE layer at once
+    def setup_fp8():
+        w = torch.randint(0, 0x77, (64 * 2048, 7168), device='cuda', dtype=torch.uint8).view(torch.float8_e4m3fn)
+        return w, torch.rand(64 * 16, 56, device='cuda') * 0.01 + 1e-3
+    yield ('ckpt_block_dequant fp8 -> bf16 [131072x7168], 128x128 scales', setup_fp8,
+           lambda t: (lambda: ops.ckpt_block_dequant(t[0], t[1])), dict(nbytes=131072 * 7168 * 3))
+    for bits in (8, 4):
+        yield (f'ckpt_rowquant int{bits} per channel [131072x7168] bf16', lambda: randn(131072, 7168, torch.bfloat16, 0.02),
+               lambda w, bits=bits: (lambda: ops.ckpt_rowquant(w, bits)),
+               dict(nbytes=131072 * 7168 * 2 + 131072 * 7168 * bits // 8 + 131072 * (4 if bits == 8 else 12)))
+    # ---- KV-cache / indexer activations: 4096 tokens x 64 indexer heads of 128; attention output rows of 16384
+    yield ('dsa rotate + half + fake_quant [262144x128] bf16 -> fp16', lambda: randn(262144, 128, torch.bfloat16),
+           lambda x: (lambda: ops.dsa_rotate_fakequant(x, rotate=True, out_dtype=torch.float16)),
+           dict(nbytes=262144 * 128 * 4))
+    yield ('dsa fake_quant per token [16384x16384] bf16', lambda: randn(16384, 16384, torch.bfloat16),
+           lambda x: (lambda: ops.dsa_rotate_fakequant(x)), dict(nbytes=16384 * 16384 * 4))
+    yield ('dsa fake_quant asym + learned clip [65536x512] bf16', lambda: randn(65536, 512, torch.bfloat16),
+           lambda x: (lambda: ops.dsa_rotate_fakequant(x, symmetric=False, clip_max_sigmoid=0.9, clip_min_sigmoid=0.8)),
+           dict(nbytes=65536 * 512 * 4))
 
 
 def main():
