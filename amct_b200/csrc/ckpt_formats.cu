@@ -91,10 +91,10 @@ static int launch_block_dequant(const uint8_t* w, int64_t rows, int64_t cols, in
   if (vec) {
     const int64_t vpr = cols / 16;
     dim3 grid((unsigned)((vpr + 127) / 128), gy);
-    ckpt_block_dequant_vec_kernel<T><<<grid, 128, 0, st>>>(w, rows, vpr, ld_w, scale, ld_scale, block, o, ld_out);
+    AMCT_LAUNCH(grid, 128, st, (w, rows, vpr, ld_w, scale, ld_scale, block, o, ld_out), ckpt_block_dequant_vec_kernel<T>);
   } else {
     dim3 grid((unsigned)((cols + 127) / 128), gy);
-    ckpt_block_dequant_scalar_kernel<T><<<grid, 128, 0, st>>>(w, rows, cols, ld_w, scale, ld_scale, block, o, ld_out);
+    AMCT_LAUNCH(grid, 128, st, (w, rows, cols, ld_w, scale, ld_scale, block, o, ld_out), ckpt_block_dequant_scalar_kernel<T>);
   }
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
@@ -285,12 +285,12 @@ static int launch_rowquant(const CkptRowParams& p, cudaStream_t st) {
                    (reinterpret_cast<uintptr_t>(p.codes) & 7u) == 0 && p.ld_codes % 8 == 0;
   if (p.bits == 8) {
     const unsigned grid = (unsigned)p.rows;
-    if (vec) ckpt_rowquant_kernel<T, true, 1><<<grid, kRowThreads, 0, st>>>(p);
-    else ckpt_rowquant_kernel<T, false, 1><<<grid, kRowThreads, 0, st>>>(p);
+    if (vec) AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, true, 1>);
+    else AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, false, 1>);
   } else {
     const unsigned grid = (unsigned)(p.rows / 2);
-    if (vec) ckpt_rowquant_kernel<T, true, 2><<<grid, kRowThreads, 0, st>>>(p);
-    else ckpt_rowquant_kernel<T, false, 2><<<grid, kRowThreads, 0, st>>>(p);
+    if (vec) AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, true, 2>);
+    else AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, false, 2>);
   }
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
@@ -394,7 +394,8 @@ extern "C" int amct_ckpt_pack4_rows(const int8_t* codes, int64_t rows, int64_t k
   if (k > (int64_t)128 * 0x7fffffff) return AMCT_ERR_UNSUPPORTED;
   const int64_t pairs = rows / 2;
   dim3 grid((unsigned)((k + 127) / 128), (unsigned)(pairs < 16384 ? pairs : 16384));
-  ckpt_pack4_rows_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(codes, pairs, k, ld, out, ld_out);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  AMCT_LAUNCH(grid, 128, st, (codes, pairs, k, ld, out, ld_out), ckpt_pack4_rows_kernel);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -409,14 +410,14 @@ extern "C" int amct_ckpt_int4_bias(const int8_t* codes, int64_t rows, int64_t k,
   const unsigned grid = (unsigned)rows;
   switch (dtype) {
     case AMCT_DTYPE_F32:
-      ckpt_int4_bias_kernel<float><<<grid, kRowThreads, 0, st>>>(codes, k, ld, (const float*)scale, groups, bias);
+      AMCT_LAUNCH(grid, kRowThreads, st, (codes, k, ld, (const float*)scale, groups, bias), ckpt_int4_bias_kernel<float>);
       break;
     case AMCT_DTYPE_F16:
-      ckpt_int4_bias_kernel<__half><<<grid, kRowThreads, 0, st>>>(codes, k, ld, (const __half*)scale, groups, bias);
+      AMCT_LAUNCH(grid, kRowThreads, st, (codes, k, ld, (const __half*)scale, groups, bias), ckpt_int4_bias_kernel<__half>);
       break;
     case AMCT_DTYPE_BF16:
-      ckpt_int4_bias_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, st>>>(codes, k, ld, (const __nv_bfloat16*)scale,
-                                                                          groups, bias);
+      AMCT_LAUNCH(grid, kRowThreads, st, (codes, k, ld, (const __nv_bfloat16*)scale,
+                                                                          groups, bias), ckpt_int4_bias_kernel<__nv_bfloat16>);
       break;
     default: return AMCT_ERR_ARG;
   }
@@ -432,10 +433,10 @@ extern "C" int amct_hadamard_pow2(int n, int norm, int dtype, void* out, void* s
   const int64_t total = (int64_t)n * n;
   const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
   switch (dtype) {
-    case AMCT_DTYPE_F32: ckpt_hadamard_kernel<float><<<grid, 256, 0, st>>>(n, log2n, norm, (float*)out); break;
-    case AMCT_DTYPE_F16: ckpt_hadamard_kernel<__half><<<grid, 256, 0, st>>>(n, log2n, norm, (__half*)out); break;
+    case AMCT_DTYPE_F32: AMCT_LAUNCH(grid, 256, st, (n, log2n, norm, (float*)out), ckpt_hadamard_kernel<float>); break;
+    case AMCT_DTYPE_F16: AMCT_LAUNCH(grid, 256, st, (n, log2n, norm, (__half*)out), ckpt_hadamard_kernel<__half>); break;
     case AMCT_DTYPE_BF16:
-      ckpt_hadamard_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(n, log2n, norm, (__nv_bfloat16*)out);
+      AMCT_LAUNCH(grid, 256, st, (n, log2n, norm, (__nv_bfloat16*)out), ckpt_hadamard_kernel<__nv_bfloat16>);
       break;
     default: return AMCT_ERR_ARG;
   }

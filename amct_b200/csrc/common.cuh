@@ -15,11 +15,19 @@
 
 #define AMCT_FLT_EPSILON 1.192092896e-7f   // amct_pytorch/quantize_op/utils.py:23
 
+#ifndef AMCT_CHECK_LAUNCH
 #define AMCT_CHECK_LAUNCH()                                         \
   do {                                                              \
     cudaError_t e__ = cudaGetLastError();                           \
     if (e__ != cudaSuccess) return AMCT_ERR_CUDA;                   \
   } while (0)
+#endif
+
+// Kernel launch written so that a test harness can substitute its own launcher (the newer files use it):
+// AMCT_LAUNCH(grid, threads, stream, (arguments), kernel<template arguments>).
+#ifndef AMCT_LAUNCH
+#define AMCT_LAUNCH(grid, threads, stream, args, ...) __VA_ARGS__<<<(grid), (threads), 0, (stream)>>> args
+#endif
 
 namespace amct {
 

@@ -206,19 +206,19 @@ static int launch_dsa(const DsaParams& p, int rotate, cudaStream_t st) {
   const int threads = kDsaWarps * 32;
   if (rotate) {
     switch (p.k) {
-      case 32: dsa_rotate_quant_kernel<TIN, TOUT, 1><<<grid, threads, 0, st>>>(p); break;
-      case 64: dsa_rotate_quant_kernel<TIN, TOUT, 2><<<grid, threads, 0, st>>>(p); break;
-      case 128: dsa_rotate_quant_kernel<TIN, TOUT, 4><<<grid, threads, 0, st>>>(p); break;
-      case 256: dsa_rotate_quant_kernel<TIN, TOUT, 8><<<grid, threads, 0, st>>>(p); break;
-      case 512: dsa_rotate_quant_kernel<TIN, TOUT, 16><<<grid, threads, 0, st>>>(p); break;
+      case 32: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 1>); break;
+      case 64: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 2>); break;
+      case 128: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 4>); break;
+      case 256: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 8>); break;
+      case 512: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 16>); break;
       default: return AMCT_ERR_UNSUPPORTED;
     }
   } else {
     constexpr int E = ElemTraits<TIN>::kPerVec;
     const bool vec = sizeof(TIN) == sizeof(TOUT) && p.k % E == 0 && aligned16(p.x) && aligned16(p.out) &&
                      (p.ld_x * (int64_t)sizeof(TIN)) % 16 == 0 && (p.ld_out * (int64_t)sizeof(TOUT)) % 16 == 0;
-    if (vec) dsa_fakequant_kernel<TIN, TOUT, sizeof(TIN) == sizeof(TOUT)><<<grid, threads, 0, st>>>(p);
-    else dsa_fakequant_kernel<TIN, TOUT, false><<<grid, threads, 0, st>>>(p);
+    if (vec) AMCT_LAUNCH(grid, threads, st, (p), dsa_fakequant_kernel<TIN, TOUT, sizeof(TIN) == sizeof(TOUT)>);
+    else AMCT_LAUNCH(grid, threads, st, (p), dsa_fakequant_kernel<TIN, TOUT, false>);
   }
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;

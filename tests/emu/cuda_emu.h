@@ -1,0 +1,163 @@
+// CPU emulation of the small part of the CUDA execution model that the HBM-bound kernels of
+// amct_b200/csrc/ckpt_formats.cu and kv_quant.cu use, so that their SOURCE -- index arithmetic, vector and scalar
+// paths, reductions, launch geometry, argument checks -- can be executed by a CPU test against the golden vectors.
+// TEST INFRASTRUCTURE ONLY: tests/test_kernel_source_emulation.py compiles those .cu files with g++ and this header
+// force-included; nothing in the product builds, loads or links it.
+//
+// Model: the threads of a block are host threads; blocks run one after another.  __syncthreads() is a barrier over
+// the block, __shfl_xor_sync a barrier-bracketed exchange inside a 32-thread warp (every lane of a warp must take
+// part, and threads may leave a kernel early only as whole warps and never before a block barrier -- true for the
+// kernels above).  __shared__ becomes a static variable (one block is alive at a time).  The arithmetic intrinsics
+// map to the IEEE operations they name (compile with -ffp-contract=off); fmaf is the C library's exact one.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <cmath>
+#include <condition_variable>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+namespace emu {
+
+class Barrier {
+ public:
+  void reset(int n) {
+    n_ = n;
+    count_ = 0;
+    phase_ = 0;
+  }
+  void wait() {
+    std::unique_lock<std::mutex> lock(m_);
+    const unsigned phase = phase_;
+    if (++count_ == n_) {
+      count_ = 0;
+      ++phase_;
+      cv_.notify_all();
+    } else {
+      cv_.wait(lock, [&] { return phase_ != phase; });
+    }
+  }
+
+ private:
+  std::mutex m_;
+  std::condition_variable cv_;
+  int n_ = 1, count_ = 0;
+  unsigned phase_ = 0;
+};
+
+struct BlockState {
+  Barrier block, step;
+  Barrier warp[32];
+  uint32_t slot[1024];
+};
+
+struct ThreadState {
+  uint3 tid{0, 0, 0}, bid{0, 0, 0};
+  dim3 bdim{1, 1, 1}, gdim{1, 1, 1};
+  BlockState* block = nullptr;
+};
+
+inline ThreadState& tls() {
+  static thread_local ThreadState s;
+  return s;
+}
+
+inline unsigned as_dim(const dim3& d, int axis) { return axis == 0 ? d.x : axis == 1 ? d.y : d.z; }
+
+// runs `body` once per (block, thread); `threads` is one-dimensional like every launch of the emulated files
+inline void launch(dim3 grid, int threads, const std::function<void()>& body) {
+  static BlockState state;                       // launches are serial
+  state.block.reset(threads);
+  state.step.reset(threads);
+  for (int w = 0; w < 32; ++w) {
+    const int in_warp = threads - w * 32;
+    state.warp[w].reset(in_warp >= 32 ? 32 : (in_warp > 0 ? in_warp : 1));
+  }
+  std::vector<std::thread> pool;
+  for (int t = 0; t < threads; ++t) {
+    pool.emplace_back([&, t] {
+      ThreadState& s = tls();
+      s.block = &state;
+      s.tid = uint3{(unsigned)t, 0, 0};
+      s.bdim = dim3((unsigned)threads, 1, 1);
+      s.gdim = grid;
+      for (unsigned by = 0; by < grid.y; ++by) {
+        for (unsigned bx = 0; bx < grid.x; ++bx) {
+          s.bid = uint3{bx, by, 0};
+          body();
+          state.step.wait();                     // next block only when every thread has left this one
+        }
+      }
+    });
+  }
+  for (auto& th : pool) th.join();
+}
+
+inline uint32_t shfl_xor_bits(uint32_t bits, int lane_mask) {
+  ThreadState& s = tls();
+  const unsigned t = s.tid.x;
+  s.block->slot[t] = bits;
+  s.block->warp[t >> 5].wait();
+  const uint32_t other = s.block->slot[t ^ (unsigned)lane_mask];
+  s.block->warp[t >> 5].wait();
+  return other;
+}
+
+}  // namespace emu
+
+#undef __shared__
+#undef __launch_bounds__
+#define threadIdx (emu::tls().tid)
+#define blockIdx (emu::tls().bid)
+#define blockDim (emu::tls().bdim)
+#define gridDim (emu::tls().gdim)
+#define __shared__ static
+#define __launch_bounds__(...)
+#define __syncthreads() (emu::tls().block->block.wait())
+
+#define AMCT_LAUNCH(grid, threads, stream, args, ...) \
+  emu::launch(dim3(grid), (int)(threads), [&] { __VA_ARGS__ args; })
+#define AMCT_CHECK_LAUNCH() \
+  do {                      \
+  } while (0)
+
+static inline float __shfl_xor_sync(unsigned, float v, int lane_mask) {
+  uint32_t b;
+  std::memcpy(&b, &v, 4);
+  b = emu::shfl_xor_bits(b, lane_mask);
+  std::memcpy(&v, &b, 4);
+  return v;
+}
+static inline float __fmul_rn(float a, float b) { return a * b; }
+static inline float __fadd_rn(float a, float b) { return a + b; }
+static inline float __fsub_rn(float a, float b) { return a - b; }
+static inline float __fdiv_rn(float a, float b) { return a / b; }
+static inline float __frcp_rn(float a) { return 1.0f / a; }
+static inline float __fmaf_rn(float a, float b, float c) { return std::fmaf(a, b, c); }
+static inline int __float_as_int(float f) {
+  int i;
+  std::memcpy(&i, &f, 4);
+  return i;
+}
+static inline unsigned __float_as_uint(float f) {
+  unsigned i;
+  std::memcpy(&i, &f, 4);
+  return i;
+}
+static inline float __int_as_float(int i) {
+  float f;
+  std::memcpy(&f, &i, 4);
+  return f;
+}
+static inline int __popc(unsigned v) { return __builtin_popcount(v); }
+template <typename T> static inline T __ldg(const T* p) { return *p; }
+template <typename T> static inline T __ldcs(const T* p) { return *p; }
+template <typename T> static inline void __stcs(T* p, T v) { *p = v; }
+using std::isfinite;
