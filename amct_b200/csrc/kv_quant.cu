@@ -98,55 +98,109 @@ __device__ __forceinline__ float dsa_fake_quant(float v, const DsaRow& r, const 
 
 constexpr int kDsaWarps = 4;
 
-// Rotation (+ cast + fake quantization): k = 32 * EPL, lane l holds elements l, 32 + l, 64 + l, ...
-template <typename TIN, typename TOUT, int EPL>
-__global__ void __launch_bounds__(kDsaWarps * 32) dsa_rotate_quant_kernel(DsaParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kDsaWarps + (threadIdx.x >> 5);
-  if (row >= p.rows) return;                                  // whole warps leave together
-  const TIN* x = reinterpret_cast<const TIN*>(p.x) + row * p.ld_x;
-  float v[EPL];
+// EPL consecutive elements of T <-> floats, with the widest naturally aligned accesses when `wide` is set
+// (the caller has checked that every row starts on a multiple of EPL * sizeof(T) bytes, up to 16).
+template <typename T, int EPL>
+__device__ __forceinline__ void load_run(const T* p, float* v, bool wide) {
+  constexpr int kBytes = EPL * (int)sizeof(T);
+  if (wide && kBytes >= 4) {
+    constexpr int kWord = kBytes >= 16 ? 16 : kBytes;            // 4, 8 or 16 bytes per access
+    constexpr int kPerWord = kWord / (int)sizeof(T);
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) v[e] = ElemTraits<TIN>::to_f(x[e * 32 + lane]);
+    for (int i = 0; i < kBytes / kWord; ++i) {
+      alignas(16) T tmp[kPerWord];
+      if (kWord == 16) *reinterpret_cast<uint4*>(tmp) = __ldcs(reinterpret_cast<const uint4*>(p + i * kPerWord));
+      else if (kWord == 8) *reinterpret_cast<uint2*>(tmp) = __ldcs(reinterpret_cast<const uint2*>(p + i * kPerWord));
+      else *reinterpret_cast<uint32_t*>(tmp) = __ldcs(reinterpret_cast<const uint32_t*>(p + i * kPerWord));
+#pragma unroll
+      for (int e = 0; e < kPerWord; ++e) v[i * kPerWord + e] = ElemTraits<T>::to_f(tmp[e]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = ElemTraits<T>::to_f(p[e]);
+  }
+}
+template <typename T, int EPL>
+__device__ __forceinline__ void store_run(T* p, const float* v, bool wide) {
+  constexpr int kBytes = EPL * (int)sizeof(T);
+  if (wide && kBytes >= 4) {
+    constexpr int kWord = kBytes >= 16 ? 16 : kBytes;
+    constexpr int kPerWord = kWord / (int)sizeof(T);
+#pragma unroll
+    for (int i = 0; i < kBytes / kWord; ++i) {
+      alignas(16) T tmp[kPerWord];
+#pragma unroll
+      for (int e = 0; e < kPerWord; ++e) tmp[e] = ElemTraits<T>::from_f(v[i * kPerWord + e]);
+      if (kWord == 16) *reinterpret_cast<uint4*>(p + i * kPerWord) = *reinterpret_cast<const uint4*>(tmp);
+      else if (kWord == 8) *reinterpret_cast<uint2*>(p + i * kPerWord) = *reinterpret_cast<const uint2*>(tmp);
+      else *reinterpret_cast<uint32_t*>(p + i * kPerWord) = *reinterpret_cast<const uint32_t*>(tmp);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) p[e] = ElemTraits<T>::from_f(v[e]);
+  }
+}
 
-  // butterflies over the index bits held in the lane number ...
+// Rotation (+ cast + fake quantization): k = 32 * EPL, lane l holds the EPL consecutive elements from l * EPL, and
+// one warp works on RPW rows at a time so that enough loads are in flight (RPW * EPL = 16 values per lane).
+// The transform is the same whichever index bits sit in the lane number: every bit gets its butterfly.
+template <typename TIN, typename TOUT, int EPL, int RPW>
+__global__ void __launch_bounds__(kDsaWarps * 32) dsa_rotate_quant_kernel(DsaParams p, int wide_in, int wide_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row0 = ((int64_t)blockIdx.x * kDsaWarps + (threadIdx.x >> 5)) * RPW;
+  if (row0 >= p.rows) return;                                 // whole warps leave together
+  float v[RPW][EPL];
 #pragma unroll
-  for (int m = 1; m < 32; m <<= 1) {
+  for (int r = 0; r < RPW; ++r) {
+    if (row0 + r < p.rows) {
+      load_run<TIN, EPL>(reinterpret_cast<const TIN*>(p.x) + (row0 + r) * p.ld_x + lane * EPL, v[r], wide_in != 0);
+    } else {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
-      v[e] = (lane & m) ? __fsub_rn(other, v[e]) : __fadd_rn(v[e], other);
+      for (int e = 0; e < EPL; ++e) v[r][e] = 0.f;
     }
   }
-  // ... and over the bits held in the register number
 #pragma unroll
-  for (int m = 1; m < EPL; m <<= 1) {
+  for (int r = 0; r < RPW; ++r) {
+    // butterflies over the index bits held in the register number ...
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      if ((e & m) == 0) {
-        const float a = v[e], c = v[e | m];
-        v[e] = __fadd_rn(a, c);
-        v[e | m] = __fsub_rn(a, c);
+    for (int m = 1; m < EPL; m <<= 1) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        if ((e & m) == 0) {
+          const float a = v[r][e], c = v[r][e | m];
+          v[r][e] = __fadd_rn(a, c);
+          v[r][e | m] = __fsub_rn(a, c);
+        }
+      }
+    }
+    // ... and over the bits held in the lane number
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[r][e], m);
+        v[r][e] = (lane & m) ? __fsub_rn(other, v[r][e]) : __fadd_rn(v[r][e], other);
       }
     }
   }
-  // scale, round to the input dtype (the rotation's result), then to the output dtype (.half() of the caller)
-  float hi = -INFINITY, lo = INFINITY;
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) {
-    v[e] = round_to<TOUT>(round_to<TIN>(__fmul_rn(v[e], p.had_entry)));
-    hi = fmaxf(hi, v[e]);
-    lo = fminf(lo, v[e]);
+  for (int r = 0; r < RPW; ++r) {
+    // scale, round to the input dtype (the rotation's result), then to the output dtype (.half() of the caller)
+    float hi = -INFINITY, lo = INFINITY;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      v[r][e] = round_to<TOUT>(round_to<TIN>(__fmul_rn(v[r][e], p.had_entry)));
+      hi = fmaxf(hi, v[r][e]);
+      lo = fminf(lo, v[r][e]);
+    }
+    if (p.bits != 16) {
+      const DsaRow q = dsa_row_params<TOUT>(warp_max(hi), warp_min(lo), p);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) v[r][e] = dsa_fake_quant<TOUT>(v[r][e], q, p);
+    }
+    if (row0 + r < p.rows)
+      store_run<TOUT, EPL>(reinterpret_cast<TOUT*>(p.out) + (row0 + r) * p.ld_out + lane * EPL, v[r], wide_out != 0);
   }
-  TOUT* out = reinterpret_cast<TOUT*>(p.out) + row * p.ld_out;
-  if (p.bits == 16) {
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) out[e * 32 + lane] = ElemTraits<TOUT>::from_f(v[e]);
-    return;
-  }
-  const DsaRow r = dsa_row_params<TOUT>(warp_max(hi), warp_min(lo), p);
-#pragma unroll
-  for (int e = 0; e < EPL; ++e) out[e * 32 + lane] = ElemTraits<TOUT>::from_f(dsa_fake_quant<TOUT>(v[e], r, p));
 }
 
 // Fake quantization alone (any k): pass 1 takes the bounds, pass 2 re-reads the row (an L1 / L2 hit).
@@ -205,12 +259,21 @@ static int launch_dsa(const DsaParams& p, int rotate, cudaStream_t st) {
   const unsigned grid = (unsigned)((p.rows + kDsaWarps - 1) / kDsaWarps);
   const int threads = kDsaWarps * 32;
   if (rotate) {
+    // a lane's run of k / 32 elements can be moved with wide accesses when every run starts on a multiple of its size
+    auto run_aligned = [&](const void* base, int64_t ld, size_t elem) {
+      const int64_t run = (p.k / 32) * (int64_t)elem;
+      const int64_t need = run >= 16 ? 16 : run;
+      return need >= 4 && reinterpret_cast<uintptr_t>(base) % need == 0 && (ld * (int64_t)elem) % need == 0;
+    };
+    const int wi = run_aligned(p.x, p.ld_x, sizeof(TIN)) ? 1 : 0;
+    const int wo = run_aligned(p.out, p.ld_out, sizeof(TOUT)) ? 1 : 0;
+    auto blocks = [&](int rpw) { return (unsigned)((p.rows + (int64_t)kDsaWarps * rpw - 1) / ((int64_t)kDsaWarps * rpw)); };
     switch (p.k) {
-      case 32: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 1>); break;
-      case 64: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 2>); break;
-      case 128: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 4>); break;
-      case 256: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 8>); break;
-      case 512: AMCT_LAUNCH(grid, threads, st, (p), dsa_rotate_quant_kernel<TIN, TOUT, 16>); break;
+      case 32: AMCT_LAUNCH(blocks(4), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 1, 4>); break;
+      case 64: AMCT_LAUNCH(blocks(4), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 2, 4>); break;
+      case 128: AMCT_LAUNCH(blocks(4), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 4, 4>); break;
+      case 256: AMCT_LAUNCH(blocks(2), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 8, 2>); break;
+      case 512: AMCT_LAUNCH(blocks(1), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 16, 1>); break;
       default: return AMCT_ERR_UNSUPPORTED;
     }
   } else {

@@ -131,6 +131,7 @@ def test_emulated_rotation_and_chain(on_cpu):
             G.test_rotation_golden(dtype, d)
     for d in (32, 64, 128, 256, 512):
         G.test_rotation_widths_and_round_trip(d, rows=9)
+    G.test_rotation_unaligned_rows()
     G.test_indexer_chain()
     G.test_module_with_learned_clipping()
 

@@ -94,6 +94,18 @@ def test_rotation_widths_and_round_trip(d, rows=257):
     assert bool((torch.sign(rows) == torch.sign(O.rotate_activation(basis))).all())
 
 
+def test_rotation_unaligned_rows():
+    """Rows that do not start on a multiple of a lane's run take the element-wise loads and stores."""
+    gen = torch.Generator().manual_seed(44)
+    for dtype, start in ((torch.float32, 3), (torch.bfloat16, 2), (torch.bfloat16, 1), (torch.float16, 4)):
+        big = torch.randn(11, 200, generator=gen).to(dtype)
+        view = big[:, start:start + 128]
+        got = ops().dsa_rotate_fakequant(big.cuda()[:, start:start + 128], rotate=True, bits=16)
+        assert close_rotation(got, O.rotate_activation(view.contiguous()))
+        fused = ops().dsa_rotate_fakequant(big.cuda()[:, start:start + 128], rotate=True, out_dtype=torch.float16, bits=8)
+        assert bits_equal(fused, O.activation_fake_quant(got.cpu().half()))
+
+
 def test_indexer_chain():
     """rotate -> .half() -> symmetric fake quantization, one launch, against the same steps launched one by one and
     against the reference's result for the chain."""
