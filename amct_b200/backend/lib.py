@@ -22,6 +22,7 @@ RULE = {'released': 0, 'experimental': 1}
 PRE_NONE, PRE_MUL, PRE_DIV = 0, 1, 2
 OUT_NONE, OUT_I8, OUT_I32, OUT_PACK4, OUT_FAKE, OUT_FAKE_AWQ = range(6)
 AXIS_TENSOR, AXIS_COLUMN = 0, 1
+DSA_DYNAMIC, DSA_LEARNED_CLIP, DSA_CLIP_RATIO, DSA_STATIC, DSA_STATIC_F32 = range(5)
 
 _lib = None
 

@@ -748,22 +748,33 @@ def hadamard_pow2(n, norm=True, dtype=torch.bfloat16, device='cuda'):
 # ---------------------------------------------------------------------------
 # KV-cache / indexer activations (amct_pytorch/experimental/quantization/DeepSeekV3.2/cores)
 def dsa_rotate_fakequant(x, rotate=False, out_dtype=None, bits=8, symmetric=True, clip_max_sigmoid=None,
-                         clip_min_sigmoid=None):
-    """Optional Hadamard rotation of the last axis, optional cast, per-token dynamic fake quantization (bits=16:
-    none) in one pass.  Learned clipping is on when clip_max_sigmoid is given (then fp32 arithmetic, as torch
-    promotes); the asymmetric rule also needs clip_min_sigmoid."""
+                         clip_min_sigmoid=None, clip_ratio=None, static=None, static_fp32=False):
+    """Optional Hadamard rotation of the last axis, optional cast, fake quantization (bits=16: none) in one pass.
+
+    Per token and dynamic by default.  clip_max_sigmoid (and, asymmetric, clip_min_sigmoid): learned clipping, fp32
+    arithmetic as torch promotes.  clip_ratio: both bounds times a plain ratio.  static=(scale, zero): one given
+    scale and zero point for the whole tensor; static_fp32 says whether torch would promote that arithmetic to fp32.
+    """
     _need_cuda(x)
     out_dtype = out_dtype or x.dtype
     x2, rows, k, ld = _rows2d(x)
     out = torch.empty((rows, k), dtype=out_dtype, device=x.device)
-    lac = clip_max_sigmoid is not None
-    if lac and not symmetric and clip_min_sigmoid is None:
-        raise ValueError('the asymmetric rule with learned clipping needs both sigmoids')
+    chosen = [clip_max_sigmoid is not None, clip_ratio is not None, static is not None]
+    if sum(chosen) > 1:
+        raise ValueError('learned clipping, clip_ratio and a static scale exclude one another')
+    mode, a, b = _l.DSA_DYNAMIC, 1.0, 1.0
+    if clip_max_sigmoid is not None:
+        if not symmetric and clip_min_sigmoid is None:
+            raise ValueError('the asymmetric rule with learned clipping needs both sigmoids')
+        mode, a = _l.DSA_LEARNED_CLIP, float(clip_max_sigmoid)
+        b = float(clip_min_sigmoid) if clip_min_sigmoid is not None else 1.0
+    elif clip_ratio is not None:
+        mode, a = _l.DSA_CLIP_RATIO, float(clip_ratio)
+    elif static is not None:
+        mode, a, b = (_l.DSA_STATIC_F32 if static_fp32 else _l.DSA_STATIC), float(static[0]), float(static[1])
     rc = _l.load().amct_dsa_rotate_fakequant(
         _p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), c_int(int(bool(rotate))), c_int(_DT[out_dtype]),
-        c_int(bits), c_int(int(bool(symmetric))), c_int(int(lac)),
-        ctypes.c_float(float(clip_max_sigmoid) if lac else 1.0),
-        ctypes.c_float(float(clip_min_sigmoid) if clip_min_sigmoid is not None else 1.0),
+        c_int(bits), c_int(int(bool(symmetric))), c_int(mode), ctypes.c_float(a), ctypes.c_float(b),
         _p(out), c_int64(k), _stream())
     _l.check(rc, 'amct_dsa_rotate_fakequant')
     COUNTERS['launches'] += 1

@@ -24,8 +24,8 @@ struct DsaParams {
   int64_t rows, k, ld_x;
   int bits;            // 16: no quantization (rotation / cast only)
   int symmetric;
-  int learned_clip;    // 1: bounds times the sigmoids below, computation in fp32
-  float sig_max, sig_min;
+  int mode;            // AMCT_DSA_*
+  float a, b;          // LEARNED_CLIP: sigmoid of the max / min clip parameter; CLIP_RATIO: a = ratio; STATIC*: scale, zero
   float had_entry;     // fl32(1 / fl32(sqrt(k))) when rotating
   void* out;
   int64_t ld_out;
@@ -34,6 +34,15 @@ struct DsaParams {
 struct DsaRow {
   float scale, recip, zero, qlo, qhi;
 };
+
+// torch promotes to fp32 when the bounds or the scale meet a one-element fp32 tensor (the clip parameter, a loaded
+// scale buffer); otherwise every step stays in the activation dtype
+__device__ __forceinline__ bool dsa_fp32_math(const DsaParams& p) {
+  return p.mode == AMCT_DSA_LEARNED_CLIP || p.mode == AMCT_DSA_STATIC_F32;
+}
+__device__ __forceinline__ bool dsa_static(const DsaParams& p) {
+  return p.mode == AMCT_DSA_STATIC || p.mode == AMCT_DSA_STATIC_F32;
+}
 
 // rounding to the dtype torch computes in: fp32 with learned clipping, else the output dtype
 template <typename T>
@@ -44,31 +53,45 @@ __device__ __forceinline__ float round_c(float v, bool fp32_math) {
 // row bounds (values of the output dtype) -> scale, zero point and code range          node.py:181-215
 template <typename T>
 __device__ __forceinline__ DsaRow dsa_row_params(float row_max, float row_min, const DsaParams& p) {
-  const bool f32 = p.learned_clip != 0;
+  const bool f32 = dsa_fp32_math(p);
+  const bool clip = p.mode == AMCT_DSA_LEARNED_CLIP;
   float hi = fmaxf(row_max, 0.f), lo = fminf(row_min, 0.f);
+  if (p.mode == AMCT_DSA_CLIP_RATIO) {                          // node.py:198-200, in the activation dtype
+    hi = round_to<T>(__fmul_rn(hi, p.a));
+    lo = round_to<T>(__fmul_rn(lo, p.a));
+  }
   DsaRow r;
   if (p.symmetric) {
     const float qmax = (float)((1 << (p.bits - 1)) - 1);
-    const float bound = f32 ? __fmul_rn(fmaxf(fabsf(lo), hi), p.sig_max) : hi;
-    r.scale = round_c<T>(__fdiv_rn(bound, qmax), f32);
-    if (bound == 0.f) r.scale = 1.f;
     r.zero = 0.f;
     r.qlo = -(qmax + 1.f);
     r.qhi = qmax;
+    if (dsa_static(p)) {
+      r.scale = p.a;
+    } else {
+      const float bound = clip ? __fmul_rn(fmaxf(fabsf(lo), hi), p.a) : hi;
+      r.scale = round_c<T>(__fdiv_rn(bound, qmax), f32);
+      if (bound == 0.f) r.scale = 1.f;
+    }
   } else {
     const float qmax = (float)((1 << p.bits) - 1);
-    if (f32) {
-      hi = __fmul_rn(hi, p.sig_max);
-      lo = __fmul_rn(lo, p.sig_min);
-    }
-    if (hi == 0.f && lo == 0.f) {
-      hi = 1.f;
-      lo = -1.f;
-    }
-    r.scale = round_c<T>(__fdiv_rn(round_c<T>(__fsub_rn(hi, lo), f32), qmax), f32);
-    r.zero = rintf(round_c<T>(__fdiv_rn(-lo, r.scale), f32));
     r.qlo = 0.f;
     r.qhi = qmax;
+    if (dsa_static(p)) {
+      r.scale = p.a;
+      r.zero = p.b;
+    } else {
+      if (clip) {
+        hi = __fmul_rn(hi, p.a);
+        lo = __fmul_rn(lo, p.b);
+      }
+      if (hi == 0.f && lo == 0.f) {
+        hi = 1.f;
+        lo = -1.f;
+      }
+      r.scale = round_c<T>(__fdiv_rn(round_c<T>(__fsub_rn(hi, lo), f32), qmax), f32);
+      r.zero = rintf(round_c<T>(__fdiv_rn(-lo, r.scale), f32));
+    }
   }
   const float y = __frcp_rn(r.scale);
   const bool ok = fabsf(r.scale) >= 1.17549435e-38f && fabsf(y) >= 1.17549435e-38f && isfinite(y) && isfinite(r.scale);
@@ -79,7 +102,7 @@ __device__ __forceinline__ DsaRow dsa_row_params(float row_max, float row_min, c
 // one value of the output dtype -> its fake-quantized value (as fp32, representable in T)   node.py:39-66
 template <typename T>
 __device__ __forceinline__ float dsa_fake_quant(float v, const DsaRow& r, const DsaParams& p) {
-  const bool f32 = p.learned_clip != 0;
+  const bool f32 = dsa_fp32_math(p);
   float q;
   if (r.recip != 0.f) {
     q = div_by_recip(v, r.scale, r.recip);
@@ -216,7 +239,9 @@ __global__ void __launch_bounds__(kDsaWarps * 32) dsa_fakequant_kernel(DsaParams
   const int64_t nvec = VEC ? p.k / E : 0;
 
   float hi = -INFINITY, lo = INFINITY;
-  if (VEC) {
+  if (dsa_static(p)) {
+    hi = lo = 0.f;                                             // given scale: no pass over the row for its bounds
+  } else if (VEC) {
     for (int64_t i = lane; i < nvec; i += 32) {
       const Vec16<TIN> raw = ld_vec(x + i * E);
 #pragma unroll
@@ -302,11 +327,11 @@ static int dispatch_dsa_out(const DsaParams& p, int rotate, int out_dtype, cudaS
 using namespace amct;
 
 extern "C" int amct_dsa_rotate_fakequant(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int rotate,
-                                         int out_dtype, int bits, int symmetric, int learned_clip,
-                                         float clip_max_sigmoid, float clip_min_sigmoid, void* out, int64_t ld_out,
-                                         void* stream) {
+                                         int out_dtype, int bits, int symmetric, int mode, float a, float b,
+                                         void* out, int64_t ld_out, void* stream) {
   if (rows < 0 || k <= 0 || ld_x < k || ld_out < k) return AMCT_ERR_ARG;
   if (bits != 16 && (bits < 2 || bits > 8)) return AMCT_ERR_ARG;
+  if (mode < AMCT_DSA_DYNAMIC || mode > AMCT_DSA_STATIC_F32) return AMCT_ERR_ARG;
   if (rotate && (k & (k - 1)) != 0) return AMCT_ERR_ARG;
   if (rotate && (k < 32 || k > 512)) return AMCT_ERR_UNSUPPORTED;
   if (rows == 0) return AMCT_OK;
@@ -319,9 +344,9 @@ extern "C" int amct_dsa_rotate_fakequant(const void* x, int dtype, int64_t rows,
   p.ld_x = ld_x;
   p.bits = bits;
   p.symmetric = symmetric ? 1 : 0;
-  p.learned_clip = learned_clip ? 1 : 0;
-  p.sig_max = clip_max_sigmoid;
-  p.sig_min = clip_min_sigmoid;
+  p.mode = mode;
+  p.a = a;
+  p.b = b;
   p.had_entry = rotate ? 1.0f / sqrtf((float)k) : 1.0f;
   p.out = out;
   p.ld_out = ld_out;

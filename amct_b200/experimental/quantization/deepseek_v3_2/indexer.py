@@ -23,6 +23,5 @@ def rotate_activation(x):
 
 def rotate_half_fake_quant(x, quantizer):
     """quantizer(rotate_activation(x).half()) for a symmetric or asymmetric ``ActivationQuantizer`` of this package."""
-    sig_max, sig_min = quantizer._sigmoids()
     return _ops.dsa_rotate_fakequant(x, rotate=True, out_dtype=torch.float16, bits=quantizer.bits,
-                                     symmetric=quantizer.sym, clip_max_sigmoid=sig_max, clip_min_sigmoid=sig_min)
+                                     symmetric=quantizer.sym, **quantizer.kernel_arguments(torch.float16))

@@ -1,13 +1,16 @@
 """Activation quantizer of the reference's DeepSeek-V3.2 tree on the CUDA kernel.
 
 Drop-in for ``ActivationQuantizer`` of amct_pytorch/experimental/quantization/DeepSeekV3.2/cores/quantization/node.py
-("node.py" below) in the configuration its attention module uses (cores/models/deepseek_v3_2/quant_dsa.py:46-49,
-:113-124): dynamic per-token fake quantization, symmetric without learned clipping, symmetric or asymmetric with
-it.  Same constructor arguments, parameter and buffer names (``clip_factor_a_max``, ``clip_factor_a_min``,
-``maxval``, ``minval``, ``scale``, ``zero``), observe mode and bits=16 pass-through.  The quantization itself is
-``amct_dsa_rotate_fakequant`` (``amct_b200/csrc/kv_quant.cu``); it is an inference-time path: the kernel has no
-backward, so the learned clip factors are read, not trained, here.  Not covered: ``per_tensor=True`` (static
-scale) and ``clip_ratio`` -- both raise NotImplementedError rather than fall back to torch arithmetic.
+("node.py" below): dynamic per-token fake quantization -- symmetric without learned clipping, symmetric or
+asymmetric with it, as its attention module builds them (cores/models/deepseek_v3_2/quant_dsa.py:46-49, :113-124),
+or with a ``clip_ratio`` -- and per-tensor quantization with the scale taken from observed bounds or loaded
+(``deploy`` / ``load_deploy``).  Same constructor arguments, parameter and buffer names (``clip_factor_a_max``,
+``clip_factor_a_min``, ``maxval``, ``minval``, ``scale``, ``zero``), observe mode and bits=16 pass-through.  The
+quantization itself is ``amct_dsa_rotate_fakequant`` (``amct_b200/csrc/kv_quant.cu``); it is an inference-time path:
+the kernel has no backward, so the learned clip factors are read, not trained, here.  What stays on the host is the
+per-tensor scale and zero point: a handful of operations on one-element tensors, written with torch so that their
+dtypes -- which decide, by promotion, whether the kernel rounds every step to the activation dtype or works in
+fp32 -- come out as in the reference.
 """
 import torch
 
@@ -29,10 +32,6 @@ class ActivationQuantizer(torch.nn.Module):
         super().__init__()
         if groupsize > 0:
             raise NotImplementedError('Not support per-group quantization for activation yet.')       # node.py:98-99
-        if per_tensor:
-            raise NotImplementedError('per_tensor=True (a static scale) is not built on the CUDA path')
-        if clip_ratio is not None:
-            raise NotImplementedError('clip_ratio is not built on the CUDA path')
         self.bits, self.sym, self.lac, self.groupsize = bits, sym, lac, groupsize
         self.q_max, self.q_min = get_qmin_qmax(bits, sym)
         self._clip_ratio = clip_ratio
@@ -62,6 +61,29 @@ class ActivationQuantizer(torch.nn.Module):
             return x
         return self.fake_quant(x)
 
+    def get_scale_zero_pertensor(self):
+        """(scale, zero) from the observed bounds (node.py:161-179)."""
+        q_max = self.q_max.to(self.maxval.device)
+        hi, lo = self.maxval.clone(), self.minval.clone()
+        if self.lac:
+            hi = hi * self.sigmoid(self.clip_factor_a_max)
+            lo = lo * self.sigmoid(self.clip_factor_a_min)
+        elif self._clip_ratio is not None:
+            hi, lo = hi * self._clip_ratio, lo * self._clip_ratio
+        if self.sym:
+            scale = torch.maximum(lo.abs(), hi) / q_max
+            return scale, torch.zeros_like(scale)
+        scale = (hi - lo) / q_max
+        return scale, torch.round(-lo / scale)
+
+    def deploy(self):
+        scale, zero = self.get_scale_zero_pertensor()
+        self.scale.data, self.zero.data = scale, zero
+
+    def load_deploy(self, scale, zero):
+        self.scale.data, self.zero.data = scale, zero
+        self.is_deploy = True
+
     def _sigmoids(self):
         if not self.lac:
             return None, None
@@ -71,9 +93,26 @@ class ActivationQuantizer(torch.nn.Module):
             return (float(torch.sigmoid(self.clip_factor_a_max.float())),
                     float(torch.sigmoid(self.clip_factor_a_min.float())))
 
+    def kernel_arguments(self, x_dtype):
+        """Keyword arguments of ``ops.dsa_rotate_fakequant`` for an activation of ``x_dtype``."""
+        if self.is_per_tensor:
+            with torch.no_grad():
+                scale, zero = (self.scale.data, self.zero.data) if self.is_deploy else self.get_scale_zero_pertensor()
+            if scale.numel() != 1:
+                raise NotImplementedError('per-tensor quantization takes a one-element scale')
+            promoted = torch.result_type(torch.empty(1, dtype=x_dtype), scale)
+            if promoted not in (x_dtype, torch.float32):
+                raise NotImplementedError(f'arithmetic in {promoted} is not built')
+            return {'static': (float(scale), float(zero)), 'static_fp32': promoted == torch.float32 and x_dtype != torch.float32}
+        if self.lac:
+            sig_max, sig_min = self._sigmoids()
+            return {'clip_max_sigmoid': sig_max, 'clip_min_sigmoid': sig_min}
+        if self._clip_ratio is not None:
+            return {'clip_ratio': float(self._clip_ratio)}
+        return {}
+
     def fake_quant(self, x):
-        sig_max, sig_min = self._sigmoids()
         if self.sym:
             self.cnt += 1
         return _ops.dsa_rotate_fakequant(x, rotate=False, bits=self.bits, symmetric=self.sym,
-                                         clip_max_sigmoid=sig_max, clip_min_sigmoid=sig_min)
+                                         **self.kernel_arguments(x.dtype))

@@ -34,6 +34,8 @@ enum { AMCT_PRE_NONE = 0, AMCT_PRE_MUL = 1, AMCT_PRE_DIV = 2 };
 enum { AMCT_OUT_NONE = 0, AMCT_OUT_I8 = 1, AMCT_OUT_I32 = 2, AMCT_OUT_PACK4 = 3, AMCT_OUT_FAKE = 4,
        AMCT_OUT_FAKE_AWQ = 5 };
 enum { AMCT_AXIS_TENSOR = 0, AMCT_AXIS_COLUMN = 1 };
+enum { AMCT_DSA_DYNAMIC = 0, AMCT_DSA_LEARNED_CLIP = 1, AMCT_DSA_CLIP_RATIO = 2, AMCT_DSA_STATIC = 3,
+       AMCT_DSA_STATIC_F32 = 4 };
 
 /* Version of this ABI; bumped when a signature changes. */
 int amct_abi_version(void);
@@ -295,19 +297,23 @@ int amct_hadamard_pow2(int n, int norm, int dtype, void* out, void* stream);
  *   rotate != 0: r = dtype(x @ (H / sqrt(k))) in fp32, H the k x k Sylvester Hadamard matrix, k a power of two in
  *                32 .. 512 (rotate_activation, cores/models/deepseek_v3_2/indexer.py:140-151); else r = x;
  *   y = out_dtype(r) (the `.half()` of cores/models/deepseek_v3_2/quant_dsa.py:78-79 when out_dtype differs);
- *   bits == 16: out = y.  Otherwise out = the per-token dynamic fake quantization of y, any k
- *   (ActivationQuantizer.fake_quant with per_tensor=False, cores/quantization/node.py:140-215 and :39-66):
+ *   bits == 16: out = y.  Otherwise out = the fake quantization of y, any k (ActivationQuantizer.fake_quant,
+ *   cores/quantization/node.py:140-215 and :39-66), per token and dynamic unless the mode is static:
  *     bounds hi = max(row max, 0), lo = min(row min, 0);
- *     symmetric, learned_clip = 0: scale = hi / qmax (the negative side does not widen it; 1 when hi == 0),
- *       codes in [-(qmax + 1), qmax], qmax = 2^(bits-1) - 1, every step rounded to out_dtype;
- *     symmetric, learned_clip = 1: scale = max(|lo|, hi) * clip_max_sigmoid / qmax in fp32, all steps in fp32;
- *     asymmetric: hi *= clip_max_sigmoid, lo *= clip_min_sigmoid when learned_clip (fp32 steps), a row of zeros uses
- *       [-1, 1], scale = (hi - lo) / qmax, zero = round(-lo / scale), codes in [0, qmax], qmax = 2^bits - 1.
- *   clip_*_sigmoid are host values: the sigmoid of the module's clip_factor_a_max / clip_factor_a_min parameters.
- * out [rows, k] in out_dtype (ld_out).  One warp per row; one pass over HBM. */
+ *     AMCT_DSA_DYNAMIC, symmetric: scale = hi / qmax (the negative side does not widen it; 1 when hi == 0), codes in
+ *       [-(qmax + 1), qmax], qmax = 2^(bits-1) - 1; asymmetric: a row of zeros uses [-1, 1], scale = (hi - lo) / qmax,
+ *       zero = round(-lo / scale), codes in [0, qmax], qmax = 2^bits - 1; every step rounded to out_dtype;
+ *     AMCT_DSA_LEARNED_CLIP (lac=True): symmetric bound = max(|lo|, hi) * a; asymmetric hi *= a, lo *= b; a, b = the
+ *       sigmoid of clip_factor_a_max / clip_factor_a_min; every step in fp32 (the fp32 parameter promotes);
+ *     AMCT_DSA_CLIP_RATIO (clip_ratio): hi *= a, lo *= a, rounded to out_dtype, then as AMCT_DSA_DYNAMIC;
+ *     AMCT_DSA_STATIC / AMCT_DSA_STATIC_F32 (per_tensor=True): scale = a, zero = b for every element; steps
+ *       rounded to out_dtype / kept in fp32 -- torch's promotion of the activation with the module's scale tensor
+ *       (a 0-dim scale taken from observed 16-bit data keeps 16-bit steps; a one-element fp32 buffer promotes).
+ *   a and b are host values.
+ * out [rows, k] in out_dtype (ld_out).  One warp per row (up to four rows at a time when rotating); one pass over HBM. */
 int amct_dsa_rotate_fakequant(const void* x, int dtype, int64_t rows, int64_t k, int64_t ld_x, int rotate, int out_dtype,
-                              int bits, int symmetric, int learned_clip, float clip_max_sigmoid, float clip_min_sigmoid,
-                              void* out, int64_t ld_out, void* stream);
+                              int bits, int symmetric, int mode, float a, float b, void* out, int64_t ld_out,
+                              void* stream);
 
 /* ---- Glue of the sharded deploy workload (no counterpart in the reference) ---- */
 

@@ -24,7 +24,7 @@ def rt(x, dtype):
 
 
 # node.py:181-215 (bounds and scale), :39-66 (quantize / dequantize), :140-159 (fake_quant)
-def activation_fake_quant(x, bits=8, sym=True, lac=False, clip_max_raw=None, clip_min_raw=None):
+def activation_fake_quant(x, bits=8, sym=True, lac=False, clip_max_raw=None, clip_min_raw=None, clip_ratio=None):
     """Per-token (last axis) dynamic fake quantization of ActivationQuantizer with per_tensor=False.
 
     Bounds: hi = max(row max, 0), lo = min(row min, 0) (node.py:186-188).
@@ -33,6 +33,8 @@ def activation_fake_quant(x, bits=8, sym=True, lac=False, clip_max_raw=None, cli
     asym (clipping): hi *= sigmoid(clip_max_raw), lo *= sigmoid(clip_min_raw); a row of zeros uses [-1, 1];
     scale = (hi - lo) / qmax, zero = round(-lo / scale).
     Codes are clamped to [-(qmax + 1), qmax] (sym) or [0, qmax] (asym).
+    clip_ratio (a plain number, only without learned clipping): both bounds times the ratio, rounded to the
+    activation dtype (node.py:198-200).
     """
     if bits == 16:
         return x
@@ -42,6 +44,8 @@ def activation_fake_quant(x, bits=8, sym=True, lac=False, clip_max_raw=None, cli
     xf = x.reshape(-1, shape[-1]).to(torch.float32)
     hi = xf.amax(1, keepdim=True).clamp(min=0)
     lo = xf.amin(1, keepdim=True).clamp(max=0)
+    if clip_ratio is not None and not lac:
+        hi, lo = rt(hi * clip_ratio, dtype), rt(lo * clip_ratio, dtype)
     if sym:
         qmax = float(2 ** (bits - 1) - 1)
         if lac:
@@ -64,6 +68,51 @@ def activation_fake_quant(x, bits=8, sym=True, lac=False, clip_max_raw=None, cli
     zero = torch.round(rt(-lo / scale, comp))
     level = rt(torch.round(rt(xf / scale, comp)) + zero, comp).clamp(0, qmax)
     return rt(scale * rt(level - zero, comp), comp).to(dtype).reshape(shape)
+
+
+# node.py:161-179 (per-tensor bounds -> scale / zero), :117-128 (observation)
+def observe(chunks):
+    """Running bounds as the observe mode keeps them: fp32 one-element buffers of zeros, REPLACED by the chunk's own
+    0-dim max / min (in the chunk's dtype) whenever that exceeds them."""
+    hi, lo = torch.zeros(1), torch.zeros(1)
+    for x in chunks:
+        if x.max() > hi:
+            hi = x.max()
+        if x.min() < lo:
+            lo = x.min()
+    return hi, lo
+
+
+def per_tensor_scale_zero(hi, lo, bits=8, sym=True, lac=False, clip_max_raw=None, clip_min_raw=None):
+    """(scale, zero) tensors with the dtypes and shapes torch gives them: they decide, by promotion against the
+    activation, whether the quantization runs in the activation dtype or in fp32."""
+    if lac:
+        hi = hi * torch.sigmoid(torch.full((1,), clip_max_raw))
+        lo = lo * torch.sigmoid(torch.full((1,), clip_min_raw))
+    if sym:
+        bound = torch.maximum(lo.abs(), hi)
+        scale = bound / torch.tensor(2 ** (bits - 1) - 1)
+        return scale, torch.zeros_like(scale)
+    scale = (hi - lo) / torch.tensor(2 ** bits - 1)
+    return scale, torch.round(-lo / scale)
+
+
+# node.py:140-159 with a given scale and zero point, :39-66
+def static_fake_quant(x, scale, zero, bits=8, sym=True):
+    """Fake quantization with one given scale / zero point; the arithmetic dtype is torch's promotion of the
+    activation with the scale tensor (a 0-dim scale of a 16-bit dtype keeps 16-bit steps, a one-element fp32
+    buffer promotes to fp32)."""
+    dtype = x.dtype
+    comp = torch.result_type(x, scale)
+    xf = x.to(torch.float32)
+    s, z = float(scale), float(zero)
+    if sym:
+        qmax = float(2 ** (bits - 1) - 1)
+        level = (torch.round(rt(xf / s, comp)) + 0.0).clamp(-(qmax + 1), qmax)
+        return rt(s * level, comp).to(dtype)
+    qmax = float(2 ** bits - 1)
+    level = rt(torch.round(rt(xf / s, comp)) + z, comp).clamp(0, qmax)
+    return rt(s * rt(level - z, comp), comp).to(dtype)
 
 
 # indexer.py:140-151

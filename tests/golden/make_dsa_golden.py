@@ -72,6 +72,30 @@ def main():
         r = rotate_activation(x)
         put('chain.rotated', r)
         put('chain.out', aq(r.half()))
+    # clip_ratio (a plain number: the bounds stay in the activation dtype) and per-tensor static scales taken from an
+    # observation pass (fp32 buffers of one element: they promote the arithmetic to fp32)
+    for dname, dt in {'fp16': torch.float16, 'bf16': torch.bfloat16, 'fp32': torch.float32}.items():
+        x = activations(gen, 12, 256, dt)
+        put(f'ext.{dname}.x', x)
+        with torch.no_grad():
+            for sym in (True, False):
+                tag = 'sym' if sym else 'asym'
+                aq = ActivationQuantizer(bits=8, sym=sym, lac=False, groupsize=-1, clip_ratio=0.9, per_tensor=False)
+                put(f'ext.{dname}.ratio.{tag}', aq(x))
+                for lac in (False, True):
+                    aq = ActivationQuantizer(bits=8, sym=sym, lac=lac, groupsize=-1, per_tensor=True)
+                    if lac:
+                        aq.clip_factor_a_max.data.fill_(1.7)
+                        aq.clip_factor_a_min.data.fill_(0.9)
+                    aq.is_observe = True
+                    aq(x[:6])
+                    aq(x[6:])
+                    aq.is_observe = False
+                    put(f"ext.{dname}.tensor.{tag}.{'lac' if lac else 'plain'}", aq(x))
+                    if dname == 'fp16' and lac:
+                        aq.deploy()
+                        put(f'ext.deploy.{tag}.scale', aq.scale.data.float().reshape(-1))
+                        put(f'ext.deploy.{tag}.zero', aq.zero.data.float().reshape(-1))
     np.savez_compressed(os.path.join(HERE, 'dsa_golden.npz'), **store)
     print(len(store), 'arrays')
 

@@ -34,6 +34,19 @@ def test_oracle_rotation(dtype, d):
     assert bool(((got.float() - want.float()).abs() <= ulp).all())
 
 
+@pytest.mark.parametrize('dtype', ['fp16', 'bf16', 'fp32'])
+def test_oracle_clip_ratio_and_per_tensor(dtype):
+    x = GOLD.get(f'ext.{dtype}.x')
+    for sym in (True, False):
+        tag = 'sym' if sym else 'asym'
+        assert bits_equal(O.activation_fake_quant(x, 8, sym, False, clip_ratio=0.9), GOLD.get(f'ext.{dtype}.ratio.{tag}'))
+        hi, lo = O.observe([x[:6], x[6:]])
+        for lac in (False, True):
+            scale, zero = O.per_tensor_scale_zero(hi, lo, 8, sym, lac, CLIP_MAX, CLIP_MIN)
+            want = GOLD.get(f"ext.{dtype}.tensor.{tag}.{'lac' if lac else 'plain'}")
+            assert bits_equal(O.static_fake_quant(x, scale, zero, 8, sym), want)
+
+
 def test_oracle_indexer_chain():
     r = O.rotate_activation(GOLD.get('chain.x'))
     assert bits_equal(O.activation_fake_quant(GOLD.get('chain.rotated').half()), GOLD.get('chain.out'))
@@ -52,16 +65,38 @@ def test_module_mirror_names_and_refusals():
     from amct_b200.experimental.quantization.deepseek_v3_2.node import ActivationQuantizer, get_qmin_qmax
     q = ActivationQuantizer(bits=8, sym=True, lac=True, groupsize=-1, per_tensor=False)
     assert sorted(q.state_dict()) == ['clip_factor_a_max', 'clip_factor_a_min', 'maxval', 'minval', 'scale', 'zero']
-    assert float(q.clip_factor_a_max) == 4.0 and int(q.q_max) == 127 and int(q.q_min) == -128
+    assert float(q.clip_factor_a_max.detach()) == 4.0 and int(q.q_max) == 127 and int(q.q_min) == -128
     assert [int(v) for v in get_qmin_qmax(8, False)] == [255, 0]
     x = torch.randn(3, 8)
     assert ActivationQuantizer(bits=16)(x) is x                                # pass-through needs no kernel
     obs = ActivationQuantizer(bits=8, sym=True)
     obs.is_observe = True
     assert obs(x) is x and float(obs.maxval) == float(x.max()) and float(obs.minval) == float(x.min())
-    for kwargs in ({'groupsize': 64}, {'per_tensor': True}, {'clip_ratio': 0.9}):
-        with pytest.raises(NotImplementedError):
-            ActivationQuantizer(bits=8, sym=True, **kwargs)
+    with pytest.raises(NotImplementedError):
+        ActivationQuantizer(bits=8, sym=True, groupsize=64)
+    # per-tensor: the host side (bounds -> scale / zero, and which arithmetic dtype torch would use)
+    x16 = GOLD.get('ext.fp16.x')
+    for sym in (True, False):
+        tag = 'sym' if sym else 'asym'
+        pt = ActivationQuantizer(bits=8, sym=sym, lac=True, per_tensor=True)
+        pt.clip_factor_a_max.data.fill_(CLIP_MAX)
+        pt.clip_factor_a_min.data.fill_(CLIP_MIN)
+        pt.is_observe = True
+        pt(x16[:6])
+        pt(x16[6:])
+        pt.is_observe = False
+        assert pt.maxval.dtype == torch.float16 and pt.maxval.dim() == 0          # replaced by the chunk's own max
+        args = pt.kernel_arguments(torch.float16)
+        assert args['static_fp32'] is True                                        # the fp32 clip parameter promotes
+        assert args['static'][0] == float(GOLD.get(f'ext.deploy.{tag}.scale')) and args['static'][1] == float(GOLD.get(f'ext.deploy.{tag}.zero'))
+        pt.deploy()
+        assert bits_equal(pt.scale.data.float().reshape(-1), GOLD.get(f'ext.deploy.{tag}.scale'))
+        plain = ActivationQuantizer(bits=8, sym=sym, lac=False, per_tensor=True)
+        plain.is_observe = True
+        plain(x16)
+        plain.is_observe = False
+        assert plain.kernel_arguments(torch.float16)['static_fp32'] is False      # 0-dim fp16 bounds: fp16 steps
+    assert ActivationQuantizer(bits=8, sym=True, clip_ratio=0.9).kernel_arguments(torch.bfloat16) == {'clip_ratio': 0.9}
     from amct_b200.backend.lib import BackendError
     with pytest.raises(BackendError):                                          # no CPU fallback
         ActivationQuantizer(bits=8, sym=True)(x)

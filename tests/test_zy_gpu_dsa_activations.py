@@ -136,6 +136,31 @@ def test_module_with_learned_clipping():
         assert bits_equal(q(x.unsqueeze(1)).squeeze(1), GOLD.get(f"fq.bf16.512.lac.{'sym' if sym else 'asym'}"))
 
 
+@pytest.mark.parametrize('dtype', ['fp16', 'bf16', 'fp32'])
+def test_clip_ratio_and_per_tensor_modules(dtype):
+    """ActivationQuantizer with a clip_ratio, and per-tensor with observed bounds (with and without learned clipping:
+    fp32 and activation-dtype arithmetic), through the module, against the reference's outputs."""
+    from amct_b200.experimental.quantization.deepseek_v3_2.node import ActivationQuantizer
+    x = GOLD.get(f'ext.{dtype}.x').cuda()
+    for sym in (True, False):
+        tag = 'sym' if sym else 'asym'
+        q = ActivationQuantizer(bits=8, sym=sym, lac=False, groupsize=-1, clip_ratio=0.9, per_tensor=False)
+        assert bits_equal(q(x), GOLD.get(f'ext.{dtype}.ratio.{tag}'))
+        for lac in (False, True):
+            q = ActivationQuantizer(bits=8, sym=sym, lac=lac, groupsize=-1, per_tensor=True)
+            if lac:
+                q.clip_factor_a_max.data.fill_(CLIP_MAX)
+                q.clip_factor_a_min.data.fill_(CLIP_MIN)
+            q.is_observe = True
+            q(x[:6])
+            q(x[6:])
+            q.is_observe = False
+            assert bits_equal(q(x), GOLD.get(f"ext.{dtype}.tensor.{tag}.{'lac' if lac else 'plain'}"))
+            scale, zero = q.get_scale_zero_pertensor()
+            q.load_deploy(scale, zero)
+            assert bits_equal(q(x), GOLD.get(f"ext.{dtype}.tensor.{tag}.{'lac' if lac else 'plain'}"))
+
+
 def test_argument_errors():
     from amct_b200.backend.lib import BackendError
     x = torch.zeros(4, 48, device='cuda')
@@ -147,3 +172,5 @@ def test_argument_errors():
         ops().dsa_rotate_fakequant(x, bits=9)
     with pytest.raises(ValueError):
         ops().dsa_rotate_fakequant(x, symmetric=False, clip_max_sigmoid=0.5)
+    with pytest.raises(ValueError):
+        ops().dsa_rotate_fakequant(x, clip_ratio=0.9, static=(1.0, 0.0))
