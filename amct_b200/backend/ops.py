@@ -699,6 +699,36 @@ def ckpt_rowquant(weight, bits=8, clip_factor=None):
     return codes, scale, bias
 
 
+def ckpt_dequant_rowquant(weight_fp8, block_scale, bits=8, clip_factor=None, block_size=128, dtype=torch.bfloat16):
+    """ckpt_rowquant(ckpt_block_dequant(weight_fp8, block_scale)) in one pass over the FP8 weight; same results."""
+    _need_cuda(weight_fp8, block_scale)
+    if weight_fp8.dim() != 2 or weight_fp8.element_size() != 1:
+        raise ValueError('weight must be a 2-D tensor of one-byte E4M3 values')
+    if bits not in (8, 4):
+        raise ValueError('bits must be 8 or 4')
+    rows, k = weight_fp8.shape
+    if tuple(block_scale.shape) != ((rows + block_size - 1) // block_size, (k + block_size - 1) // block_size):
+        raise AssertionError('Mismatch in scale shape and weight shape.')          # deploy.py:70-73
+    if bits == 4 and rows % 2:
+        raise ValueError('INT4 packing pairs output channels: the row count must be even')
+    w = weight_fp8.contiguous().view(torch.uint8)
+    s = block_scale.to(torch.float32).contiguous()
+    dev = w.device
+    codes = torch.empty((rows if bits == 8 else rows // 2, k), dtype=torch.int8, device=dev)
+    scale = torch.empty((rows, 1), dtype=torch.float32 if bits == 8 else torch.int64, device=dev)
+    bias = torch.empty(rows, dtype=torch.float32, device=dev) if bits == 4 else None
+    use_clip = clip_factor is not None
+    rc = _l.load().amct_ckpt_dequant_rowquant(
+        _p(w), c_int64(rows), c_int64(k), c_int64(k), _p(s), c_int64(s.shape[1]), c_int(block_size), c_int(_DT[dtype]),
+        c_int(bits), c_int(int(use_clip)), ctypes.c_float(float(clip_factor) if use_clip else 1.0),
+        _p(codes), c_int64(k), _p(scale), _p(bias), _stream())
+    _l.check(rc, 'amct_ckpt_dequant_rowquant')
+    COUNTERS['launches'] += 1
+    if bits == 4:
+        scale = scale.view(torch.uint64)
+    return codes, scale, bias
+
+
 def ckpt_pack4_rows(codes):
     """int8 [N, K] of 4-bit values, N even -> int8 [N / 2, K] (row 2j low nibble, row 2j + 1 high nibble)."""
     _need_cuda(codes)

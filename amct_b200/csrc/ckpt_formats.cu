@@ -166,16 +166,65 @@ __device__ __forceinline__ float ckpt_bias_term(float level, float s) {
   return round_to<T>(__fmul_rn(round_to<T>(__fmul_rn(s, level)), 8.f));
 }
 
+// Where the rows come from: values of T as they are, or an E4M3 matrix with block scales, dequantized on the fly
+// to the value weight_dequant would have stored in T (so the fused path is bit-identical to dequant + quant, and
+// the T copy of the weight never goes to HBM).
+template <typename T>
+struct SrcRows {
+  static constexpr int kElems = ElemTraits<T>::kPerVec;      // elements per 16-byte load
+  const T* base;
+  int64_t ld;
+  __device__ __forceinline__ void load_vec(int64_t row, int64_t v, float* f, bool stream) const {
+    const T* q = base + row * ld + v * kElems;
+    const Vec16<T> raw = stream ? ld_vec_stream(q) : ld_vec(q);
+#pragma unroll
+    for (int e = 0; e < kElems; ++e) f[e] = ElemTraits<T>::to_f(raw.v[e]);
+  }
+  __device__ __forceinline__ float load_one(int64_t row, int64_t j) const { return ElemTraits<T>::to_f(base[row * ld + j]); }
+};
+template <typename T>
+struct SrcFp8Blocks {
+  static constexpr int kElems = 16;
+  const uint8_t* base;
+  int64_t ld;
+  const float* scale;
+  int64_t ld_scale;
+  int block;
+  __device__ __forceinline__ void load_vec(int64_t row, int64_t v, float* f, bool stream) const {
+    const float s = __ldg(scale + (row / block) * ld_scale + (v * 16) / block);
+    const uint4* q = reinterpret_cast<const uint4*>(base + row * ld + v * 16);
+    const uint4 raw = stream ? __ldcs(q) : __ldg(q);
+    const uint32_t word[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 lo = e4m3x2_to_float2(word[j]);
+      const float2 hi = e4m3x2_to_float2(word[j] >> 16);
+      f[4 * j + 0] = round_to<T>(__fmul_rn(lo.x, s));
+      f[4 * j + 1] = round_to<T>(__fmul_rn(lo.y, s));
+      f[4 * j + 2] = round_to<T>(__fmul_rn(hi.x, s));
+      f[4 * j + 3] = round_to<T>(__fmul_rn(hi.y, s));
+    }
+  }
+  __device__ __forceinline__ float load_one(int64_t row, int64_t j) const {
+    const float s = __ldg(scale + (row / block) * ld_scale + j / block);
+    return round_to<T>(__fmul_rn(e4m3_to_float(base[row * ld + j]), s));
+  }
+};
+
+template <int N>
+__device__ __forceinline__ void store_codes(int8_t* dst, const int8_t* bytes) {
+  if (N == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(bytes);
+  else if (N == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(bytes);
+  else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(bytes);
+}
+
 // One CTA per row (INT8) or per pair of rows 2j, 2j + 1 (INT4: their codes share the bytes of output row j).
-template <typename T, bool VEC, int NROW>
-__global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParams p) {
-  constexpr int E = ElemTraits<T>::kPerVec;
+template <typename T, typename SRC, bool VEC, int NROW>
+__global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParams p, SRC src) {
+  constexpr int E = SRC::kElems;
   __shared__ float red[kRowThreads / 32];
   const int tid = threadIdx.x;
   const int64_t row0 = (int64_t)blockIdx.x * NROW;
-  const T* x[NROW];
-#pragma unroll
-  for (int r = 0; r < NROW; ++r) x[r] = reinterpret_cast<const T*>(p.w) + (row0 + r) * p.ld;
   const float qmax = (float)((1 << (p.bits - 1)) - 1);
   const int64_t nvec = VEC ? p.k / E : 0;
 
@@ -186,17 +235,17 @@ __global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParam
     float m = 0.f, bad = 0.f;
     if (VEC) {
       for (int64_t v = tid; v < nvec; v += kRowThreads) {
-        const Vec16<T> raw = ld_vec(x[r] + v * E);
+        float f[E];
+        src.load_vec(row0 + r, v, f, false);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-          const float f = ElemTraits<T>::to_f(raw.v[e]);
-          m = fmaxf(m, fabsf(f));
-          if (f != f) bad = 1.f;
+          m = fmaxf(m, fabsf(f[e]));
+          if (f[e] != f[e]) bad = 1.f;
         }
       }
     } else {
       for (int64_t j = tid; j < p.k; j += kRowThreads) {
-        const float f = ElemTraits<T>::to_f(x[r][j]);
+        const float f = src.load_one(row0 + r, j);
         m = fmaxf(m, fabsf(f));
         if (f != f) bad = 1.f;
       }
@@ -213,7 +262,7 @@ __global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParam
     u[r] = make_scale(round_to<T>(__fdiv_rn(a, qmax)));                        // deploy.py:134
   }
 
-  // pass 2: codes (and the bias terms of INT4)
+  // pass 2: codes (and the bias terms of INT4); the row comes back from L1 / L2
   float acc[NROW];
 #pragma unroll
   for (int r = 0; r < NROW; ++r) acc[r] = 0.f;
@@ -223,11 +272,11 @@ __global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParam
       float lvl[NROW][E];
 #pragma unroll
       for (int r = 0; r < NROW; ++r) {
-        const Vec16<T> raw = ld_vec_stream(x[r] + v * E);
+        src.load_vec(row0 + r, v, lvl[r], true);
 #pragma unroll
-        for (int e = 0; e < E; ++e) lvl[r][e] = ckpt_level<T>(ElemTraits<T>::to_f(raw.v[e]), u[r], qmax);
+        for (int e = 0; e < E; ++e) lvl[r][e] = ckpt_level<T>(lvl[r][e], u[r], qmax);
       }
-      alignas(8) int8_t bytes[E];
+      alignas(16) int8_t bytes[E];
 #pragma unroll
       for (int e = 0; e < E; ++e) {
         if (NROW == 1) {
@@ -239,17 +288,13 @@ __global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParam
           for (int r = 0; r < NROW; ++r) acc[r] = __fadd_rn(acc[r], ckpt_bias_term<T>(lvl[r][e], u[r].s));
         }
       }
-      if (E == 8) {
-        *reinterpret_cast<uint2*>(out_row + v * E) = *reinterpret_cast<const uint2*>(bytes);
-      } else {
-        *reinterpret_cast<uint32_t*>(out_row + v * E) = *reinterpret_cast<const uint32_t*>(bytes);
-      }
+      store_codes<E>(out_row + v * E, bytes);
     }
   } else {
     for (int64_t j = tid; j < p.k; j += kRowThreads) {
       float lvl[NROW];
 #pragma unroll
-      for (int r = 0; r < NROW; ++r) lvl[r] = ckpt_level<T>(ElemTraits<T>::to_f(x[r][j]), u[r], qmax);
+      for (int r = 0; r < NROW; ++r) lvl[r] = ckpt_level<T>(src.load_one(row0 + r, j), u[r], qmax);
       if (NROW == 1) {
         out_row[j] = (int8_t)(int)lvl[0];
       } else {
@@ -278,22 +323,38 @@ __global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParam
   }
 }
 
-template <typename T>
-static int launch_rowquant(const CkptRowParams& p, cudaStream_t st) {
-  constexpr int E = ElemTraits<T>::kPerVec;
-  const bool vec = p.k % E == 0 && aligned16(p.w) && (p.ld * (int64_t)sizeof(T)) % 16 == 0 &&
-                   (reinterpret_cast<uintptr_t>(p.codes) & 7u) == 0 && p.ld_codes % 8 == 0;
+template <typename T, typename SRC>
+static int launch_rowquant(const CkptRowParams& p, const SRC& src, bool vec, cudaStream_t st) {
   if (p.bits == 8) {
     const unsigned grid = (unsigned)p.rows;
-    if (vec) AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, true, 1>);
-    else AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, false, 1>);
+    if (vec) AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_kernel<T, SRC, true, 1>);
+    else AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_kernel<T, SRC, false, 1>);
   } else {
     const unsigned grid = (unsigned)(p.rows / 2);
-    if (vec) AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, true, 2>);
-    else AMCT_LAUNCH(grid, kRowThreads, st, (p), ckpt_rowquant_kernel<T, false, 2>);
+    if (vec) AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_kernel<T, SRC, true, 2>);
+    else AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_kernel<T, SRC, false, 2>);
   }
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
+}
+
+// rows of T
+template <typename T>
+static int launch_rowquant_plain(const CkptRowParams& p, cudaStream_t st) {
+  constexpr int E = ElemTraits<T>::kPerVec;
+  const bool vec = p.k % E == 0 && aligned16(p.w) && (p.ld * (int64_t)sizeof(T)) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(p.codes) % E) == 0 && p.ld_codes % E == 0;
+  SrcRows<T> src{reinterpret_cast<const T*>(p.w), p.ld};
+  return launch_rowquant<T, SrcRows<T>>(p, src, vec, st);
+}
+
+// E4M3 rows with block scales, dequantized to T on the fly
+template <typename T>
+static int launch_rowquant_fp8(const CkptRowParams& p, const float* scale, int64_t ld_scale, int block, cudaStream_t st) {
+  const bool vec = p.k % 16 == 0 && block % 16 == 0 && aligned16(p.w) && p.ld % 16 == 0 && aligned16(p.codes) &&
+                   p.ld_codes % 16 == 0;
+  SrcFp8Blocks<T> src{reinterpret_cast<const uint8_t*>(p.w), p.ld, scale, ld_scale, block};
+  return launch_rowquant<T, SrcFp8Blocks<T>>(p, src, vec, st);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -379,9 +440,30 @@ extern "C" int amct_ckpt_rowquant(const void* w, int dtype, int64_t rows, int64_
   CkptRowParams p{w, rows, k, ld, bits, use_clip ? 1 : 0, clip_factor, codes, ld_codes, scale, bias};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case AMCT_DTYPE_F32: return launch_rowquant<float>(p, st);
-    case AMCT_DTYPE_F16: return launch_rowquant<__half>(p, st);
-    case AMCT_DTYPE_BF16: return launch_rowquant<__nv_bfloat16>(p, st);
+    case AMCT_DTYPE_F32: return launch_rowquant_plain<float>(p, st);
+    case AMCT_DTYPE_F16: return launch_rowquant_plain<__half>(p, st);
+    case AMCT_DTYPE_BF16: return launch_rowquant_plain<__nv_bfloat16>(p, st);
+  }
+  return AMCT_ERR_ARG;
+}
+
+extern "C" int amct_ckpt_dequant_rowquant(const void* w_fp8, int64_t rows, int64_t k, int64_t ld_w, const float* block_scale,
+                                          int64_t ld_scale, int block, int dtype, int bits, int use_clip,
+                                          float clip_factor, int8_t* codes, int64_t ld_codes, void* scale, float* bias,
+                                          void* stream) {
+  if (rows < 0 || k < 0 || ld_w < k || ld_codes < k || block <= 0) return AMCT_ERR_ARG;
+  if (ld_scale < (k + block - 1) / block) return AMCT_ERR_ARG;
+  if (bits != 8 && bits != 4) return AMCT_ERR_ARG;
+  if (bits == 4 && rows % 2 != 0) return AMCT_ERR_ARG;
+  if (rows == 0) return AMCT_OK;
+  if (!w_fp8 || !block_scale || !codes || !scale || (bits == 4 && !bias)) return AMCT_ERR_ARG;
+  if (rows > 0x7fffffff) return AMCT_ERR_UNSUPPORTED;
+  CkptRowParams p{w_fp8, rows, k, ld_w, bits, use_clip ? 1 : 0, clip_factor, codes, ld_codes, scale, bias};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case AMCT_DTYPE_F32: return launch_rowquant_fp8<float>(p, block_scale, ld_scale, block, st);
+    case AMCT_DTYPE_F16: return launch_rowquant_fp8<__half>(p, block_scale, ld_scale, block, st);
+    case AMCT_DTYPE_BF16: return launch_rowquant_fp8<__nv_bfloat16>(p, block_scale, ld_scale, block, st);
   }
   return AMCT_ERR_ARG;
 }

@@ -74,6 +74,16 @@ def int_weight_quant(tensor, bits=8, weight_clip_factor=None):
     return _ops.ckpt_rowquant(tensor, bits=bits, clip_factor=weight_clip_factor)
 
 
+def dequant_int_weight_quant(weight, scale, bits=8, weight_clip_factor=None, block_size=128):
+    """int_weight_quant(weight_dequant(weight, scale), bits, weight_clip_factor) in one pass over the FP8 weight:
+    the dequantized copy stays in registers.  Same results; no counterpart function in the reference, whose main
+    runs the two steps one after the other (deploy.py:437-463)."""
+    if weight_clip_factor is not None:
+        weight_clip_factor = float(weight_clip_factor)
+    return _ops.ckpt_dequant_rowquant(weight, scale, bits=bits, clip_factor=weight_clip_factor, block_size=block_size,
+                                      dtype=torch.get_default_dtype())
+
+
 def generate_li_hadamard_matrix(num_layers, dim=128, device='cuda'):
     """One bf16 Hadamard matrix per layer for the lightning indexer (deploy.py:241-247)."""
     had = get_had_pow2(dim, norm=True, device=device).to(torch.bfloat16)
@@ -295,9 +305,8 @@ def main(weight_path, output_path, quant_type, clip=False, mla_param_path=None, 
                 shards[file_name] = load_file(os.path.join(weight_path, file_name), device='cpu')
             return shards[file_name]
 
-        def quantize(name, weight_dev):
-            factor = weight_clip.get(name.replace('weight', 'w_alpha')) if plan.clip else None
-            return int_weight_quant(weight_dev, bits=plan.bits(name), weight_clip_factor=factor)
+        def clip_factor(name):
+            return weight_clip.get(name.replace('weight', 'w_alpha')) if plan.clip else None
 
         new_weight_map = {}
         files = sorted(glob(os.path.join(weight_path, '*.safetensors')))
@@ -317,17 +326,18 @@ def main(weight_path, output_path, quant_type, clip=False, mla_param_path=None, 
                     results = [tensor]
                 else:
                     dev = tensor.to(device)
-                    if action != plan.QUANT:
-                        scale_inv = shard(weight_map[scale_name])[scale_name]
-                        dev = weight_dequant(dev, scale_inv.to(device))
-                    if action == plan.DEQUANT:
-                        if plan.w8a8 or plan.w4a8:
-                            print(f'Ignore quantization {name}')
-                        results = [dev]
+                    if action == plan.QUANT:
+                        results = int_weight_quant(dev, bits=plan.bits(name), weight_clip_factor=clip_factor(name))
                     else:
-                        results = [r for r in quantize(name, dev) if r is not None]
-                        if len(results) == 3 and not plan.w4a8:
-                            results.pop()
+                        scale_inv = shard(weight_map[scale_name])[scale_name].to(device)
+                        if action == plan.DEQUANT:
+                            if plan.w8a8 or plan.w4a8:
+                                print(f'Ignore quantization {name}')
+                            results = [weight_dequant(dev, scale_inv)]
+                        else:           # dequantize and re-quantize without writing the bf16 weight
+                            results = dequant_int_weight_quant(dev, scale_inv, bits=plan.bits(name),
+                                                               weight_clip_factor=clip_factor(name))
+                    results = [r for r in results if r is not None]
                 for out_name, value in zip(plan.output_names(name, action), results):
                     out[out_name] = value.cpu().contiguous()
                     new_weight_map[out_name] = file_name

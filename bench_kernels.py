@@ -257,6 +257,10 @@ def cases():
         yield (f'ckpt_rowquant int{bits} per channel [131072x7168] bf16', lambda: randn(131072, 7168, torch.bfloat16, 0.02),
                lambda w, bits=bits: (lambda: ops.ckpt_rowquant(w, bits)),
                dict(nbytes=131072 * 7168 * 2 + 131072 * 7168 * bits // 8 + 131072 * (4 if bits == 8 else 12)))
+    for bits in (8, 4):
+        yield (f'ckpt_dequant_rowquant fp8 -> int{bits} in one pass [131072x7168]', setup_fp8,
+               lambda t, bits=bits: (lambda: ops.ckpt_dequant_rowquant(t[0], t[1], bits)),
+               dict(nbytes=131072 * 7168 + 131072 * 7168 * bits // 8 + 131072 * (4 if bits == 8 else 12)))
     # ---- KV-cache / indexer activations: 4096 tokens x 64 indexer heads of 128; attention output rows of 16384
     yield ('dsa rotate + half + fake_quant [262144x128] bf16 -> fp16', lambda: randn(262144, 128, torch.bfloat16),
            lambda x: (lambda: ops.dsa_rotate_fakequant(x, rotate=True, out_dtype=torch.float16)),

@@ -276,6 +276,16 @@ int amct_ckpt_block_dequant(const void* w_fp8, int64_t rows, int64_t cols, int64
 int amct_ckpt_rowquant(const void* w, int dtype, int64_t rows, int64_t k, int64_t ld, int bits, int use_clip,
                        float clip_factor, int8_t* codes, int64_t ld_codes, void* scale, float* bias, void* stream);
 
+/* amct_ckpt_block_dequant followed by amct_ckpt_rowquant in ONE pass, for the weights the export both dequantizes
+ * and re-quantizes (deploy.py:437-463): each E4M3 element is scaled, rounded to `dtype` (the value weight_dequant
+ * would have stored) and quantized from registers, so the 16-bit copy of the weight never goes to memory --
+ * 1 byte read and 1 (INT8) or 0.5 (INT4) written per element instead of 1 + 2 and 2 + 1.  Results are bit-identical
+ * to the two calls.  w_fp8 [rows, k] (ld_w), block_scale [ceil(rows / block), ceil(k / block)] (ld_scale); the other
+ * arguments as amct_ckpt_rowquant. */
+int amct_ckpt_dequant_rowquant(const void* w_fp8, int64_t rows, int64_t k, int64_t ld_w, const float* block_scale,
+                               int64_t ld_scale, int block, int dtype, int bits, int use_clip, float clip_factor,
+                               int8_t* codes, int64_t ld_codes, void* scale, float* bias, void* stream);
+
 /* pack_4bit alone (deploy.py:109-125): codes int8 [rows, k] (ld), rows even -> out int8 [rows / 2, k] (ld_out). */
 int amct_ckpt_pack4_rows(const int8_t* codes, int64_t rows, int64_t k, int64_t ld, int8_t* out, int64_t ld_out,
                          void* stream);

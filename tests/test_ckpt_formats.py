@@ -1,6 +1,6 @@
 """Offline checkpoint formats on the CPU: the oracle against the reference's outputs (tests/golden/ckpt_golden.*),
 and the host side of the export (which tensor gets which treatment, clip-factor files, config block, index)
-against the same fixtures.  The end-to-end host test swaps the three CUDA tensor steps of the export module for the
+against the same fixtures.  The end-to-end host test swaps the CUDA tensor steps of the export module for the
 oracle's -- only here, by monkeypatching; the module itself has no CPU implementation."""
 import json
 
@@ -131,8 +131,12 @@ def test_export_host_logic_end_to_end(quant_type, clip, tmp_path, monkeypatch):
         had = O.get_had_pow2(dim, True, torch.get_default_dtype()).to(torch.bfloat16)
         return {f'model.layers.{i}.self_attn.indexer.hadamard_matrix': had.clone() for i in range(num_layers)}
 
+    def dequant_quant(weight, scale, bits=8, weight_clip_factor=None, block_size=128):
+        return quant(dequant(weight, scale, block_size), bits, weight_clip_factor)
+
     monkeypatch.setattr(D, 'weight_dequant', dequant)
     monkeypatch.setattr(D, 'int_weight_quant', quant)
+    monkeypatch.setattr(D, 'dequant_int_weight_quant', dequant_quant)
     monkeypatch.setattr(D, 'generate_li_hadamard_matrix', hadamards)
     src, dst, par = tmp_path / 'src', tmp_path / 'dst', tmp_path / 'par'
     src.mkdir()

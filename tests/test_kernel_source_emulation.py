@@ -85,6 +85,10 @@ def test_emulated_rowquant_shapes(on_cpu):
     G.test_rowquant_oracle((4, 7168), torch.bfloat16, 4)
     G.test_rowquant_oracle((4, 96), torch.float16, 4)
     G.test_rowquant_strided_rows_zero_row_and_nan()
+    for shape in [(4, 7168), (6, 200)]:
+        for bits in (8, 4):
+            G.test_fused_dequant_rowquant(shape, bits)
+    G.test_fused_dequant_rowquant((130, 96), 4)                  # a second row of scale blocks
     with pytest.raises(ValueError):
         on_cpu.ckpt_rowquant(torch.zeros(3, 16, dtype=torch.bfloat16), 4)
 

@@ -140,6 +140,29 @@ def test_rowquant_strided_rows_zero_row_and_nan():
     assert bits_equal(codes[[0, 3]], want[0]) and bits_equal(scale[[0, 3]], want[1])
 
 
+@pytest.mark.parametrize('shape', [(128, 7168), (130, 96), (6, 200), (258, 2064)])
+@pytest.mark.parametrize('bits', [8, 4])
+def test_fused_dequant_rowquant(shape, bits):
+    """One pass over the FP8 weight gives exactly what dequantize-then-quantize gives (the reference's two steps), for
+    bf16 and fp16 intermediates, with and without a clip factor, on the vector and the element-wise path."""
+    gen = torch.Generator().manual_seed(27)
+    m, n = shape
+    w = fp8_weight(gen, m, n)
+    w.view(torch.uint8)[(w.view(torch.uint8) & 0x7F) == 0x7F] = 0x2C                # a checkpoint holds no NaN
+    s = torch.rand((m + 127) // 128, (n + 127) // 128, generator=gen) * 0.02 + 1e-4
+    clip = torch.sigmoid(torch.tensor(1.1))
+    for dtype in (torch.bfloat16, torch.float16):
+        if bits == 4 and n > (8000 if dtype == torch.bfloat16 else 1000):
+            continue                                                               # bias order dependent beyond this
+        for factor in (None, clip):
+            got = ops().ckpt_dequant_rowquant(w.cuda(), s.cuda(), bits, None if factor is None else float(factor), dtype=dtype)
+            check_quant(got, O.int_weight_quant(O.weight_dequant(w, s, 128, dtype), bits, factor), dtype)
+    two_steps = ops().ckpt_rowquant(ops().ckpt_block_dequant(w.cuda(), s.cuda()), bits)
+    fused = ops().ckpt_dequant_rowquant(w.cuda(), s.cuda(), bits)
+    for a, b in zip(fused, two_steps):
+        assert bits_equal(a, b)
+
+
 def test_rowquant_argument_errors():
     w = torch.zeros(3, 16, dtype=torch.bfloat16, device='cuda')
     with pytest.raises(ValueError):
