@@ -5,7 +5,9 @@ emulates blocks, threads, ``__syncthreads`` and warp shuffles with host threads 
 the IEEE operations they name.  The same C ABI entry points are then called, through the same Python wrappers
 (``amct_b200.backend.ops``, patched here to accept host pointers), by the very test functions that run on the GPU
 (``tests/test_zy_gpu_*.py``): argument checks, launch geometry, vector and scalar paths, reductions and index
-arithmetic are all exercised against the reference's golden vectors and the oracle without a GPU.
+arithmetic are all exercised against the reference's golden vectors and the oracle without a GPU.  The build checks
+every access for its type's alignment, so a 16-byte vector access on an address the launch conditions should have
+ruled out stops the test, as it would fault on the GPU.
 
 This is a check of the kernel source, not a product path: the emulation library is built into a temporary directory
 by this test alone, and ``amct_b200`` can neither build nor load it.  What it cannot show is anything that depends on
@@ -32,7 +34,9 @@ def emu_lib(tmp_path_factory):
     if gxx is None or not os.path.exists(os.path.join(CUDA_INCLUDE, 'cuda_fp8.h')):
         pytest.skip('needs g++ and the CUDA headers')
     out = str(tmp_path_factory.mktemp('emu') / 'libamct_emu.so')
-    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fPIC', '-shared', '-x', 'c++',
+    # -fsanitize=alignment: a vector access the GPU would fault on ("misaligned address") aborts the test here
+    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fsanitize=alignment', '-fno-sanitize-recover=alignment',
+           '-fPIC', '-shared', '-x', 'c++',
            '-include', os.path.join(ROOT, 'tests', 'emu', 'cuda_emu.h'), '-I', CUDA_INCLUDE,
            os.path.join(CSRC, 'ckpt_formats.cu'), os.path.join(CSRC, 'kv_quant.cu'), '-o', out, '-lpthread']
     subprocess.check_call(cmd)
