@@ -15,41 +15,42 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
 #include <cmath>
-#include <condition_variable>
 #include <cstdint>
 #include <cstring>
 #include <functional>
-#include <mutex>
 #include <thread>
 #include <vector>
 
 namespace emu {
 
+// Sense-reversing barrier: a short spin, then yield; the emulated blocks are far more threads than host cores, so
+// a waiting thread must give its core away quickly.
 class Barrier {
  public:
   void reset(int n) {
     n_ = n;
-    count_ = 0;
-    phase_ = 0;
+    count_.store(0);
+    phase_.store(0);
   }
   void wait() {
-    std::unique_lock<std::mutex> lock(m_);
-    const unsigned phase = phase_;
-    if (++count_ == n_) {
-      count_ = 0;
-      ++phase_;
-      cv_.notify_all();
+    const unsigned phase = phase_.load(std::memory_order_acquire);
+    if (count_.fetch_add(1, std::memory_order_acq_rel) + 1 == n_) {
+      count_.store(0, std::memory_order_relaxed);
+      phase_.store(phase + 1, std::memory_order_release);
     } else {
-      cv_.wait(lock, [&] { return phase_ != phase; });
+      int spins = 0;
+      while (phase_.load(std::memory_order_acquire) == phase) {
+        if (++spins > 64) std::this_thread::yield();
+      }
     }
   }
 
  private:
-  std::mutex m_;
-  std::condition_variable cv_;
-  int n_ = 1, count_ = 0;
-  unsigned phase_ = 0;
+  int n_ = 1;
+  std::atomic<int> count_{0};
+  std::atomic<unsigned> phase_{0};
 };
 
 struct BlockState {

@@ -63,7 +63,7 @@ def test_emulated_block_dequant(on_cpu):
     import test_zy_gpu_ckpt_formats as G
     for tag in ('ragged', 'even'):
         G.test_block_dequant_golden(tag)
-    for shape in [(130, 96), (1, 16), (257, 2064), (5, 3)]:
+    for shape in [(256, 7168), (130, 96), (1, 16), (257, 2064), (5, 3)]:
         for dtype in (torch.bfloat16, torch.float16, torch.float32):
             G.test_block_dequant_oracle(shape, dtype)
     G.test_block_dequant_other_block_and_errors()
@@ -79,20 +79,17 @@ def test_emulated_rowquant_golden(on_cpu, dtype):
 
 def test_emulated_rowquant_shapes(on_cpu):
     import test_zy_gpu_ckpt_formats as G
-    for shape in [(6, 515), (2, 8), (4, 20000)]:
-        for dtype in (torch.bfloat16, torch.float32):
+    for shape in [(64, 7168), (6, 515), (2, 8), (130, 96), (4, 20000)]:
+        for dtype in (torch.bfloat16, torch.float16, torch.float32):
             for bits in (8, 4):
                 try:
                     G.test_rowquant_oracle(shape, dtype, bits)
                 except pytest.skip.Exception:
                     pass
-    G.test_rowquant_oracle((4, 7168), torch.bfloat16, 4)
-    G.test_rowquant_oracle((4, 96), torch.float16, 4)
     G.test_rowquant_strided_rows_zero_row_and_nan()
-    for shape in [(4, 7168), (6, 200)]:
+    for shape in [(128, 7168), (130, 96), (6, 200), (258, 2064)]:
         for bits in (8, 4):
             G.test_fused_dequant_rowquant(shape, bits)
-    G.test_fused_dequant_rowquant((130, 96), 4)                  # a second row of scale blocks
     with pytest.raises(ValueError):
         on_cpu.ckpt_rowquant(torch.zeros(3, 16, dtype=torch.bfloat16), 4)
 
@@ -102,7 +99,12 @@ def test_emulated_pack_bias_hadamard(on_cpu):
     G.test_pack4_bias_scale_words_hadamard()
 
 
-@pytest.mark.parametrize('quant_type,clip', [('w4a8c8', True)])
+def test_emulated_full_size_properties(on_cpu):
+    import test_zy_gpu_ckpt_formats as G
+    G.test_full_size_properties()
+
+
+@pytest.mark.parametrize('quant_type,clip', [('bfloat16', False), ('w8a8c16', False), ('w4a8c16', False), ('w8a8c8', True), ('w4a8c8', True)])
 def test_emulated_export_end_to_end(on_cpu, quant_type, clip, tmp_path):
     from ckpt_fixture import compare_export, golden, write_checkpoint
     from amct_b200.experimental.quantization.deepseek_v3_2 import deploy
@@ -128,7 +130,7 @@ def test_emulated_fake_quant_golden(on_cpu, dtype):
 def test_emulated_fake_quant_shapes(on_cpu):
     import test_zy_gpu_dsa_activations as G
     for dtype in (torch.float16, torch.bfloat16, torch.float32):
-        for shape in [(3, 3, 1536), (20, 128), (2, 16384), (7, 33), (6, 8)]:
+        for shape in [(3, 70, 1536), (1000, 128), (5, 16384), (7, 33), (2, 4, 9, 512), (6, 8)]:
             G.test_fake_quant_oracle(dtype, shape)
     G.test_fake_quant_strided_and_cast()
 
@@ -139,7 +141,7 @@ def test_emulated_rotation_and_chain(on_cpu):
         for d in (128, 64):
             G.test_rotation_golden(dtype, d)
     for d in (32, 64, 128, 256, 512):
-        G.test_rotation_widths_and_round_trip(d, rows=9)
+        G.test_rotation_widths_and_round_trip(d)
     G.test_rotation_unaligned_rows()
     G.test_indexer_chain()
     G.test_module_with_learned_clipping()
