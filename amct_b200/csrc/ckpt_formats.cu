@@ -42,27 +42,42 @@ __global__ void __launch_bounds__(128) ckpt_block_dequant_vec_kernel(
   if (v >= vec_per_row) return;
   const int64_t c0 = v * 16;
   const int64_t sc = c0 / block;
-  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
-    const float s = __ldg(scale + (r / block) * ld_scale + sc);
-    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(w + r * ld_w + c0));
-    const uint32_t word[4] = {raw.x, raw.y, raw.z, raw.w};
-    float f[16];
+  constexpr int U = 4;                             // rows in flight per thread: 64 bytes of loads
+  const int64_t step = gridDim.y;
+  for (int64_t r0 = blockIdx.y; r0 < rows; r0 += step * U) {
+    uint4 raw[U];
+    float s[U];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 lo = e4m3x2_to_float2(word[j]);
-      const float2 hi = e4m3x2_to_float2(word[j] >> 16);
-      f[4 * j + 0] = __fmul_rn(lo.x, s);
-      f[4 * j + 1] = __fmul_rn(lo.y, s);
-      f[4 * j + 2] = __fmul_rn(hi.x, s);
-      f[4 * j + 3] = __fmul_rn(hi.y, s);
+    for (int u = 0; u < U; ++u) {
+      const int64_t r = r0 + u * step;
+      if (r < rows) {
+        s[u] = __ldg(scale + (r / block) * ld_scale + sc);
+        raw[u] = __ldcs(reinterpret_cast<const uint4*>(w + r * ld_w + c0));
+      }
     }
-    T* dst = out + r * ld_out + c0;
 #pragma unroll
-    for (int j = 0; j < 16 / E; ++j) {
-      Vec16<T> o;
+    for (int u = 0; u < U; ++u) {
+      const int64_t r = r0 + u * step;
+      if (r >= rows) break;
+      const uint32_t word[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+      float f[16];
 #pragma unroll
-      for (int e = 0; e < E; ++e) o.v[e] = ElemTraits<T>::from_f(f[j * E + e]);
-      __stcs(reinterpret_cast<uint4*>(dst + j * E), *reinterpret_cast<const uint4*>(&o));
+      for (int j = 0; j < 4; ++j) {
+        const float2 lo = e4m3x2_to_float2(word[j]);
+        const float2 hi = e4m3x2_to_float2(word[j] >> 16);
+        f[4 * j + 0] = __fmul_rn(lo.x, s[u]);
+        f[4 * j + 1] = __fmul_rn(lo.y, s[u]);
+        f[4 * j + 2] = __fmul_rn(hi.x, s[u]);
+        f[4 * j + 3] = __fmul_rn(hi.y, s[u]);
+      }
+      T* dst = out + r * ld_out + c0;
+#pragma unroll
+      for (int j = 0; j < 16 / E; ++j) {
+        Vec16<T> o;
+#pragma unroll
+        for (int e = 0; e < E; ++e) o.v[e] = ElemTraits<T>::from_f(f[j * E + e]);
+        __stcs(reinterpret_cast<uint4*>(dst + j * E), *reinterpret_cast<const uint4*>(&o));
+      }
     }
   }
 }
@@ -87,12 +102,14 @@ static int launch_block_dequant(const uint8_t* w, int64_t rows, int64_t cols, in
   T* o = reinterpret_cast<T*>(out);
   const bool vec = cols % 16 == 0 && block % 16 == 0 && ld_w % 16 == 0 && aligned16(w) && aligned16(out) &&
                    (ld_out * (int64_t)sizeof(T)) % 16 == 0;
-  const unsigned gy = (unsigned)(rows < 16384 ? rows : 16384);
   if (vec) {
+    const int64_t quarter = (rows + 3) / 4;                       // the kernel keeps four rows in flight per thread
+    const unsigned gy = (unsigned)(quarter < 16384 ? quarter : 16384);
     const int64_t vpr = cols / 16;
     dim3 grid((unsigned)((vpr + 127) / 128), gy);
     AMCT_LAUNCH(grid, 128, st, (w, rows, vpr, ld_w, scale, ld_scale, block, o, ld_out), ckpt_block_dequant_vec_kernel<T>);
   } else {
+    const unsigned gy = (unsigned)(rows < 16384 ? rows : 16384);
     dim3 grid((unsigned)((cols + 127) / 128), gy);
     AMCT_LAUNCH(grid, 128, st, (w, rows, cols, ld_w, scale, ld_scale, block, o, ld_out), ckpt_block_dequant_scalar_kernel<T>);
   }
