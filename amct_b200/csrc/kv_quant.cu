@@ -11,8 +11,9 @@
 // One warp owns one row (a token, or a token-head of the indexer).  Arithmetic follows torch's dtypes: without
 // learned clipping every step is rounded to the activation dtype; with it the fp32 clip parameter promotes the
 // bounds and all later steps to fp32 and only the result is cast back.  round_ste(t) = (round(t) - t) + t is
-// exact except that it turns a zero into +0, which the symmetric path reproduces.  NaN inputs are not handled
-// like torch.clamp (which propagates them).  Compiled without FMA contraction.
+// exact except that it turns a zero into +0, which the symmetric path reproduces.  A NaN quotient stays NaN through the
+// clamp as in torch; a NaN INPUT is not treated like torch's amax (which makes the whole row NaN).  Compiled without
+// FMA contraction.
 //
 // Algorithmic HBM bytes per element: sizeof(in) read + sizeof(out) written.
 #include "common.cuh"
@@ -111,11 +112,15 @@ __device__ __forceinline__ float dsa_fake_quant(float v, const DsaRow& r, const 
     q = __fdiv_rn(v, r.scale);
   }
   float level = rintf(round_c<T>(q, f32));
+  // torch.clamp keeps a NaN (0 / 0 when a tiny 16-bit scale underflows to zero); fminf / fmaxf would drop it
+  const bool is_nan = level != level;
   if (p.symmetric) {
     level = fminf(fmaxf(__fadd_rn(level, 0.f), r.qlo), r.qhi);           // -0 -> +0 like round_ste
+    if (is_nan) level = __int_as_float(0x7fc00000);
     return round_to<T>(round_c<T>(__fmul_rn(r.scale, level), f32));
   }
   level = fminf(fmaxf(round_c<T>(__fadd_rn(level, r.zero), f32), r.qlo), r.qhi);
+  if (is_nan) level = __int_as_float(0x7fc00000);
   return round_to<T>(round_c<T>(__fmul_rn(r.scale, round_c<T>(__fsub_rn(level, r.zero), f32)), f32));
 }
 

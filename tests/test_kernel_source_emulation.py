@@ -133,6 +133,7 @@ def test_emulated_fake_quant_shapes(on_cpu):
         for shape in [(3, 70, 1536), (1000, 128), (5, 16384), (7, 33), (2, 4, 9, 512), (6, 8)]:
             G.test_fake_quant_oracle(dtype, shape)
     G.test_fake_quant_strided_and_cast()
+    G.test_fake_quant_scale_underflow_keeps_nan()
 
 
 def test_emulated_rotation_and_chain(on_cpu):

@@ -63,6 +63,20 @@ def test_fake_quant_oracle(dtype, shape):
     assert bits_equal(got, O.activation_fake_quant(x, 8, False, True, CLIP_MAX, CLIP_MIN))
 
 
+def test_fake_quant_scale_underflow_keeps_nan():
+    """fp16 rows so small that hi / 127 rounds to zero in fp16: x / 0 is +-inf (clamped) or, for a zero element, NaN,
+    which torch.clamp keeps and the kernel must keep too."""
+    gen = torch.Generator().manual_seed(45)
+    x = (torch.randn(6, 64, generator=gen) * 1e-6).half()
+    x[:, 5] = 0
+    got = ops().dsa_rotate_fakequant(x.cuda()).cpu()
+    want = O.activation_fake_quant(x)
+    assert bool(torch.isnan(want).any())
+    assert bool((torch.isnan(got) == torch.isnan(want)).all())
+    keep = ~torch.isnan(want)
+    assert bits_equal(torch.where(keep, got, torch.zeros_like(got)), torch.where(keep, want, torch.zeros_like(want)))
+
+
 def test_fake_quant_strided_and_cast():
     gen = torch.Generator().manual_seed(42)
     big = torch.randn(9, 300, generator=gen).to(torch.bfloat16)
