@@ -28,6 +28,14 @@
 #ifndef AMCT_LAUNCH
 #define AMCT_LAUNCH(grid, threads, stream, args, ...) __VA_ARGS__<<<(grid), (threads), 0, (stream)>>> args
 #endif
+// the same with dynamic shared memory, and the declaration of that memory inside the kernel
+#ifndef AMCT_LAUNCH_SMEM
+#define AMCT_LAUNCH_SMEM(grid, threads, smem_bytes, stream, args, ...) \
+  __VA_ARGS__<<<(grid), (threads), (smem_bytes), (stream)>>> args
+#endif
+#ifndef AMCT_DYNAMIC_SMEM
+#define AMCT_DYNAMIC_SMEM(type, name) extern __shared__ type name[]
+#endif
 
 namespace amct {
 

@@ -86,7 +86,8 @@ __device__ __forceinline__ float level_of(float x, const UnitQ& u, const RowPara
   if (p.rule == AMCT_RULE_EXPERIMENTAL) {
     // division carried out in the input dtype (node.py:39-43 on T tensors)
     float t = round_to<T>(quotient(x, u));
-    return fminf(fmaxf(rintf(t), qmin), qmax);
+    // a 16-bit scale that underflowed to zero makes 0 / 0: the reference's level is NaN there, stored as code 0
+    return (t != t) ? 0.f : fminf(fmaxf(rintf(t), qmin), qmax);
   }
   if (p.out_mode == AMCT_OUT_FAKE_AWQ) {
     float t = quotient(x, u);
@@ -111,7 +112,7 @@ __device__ __forceinline__ float dequant_of(float level, const UnitQ& u) {
 template <typename T, int NV>
 __global__ void __launch_bounds__(512) quant_rows_vec_kernel(RowParams p) {
   constexpr int E = ElemTraits<T>::kPerVec;
-  extern __shared__ float smem[];
+  AMCT_DYNAMIC_SMEM(float, smem);
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int64_t row = blockIdx.x;
   const int nvec = (int)(p.k / E);
@@ -275,7 +276,7 @@ __global__ void __launch_bounds__(512) quant_rows_vec_kernel(RowParams p) {
 // scalar accesses.  Used for ragged shapes only.
 template <typename T>
 __global__ void __launch_bounds__(256) quant_rows_generic_kernel(RowParams p) {
-  extern __shared__ float smem[];
+  AMCT_DYNAMIC_SMEM(float, smem);
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int64_t row = blockIdx.x;
   const int nunits = units_per_row(p);
@@ -387,7 +388,7 @@ static int launch_rows(const RowParams& p, cudaStream_t st) {
   if (nv <= NVC) {                                                                              \
     if (smem > 48 * 1024)                                                                       \
       cudaFuncSetAttribute(quant_rows_vec_kernel<T, NVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    quant_rows_vec_kernel<T, NVC><<<grid, threads, smem, st>>>(p);                              \
+    AMCT_LAUNCH_SMEM(grid, threads, smem, st, (p), quant_rows_vec_kernel<T, NVC>);              \
     AMCT_CHECK_LAUNCH();                                                                        \
     return AMCT_OK;                                                                             \
   }
@@ -398,7 +399,7 @@ static int launch_rows(const RowParams& p, cudaStream_t st) {
   if (smem > 200 * 1024) return AMCT_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(quant_rows_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  quant_rows_generic_kernel<T><<<(unsigned)p.rows, 256, smem, st>>>(p);
+  AMCT_LAUNCH_SMEM((unsigned)p.rows, 256, smem, st, (p), quant_rows_generic_kernel<T>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }

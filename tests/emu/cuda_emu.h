@@ -101,6 +101,12 @@ inline void launch(dim3 grid, int threads, const std::function<void()>& body) {
   for (auto& th : pool) th.join();
 }
 
+// dynamic shared memory of the block that is running
+inline void* dynamic_smem() {
+  alignas(128) static unsigned char buffer[256 * 1024];
+  return buffer;
+}
+
 inline uint32_t shfl_xor_bits(uint32_t bits, int lane_mask) {
   ThreadState& s = tls();
   const unsigned t = s.tid.x;
@@ -125,6 +131,10 @@ inline uint32_t shfl_xor_bits(uint32_t bits, int lane_mask) {
 
 #define AMCT_LAUNCH(grid, threads, stream, args, ...) \
   emu::launch(dim3(grid), (int)(threads), [&] { __VA_ARGS__ args; })
+#define AMCT_LAUNCH_SMEM(grid, threads, smem_bytes, stream, args, ...) \
+  emu::launch(dim3(grid), (int)(threads), [&] { __VA_ARGS__ args; })
+#define AMCT_DYNAMIC_SMEM(type, name) type* name = reinterpret_cast<type*>(emu::dynamic_smem())
+#define cudaFuncSetAttribute(...) cudaSuccess
 #define AMCT_CHECK_LAUNCH() \
   do {                      \
   } while (0)
@@ -158,7 +168,27 @@ static inline float __int_as_float(int i) {
   return f;
 }
 static inline int __popc(unsigned v) { return __builtin_popcount(v); }
+static inline int atomicOr(int* p, int v) { return __atomic_fetch_or(p, v, __ATOMIC_SEQ_CST); }
+static inline int atomicMin(int* p, int v) {
+  int old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
+  while (old > v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST)) {
+  }
+  return old;
+}
+static inline int atomicMax(int* p, int v) {
+  int old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
+  while (old < v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST)) {
+  }
+  return old;
+}
 template <typename T> static inline T __ldg(const T* p) { return *p; }
 template <typename T> static inline T __ldcs(const T* p) { return *p; }
 template <typename T> static inline void __stcs(T* p, T v) { *p = v; }
 using std::isfinite;
+// CUDA's global integer min / max
+static inline int min(int a, int b) { return a < b ? a : b; }
+static inline int max(int a, int b) { return a > b ? a : b; }
+static inline unsigned min(unsigned a, unsigned b) { return a < b ? a : b; }
+static inline unsigned max(unsigned a, unsigned b) { return a > b ? a : b; }
+static inline long long min(long long a, long long b) { return a < b ? a : b; }
+static inline long long max(long long a, long long b) { return a > b ? a : b; }

@@ -1,6 +1,6 @@
 """The SOURCE of the checkpoint-format and KV-cache activation kernels, executed on the CPU.
 
-``amct_b200/csrc/ckpt_formats.cu`` and ``kv_quant.cu`` are compiled with g++ under ``tests/emu/cuda_emu.h``, which
+``amct_b200/csrc/ckpt_formats.cu``, ``kv_quant.cu`` and (on its own) ``quant_rows.cu`` are compiled with g++ under ``tests/emu/cuda_emu.h``, which
 emulates blocks, threads, ``__syncthreads`` and warp shuffles with host threads and maps the rounding intrinsics to
 the IEEE operations they name.  The same C ABI entry points are then called, through the same Python wrappers
 (``amct_b200.backend.ops``, patched here to accept host pointers), by the very test functions that run on the GPU
@@ -43,16 +43,42 @@ def emu_lib(tmp_path_factory):
     return ctypes.CDLL(out)
 
 
+@pytest.fixture(scope='module')
+def emu_rows_lib(tmp_path_factory):
+    """quant_rows.cu on its own: the specialised kernels it would try first (other source files) are replaced by stubs
+    that decline every shape, so each request runs through the general row kernels."""
+    gxx = shutil.which('g++')
+    if gxx is None or not os.path.exists(os.path.join(CUDA_INCLUDE, 'cuda_fp16.h')):
+        pytest.skip('needs g++ and the CUDA headers')
+    out = str(tmp_path_factory.mktemp('emu_rows') / 'libamct_emu_rows.so')
+    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fsanitize=alignment', '-fno-sanitize-recover=alignment',
+           '-fPIC', '-shared', '-x', 'c++', '-include', os.path.join(ROOT, 'tests', 'emu', 'cuda_emu.h'), '-I', CUDA_INCLUDE,
+           os.path.join(CSRC, 'quant_rows.cu'), os.path.join(ROOT, 'tests', 'emu', 'quant_rows_alone.cpp'), '-o', out,
+           '-lpthread']
+    subprocess.check_call(cmd)
+    return ctypes.CDLL(out)
+
+
+def _patch_ops(monkeypatch, library):
+    from amct_b200.backend import lib, ops
+    monkeypatch.setattr(lib, 'load', lambda: library)
+    monkeypatch.setattr(ops, '_need_cuda', lambda *tensors: None)
+    monkeypatch.setattr(ops, '_stream', lambda: ctypes.c_void_p(0))
+    monkeypatch.setattr(torch.Tensor, 'cuda', lambda self, *args, **kwargs: self)
+    return ops
+
+
+@pytest.fixture
+def rows_on_cpu(emu_rows_lib, monkeypatch):
+    return _patch_ops(monkeypatch, emu_rows_lib)
+
+
 @pytest.fixture
 def on_cpu(emu_lib, monkeypatch):
     """The ops wrappers talking to the emulation library with host tensors."""
-    from amct_b200.backend import lib, ops
-    monkeypatch.setattr(lib, 'load', lambda: emu_lib)
-    monkeypatch.setattr(ops, '_need_cuda', lambda *tensors: None)
-    monkeypatch.setattr(ops, '_stream', lambda: ctypes.c_void_p(0))
+    ops = _patch_ops(monkeypatch, emu_lib)
     monkeypatch.setattr(ops, 'hadamard_pow2', functools.partial(ops.hadamard_pow2, device='cpu'))
     monkeypatch.setattr(torch.cuda, 'device', lambda device: contextlib.nullcontext())
-    monkeypatch.setattr(torch.Tensor, 'cuda', lambda self, *args, **kwargs: self)
     return ops
 
 
@@ -157,3 +183,65 @@ def test_emulated_argument_checks(on_cpu):
         on_cpu.dsa_rotate_fakequant(torch.zeros(4, 1024), rotate=True, bits=16)
     with pytest.raises(BackendError):
         on_cpu.dsa_rotate_fakequant(x, bits=9)
+
+
+# ---------------------------------------------------------------------------------------------
+# the general row quantizer (quant_rows.cu): weight scales, codes, nibble packing, both fake-quant variants, and the
+# per-token rules, with every shape forced through its two general kernels
+# ---------------------------------------------------------------------------------------------
+def test_emulated_row_quantizer_group_cases(rows_on_cpu):
+    import test_gpu_intq as G
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for qt, sym in [('int4', False), ('int4', True), ('int8', False)]:
+            for rows, k, gs in [(37, 1024, 128), (5, 512, 64), (16, 96, 48), (3, 200, 64)]:
+                G.test_group_weight_quant_oracle(dtype, qt, sym, rows, k, gs)
+    for dtype in (torch.bfloat16, torch.float32):
+        G.test_group_weight_quant_rounding_ties(dtype)
+
+
+def test_emulated_row_quantizer_extreme_magnitudes(rows_on_cpu):
+    """Channel and group strategies, both rules per token, on magnitudes from 1e-30 to 1e30 (fp16: 1e-7 to 1e4): scales
+    that underflow, saturate or are replaced by 1, all-zero and all-negative rows.  Where the oracle raises the
+    reference's error for a non-finite scale, so must the kernel's status word."""
+    from oracle import intq
+    from golden_io import bits_equal
+    ops = rows_on_cpu
+    gen = torch.Generator().manual_seed(77)
+
+    def attempt(fn):
+        try:
+            return fn(), None
+        except RuntimeError as err:
+            return None, err
+
+    case = 0
+    for dtype, mags in ((torch.bfloat16, (-30, -12, -3, 0, 4, 30)), (torch.float16, (-7, -5, 0, 4)), (torch.float32, (-30, -6, 0, 10, 30))):
+        for mag in mags:
+            for strat, gs, k in (('channel', None, 200), ('group', 64, 256), ('group', 48, 96)):
+                case += 1
+                rows = 3
+                w = torch.randn(rows, k, generator=gen) * 10.0 ** mag * torch.exp(torch.randn(rows, 1, generator=gen))
+                w = w.clamp(-torch.finfo(dtype).max, torch.finfo(dtype).max).to(dtype)        # finite inputs only
+                w[0] = 0
+                w[2] = -w[2].abs()
+                w = torch.where(w == 0, torch.zeros_like(w), w)          # no -0.0: its sign is not kept (see DESIGN)
+                qt, sym = ('int8', 'int4')[case % 2], bool(case % 3)
+                want, err_o = attempt(lambda: intq.weight_scale_offset(w, qt, sym, strat, gs))
+                got, err_k = attempt(lambda: ops.quant_rows(w, qt, sym, strat, gs, out='i32'))
+                assert (err_o is None) == (err_k is None), (dtype, mag, strat, qt, sym)
+                if err_o is None:
+                    scale, offset = want
+                    assert bits_equal(got[0].reshape(scale.shape), scale)
+                    codes = intq.weight_codes(w, qt, scale, offset, gs)
+                    codes = (intq.crop_groups(codes, w.shape) if gs else codes).to(torch.int32).contiguous()
+                    assert bits_equal(got[2], codes)
+                    fake = ops.quant_rows(w, qt, sym, strat, gs, scale=scale, offset=offset, out='fake')[2]
+                    assert bits_equal(fake, intq.fake_quant(w, qt, scale, offset, gs))
+                    fake = ops.quant_rows(w, qt, sym, strat, gs, scale=scale, offset=offset, out='fake_awq')[2]
+                    assert bits_equal(fake, intq.fake_quant_awq(w, qt, scale, offset, gs))
+                for rule in ('released', 'experimental'):
+                    want, err_o = attempt(lambda: intq.dynamic_per_token(w, rule))
+                    got, err_k = attempt(lambda: ops.quant_dynamic_per_token(w, rule=rule, check=True))
+                    assert (err_o is None) == (err_k is None), (dtype, mag, rule)
+                    if err_o is None:
+                        assert bits_equal(got[0], want[0]) and bits_equal(got[1], want[1]), (dtype, mag, rule)
