@@ -122,7 +122,7 @@ static int ensure_tables(cudaStream_t st) {
   if (cudaGetDevice(&dev) != cudaSuccess) return AMCT_ERR_CUDA;
   if (dev >= 0 && dev < 64 && done[dev]) return AMCT_OK;
   // the tables must be complete before any later kernel on any stream reads them
-  hif8_init_tables<<<16, 256, 0, st>>>();
+  AMCT_LAUNCH(16, 256, st, (), hif8_init_tables);
   AMCT_CHECK_LAUNCH();
   if (cudaStreamSynchronize(st) != cudaSuccess) return AMCT_ERR_CUDA;
   if (dev >= 0 && dev < 64) done[dev] = true;
@@ -215,8 +215,8 @@ template <typename T>
 static int run_encode(const T* x, int64_t n, uint8_t* codes, T* fake, cudaStream_t st) {
   const int rc = ensure_tables(st);
   if (rc != AMCT_OK) return rc;
-  if (codes) hif8_encode_kernel<T, 0><<<grid_for(n), 256, 0, st>>>(x, n, codes, nullptr);
-  else hif8_encode_kernel<T, 1><<<grid_for(n), 256, 0, st>>>(x, n, nullptr, fake);
+  if (codes) AMCT_LAUNCH(grid_for(n), 256, st, (x, n, codes, nullptr), hif8_encode_kernel<T, 0>);
+  else AMCT_LAUNCH(grid_for(n), 256, st, (x, n, nullptr, fake), hif8_encode_kernel<T, 1>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -251,9 +251,9 @@ extern "C" int amct_hif8_decode(const void* codes, int64_t n, int dtype, void* o
   if (rc != AMCT_OK) return rc;
   const unsigned grid = amct::grid_for(n);
   switch (dtype) {
-    case AMCT_DTYPE_F32: amct::hif8_decode_kernel<float><<<grid, 256, 0, st>>>(c, n, (float*)out); break;
-    case AMCT_DTYPE_F16: amct::hif8_decode_kernel<__half><<<grid, 256, 0, st>>>(c, n, (__half*)out); break;
-    case AMCT_DTYPE_BF16: amct::hif8_decode_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(c, n, (__nv_bfloat16*)out); break;
+    case AMCT_DTYPE_F32: AMCT_LAUNCH(grid, 256, st, (c, n, (float*)out), amct::hif8_decode_kernel<float>); break;
+    case AMCT_DTYPE_F16: AMCT_LAUNCH(grid, 256, st, (c, n, (__half*)out), amct::hif8_decode_kernel<__half>); break;
+    case AMCT_DTYPE_BF16: AMCT_LAUNCH(grid, 256, st, (c, n, (__nv_bfloat16*)out), amct::hif8_decode_kernel<__nv_bfloat16>); break;
     default: return AMCT_ERR_ARG;
   }
   AMCT_CHECK_LAUNCH();

@@ -194,8 +194,8 @@ static int run_mx(const T* x, int64_t rows, int64_t k, int64_t ld, int fmt, uint
     const int64_t need = (rows + 1) / 2;
     if (gy > need) gy = need;
     grid.y = (unsigned)(gy < 1 ? 1 : gy);
-    if (fmt == 8) mx_quant_rows_kernel<T, 8><<<grid, 256, 0, stream>>>(x, (int)rows, (int)k, ld, payload, srm, st, tile_rows);
-    else mx_quant_rows_kernel<T, 4><<<grid, 256, 0, stream>>>(x, (int)rows, (int)k, ld, payload, srm, st, tile_rows);
+    if (fmt == 8) AMCT_LAUNCH(grid, 256, stream, (x, (int)rows, (int)k, ld, payload, srm, st, tile_rows), mx_quant_rows_kernel<T, 8>);
+    else AMCT_LAUNCH(grid, 256, stream, (x, (int)rows, (int)k, ld, payload, srm, st, tile_rows), mx_quant_rows_kernel<T, 4>);
     AMCT_CHECK_LAUNCH();
     return AMCT_OK;
   }
@@ -204,8 +204,8 @@ static int run_mx(const T* x, int64_t rows, int64_t k, int64_t ld, int fmt, uint
   if (blocks < 1) blocks = 1;
   const int64_t cap = 148LL * 8 * 4;
   if (blocks > cap) blocks = cap;
-  if (fmt == 8) mx_quant_kernel<T, 8><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st, tile_rows);
-  else mx_quant_kernel<T, 4><<<(unsigned)blocks, 256, 0, stream>>>(x, rows, k, ld, payload, srm, st, tile_rows);
+  if (fmt == 8) AMCT_LAUNCH((unsigned)blocks, 256, stream, (x, rows, k, ld, payload, srm, st, tile_rows), mx_quant_kernel<T, 8>);
+  else AMCT_LAUNCH((unsigned)blocks, 256, stream, (x, rows, k, ld, payload, srm, st, tile_rows), mx_quant_kernel<T, 4>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }

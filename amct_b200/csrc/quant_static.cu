@@ -133,7 +133,7 @@ static int run_static(const T* x, int64_t outer, int64_t tokens, int64_t k, cons
     const int64_t need = (nrows + 3) / 4;
     if (gy > need) gy = need;
     grid.y = (unsigned)(gy < 1 ? 1 : gy);
-    quantize_static_rows_kernel<T><<<grid, 256, 0, st>>>(x, (int)nrows, (int)tokens, (int)k, scale, offset, per_token, smooth, q);
+    AMCT_LAUNCH(grid, 256, st, (x, (int)nrows, (int)tokens, (int)k, scale, offset, per_token, smooth, q), quantize_static_rows_kernel<T>);
     AMCT_CHECK_LAUNCH();
     return AMCT_OK;
   }
@@ -142,8 +142,8 @@ static int run_static(const T* x, int64_t outer, int64_t tokens, int64_t k, cons
   if (blocks < 1) blocks = 1;
   const int64_t cap = 148LL * 8 * 2;
   if (blocks > cap) blocks = cap;
-  if (vec) quantize_static_kernel<T, true><<<(unsigned)blocks, 256, 0, st>>>(x, nrows, tokens, k, scale, offset, per_token, smooth, q);
-  else quantize_static_kernel<T, false><<<(unsigned)blocks, 256, 0, st>>>(x, nrows, tokens, k, scale, offset, per_token, smooth, q);
+  if (vec) AMCT_LAUNCH((unsigned)blocks, 256, st, (x, nrows, tokens, k, scale, offset, per_token, smooth, q), quantize_static_kernel<T, true>);
+  else AMCT_LAUNCH((unsigned)blocks, 256, st, (x, nrows, tokens, k, scale, offset, per_token, smooth, q), quantize_static_kernel<T, false>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }

@@ -52,7 +52,7 @@ static int run_rope(T* x, int64_t tokens, int64_t ld, int heads, int head_dim, c
   if (gy > tokens) gy = tokens;
   if (gy > 65535) gy = 65535;
   grid.y = (unsigned)gy;
-  rope_inplace_kernel<T><<<grid, 256, 0, st>>>(x, (uint32_t)tokens, ld, heads, head_dim, c, s, (uint32_t)seq);
+  AMCT_LAUNCH(grid, 256, st, (x, (uint32_t)tokens, ld, heads, head_dim, c, s, (uint32_t)seq), rope_inplace_kernel<T>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }

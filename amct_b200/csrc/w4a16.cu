@@ -70,8 +70,8 @@ static int run_dequant(const uint8_t* codes, int bits, int64_t n_rows, int64_t k
   const int64_t need = (n_rows + 1) / 2;
   if (gy > need) gy = need;
   grid.y = (unsigned)(gy < 1 ? 1 : gy);
-  if (bits == 8) dequant_weight_kernel<T, 8><<<grid, 256, 0, st>>>(codes, (int)n_rows, (int)k, ld_codes, scale, offset, group, out, ld_out);
-  else dequant_weight_kernel<T, 4><<<grid, 256, 0, st>>>(codes, (int)n_rows, (int)k, ld_codes, scale, offset, group, out, ld_out);
+  if (bits == 8) AMCT_LAUNCH(grid, 256, st, (codes, (int)n_rows, (int)k, ld_codes, scale, offset, group, out, ld_out), dequant_weight_kernel<T, 8>);
+  else AMCT_LAUNCH(grid, 256, st, (codes, (int)n_rows, (int)k, ld_codes, scale, offset, group, out, ld_out), dequant_weight_kernel<T, 4>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }

@@ -14,10 +14,13 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 
 #include <atomic>
 #include <cmath>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <thread>
@@ -107,6 +110,17 @@ inline void* dynamic_smem() {
   return buffer;
 }
 
+// value of lane `src` (index inside the warp), all 32 lanes taking part
+inline uint32_t shfl_idx_bits(uint32_t bits, int src) {
+  ThreadState& s = tls();
+  const unsigned t = s.tid.x;
+  s.block->slot[t] = bits;
+  s.block->warp[t >> 5].wait();
+  const uint32_t other = s.block->slot[(t & ~31u) + ((unsigned)src & 31u)];
+  s.block->warp[t >> 5].wait();
+  return other;
+}
+
 inline uint32_t shfl_xor_bits(uint32_t bits, int lane_mask) {
   ThreadState& s = tls();
   const unsigned t = s.tid.x;
@@ -135,6 +149,8 @@ inline uint32_t shfl_xor_bits(uint32_t bits, int lane_mask) {
   emu::launch(dim3(grid), (int)(threads), [&] { __VA_ARGS__ args; })
 #define AMCT_DYNAMIC_SMEM(type, name) type* name = reinterpret_cast<type*>(emu::dynamic_smem())
 #define cudaFuncSetAttribute(...) cudaSuccess
+#define cudaGetDevice(p) (*(p) = 0, cudaSuccess)
+#define cudaStreamSynchronize(stream) cudaSuccess
 #define AMCT_CHECK_LAUNCH() \
   do {                      \
   } while (0)
@@ -145,6 +161,39 @@ static inline float __shfl_xor_sync(unsigned, float v, int lane_mask) {
   b = emu::shfl_xor_bits(b, lane_mask);
   std::memcpy(&v, &b, 4);
   return v;
+}
+static inline unsigned __shfl_xor_sync(unsigned, unsigned v, int lane_mask) { return emu::shfl_xor_bits(v, lane_mask); }
+static inline int __shfl_xor_sync(unsigned, int v, int lane_mask) { return (int)emu::shfl_xor_bits((uint32_t)v, lane_mask); }
+static inline unsigned __shfl_sync(unsigned, unsigned v, int src) { return emu::shfl_idx_bits(v, src); }
+static inline int __shfl_sync(unsigned, int v, int src) { return (int)emu::shfl_idx_bits((uint32_t)v, src); }
+static inline float __shfl_sync(unsigned, float v, int src) {
+  uint32_t b;
+  std::memcpy(&b, &v, 4);
+  b = emu::shfl_idx_bits(b, src);
+  std::memcpy(&v, &b, 4);
+  return v;
+}
+// Which lanes run together at a given point cannot be known in this model, and shuffles here always involve the whole
+// warp: a kernel path that asks is not emulated (the tests keep away from it).
+static inline unsigned __activemask() {
+  std::fprintf(stderr, "cuda_emu: __activemask() is not emulated\n");
+  std::abort();
+}
+static inline unsigned __byte_perm(unsigned a, unsigned b, unsigned selector) {
+  const uint64_t both = ((uint64_t)b << 32) | a;
+  unsigned out = 0;
+  for (int i = 0; i < 4; ++i) {
+    const unsigned sel = (selector >> (4 * i)) & 0xF;
+    unsigned byte = (unsigned)(both >> (8 * (sel & 7))) & 0xFF;
+    if (sel & 8) byte = (byte & 0x80) ? 0xFF : 0x00;          // replicate the sign bit
+    out |= byte << (8 * i);
+  }
+  return out;
+}
+static inline float __uint_as_float(unsigned i) {
+  float f;
+  std::memcpy(&f, &i, 4);
+  return f;
 }
 static inline float __fmul_rn(float a, float b) { return a * b; }
 static inline float __fadd_rn(float a, float b) { return a + b; }

@@ -1,6 +1,7 @@
 """The SOURCE of the checkpoint-format and KV-cache activation kernels, executed on the CPU.
 
-``amct_b200/csrc/ckpt_formats.cu``, ``kv_quant.cu`` and (on its own) ``quant_rows.cu`` are compiled with g++ under ``tests/emu/cuda_emu.h``, which
+``amct_b200/csrc/ckpt_formats.cu`` and ``kv_quant.cu``, ``quant_rows.cu`` on its own, and the element-wise kernels
+(``quant_static.cu``, ``mx_quant.cu``, ``hif8.cu``, ``w4a16.cu``, ``rope.cu``) are compiled with g++ under ``tests/emu/cuda_emu.h``, which
 emulates blocks, threads, ``__syncthreads`` and warp shuffles with host threads and maps the rounding intrinsics to
 the IEEE operations they name.  The same C ABI entry points are then called, through the same Python wrappers
 (``amct_b200.backend.ops``, patched here to accept host pointers), by the very test functions that run on the GPU
@@ -59,6 +60,24 @@ def emu_rows_lib(tmp_path_factory):
     return ctypes.CDLL(out)
 
 
+@pytest.fixture(scope='module')
+def emu_elementwise_lib(tmp_path_factory):
+    """The element-wise and block-wise kernels that need no other source file: static quantize, MX block quantization,
+    HiFloat8 encode / decode, weight dequantization, rotary embedding."""
+    gxx = shutil.which('g++')
+    if gxx is None or not os.path.exists(os.path.join(CUDA_INCLUDE, 'cuda_fp4.h')):
+        pytest.skip('needs g++ and the CUDA headers')
+    out = str(tmp_path_factory.mktemp('emu_elem') / 'libamct_emu_elem.so')
+    sources = [os.path.join(CSRC, f) for f in ('quant_static.cu', 'mx_quant.cu', 'hif8.cu', 'w4a16.cu', 'rope.cu')]
+    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fsanitize=alignment', '-fno-sanitize-recover=alignment',
+           '-fPIC', '-shared', '-x', 'c++', '-include', os.path.join(ROOT, 'tests', 'emu', 'cuda_emu.h'), '-I', CUDA_INCLUDE,
+           *sources, '-o', out, '-lpthread']
+    subprocess.check_call(cmd)
+    library = ctypes.CDLL(out)
+    library.amct_mx_tiled_scale_bytes.restype = ctypes.c_int64
+    return library
+
+
 def _patch_ops(monkeypatch, library):
     from amct_b200.backend import lib, ops
     monkeypatch.setattr(lib, 'load', lambda: library)
@@ -71,6 +90,11 @@ def _patch_ops(monkeypatch, library):
 @pytest.fixture
 def rows_on_cpu(emu_rows_lib, monkeypatch):
     return _patch_ops(monkeypatch, emu_rows_lib)
+
+
+@pytest.fixture
+def elementwise_on_cpu(emu_elementwise_lib, monkeypatch):
+    return _patch_ops(monkeypatch, emu_elementwise_lib)
 
 
 @pytest.fixture
@@ -245,3 +269,40 @@ def test_emulated_row_quantizer_extreme_magnitudes(rows_on_cpu):
                     assert (err_o is None) == (err_k is None), (dtype, mag, rule)
                     if err_o is None:
                         assert bits_equal(got[0], want[0]) and bits_equal(got[1], want[1]), (dtype, mag, rule)
+
+
+# ---------------------------------------------------------------------------------------------
+# static quantize, MX block quantization, HiFloat8, weight dequantization, rotary embedding: the GPU tests' own
+# functions on the emulated source (the MX path for blocks holding NaN / Inf asks which lanes are active, which this
+# model cannot answer, and stays a GPU-only test)
+# ---------------------------------------------------------------------------------------------
+def test_emulated_mx_block_quantization(elementwise_on_cpu):
+    import test_gpu_mx as G
+    for fmt in ('fp8', 'fp4'):
+        for dtype in (torch.bfloat16, torch.float16, torch.float32):
+            for rows, k in [(1, 32), (5, 96), (130, 256), (33, 1024), (8, 8192)]:
+                G.test_mx_quant_matches_oracle(fmt, dtype, rows, k)
+    G.test_mx_roundtrip_properties_full_width()
+
+
+def test_emulated_hifloat8(elementwise_on_cpu):
+    import test_gpu_hif8 as G
+    G.test_decode_all_codes()
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        G.test_encode_matches_oracle(dtype)
+    G.test_encode_is_monotonic_and_idempotent()
+
+
+def test_emulated_static_quantize_dequant_and_rope(elementwise_on_cpu):
+    import test_gpu_glue as GL
+    import test_gpu_intq as G
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for shape in [(5, 64), (2, 7, 72), (3, 33), (1, 4, 16, 40)]:
+            for per_token, offset, smooth in [(False, False, False), (False, True, True), (True, False, False), (True, True, True)]:
+                G.test_quantize_static_oracle(dtype, shape, per_token, offset, smooth)
+    for bits, group, offset in [(8, 0, False), (8, 0, True), (4, 32, True), (4, 128, False), (8, 64, True)]:
+        for dtype in (torch.bfloat16, torch.float16):
+            G.test_dequant_weight_oracle(bits, group, offset, dtype)
+    for dtype in (torch.bfloat16, torch.float16):
+        for b, s, heads, kv, hd in [(2, 5, 4, 2, 128), (1, 300, 8, 1, 64), (3, 64, 64, 8, 128), (1, 1, 2, 2, 32)]:
+            GL.test_rope_inplace_bit_identical_to_torch_ops(dtype, b, s, heads, kv, hd)
