@@ -207,11 +207,11 @@ static int launch_norm_quant(const NormQuantParams& p, cudaStream_t st) {
   int64_t grid = (int64_t)sms * 8;
   if (grid > p.rows) grid = p.rows;
   const unsigned g = (unsigned)grid;
-  if (nvec <= 128) addnorm_quant_kernel<T, 1, 128><<<g, 128, 0, st>>>(p);
-  else if (nvec <= 256) addnorm_quant_kernel<T, 1, 256><<<g, 256, 0, st>>>(p);
-  else if (nvec <= 512) addnorm_quant_kernel<T, 2, 256><<<g, 256, 0, st>>>(p);
-  else if (nvec <= 1024) addnorm_quant_kernel<T, 2, 512><<<g, 512, 0, st>>>(p);
-  else if (nvec <= 2048) addnorm_quant_kernel<T, 4, 512><<<g, 512, 0, st>>>(p);
+  if (nvec <= 128) AMCT_LAUNCH(g, 128, st, (p), addnorm_quant_kernel<T, 1, 128>);
+  else if (nvec <= 256) AMCT_LAUNCH(g, 256, st, (p), addnorm_quant_kernel<T, 1, 256>);
+  else if (nvec <= 512) AMCT_LAUNCH(g, 256, st, (p), addnorm_quant_kernel<T, 2, 256>);
+  else if (nvec <= 1024) AMCT_LAUNCH(g, 512, st, (p), addnorm_quant_kernel<T, 2, 512>);
+  else if (nvec <= 2048) AMCT_LAUNCH(g, 512, st, (p), addnorm_quant_kernel<T, 4, 512>);
   else return AMCT_ERR_UNSUPPORTED;
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;

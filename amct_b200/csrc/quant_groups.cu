@@ -291,12 +291,12 @@ static int launch_groups(GroupParams p, int group, cudaStream_t st) {
   if (gy > 65535) gy = 65535;
   grid.y = (unsigned)(gy < 1 ? 1 : gy);
   switch (p.out_mode) {
-    case AMCT_OUT_NONE: quant_groups_kernel<T, AMCT_OUT_NONE><<<grid, 256, 0, st>>>(p); break;
-    case AMCT_OUT_I8: quant_groups_kernel<T, AMCT_OUT_I8><<<grid, 256, 0, st>>>(p); break;
-    case AMCT_OUT_I32: quant_groups_kernel<T, AMCT_OUT_I32><<<grid, 256, 0, st>>>(p); break;
-    case AMCT_OUT_PACK4: quant_groups_kernel<T, AMCT_OUT_PACK4><<<grid, 256, 0, st>>>(p); break;
-    case AMCT_OUT_FAKE: quant_groups_kernel<T, AMCT_OUT_FAKE><<<grid, 256, 0, st>>>(p); break;
-    case AMCT_OUT_FAKE_AWQ: quant_groups_kernel<T, AMCT_OUT_FAKE_AWQ><<<grid, 256, 0, st>>>(p); break;
+    case AMCT_OUT_NONE: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_NONE>); break;
+    case AMCT_OUT_I8: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_I8>); break;
+    case AMCT_OUT_I32: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_I32>); break;
+    case AMCT_OUT_PACK4: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_PACK4>); break;
+    case AMCT_OUT_FAKE: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_FAKE>); break;
+    case AMCT_OUT_FAKE_AWQ: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_FAKE_AWQ>); break;
     default: return AMCT_ERR_ARG;
   }
   AMCT_CHECK_LAUNCH();

@@ -204,10 +204,10 @@ static int run_minmax(const T* x, int64_t rows, int64_t k, int64_t ld, int axis,
   const bool vec = aligned16(x) && (ld * (int64_t)sizeof(T)) % 16 == 0 && k % E == 0;
   if (axis == AMCT_AXIS_TENSOR) {
     int blocks = (int)(rows < kTensorBlocks ? rows : kTensorBlocks);
-    if (vec) minmax_tensor_kernel<T, true><<<blocks, 256, 0, st>>>(x, rows, k, ld, ws, status);
-    else minmax_tensor_kernel<T, false><<<blocks, 256, 0, st>>>(x, rows, k, ld, ws, status);
+    if (vec) AMCT_LAUNCH(blocks, 256, st, (x, rows, k, ld, ws, status), minmax_tensor_kernel<T, true>);
+    else AMCT_LAUNCH(blocks, 256, st, (x, rows, k, ld, ws, status), minmax_tensor_kernel<T, false>);
     AMCT_CHECK_LAUNCH();
-    minmax_tensor_final_kernel<T><<<1, 256, 0, st>>>(ws, blocks, merge, out_min, out_max);
+    AMCT_LAUNCH(1, 256, st, (ws, blocks, merge, out_min, out_max), minmax_tensor_final_kernel<T>);
     AMCT_CHECK_LAUNCH();
     return AMCT_OK;
   }
@@ -220,10 +220,10 @@ static int run_minmax(const T* x, int64_t rows, int64_t k, int64_t ld, int axis,
   if ((int64_t)chunks * 8 > rows) chunks = (int)((rows + 7) / 8);
   if (chunks < 1) chunks = 1;
   dim3 grid(cblocks, (unsigned)chunks);
-  if (vec) minmax_column_kernel<T, true><<<grid, 128, 0, st>>>(x, rows, k, ld, ws, status);
-  else minmax_column_kernel<T, false><<<grid, 128, 0, st>>>(x, rows, k, ld, ws, status);
+  if (vec) AMCT_LAUNCH(grid, 128, st, (x, rows, k, ld, ws, status), minmax_column_kernel<T, true>);
+  else AMCT_LAUNCH(grid, 128, st, (x, rows, k, ld, ws, status), minmax_column_kernel<T, false>);
   AMCT_CHECK_LAUNCH();
-  minmax_column_final_kernel<T><<<(unsigned)((k + 255) / 256), 256, 0, st>>>(ws, chunks, k, merge, out_min, out_max);
+  AMCT_LAUNCH((unsigned)((k + 255) / 256), 256, st, (ws, chunks, k, merge, out_min, out_max), minmax_column_final_kernel<T>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -276,8 +276,8 @@ static int run_minmax_rows(const T* x, int64_t rows, int64_t k, int64_t ld, cons
                            T* out_min, T* out_max, int* status, cudaStream_t st) {
   constexpr int E = ElemTraits<T>::kPerVec;
   const bool vec = aligned16(x) && (ld * (int64_t)sizeof(T)) % 16 == 0 && k % E == 0;
-  if (vec) minmax_rows_kernel<T, true><<<(unsigned)rows, 128, 0, st>>>(x, k, ld, pre, pre_op, merge, out_min, out_max, status);
-  else minmax_rows_kernel<T, false><<<(unsigned)rows, 128, 0, st>>>(x, k, ld, pre, pre_op, merge, out_min, out_max, status);
+  if (vec) AMCT_LAUNCH((unsigned)rows, 128, st, (x, k, ld, pre, pre_op, merge, out_min, out_max, status), minmax_rows_kernel<T, true>);
+  else AMCT_LAUNCH((unsigned)rows, 128, st, (x, k, ld, pre, pre_op, merge, out_min, out_max, status), minmax_rows_kernel<T, false>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -453,14 +453,14 @@ extern "C" int amct_scale_offset(const void* vmax, const void* vmin, int dtype, 
   int* off = symmetric ? nullptr : offset;
   switch (dtype) {
     case AMCT_DTYPE_F32:
-      amct::scale_offset_kernel<float><<<blocks, 256, 0, st>>>((const float*)vmax, (const float*)vmin, n, bits, symmetric, scale, off, status);
+      AMCT_LAUNCH(blocks, 256, st, ((const float*)vmax, (const float*)vmin, n, bits, symmetric, scale, off, status), amct::scale_offset_kernel<float>);
       break;
     case AMCT_DTYPE_F16:
-      amct::scale_offset_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)vmax, (const __half*)vmin, n, bits, symmetric, scale, off, status);
+      AMCT_LAUNCH(blocks, 256, st, ((const __half*)vmax, (const __half*)vmin, n, bits, symmetric, scale, off, status), amct::scale_offset_kernel<__half>);
       break;
     case AMCT_DTYPE_BF16:
-      amct::scale_offset_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)vmax, (const __nv_bfloat16*)vmin, n, bits,
-                                                                       symmetric, scale, off, status);
+      AMCT_LAUNCH(blocks, 256, st, ((const __nv_bfloat16*)vmax, (const __nv_bfloat16*)vmin, n, bits,
+                                                                       symmetric, scale, off, status), amct::scale_offset_kernel<__nv_bfloat16>);
       break;
     default:
       return AMCT_ERR_ARG;
@@ -474,7 +474,7 @@ extern "C" int amct_rowsum_i8(const int8_t* wq, int64_t n_rows, int64_t k, int64
   if (n_rows == 0) return AMCT_OK;
   int vec = amct::aligned16(wq) && ld % 16 == 0;
   unsigned blocks = (unsigned)((n_rows + 7) / 8);
-  amct::rowsum_i8_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(wq, n_rows, k, ld, out, vec);
+  AMCT_LAUNCH(blocks, 256, (cudaStream_t)stream, (wq, n_rows, k, ld, out, vec), amct::rowsum_i8_kernel);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -484,7 +484,7 @@ extern "C" int amct_transpose_i8(const int8_t* in, int64_t rows, int64_t cols, i
   if (rows == 0 || cols == 0) return AMCT_OK;
   dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
   if (grid.y > 65535) return AMCT_ERR_UNSUPPORTED;
-  amct::transpose_i8_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(in, rows, cols, out);
+  AMCT_LAUNCH(grid, 256, (cudaStream_t)stream, (in, rows, cols, out), amct::transpose_i8_kernel);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }

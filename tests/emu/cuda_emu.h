@@ -134,6 +134,8 @@ inline uint32_t shfl_xor_bits(uint32_t bits, int lane_mask) {
 }  // namespace emu
 
 #undef __shared__
+#undef __noinline__
+#define __noinline__ __attribute__((noinline))
 #undef __launch_bounds__
 #define threadIdx (emu::tls().tid)
 #define blockIdx (emu::tls().bid)
@@ -151,6 +153,8 @@ inline uint32_t shfl_xor_bits(uint32_t bits, int lane_mask) {
 #define cudaFuncSetAttribute(...) cudaSuccess
 #define cudaGetDevice(p) (*(p) = 0, cudaSuccess)
 #define cudaStreamSynchronize(stream) cudaSuccess
+#define cudaDeviceGetAttribute(p, attr, dev) (*(p) = 148, cudaSuccess)
+#define cudaGetSymbolAddress(pp, symbol) (*(pp) = (void*)(symbol), cudaSuccess)   // a __device__ array is a host array here
 #define AMCT_CHECK_LAUNCH() \
   do {                      \
   } while (0)
@@ -217,6 +221,12 @@ static inline float __int_as_float(int i) {
   return f;
 }
 static inline int __popc(unsigned v) { return __builtin_popcount(v); }
+static inline int __dp4a(int a, int b, int c) {
+  for (int i = 0; i < 4; ++i) c += (int)(int8_t)(a >> (8 * i)) * (int)(int8_t)(b >> (8 * i));
+  return c;
+}
+// correctly rounded 1 / sqrt(x): through double, whose error is far below half an fp32 ulp except on measure-zero ties
+static inline float __frsqrt_rn(float x) { return (float)(1.0 / std::sqrt((double)x)); }
 static inline int atomicOr(int* p, int v) { return __atomic_fetch_or(p, v, __ATOMIC_SEQ_CST); }
 static inline int atomicMin(int* p, int v) {
   int old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
@@ -239,5 +249,7 @@ static inline int min(int a, int b) { return a < b ? a : b; }
 static inline int max(int a, int b) { return a > b ? a : b; }
 static inline unsigned min(unsigned a, unsigned b) { return a < b ? a : b; }
 static inline unsigned max(unsigned a, unsigned b) { return a > b ? a : b; }
+static inline long min(long a, long b) { return a < b ? a : b; }
+static inline long max(long a, long b) { return a > b ? a : b; }
 static inline long long min(long long a, long long b) { return a < b ? a : b; }
 static inline long long max(long long a, long long b) { return a > b ? a : b; }

@@ -1,22 +1,29 @@
-"""The SOURCE of the checkpoint-format and KV-cache activation kernels, executed on the CPU.
+"""The SOURCE of the bandwidth-bound kernels, executed on the CPU.
 
-``amct_b200/csrc/ckpt_formats.cu`` and ``kv_quant.cu``, ``quant_rows.cu`` on its own, and the element-wise kernels
-(``quant_static.cu``, ``mx_quant.cu``, ``hif8.cu``, ``w4a16.cu``, ``rope.cu``) are compiled with g++ under ``tests/emu/cuda_emu.h``, which
-emulates blocks, threads, ``__syncthreads`` and warp shuffles with host threads and maps the rounding intrinsics to
-the IEEE operations they name.  The same C ABI entry points are then called, through the same Python wrappers
-(``amct_b200.backend.ops``, patched here to accept host pointers), by the very test functions that run on the GPU
-(``tests/test_zy_gpu_*.py``): argument checks, launch geometry, vector and scalar paths, reductions and index
-arithmetic are all exercised against the reference's golden vectors and the oracle without a GPU.  The build checks
-every access for its type's alignment, so a 16-byte vector access on an address the launch conditions should have
-ruled out stops the test, as it would fault on the GPU.
+Every ``.cu`` file of ``amct_b200/csrc`` that uses neither tensor cores, bulk asynchronous copies nor inline PTX --
+``quant_rows.cu``, ``quant_groups.cu``, ``reduce.cu``, ``norm_quant.cu``, ``quant_static.cu``, ``mx_quant.cu``,
+``hif8.cu``, ``w4a16.cu``, ``rope.cu``, ``ckpt_formats.cu``, ``kv_quant.cu`` -- is compiled with g++ under
+``tests/emu/cuda_emu.h``, which emulates blocks, threads, ``__syncthreads`` and warp shuffles with host threads and maps
+the rounding intrinsics to the IEEE operations they name.  The same C ABI entry points are then called, through the
+same Python wrappers (``amct_b200.backend.ops``, patched here to accept host pointers), by the very test functions that
+run on the GPU (``tests/test_gpu_*.py``, ``tests/test_zy_gpu_*.py``): argument checks, launch geometry, vector and
+scalar paths, reductions and index arithmetic are exercised against the reference's golden vectors and the oracle
+without a GPU.  The build checks every access for its type's alignment, so a 16-byte vector access on an address the
+launch conditions should have ruled out stops the test, as it would fault on the GPU.
+
+Not emulated: the GEMMs (tcgen05, TMA), the streaming per-row quantizer ``quant_token.cu`` (bulk copies and mbarriers;
+its requests are answered by the general row kernel here, which computes the same function), the peer barrier (PTX),
+and the MX path for blocks holding NaN / Inf (it asks which lanes are active, which this model cannot answer).
 
 This is a check of the kernel source, not a product path: the emulation library is built into a temporary directory
 by this test alone, and ``amct_b200`` can neither build nor load it.  What it cannot show is anything that depends on
-the GPU itself (the hardware FP8 conversion, memory ordering, performance); the GPU tests remain the parity tests.
+the GPU itself (hardware conversions, memory ordering, performance); the GPU tests remain the parity tests.
 """
 import contextlib
 import ctypes
 import functools
+import inspect
+import itertools
 import os
 import shutil
 import subprocess
@@ -26,84 +33,128 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(ROOT, 'amct_b200', 'csrc')
+EMU = os.path.join(ROOT, 'tests', 'emu')
 CUDA_INCLUDE = os.path.join(os.environ.get('CUDA_HOME', '/usr/local/cuda'), 'include')
+EMULATED = ('quant_rows.cu', 'quant_groups.cu', 'reduce.cu', 'norm_quant.cu', 'quant_static.cu', 'mx_quant.cu', 'hif8.cu',
+            'w4a16.cu', 'rope.cu', 'ckpt_formats.cu', 'kv_quant.cu')
+
+
+def build(out, sources):
+    gxx = shutil.which('g++')
+    if gxx is None or not os.path.exists(os.path.join(CUDA_INCLUDE, 'cuda_fp4.h')):
+        pytest.skip('needs g++ and the CUDA headers')
+    # -fsanitize=alignment: a vector access the GPU would fault on ("misaligned address") aborts the test here
+    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fsanitize=alignment', '-fno-sanitize-recover=alignment',
+           '-fPIC', '-shared', '-x', 'c++', '-include', os.path.join(EMU, 'cuda_emu.h'), '-I', CUDA_INCLUDE, *sources,
+           '-o', out, '-lpthread']
+    subprocess.check_call(cmd)
+    library = ctypes.CDLL(out)
+    for name in ('amct_mx_tiled_scale_bytes', 'amct_minmax_workspace_bytes', 'amct_minmax_noalloc_max_k'):
+        if hasattr(library, name):
+            getattr(library, name).restype = ctypes.c_int64
+    if hasattr(library, 'amct_minmax_workspace_bytes'):
+        library.amct_minmax_workspace_bytes.argtypes = [ctypes.c_int64]
+    return library
 
 
 @pytest.fixture(scope='module')
 def emu_lib(tmp_path_factory):
-    gxx = shutil.which('g++')
-    if gxx is None or not os.path.exists(os.path.join(CUDA_INCLUDE, 'cuda_fp8.h')):
-        pytest.skip('needs g++ and the CUDA headers')
+    """All emulated files in one library; the streaming kernel's entry declines every shape."""
     out = str(tmp_path_factory.mktemp('emu') / 'libamct_emu.so')
-    # -fsanitize=alignment: a vector access the GPU would fault on ("misaligned address") aborts the test here
-    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fsanitize=alignment', '-fno-sanitize-recover=alignment',
-           '-fPIC', '-shared', '-x', 'c++',
-           '-include', os.path.join(ROOT, 'tests', 'emu', 'cuda_emu.h'), '-I', CUDA_INCLUDE,
-           os.path.join(CSRC, 'ckpt_formats.cu'), os.path.join(CSRC, 'kv_quant.cu'), '-o', out, '-lpthread']
-    subprocess.check_call(cmd)
-    return ctypes.CDLL(out)
+    return build(out, [os.path.join(CSRC, f) for f in EMULATED] + [os.path.join(EMU, 'no_streaming_kernel.cpp')])
 
 
 @pytest.fixture(scope='module')
 def emu_rows_lib(tmp_path_factory):
-    """quant_rows.cu on its own: the specialised kernels it would try first (other source files) are replaced by stubs
-    that decline every shape, so each request runs through the general row kernels."""
-    gxx = shutil.which('g++')
-    if gxx is None or not os.path.exists(os.path.join(CUDA_INCLUDE, 'cuda_fp16.h')):
-        pytest.skip('needs g++ and the CUDA headers')
+    """quant_rows.cu on its own: the specialised kernels it would try first decline every shape, so each request runs
+    through the general row kernels -- also the shapes that the group kernel serves in the full library."""
     out = str(tmp_path_factory.mktemp('emu_rows') / 'libamct_emu_rows.so')
-    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fsanitize=alignment', '-fno-sanitize-recover=alignment',
-           '-fPIC', '-shared', '-x', 'c++', '-include', os.path.join(ROOT, 'tests', 'emu', 'cuda_emu.h'), '-I', CUDA_INCLUDE,
-           os.path.join(CSRC, 'quant_rows.cu'), os.path.join(ROOT, 'tests', 'emu', 'quant_rows_alone.cpp'), '-o', out,
-           '-lpthread']
-    subprocess.check_call(cmd)
-    return ctypes.CDLL(out)
+    return build(out, [os.path.join(CSRC, 'quant_rows.cu'), os.path.join(EMU, 'no_streaming_kernel.cpp'),
+                       os.path.join(EMU, 'no_group_kernel.cpp')])
 
 
-@pytest.fixture(scope='module')
-def emu_elementwise_lib(tmp_path_factory):
-    """The element-wise and block-wise kernels that need no other source file: static quantize, MX block quantization,
-    HiFloat8 encode / decode, weight dequantization, rotary embedding."""
-    gxx = shutil.which('g++')
-    if gxx is None or not os.path.exists(os.path.join(CUDA_INCLUDE, 'cuda_fp4.h')):
-        pytest.skip('needs g++ and the CUDA headers')
-    out = str(tmp_path_factory.mktemp('emu_elem') / 'libamct_emu_elem.so')
-    sources = [os.path.join(CSRC, f) for f in ('quant_static.cu', 'mx_quant.cu', 'hif8.cu', 'w4a16.cu', 'rope.cu')]
-    cmd = [gxx, '-std=c++17', '-O1', '-w', '-ffp-contract=off', '-fsanitize=alignment', '-fno-sanitize-recover=alignment',
-           '-fPIC', '-shared', '-x', 'c++', '-include', os.path.join(ROOT, 'tests', 'emu', 'cuda_emu.h'), '-I', CUDA_INCLUDE,
-           *sources, '-o', out, '-lpthread']
-    subprocess.check_call(cmd)
-    library = ctypes.CDLL(out)
-    library.amct_mx_tiled_scale_bytes.restype = ctypes.c_int64
-    return library
-
-
-def _patch_ops(monkeypatch, library):
+def patch_ops(monkeypatch, library):
+    """The ops wrappers talking to an emulation library with host tensors."""
     from amct_b200.backend import lib, ops
     monkeypatch.setattr(lib, 'load', lambda: library)
     monkeypatch.setattr(ops, '_need_cuda', lambda *tensors: None)
     monkeypatch.setattr(ops, '_stream', lambda: ctypes.c_void_p(0))
+    monkeypatch.setattr(ops, 'hadamard_pow2', functools.partial(ops.hadamard_pow2, device='cpu'))
+    monkeypatch.setattr(torch.cuda, 'device', lambda device: contextlib.nullcontext())
     monkeypatch.setattr(torch.Tensor, 'cuda', lambda self, *args, **kwargs: self)
+    monkeypatch.setattr(torch.Tensor, 'is_cuda', property(lambda self: True))     # wrappers that check their outputs
     return ops
-
-
-@pytest.fixture
-def rows_on_cpu(emu_rows_lib, monkeypatch):
-    return _patch_ops(monkeypatch, emu_rows_lib)
-
-
-@pytest.fixture
-def elementwise_on_cpu(emu_elementwise_lib, monkeypatch):
-    return _patch_ops(monkeypatch, emu_elementwise_lib)
 
 
 @pytest.fixture
 def on_cpu(emu_lib, monkeypatch):
-    """The ops wrappers talking to the emulation library with host tensors."""
-    ops = _patch_ops(monkeypatch, emu_lib)
-    monkeypatch.setattr(ops, 'hadamard_pow2', functools.partial(ops.hadamard_pow2, device='cpu'))
-    monkeypatch.setattr(torch.cuda, 'device', lambda device: contextlib.nullcontext())
-    return ops
+    return patch_ops(monkeypatch, emu_lib)
+
+
+@pytest.fixture
+def rows_on_cpu(emu_rows_lib, monkeypatch):
+    return patch_ops(monkeypatch, emu_rows_lib)
+
+
+def parametrizations(fn):
+    """Keyword arguments of every combination of a test function's ``parametrize`` marks."""
+    marks = [m for m in getattr(fn, 'pytestmark', []) if m.name == 'parametrize']
+    names = [[n.strip() for n in m.args[0].split(',')] for m in marks]
+    for combo in itertools.product(*[list(m.args[1]) for m in marks]):
+        kwargs = {}
+        for group, value in zip(names, combo):
+            kwargs.update({group[0]: value} if len(group) == 1 else dict(zip(group, value)))
+        yield kwargs
+
+
+def run_gpu_tests(module, skip=()):
+    """Calls every test function of a GPU test module with all its parameters; returns how many ran."""
+    ran = 0
+    for name, fn in inspect.getmembers(module, inspect.isfunction):
+        if not name.startswith('test_') or name in skip:
+            continue
+        for kwargs in parametrizations(fn):
+            try:
+                fn(**kwargs)
+                ran += 1
+            except pytest.skip.Exception:
+                pass
+    return ran
+
+
+# ---------------------------------------------------------------------------------------------
+# whole GPU test modules on the emulated source
+# ---------------------------------------------------------------------------------------------
+def test_emulated_integer_quantizers(on_cpu):
+    """tests/test_gpu_intq.py: scale rule, every weight granularity, per-token rules, observers, static quantize,
+    weight dequantization, against the reference's golden vectors and the oracle.  The two tests aimed at the streaming
+    kernel are left out (their shapes are large and the kernel is not emulated)."""
+    import test_gpu_intq as G
+    ran = run_gpu_tests(G, skip=('test_dynamic_per_token_streaming_kernel', 'test_channel_int8_weight_quant_streaming_path'))
+    assert ran > 200
+
+
+def test_emulated_decoder_glue(on_cpu):
+    """tests/test_gpu_glue.py: add + RMSNorm + per-token quantization and the rotary embedding (the two tests that
+    build the whole Llama workload need the GEMMs)."""
+    import test_gpu_glue as G
+    ran = run_gpu_tests(G, skip=('test_workload_fused_glue_matches_unfused_layers',
+                                 'test_decode_in_place_kv_cache_matches_concatenation'))
+    assert ran > 40
+
+
+def test_emulated_hifloat8(on_cpu):
+    import test_gpu_hif8 as G
+    assert run_gpu_tests(G, skip=('test_hifloat8_linear_through_the_public_api',)) >= 5
+
+
+def test_emulated_mx_block_quantization(on_cpu):
+    import test_gpu_mx as G
+    for fmt in ('fp8', 'fp4'):
+        for dtype in (torch.bfloat16, torch.float16, torch.float32):
+            for rows, k in [(1, 32), (5, 96), (130, 256), (33, 1024), (8, 8192)]:
+                G.test_mx_quant_matches_oracle(fmt, dtype, rows, k)
+    G.test_mx_roundtrip_properties_full_width()
 
 
 # ---------------------------------------------------------------------------------------------
@@ -269,40 +320,3 @@ def test_emulated_row_quantizer_extreme_magnitudes(rows_on_cpu):
                     assert (err_o is None) == (err_k is None), (dtype, mag, rule)
                     if err_o is None:
                         assert bits_equal(got[0], want[0]) and bits_equal(got[1], want[1]), (dtype, mag, rule)
-
-
-# ---------------------------------------------------------------------------------------------
-# static quantize, MX block quantization, HiFloat8, weight dequantization, rotary embedding: the GPU tests' own
-# functions on the emulated source (the MX path for blocks holding NaN / Inf asks which lanes are active, which this
-# model cannot answer, and stays a GPU-only test)
-# ---------------------------------------------------------------------------------------------
-def test_emulated_mx_block_quantization(elementwise_on_cpu):
-    import test_gpu_mx as G
-    for fmt in ('fp8', 'fp4'):
-        for dtype in (torch.bfloat16, torch.float16, torch.float32):
-            for rows, k in [(1, 32), (5, 96), (130, 256), (33, 1024), (8, 8192)]:
-                G.test_mx_quant_matches_oracle(fmt, dtype, rows, k)
-    G.test_mx_roundtrip_properties_full_width()
-
-
-def test_emulated_hifloat8(elementwise_on_cpu):
-    import test_gpu_hif8 as G
-    G.test_decode_all_codes()
-    for dtype in (torch.float32, torch.bfloat16, torch.float16):
-        G.test_encode_matches_oracle(dtype)
-    G.test_encode_is_monotonic_and_idempotent()
-
-
-def test_emulated_static_quantize_dequant_and_rope(elementwise_on_cpu):
-    import test_gpu_glue as GL
-    import test_gpu_intq as G
-    for dtype in (torch.bfloat16, torch.float16, torch.float32):
-        for shape in [(5, 64), (2, 7, 72), (3, 33), (1, 4, 16, 40)]:
-            for per_token, offset, smooth in [(False, False, False), (False, True, True), (True, False, False), (True, True, True)]:
-                G.test_quantize_static_oracle(dtype, shape, per_token, offset, smooth)
-    for bits, group, offset in [(8, 0, False), (8, 0, True), (4, 32, True), (4, 128, False), (8, 64, True)]:
-        for dtype in (torch.bfloat16, torch.float16):
-            G.test_dequant_weight_oracle(bits, group, offset, dtype)
-    for dtype in (torch.bfloat16, torch.float16):
-        for b, s, heads, kv, hd in [(2, 5, 4, 2, 128), (1, 300, 8, 1, 64), (3, 64, 64, 8, 128), (1, 1, 2, 2, 32)]:
-            GL.test_rope_inplace_bit_identical_to_torch_ops(dtype, b, s, heads, kv, hd)
