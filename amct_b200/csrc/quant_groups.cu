@@ -188,7 +188,9 @@ __global__ void __launch_bounds__(256) quant_groups_kernel(GroupParams p) {
       float poison = 0.f;
 #pragma unroll
       for (int e = 0; e < EP; ++e) {
-        float t = __fadd_rn(div_by_recip(x[e], s, y), o_add);
+        float q = div_by_recip(x[e], s, y);
+        if (kFake) q = x[e] == 0.f ? __fmul_rn(x[e], y) : q;    // -0.0 / s is -0.0 (the FMA corrections give +0.0)
+        float t = __fadd_rn(q, o_add);
         poison = __fmaf_rn(t, 0.f, poison);
         if (kAwqRounds) t = round_to<T>(t);
         t = fminf(fmaxf(t, qmin), qmax);

@@ -75,7 +75,9 @@ __device__ __forceinline__ float usable_recip(float s) {
 // valid (and the result is finite), the IEEE division otherwise
 __device__ __forceinline__ float quotient(float x, const UnitQ& u) {
   if (u.recip != 0.f) {
-    const float q = div_by_recip(x, u.scale, u.recip);
+    // the correction steps of div_by_recip turn the quotient of -0.0 into +0.0; the fake-quant outputs show that
+    // sign, so a zero input takes the plain product, whose sign is the IEEE quotient's
+    const float q = x == 0.f ? __fmul_rn(x, u.recip) : div_by_recip(x, u.scale, u.recip);
     if (fabsf(q) <= 3.0e38f) return q;
   }
   return __fdiv_rn(x, u.scale);
