@@ -143,6 +143,18 @@ def test_emulated_decoder_glue(on_cpu):
     assert ran > 40
 
 
+def test_emulated_edge_cases(on_cpu):
+    """tests/test_zy_gpu_edge_cases.py through the full library (the group kernel takes the group-wise requests)."""
+    import test_zy_gpu_edge_cases as G
+    assert run_gpu_tests(G) >= 10
+
+
+def test_emulated_edge_cases_general_kernels(rows_on_cpu):
+    """The same through the general row kernels alone."""
+    import test_zy_gpu_edge_cases as G
+    assert run_gpu_tests(G) >= 10
+
+
 def test_emulated_hifloat8(on_cpu):
     import test_gpu_hif8 as G
     assert run_gpu_tests(G, skip=('test_hifloat8_linear_through_the_public_api',)) >= 5

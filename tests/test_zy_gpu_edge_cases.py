@@ -1,0 +1,43 @@
+"""Corner cases of the integer quantizers that the CPU emulation of the kernel source turned up (see
+tests/test_kernel_source_emulation.py); on the GPU they run after the long-standing parity tests."""
+import pytest
+import torch
+
+from golden_io import bits_equal
+from oracle import intq
+
+pytestmark = pytest.mark.gpu
+
+
+def ops():
+    from amct_b200.backend import ops as o
+    return o
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize('strategy,group,k', [('channel', None, 200), ('group', 64, 256), ('group', 48, 96)])
+def test_fake_quant_keeps_the_sign_of_a_zero_input(dtype, strategy, group, k):
+    """-0.0 / scale is -0.0 in the reference's torch division; both fake-quant variants show it."""
+    gen = torch.Generator().manual_seed(51)
+    w = (torch.randn(4, k, generator=gen) * 0.05).to(dtype)
+    w[:, ::3] = -0.0
+    w[1] = -0.0                                            # a whole row of negative zeros: scale becomes 1
+    for qt, sym in (('int4', True), ('int4', False), ('int8', True)):
+        scale, offset = intq.weight_scale_offset(w, qt, sym, strategy, group)
+        dev_off = None if offset is None else offset.cuda()
+        fake = ops().quant_rows(w.cuda(), qt, sym, strategy, group, scale=scale.cuda(), offset=dev_off, out='fake')[2]
+        assert bits_equal(fake, intq.fake_quant(w, qt, scale, offset, group))
+        fake = ops().quant_rows(w.cuda(), qt, sym, strategy, group, scale=scale.cuda(), offset=dev_off, out='fake_awq')[2]
+        assert bits_equal(fake, intq.fake_quant_awq(w, qt, scale, offset, group))
+
+
+def test_experimental_rule_with_a_scale_that_underflows():
+    """fp16 rows around 1e-7: max / 127 rounds to zero in fp16, x / 0 is +-inf (clamped) or NaN for a zero element,
+    which the reference's int8 cast turns into code 0."""
+    gen = torch.Generator().manual_seed(52)
+    x = (torch.randn(5, 64, generator=gen) * 1e-7).half()
+    x[:, 7] = 0
+    want_q, want_s = intq.dynamic_per_token(x, 'experimental')
+    got_q, got_s = ops().quant_dynamic_per_token(x.cuda(), rule='experimental')
+    assert bool((want_s == 0).any())
+    assert bits_equal(got_s, want_s) and bits_equal(got_q, want_q)
