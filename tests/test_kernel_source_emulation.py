@@ -332,3 +332,56 @@ def test_emulated_row_quantizer_extreme_magnitudes(rows_on_cpu):
                     assert (err_o is None) == (err_k is None), (dtype, mag, rule)
                     if err_o is None:
                         assert bits_equal(got[0], want[0]) and bits_equal(got[1], want[1]), (dtype, mag, rule)
+
+
+def test_emulated_minmax_without_workspace(emu_lib):
+    """amct_minmax_noalloc against amct_minmax on consecutive calls (column axis twice, tensor axis, a running merge) and
+    its size limit, as tests/test_zz_no_alloc.py does on the GPU; the built-in scratch is an ordinary array here."""
+    from ctypes import c_int, c_int64, c_void_p
+    L = emu_lib
+    assert L.amct_minmax_noalloc_max_k() == 16384
+
+    def both(x, axis, merge_from=None):
+        rows, k = x.shape
+        n = 1 if axis == 0 else k
+        dt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x.dtype]
+        outs = []
+        for noalloc in (False, True):
+            mn, mx = (torch.empty(n, dtype=x.dtype), torch.empty(n, dtype=x.dtype)) if merge_from is None else \
+                (merge_from[0].clone(), merge_from[1].clone())
+            head = (c_void_p(x.data_ptr()), c_int(dt), c_int64(rows), c_int64(k), c_int64(x.stride(0)), c_int(axis),
+                    c_int(0 if merge_from is None else 1), c_void_p(mn.data_ptr()), c_void_p(mx.data_ptr()))
+            if noalloc:
+                rc = L.amct_minmax_noalloc(*head, c_void_p(0), c_void_p(0))
+            else:
+                ws = torch.empty(L.amct_minmax_workspace_bytes(c_int64(k)), dtype=torch.uint8)
+                rc = L.amct_minmax(*head, c_void_p(ws.data_ptr()), c_void_p(0), c_void_p(0))
+            assert rc == 0, rc
+            outs.append((mn, mx))
+        return outs
+
+    def same(a, b):
+        w = {2: torch.int16, 4: torch.int32}[a.element_size()]
+        return bool((a.view(w) == b.view(w)).all())
+
+    gen = torch.Generator().manual_seed(123)
+    first = torch.randn(300, 1032, generator=gen).to(torch.bfloat16)
+    second = (torch.randn(57, 520, generator=gen) * 3).to(torch.bfloat16)
+    third = torch.randn(150, 100, generator=gen)
+    prev = None
+    for x, axis in ((first, 1), (second, 1), (third, 0), (second, 0), (first, 1)):
+        (mn_a, mx_a), (mn_b, mx_b) = both(x, axis)
+        assert same(mn_a, mn_b) and same(mx_a, mx_b)
+        assert same(mn_b, x.amin(0) if axis == 1 else x.min().reshape(1))
+        assert same(mx_b, x.amax(0) if axis == 1 else x.max().reshape(1))
+        prev = (mn_b, mx_b) if axis == 1 and x is first else prev
+    shifted = (first.float() * 0.5 + 1).to(torch.bfloat16)
+    (mn_a, mx_a), (mn_b, mx_b) = both(shifted, 1, merge_from=prev)
+    assert same(mn_a, mn_b) and same(mx_a, mx_b) and same(mx_b, torch.maximum(prev[1], shifted.amax(0)))
+    k = 16384 + 8
+    x = torch.zeros(4, k, dtype=torch.bfloat16)
+    mn = torch.full((k,), 7, dtype=torch.bfloat16)
+    mx = mn.clone()
+    rc = L.amct_minmax_noalloc(c_void_p(x.data_ptr()), c_int(2), c_int64(4), c_int64(k), c_int64(k), c_int(1), c_int(0),
+                               c_void_p(mn.data_ptr()), c_void_p(mx.data_ptr()), c_void_p(0), c_void_p(0))
+    assert rc == -6 and bool((mn == 7).all()) and bool((mx == 7).all())
