@@ -31,7 +31,7 @@ def close_rotation(got, want):
     assert got.dtype == want.dtype and got.shape == want.shape
     g, w = got.cpu().float(), want.cpu().float()
     eps = torch.finfo(want.dtype).eps * (4 if want.dtype == torch.float32 else 1)
-    floor = w.abs().amax(-1, keepdim=True) * 2e-6 + torch.finfo(want.dtype).smallest_subnormal    # one step of a subnormal
+    floor = w.abs().amax(-1, keepdim=True) * 2e-6 + torch.finfo(want.dtype).tiny * torch.finfo(want.dtype).eps    # + one step of a subnormal
     return bool(((g - w).abs() <= eps * w.abs() + floor).all())
 
 
