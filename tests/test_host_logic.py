@@ -179,3 +179,28 @@ def test_dynamic_inputs_key_is_passed_through():
     assert detail['linear1']['inputs_cfg'] == {'quant_type': 'int8', 'symmetric': True, 'strategy': 'token', 'dynamic': True}
     with pytest.raises(ValueError, match='dynamic quantization only support strategy token'):
         parse_config(Net(), cfg(W8, {'type': 'int8', 'symmetric': True, 'strategy': 'tensor', 'dynamic': True}), AlgorithmRegistry)
+
+
+def test_quant_util_names_layout_and_errors():
+    """amct_b200.utils.quant_util carries the names of amct_pytorch/utils/quant_util.py; layout helpers and argument
+    errors work without a device, the arithmetic refuses CPU tensors."""
+    from amct_b200.backend.lib import BackendError
+    from amct_b200.utils import quant_util as U
+    for name in ('pad_zero_by_group', 'convert_to_per_group_shape', 'convert_dtype', 'quant_weight', 'apply_smooth_weight',
+                 'check_scale_offset_shape', 'apply_awq_quantize_weight', 'quant_dequant_weight'):
+        assert callable(getattr(U, name))
+    w = torch.arange(10, dtype=torch.float32).reshape(2, 5)
+    assert U.pad_zero_by_group(w, 4).shape == (2, 8) and float(U.pad_zero_by_group(w, 4)[0, 5:].abs().sum()) == 0
+    assert U.convert_to_per_group_shape(w, 4).shape == (2, 2, 4)
+    assert torch.equal(U.apply_smooth_weight(torch.full((1, 5), 2.0), w), w * 2)
+    assert torch.equal(U.apply_awq_quantize_weight(w, torch.full((1, 5), 2.0), 4), w / 2)
+    with pytest.raises(RuntimeError, match='smooth_factor shape should be'):
+        U.apply_smooth_weight(torch.ones(5), w)
+    with pytest.raises(RuntimeError, match='AWQ params scale.shape should be'):
+        U.apply_awq_quantize_weight(w, torch.ones(5), 4)
+    with pytest.raises(ValueError, match='Not supported quant_dtype'):
+        U.convert_dtype(w, 'int2')
+    with pytest.raises(RuntimeError, match='scale.shape should be equal to 1 or cout'):
+        U.check_scale_offset_shape(w, torch.ones(3, 1))
+    with pytest.raises(BackendError):
+        U.quant_weight(w, 'int8', torch.ones(2, 1))

@@ -385,3 +385,26 @@ def test_emulated_minmax_without_workspace(emu_lib):
     rc = L.amct_minmax_noalloc(c_void_p(x.data_ptr()), c_int(2), c_int64(4), c_int64(k), c_int64(k), c_int(1), c_int(0),
                                c_void_p(mn.data_ptr()), c_void_p(mx.data_ptr()), c_void_p(0), c_void_p(0))
     assert rc == -6 and bool((mn == 7).all()) and bool((mx == 7).all())
+
+
+def test_emulated_quant_util_functions(on_cpu):
+    """amct_b200.utils.quant_util (the reference's utils/quant_util.py by name) against the oracle's restatement of the
+    same functions: integer codes in the reference's grouped shape, ragged tail included, and the fake quantization."""
+    from golden_io import bits_equal
+    from oracle import intq
+    from amct_b200.utils import quant_util as U
+    gen = torch.Generator().manual_seed(61)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        w = (torch.randn(9, 200, generator=gen) * 0.05).to(dtype)
+        for qt, sym, strategy, gs in (('int8', True, 'channel', None), ('int8', False, 'tensor', None),
+                                      ('int4', False, 'group', 64), ('int4', True, 'group', 32), ('int8', False, 'group', 128)):
+            scale, offset = intq.weight_scale_offset(w, qt, sym, strategy, gs)
+            codes = U.quant_weight(w, qt, scale, offset, gs)
+            want = intq.weight_codes(w, qt, scale, offset, gs)
+            assert codes.shape == want.shape and bits_equal(codes, want.to(codes.dtype))
+            assert codes.dtype == (torch.int8 if qt == 'int8' else torch.int32)
+            params = {'weights_cfg': {'quant_type': qt, 'group_size': gs}}
+            assert bits_equal(U.quant_dequant_weight(w, params, scale, offset), intq.fake_quant(w, qt, scale, offset, gs))
+        t = (torch.randn(3, 5, 16, generator=gen) * 60).to(dtype)
+        assert bits_equal(U.convert_dtype(t, 'int8'), t.float().round().clamp(-128, 127).to(torch.int8))
+        assert bits_equal(U.convert_dtype(t, 'int4'), t.float().round().clamp(-8, 7).to(torch.int32))
