@@ -24,6 +24,28 @@ def fake_quantize_scaled(weight, scale_awq, quant_config):
     return fq / scale_awq
 
 
+def calculate_scale_offset_by_granularity(weight, quant_config):
+    """(scale, offset) of a weight by the configured granularity, one read of the weight (awq.py:121-126)."""
+    from ..quantize_op.utils import weight_scale_offset
+    cfg = quant_config.get('weights_cfg')
+    return weight_scale_offset(weight, cfg.get('quant_type'), cfg.get('symmetric'), cfg.get('strategy'), cfg.get('group_size'))
+
+
+def process_weights_for_layers(layers, scale_awq, quant_config):
+    """Leaves ((W * s) fake-quantized) / s in every layer's weight (awq.py:30-49).  The reference's three passes per
+    layer -- do_quant, convert_precision, do_dequant (awq.py:129-170) -- are one kernel mode here and are not offered
+    one by one."""
+    for layer in layers:
+        layer.weight.data = fake_quantize_scaled(layer.weight.data, scale_awq, quant_config)
+
+
+def apply_scale(scale_awq, ori_module, input_data):
+    """W *= s and x /= s in place, as the reference does with tensor ops (awq.py:108-118)."""
+    scale = scale_awq.to(ori_module.weight.device)
+    ori_module.weight.data.mul_(scale)
+    input_data.div_(scale)
+
+
 @torch.no_grad()
 def search_scale(inputs, layer, quant_config):
     """Grid search over s = mean|x|^(i/grids) (normalised), minimising the 4th-power output error of

@@ -56,3 +56,43 @@ def weight_scale_offset(weight, wts_type, symmetric, strategy, group_size=None, 
                                       pre=pre, pre_op=pre_op if pre is not None else 'none')
     shape = (n, 1) if strategy == 'channel' else (n, -1, 1)
     return scale.reshape(shape), None if offset is None else offset.reshape(shape)
+
+
+# ---------------------------------------------------------------------------------------------
+# The smaller pieces of the scale rule under the reference's names (amct_pytorch/quantize_op/utils.py:26-72,
+# :139-176).  calculate_scale_offset above evaluates the whole rule in one kernel; these act on factor-sized tensors
+# (one value per channel or group) and exist for callers that use them one by one.
+# ---------------------------------------------------------------------------------------------
+def get_int_quant_scope(data_type, symmetric, abs_max_is_negative=False):
+    """Divisor of the scale rule: 2^b - 1 (asymmetric) or 2^(b-1) - 1, plus one when the largest magnitude is
+    negative (utils.py:158-176)."""
+    quant_bits = int(data_type.replace('int', ''))
+    if not symmetric:
+        return pow(2, quant_bits) - 1
+    return abs_max_is_negative + pow(2, quant_bits - 1) - 1
+
+
+def check_scale_offset(scale, offset):
+    """Raises the reference's errors for a non-finite or zero scale and a non-finite offset (utils.py:54-72)."""
+    if not (torch.all(torch.isfinite(scale)) and torch.all(torch.isfinite(1 / scale))):
+        raise RuntimeError("Param scale has invalid value inf, nan or zeros!")
+    if offset is not None and not torch.all(torch.isfinite(offset)):
+        raise RuntimeError("Param offset has invalid value inf or nan!")
+
+
+def process_scale(scale, offset, symmetric, numbit=8):
+    """A scale below FLT_EPSILON becomes 1 (and its offset -2^(b-1)); then check_scale_offset (utils.py:26-51)."""
+    tiny = scale < FLT_EPSILON
+    if not symmetric:
+        offset = torch.where(tiny, torch.tensor(-pow(2.0, numbit - 1), device=offset.device), offset)
+    scale = torch.where(tiny, torch.tensor(1.0, device=scale.device), scale)
+    check_scale_offset(scale, offset)
+    return scale, offset
+
+
+def convert_to_dst_shape(input_tensor, dst_shape):
+    """[N, G, g] (padded) -> [N, K]: flattens the groups and drops the padded tail (utils.py:139-155)."""
+    if input_tensor.shape == dst_shape:
+        return input_tensor
+    flat = input_tensor.reshape(input_tensor.shape[0], input_tensor.shape[1] * input_tensor.shape[2])
+    return flat[:dst_shape[0], :dst_shape[1]]

@@ -204,3 +204,24 @@ def test_quant_util_names_layout_and_errors():
         U.check_scale_offset_shape(w, torch.ones(3, 1))
     with pytest.raises(BackendError):
         U.quant_weight(w, 'int8', torch.ones(2, 1))
+
+
+def test_scale_rule_helpers_by_the_reference_names():
+    from amct_b200.quantize_op import utils as U
+    assert U.get_int_quant_scope('int8', True) == 127 and U.get_int_quant_scope('int8', True, True) == 128
+    assert U.get_int_quant_scope('int4', False) == 15
+    scale, offset = U.process_scale(torch.tensor([1e-9, 0.5]), torch.tensor([3.0, 4.0]), False, 8)
+    assert scale.tolist() == [1.0, 0.5] and offset.tolist() == [-128.0, 4.0]
+    scale, offset = U.process_scale(torch.tensor([1e-9, 0.5]), None, True)
+    assert scale.tolist() == [1.0, 0.5] and offset is None
+    with pytest.raises(RuntimeError, match='Param scale has invalid value inf, nan or zeros!'):
+        U.check_scale_offset(torch.tensor([float('inf')]), None)
+    with pytest.raises(RuntimeError, match='Param offset has invalid value inf or nan!'):
+        U.check_scale_offset(torch.tensor([1.0]), torch.tensor([float('nan')]))
+    assert U.convert_to_dst_shape(torch.zeros(2, 3, 4), (2, 10)).shape == (2, 10)
+    from amct_b200.algorithm import awq
+    for name in ('search_scale', 'process_weights_for_layers', 'calculate_scale_offset_by_granularity', 'apply_scale'):
+        assert callable(getattr(awq, name))
+    from amct_b200.utils.data_utils import convert_precision
+    with pytest.raises(RuntimeError, match='only support float32/float16/bfloat16'):
+        convert_precision(torch.zeros(2, 2, dtype=torch.float64), 'int8')

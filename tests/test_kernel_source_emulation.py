@@ -408,3 +408,26 @@ def test_emulated_quant_util_functions(on_cpu):
         t = (torch.randn(3, 5, 16, generator=gen) * 60).to(dtype)
         assert bits_equal(U.convert_dtype(t, 'int8'), t.float().round().clamp(-128, 127).to(torch.int8))
         assert bits_equal(U.convert_dtype(t, 'int4'), t.float().round().clamp(-8, 7).to(torch.int32))
+
+
+def test_emulated_awq_helpers(on_cpu):
+    """convert_precision, calculate_scale_offset_by_granularity and process_weights_for_layers (the reference's AWQ
+    helpers by name) against the oracle's statement of do_quant -> convert_precision -> do_dequant."""
+    from golden_io import bits_equal
+    from oracle import intq
+    from amct_b200.algorithm import awq
+    from amct_b200.utils.data_utils import convert_precision
+    gen = torch.Generator().manual_seed(62)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        t = (torch.randn(4, 3, 40, generator=gen) * 6).to(dtype)
+        assert bits_equal(convert_precision(t, 'int4'), t.float().round().clamp(-8, 7).to(dtype))
+        w = (torch.randn(6, 256, generator=gen) * 0.05).to(dtype)
+        s = (torch.rand(1, 256, generator=gen) + 0.5).to(dtype)
+        cfg = {'weights_cfg': {'quant_type': 'int4', 'symmetric': False, 'strategy': 'group', 'group_size': 64}}
+        scale, offset = awq.calculate_scale_offset_by_granularity(w * s, cfg)
+        want_scale, want_offset = intq.weight_scale_offset(w * s, 'int4', False, 'group', 64)
+        assert bits_equal(scale, want_scale) and bits_equal(offset, want_offset.to(offset.dtype))
+        layer = torch.nn.Linear(256, 6, bias=False).to(dtype)
+        layer.weight.data = w.clone()
+        awq.process_weights_for_layers([layer], s, cfg)
+        assert bits_equal(layer.weight.data, intq.fake_quant_awq(w * s, 'int4', want_scale, want_offset, 64) / s)
