@@ -116,10 +116,19 @@ class NpuQuantizationLinear(torch.nn.Module):
     def _gemm(self, q, pertoken, out=None):
         k = q.shape[-1]
         wq_nk = self.quantized_weight.t()
+        deq = self.deq_scale
+        if deq.numel() != wq_nk.shape[0]:
+            # one scale for the whole weight (strategy 'tensor'): the buffer keeps the reference's one element, the
+            # GEMM epilogue takes one value per output channel
+            cached = getattr(self, '_deq_per_channel', None)
+            if cached is None or cached.device != deq.device or float(cached[0]) != float(deq.reshape(-1)[0]):
+                cached = deq.reshape(-1)[:1].to(torch.float32).expand(wq_nk.shape[0]).contiguous()
+                self._deq_per_channel = cached
+            deq = cached
         if self.fused_act == 'swiglu':
-            res = ops.gemm_w8a8_swiglu(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out=out)
+            res = ops.gemm_w8a8_swiglu(q.reshape(-1, k), wq_nk, deq, pertoken, self.bias, out=out)
             return res.reshape(*q.shape[:-1], -1)
-        res = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, self.deq_scale, pertoken, self.bias, out_dtype=self.output_dtype, out=out)
+        res = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, deq, pertoken, self.bias, out_dtype=self.output_dtype, out=out)
         return res.reshape(*q.shape[:-1], -1)
 
     @torch.no_grad()

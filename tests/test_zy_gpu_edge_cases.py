@@ -41,3 +41,33 @@ def test_experimental_rule_with_a_scale_that_underflows():
     got_q, got_s = ops().quant_dynamic_per_token(x.cuda(), rule='experimental')
     assert bool((want_s == 0).any())
     assert bits_equal(got_s, want_s) and bits_equal(got_q, want_q)
+
+
+@pytest.mark.parametrize('dynamic', [True, False])
+def test_w8a8_linear_with_one_scale_for_the_whole_weight(dynamic):
+    """weights.strategy = 'tensor' (the reference's test_int8_int8_tensor_sym_minmax_success configuration): the
+    deq_scale buffer keeps one element as in the reference; the GEMM gets it per output channel."""
+    import amct_b200 as amct
+    from oracle import npu_ops
+    torch.manual_seed(5)
+    net = torch.nn.Sequential(torch.nn.Linear(256, 192)).to(torch.bfloat16).cuda()
+    w, b = net[0].weight.data.cpu().clone(), net[0].bias.data.cpu().clone()
+    inputs = {'type': 'int8', 'symmetric': True, 'strategy': 'token', 'dynamic': True} if dynamic else \
+        {'type': 'int8', 'symmetric': True, 'strategy': 'tensor'}
+    amct.quantize(net, {'batch_num': 1, 'quant_cfg': {'weights': {'type': 'int8', 'symmetric': True, 'strategy': 'tensor'},
+                                                       'inputs': inputs}, 'algorithm': {'minmax'}})
+    x = (torch.randn(64, 256) * 2).to(torch.bfloat16)
+    net(x.cuda())                                          # calibration batch
+    amct.convert(net)
+    assert net[0].deq_scale.numel() == 1
+    got = net(x.cuda()).cpu()
+    sw, _ = intq.weight_scale_offset(w, 'int8', True, 'tensor')
+    wq = intq.w8a8_weight_codes(w, sw.reshape(-1))
+    if dynamic:
+        q, s = intq.dynamic_per_token(x)
+        want = npu_ops.npu_quant_matmul(q, wq.t(), sw.reshape(-1).expand(192), s, b, torch.bfloat16)
+        assert bits_equal(got, want)
+    else:
+        # static per-tensor activations: codes from the calibrated scale; compare against the float Linear loosely
+        ref = torch.nn.functional.linear(x.float(), w.float(), b.float())
+        assert float((got.float() - ref).abs().max()) < 0.05 * float(ref.abs().max())
