@@ -4,9 +4,18 @@ Where a checkout of the reference is available -- ``$AMCT_REFERENCE``, or a dire
 repository -- its ``tests/amct_pytorch/test_config.py`` (config schema, presets, every error message of the parser)
 and ``test_customized_algo.py`` (algorithm registry, custom quantize / deploy modules through ``quantize`` /
 ``convert``) are imported unchanged with ``amct_pytorch`` aliased to ``amct_b200`` and must pass.  Nothing is copied:
-without the checkout the test is skipped.  The reference's remaining test files drive calibration and deploy forwards
-on CPU tensors through a mocked ``torch_npu``; this package has no CPU path for those, so they are not run here (the
-GPU parity tests cover that ground against golden vectors generated from the reference).
+without the checkout the tests are skipped.
+
+The reference's remaining test files (``test_minmax``, ``test_smoothquant``, ``test_awq``, ``test_gptq``,
+``test_quantize``) drive calibration, ``convert`` and deploy forwards on CPU tensors through a mocked ``torch_npu``.
+This package has no CPU path, so the second test gives it one for the duration of the run, out of test
+infrastructure only: the quantization kernels' own source in the CPU emulation (``tests/emu``) and the oracle's
+integer / 16-bit matmul in place of the tensor-core GEMMs.  Calibration observers, scale rules, weight codes, the
+AWQ search and the GPTQ loop then run on the real kernel code, and the reference's assertions (module classes after
+``quantize`` and ``convert``, buffer names, dtypes and shapes, error messages) must hold.  Two of these 47 tests
+cannot pass: ``test_int4_awq_quant_success`` and ``test_int4_gptq_success`` expect the INT4 ``quantized_weight``
+buffer as int32, which is what the reference's mock of ``npu_convert_weight_to_int4pack`` leaves; this package stores
+packed uint8 nibbles along K for the tensor-core operand.
 """
 import importlib
 import os
@@ -45,3 +54,63 @@ def test_reference_config_and_registry_tests_pass_unchanged(tmp_path):
     assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
     ran = int(done.stdout.split('RAN')[1].split()[0])
     assert ran >= 29
+
+
+EMULATED_RUNNER = r'''
+import ctypes, importlib, pkgutil, sys, unittest
+sys.path.insert(0, {root!r})
+import torch
+import amct_b200
+sys.modules['amct_pytorch'] = amct_b200
+for m in pkgutil.walk_packages(amct_b200.__path__, 'amct_b200.'):
+    if any(part in m.name for part in ('.csrc', '.workloads', '.experimental')):
+        continue
+    sys.modules['amct_pytorch' + m.name[len('amct_b200'):]] = importlib.import_module(m.name)
+from amct_b200.backend import lib, ops
+from oracle import npu_ops
+emu = ctypes.CDLL({library!r})
+for name in ('amct_mx_tiled_scale_bytes', 'amct_minmax_workspace_bytes', 'amct_minmax_noalloc_max_k'):
+    getattr(emu, name).restype = ctypes.c_int64
+emu.amct_minmax_workspace_bytes.argtypes = [ctypes.c_int64]
+lib.load = lambda: emu
+ops._need_cuda = lambda *tensors: None
+ops._stream = lambda: ctypes.c_void_p(0)
+torch.Tensor.is_cuda = property(lambda self: True)
+
+
+def int8_gemm(q, w_nk, deq_scale=None, pertoken_scale=None, bias=None, out_dtype=torch.bfloat16, out=None, status=None):
+    assert deq_scale.numel() == w_nk.shape[0]
+    return npu_ops.npu_quant_matmul(q, w_nk.t(), deq_scale, pertoken_scale, bias, out_dtype)
+
+
+def float_gemm(a, b_nk, bias=None, out_dtype=None, out=None, status=None):
+    y = a.float() @ b_nk.float().t()
+    return (y if bias is None else y + bias.float()).to(out_dtype or a.dtype)
+
+
+ops.gemm_w8a8, ops.gemm_f16 = int8_gemm, float_gemm
+ops.gemm_w4a16 = lambda *args, **kwargs: None          # "not a shape for the fused kernel": dequantize, then gemm_f16
+sys.path.insert(0, {tests!r})
+suite = unittest.defaultTestLoader.loadTestsFromNames({names!r})
+result = unittest.TextTestRunner(verbosity=0).run(suite)
+bad = sorted(str(t).split()[0] for t, _ in result.failures + result.errors)
+print('RAN', result.testsRun, 'BAD', ','.join(bad))
+'''
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason='no checkout of the reference at hand')
+def test_reference_algorithm_tests_on_emulated_kernels(tmp_path):
+    import test_kernel_source_emulation as emulation
+    csrc = os.path.join(ROOT, 'amct_b200', 'csrc')
+    library = str(tmp_path / 'libamct_emu.so')
+    emulation.build(library, [os.path.join(csrc, f) for f in emulation.EMULATED] +
+                    [os.path.join(ROOT, 'tests', 'emu', 'no_streaming_kernel.cpp')])
+    names = ['test_minmax', 'test_smoothquant', 'test_awq', 'test_gptq', 'test_quantize']
+    code = EMULATED_RUNNER.format(root=ROOT, tests=REF_TESTS, names=names, library=library)
+    done = subprocess.run([sys.executable, '-c', code], cwd=str(tmp_path), capture_output=True, text=True, timeout=1200)
+    line = [ln for ln in done.stdout.splitlines() if ln.startswith('RAN')]
+    assert line, done.stdout[-2000:] + done.stderr[-3000:]
+    ran = int(line[-1].split()[1])
+    bad = [b for b in line[-1].split('BAD')[1].strip().split(',') if b]
+    assert ran >= 47
+    assert bad == ['test_int4_awq_quant_success', 'test_int4_gptq_success'], done.stderr[-3000:]
