@@ -18,6 +18,8 @@
 
 #include <atomic>
 #include <cmath>
+#include <condition_variable>
+#include <mutex>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -75,6 +77,52 @@ inline ThreadState& tls() {
 
 inline unsigned as_dim(const dim3& d, int axis) { return axis == 0 ? d.x : axis == 1 ? d.y : d.z; }
 
+// Host threads that live as long as the process and serve every launch (creating a few hundred threads per launch is
+// what small launches would otherwise spend their time on).  Leaked on purpose: the workers are detached.
+class Pool {
+ public:
+  void run(int n, const std::function<void(int)>& job) {
+    std::unique_lock<std::mutex> lock(m_);
+    while ((int)workers_ < n) {
+      const int id = workers_++;
+      std::thread([this, id] { loop(id); }).detach();
+    }
+    job_ = &job;
+    active_ = n;
+    remaining_ = n;
+    ++generation_;
+    start_.notify_all();
+    done_.wait(lock, [&] { return remaining_ == 0; });
+  }
+
+ private:
+  void loop(int id) {
+    uint64_t seen = 0;
+    std::unique_lock<std::mutex> lock(m_);
+    for (;;) {
+      start_.wait(lock, [&] { return generation_ != seen; });
+      seen = generation_;
+      if (id < active_) {
+        const std::function<void(int)>* job = job_;
+        lock.unlock();
+        (*job)(id);
+        lock.lock();
+        if (--remaining_ == 0) done_.notify_one();
+      }
+    }
+  }
+  std::mutex m_;
+  std::condition_variable start_, done_;
+  const std::function<void(int)>* job_ = nullptr;
+  int workers_ = 0, active_ = 0, remaining_ = 0;
+  uint64_t generation_ = 0;
+};
+
+inline Pool& pool() {
+  static Pool* p = new Pool;
+  return *p;
+}
+
 // runs `body` once per (block, thread); `threads` is one-dimensional like every launch of the emulated files
 inline void launch(dim3 grid, int threads, const std::function<void()>& body) {
   static BlockState state;                       // launches are serial
@@ -84,24 +132,20 @@ inline void launch(dim3 grid, int threads, const std::function<void()>& body) {
     const int in_warp = threads - w * 32;
     state.warp[w].reset(in_warp >= 32 ? 32 : (in_warp > 0 ? in_warp : 1));
   }
-  std::vector<std::thread> pool;
-  for (int t = 0; t < threads; ++t) {
-    pool.emplace_back([&, t] {
-      ThreadState& s = tls();
-      s.block = &state;
-      s.tid = uint3{(unsigned)t, 0, 0};
-      s.bdim = dim3((unsigned)threads, 1, 1);
-      s.gdim = grid;
-      for (unsigned by = 0; by < grid.y; ++by) {
-        for (unsigned bx = 0; bx < grid.x; ++bx) {
-          s.bid = uint3{bx, by, 0};
-          body();
-          state.step.wait();                     // next block only when every thread has left this one
-        }
+  pool().run(threads, [&](int t) {
+    ThreadState& s = tls();
+    s.block = &state;
+    s.tid = uint3{(unsigned)t, 0, 0};
+    s.bdim = dim3((unsigned)threads, 1, 1);
+    s.gdim = grid;
+    for (unsigned by = 0; by < grid.y; ++by) {
+      for (unsigned bx = 0; bx < grid.x; ++bx) {
+        s.bid = uint3{bx, by, 0};
+        body();
+        state.step.wait();                       // next block only when every thread has left this one
       }
-    });
-  }
-  for (auto& th : pool) th.join();
+    }
+  });
 }
 
 // dynamic shared memory of the block that is running

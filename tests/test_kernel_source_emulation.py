@@ -57,11 +57,23 @@ def build(out, sources):
     return library
 
 
+_FULL_LIBRARY = {}
+
+
+def full_library():
+    """(path, handle) of the library with all emulated files, built once per test session; the streaming kernel's entry
+    declines every shape."""
+    if not _FULL_LIBRARY:
+        import tempfile
+        out = os.path.join(tempfile.mkdtemp(prefix='amct_emu_'), 'libamct_emu.so')
+        handle = build(out, [os.path.join(CSRC, f) for f in EMULATED] + [os.path.join(EMU, 'no_streaming_kernel.cpp')])
+        _FULL_LIBRARY.update(path=out, handle=handle)
+    return _FULL_LIBRARY['path'], _FULL_LIBRARY['handle']
+
+
 @pytest.fixture(scope='module')
-def emu_lib(tmp_path_factory):
-    """All emulated files in one library; the streaming kernel's entry declines every shape."""
-    out = str(tmp_path_factory.mktemp('emu') / 'libamct_emu.so')
-    return build(out, [os.path.join(CSRC, f) for f in EMULATED] + [os.path.join(EMU, 'no_streaming_kernel.cpp')])
+def emu_lib():
+    return full_library()[1]
 
 
 @pytest.fixture(scope='module')
