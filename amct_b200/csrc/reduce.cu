@@ -21,6 +21,28 @@ namespace amct {
 constexpr int kMaxRowChunks = 64;
 constexpr int kTensorBlocks = 1184;          // 148 SMs x 8
 
+// torch.amax / amin / maximum / minimum return NaN when an operand is NaN, fmaxf / fminf return the other
+// operand.  The inner loops use the fast instructions and remember that a NaN went by; everything that
+// combines partial results uses these, so a NaN reaches the output and the scale rule refuses it as the
+// reference does.
+__device__ __forceinline__ float nan_max(float a, float b) { return (a != a || b != b) ? NAN : fmaxf(a, b); }
+__device__ __forceinline__ float nan_min(float a, float b) { return (a != a || b != b) ? NAN : fminf(a, b); }
+// The running merge of the observers is torch.where(batch > running, batch, running)
+// (amct_pytorch/quantize_op/minmax_module.py:108-109, smooth_quant_module.py:90-91): a NaN batch value loses the
+// comparison and is dropped, a NaN running value stays.
+__device__ __forceinline__ float merge_max(float batch, float running) { return batch > running ? batch : running; }
+__device__ __forceinline__ float merge_min(float batch, float running) { return batch < running ? batch : running; }
+__device__ __forceinline__ float warp_nan_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = nan_max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_nan_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = nan_min(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) minmax_tensor_kernel(const T* x, int64_t rows, int64_t k, int64_t ld,
                                                             float* part, int* status) {
@@ -45,7 +67,8 @@ __global__ void __launch_bounds__(256) minmax_tensor_kernel(const T* x, int64_t 
     }
   }
   __shared__ float s[64];
-  mn = warp_min(mn); mx = warp_max(mx);
+  if (nan) { mn = NAN; mx = NAN; }
+  mn = warp_nan_min(mn); mx = warp_nan_max(mx);
   int w = threadIdx.x >> 5;
   if ((threadIdx.x & 31) == 0) { s[w] = mn; s[32 + w] = mx; }
   if (nan && status) atomicOr(status, 1);
@@ -54,7 +77,7 @@ __global__ void __launch_bounds__(256) minmax_tensor_kernel(const T* x, int64_t 
     int nw = blockDim.x >> 5;
     mn = threadIdx.x < nw ? s[threadIdx.x] : INFINITY;
     mx = threadIdx.x < nw ? s[32 + threadIdx.x] : -INFINITY;
-    mn = warp_min(mn); mx = warp_max(mx);
+    mn = warp_nan_min(mn); mx = warp_nan_max(mx);
     if (threadIdx.x == 0) { part[blockIdx.x] = mn; part[gridDim.x + blockIdx.x] = mx; }
   }
 }
@@ -63,17 +86,17 @@ template <typename T>
 __global__ void __launch_bounds__(256) minmax_tensor_final_kernel(const float* part, int nblocks, int merge,
                                                                   T* out_min, T* out_max) {
   float mn = INFINITY, mx = -INFINITY;
-  for (int i = threadIdx.x; i < nblocks; i += blockDim.x) { mn = fminf(mn, part[i]); mx = fmaxf(mx, part[nblocks + i]); }
+  for (int i = threadIdx.x; i < nblocks; i += blockDim.x) { mn = nan_min(mn, part[i]); mx = nan_max(mx, part[nblocks + i]); }
   __shared__ float s[64];
-  mn = warp_min(mn); mx = warp_max(mx);
+  mn = warp_nan_min(mn); mx = warp_nan_max(mx);
   int w = threadIdx.x >> 5;
   if ((threadIdx.x & 31) == 0) { s[w] = mn; s[32 + w] = mx; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) { mn = fminf(mn, s[i]); mx = fmaxf(mx, s[32 + i]); }
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) { mn = nan_min(mn, s[i]); mx = nan_max(mx, s[32 + i]); }
     if (merge) {
-      mn = fminf(mn, ElemTraits<T>::to_f(*out_min));
-      mx = fmaxf(mx, ElemTraits<T>::to_f(*out_max));
+      mn = merge_min(mn, ElemTraits<T>::to_f(*out_min));
+      mx = merge_max(mx, ElemTraits<T>::to_f(*out_max));
     }
     *out_min = ElemTraits<T>::from_f(mn);       // exact: the extremum is one of the inputs
     *out_max = ElemTraits<T>::from_f(mx);
@@ -141,6 +164,7 @@ __global__ void __launch_bounds__(128) minmax_column_kernel(const T* x, int64_t 
       if (r0 >= r1) { mn[e] = INFINITY; mx[e] = -INFINITY; }               // empty chunk
     }
   } else {
+    unsigned nan_cols = 0;                                                   // bit e: column c0 + e has seen a NaN
 #pragma unroll
     for (int e = 0; e < E; ++e) { mn[e] = INFINITY; mx[e] = -INFINITY; }
     int64_t r = r0;
@@ -154,7 +178,7 @@ __global__ void __launch_bounds__(128) minmax_column_kernel(const T* x, int64_t 
 #pragma unroll
           for (int e = 0; e < E; ++e) {
             const float f = ElemTraits<T>::to_f(raw[u].v[e]);
-            mn[e] = fminf(mn[e], f); mx[e] = fmaxf(mx[e], f); nan |= (f != f);
+            mn[e] = fminf(mn[e], f); mx[e] = fmaxf(mx[e], f); nan_cols |= (unsigned)(f != f) << e;
           }
         }
       }
@@ -165,12 +189,17 @@ __global__ void __launch_bounds__(128) minmax_column_kernel(const T* x, int64_t 
 #pragma unroll
         for (int e = 0; e < E; ++e) {
           const float f = ElemTraits<T>::to_f(raw.v[e]);
-          mn[e] = fminf(mn[e], f); mx[e] = fmaxf(mx[e], f); nan |= (f != f);
+          mn[e] = fminf(mn[e], f); mx[e] = fmaxf(mx[e], f); nan_cols |= (unsigned)(f != f) << e;
         }
       } else {
         const float f = ElemTraits<T>::to_f(x[r * ld + c0]);
-        mn[0] = fminf(mn[0], f); mx[0] = fmaxf(mx[0], f); nan |= (f != f);
+        mn[0] = fminf(mn[0], f); mx[0] = fmaxf(mx[0], f); nan_cols |= (unsigned)(f != f);
       }
+    }
+    nan = nan_cols != 0;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      if ((nan_cols >> e) & 1u) { mn[e] = NAN; mx[e] = NAN; }
     }
   }
   if (nan && status) atomicOr(status, 1);
@@ -186,12 +215,12 @@ __global__ void minmax_column_final_kernel(const float* part, int chunks, int64_
   if (c >= k) return;
   float mn = INFINITY, mx = -INFINITY;
   for (int i = 0; i < chunks; ++i) {
-    mn = fminf(mn, part[(int64_t)i * k + c]);
-    mx = fmaxf(mx, part[(int64_t)(chunks + i) * k + c]);
+    mn = nan_min(mn, part[(int64_t)i * k + c]);
+    mx = nan_max(mx, part[(int64_t)(chunks + i) * k + c]);
   }
   if (merge) {
-    mn = fminf(mn, ElemTraits<T>::to_f(out_min[c]));
-    mx = fmaxf(mx, ElemTraits<T>::to_f(out_max[c]));
+    mn = merge_min(mn, ElemTraits<T>::to_f(out_min[c]));
+    mx = merge_max(mx, ElemTraits<T>::to_f(out_max[c]));
   }
   out_min[c] = ElemTraits<T>::from_f(mn);
   out_max[c] = ElemTraits<T>::from_f(mx);
@@ -255,16 +284,17 @@ __global__ void __launch_bounds__(128) minmax_rows_kernel(const T* x, int64_t k,
     }
   }
   if (nan && status) atomicOr(status, 1);
+  if (nan) { mn = NAN; mx = NAN; }
   __shared__ float s[8];
-  mn = warp_min(mn); mx = warp_max(mx);
+  mn = warp_nan_min(mn); mx = warp_nan_max(mx);
   const int w = threadIdx.x >> 5;
   if ((threadIdx.x & 31) == 0) { s[w] = mn; s[4 + w] = mx; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int i = 1; i < 4; ++i) { mn = fminf(mn, s[i]); mx = fmaxf(mx, s[4 + i]); }
+    for (int i = 1; i < 4; ++i) { mn = nan_min(mn, s[i]); mx = nan_max(mx, s[4 + i]); }
     if (merge) {
-      mn = fminf(mn, ElemTraits<T>::to_f(out_min[blockIdx.x]));
-      mx = fmaxf(mx, ElemTraits<T>::to_f(out_max[blockIdx.x]));
+      mn = merge_min(mn, ElemTraits<T>::to_f(out_min[blockIdx.x]));
+      mx = merge_max(mx, ElemTraits<T>::to_f(out_max[blockIdx.x]));
     }
     out_min[blockIdx.x] = ElemTraits<T>::from_f(mn);
     out_max[blockIdx.x] = ElemTraits<T>::from_f(mx);

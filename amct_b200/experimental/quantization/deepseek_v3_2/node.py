@@ -48,6 +48,7 @@ class ActivationQuantizer(torch.nn.Module):
         self.is_deploy = False
         self.is_per_tensor = per_tensor
         self.cnt = 0
+        self._deployed = None           # (key, kernel arguments) read from the deployed scale / zero
 
     def forward(self, x):
         if self.bits == 16:
@@ -61,13 +62,26 @@ class ActivationQuantizer(torch.nn.Module):
             return x
         return self.fake_quant(x)
 
+    def _bounds_device(self):
+        """The device the per-tensor arithmetic runs on: where the observed bounds live.  Observe mode replaces a
+        bound by a 0-dim tensor on the activation's device, so a module that was built on the host and fed device
+        activations holds bounds (and clip parameters) on different devices; a bound that was never exceeded is
+        still the constructor's host tensor."""
+        for t in (self.maxval, self.minval):
+            if t.device.type != 'cpu':
+                return t.device
+        return self.maxval.device
+
     def get_scale_zero_pertensor(self):
-        """(scale, zero) from the observed bounds (node.py:161-179)."""
-        q_max = self.q_max.to(self.maxval.device)
-        hi, lo = self.maxval.clone(), self.minval.clone()
+        """(scale, zero) from the observed bounds (node.py:161-179), every operand moved to one device first (the
+        dynamic rule does the same with its clip parameters, node.py:192-196); dtypes, and with them torch's
+        promotion, are left as they are."""
+        dev = self._bounds_device()
+        q_max = self.q_max.to(dev)
+        hi, lo = self.maxval.to(dev).clone(), self.minval.to(dev).clone()
         if self.lac:
-            hi = hi * self.sigmoid(self.clip_factor_a_max)
-            lo = lo * self.sigmoid(self.clip_factor_a_min)
+            hi = hi * self.sigmoid(self.clip_factor_a_max.to(dev))
+            lo = lo * self.sigmoid(self.clip_factor_a_min.to(dev))
         elif self._clip_ratio is not None:
             hi, lo = hi * self._clip_ratio, lo * self._clip_ratio
         if self.sym:
@@ -79,10 +93,12 @@ class ActivationQuantizer(torch.nn.Module):
     def deploy(self):
         scale, zero = self.get_scale_zero_pertensor()
         self.scale.data, self.zero.data = scale, zero
+        self._deployed = None
 
     def load_deploy(self, scale, zero):
         self.scale.data, self.zero.data = scale, zero
         self.is_deploy = True
+        self._deployed = None
 
     def _sigmoids(self):
         if not self.lac:
@@ -93,17 +109,38 @@ class ActivationQuantizer(torch.nn.Module):
             return (float(torch.sigmoid(self.clip_factor_a_max.float())),
                     float(torch.sigmoid(self.clip_factor_a_min.float())))
 
+    @staticmethod
+    def promoted_dtype(x_dtype, scale):
+        """dtype of ``x / scale`` for an activation of ``x_dtype`` (one or more dimensions) under torch's promotion
+        rules, evaluated without touching a device."""
+        probe = torch.empty(1, dtype=x_dtype, device='meta')
+        return torch.result_type(probe, torch.empty(scale.shape, dtype=scale.dtype, device='meta'))
+
+    def _static_arguments(self, x_dtype):
+        """Kernel arguments of the per-tensor modes.  Scale and zero point reach the kernel as host floats, and
+        reading them waits for the device: once deployed (``load_deploy``) the pair is read once and kept until the
+        buffers are replaced or written in place (``load_state_dict``); before that it is derived from the observed
+        bounds on every call, as the reference does."""
+        key = (x_dtype,) + tuple((t.data_ptr(), t._version, t.device) for t in (self.scale, self.zero))
+        if self.is_deploy and self._deployed is not None and self._deployed[0] == key:
+            return self._deployed[1]
+        with torch.no_grad():
+            scale, zero = (self.scale.data, self.zero.data) if self.is_deploy else self.get_scale_zero_pertensor()
+        if scale.numel() != 1:
+            raise NotImplementedError('per-tensor quantization takes a one-element scale')
+        promoted = self.promoted_dtype(x_dtype, scale)
+        if promoted not in (x_dtype, torch.float32):
+            raise NotImplementedError(f'arithmetic in {promoted} is not built')
+        args = {'static': (float(scale), float(zero)),
+                'static_fp32': promoted == torch.float32 and x_dtype != torch.float32}
+        if self.is_deploy:
+            self._deployed = (key, args)
+        return args
+
     def kernel_arguments(self, x_dtype):
         """Keyword arguments of ``ops.dsa_rotate_fakequant`` for an activation of ``x_dtype``."""
         if self.is_per_tensor:
-            with torch.no_grad():
-                scale, zero = (self.scale.data, self.zero.data) if self.is_deploy else self.get_scale_zero_pertensor()
-            if scale.numel() != 1:
-                raise NotImplementedError('per-tensor quantization takes a one-element scale')
-            promoted = torch.result_type(torch.empty(1, dtype=x_dtype), scale)
-            if promoted not in (x_dtype, torch.float32):
-                raise NotImplementedError(f'arithmetic in {promoted} is not built')
-            return {'static': (float(scale), float(zero)), 'static_fp32': promoted == torch.float32 and x_dtype != torch.float32}
+            return self._static_arguments(x_dtype)
         if self.lac:
             sig_max, sig_min = self._sigmoids()
             return {'clip_max_sigmoid': sig_max, 'clip_min_sigmoid': sig_min}

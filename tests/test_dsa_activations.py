@@ -100,3 +100,37 @@ def test_module_mirror_names_and_refusals():
     from amct_b200.backend.lib import BackendError
     with pytest.raises(BackendError):                                          # no CPU fallback
         ActivationQuantizer(bits=8, sym=True)(x)
+
+
+@pytest.mark.parametrize('lac', [False, True])
+@pytest.mark.parametrize('sym', [True, False])
+def test_per_tensor_bounds_on_another_device_than_the_module(sym, lac):
+    """A module built on the host whose observed bounds were replaced by 0-dim tensors on the activation's device
+    (what observe mode leaves) must derive scale and zero on that device: a one-element host parameter cannot be
+    mixed with a 0-dim device tensor.  The meta device stands in for the accelerator, so this runs without one; an
+    unexceeded bound stays the constructor's host tensor, which is the other half of the case."""
+    from amct_b200.experimental.quantization.deepseek_v3_2.node import ActivationQuantizer
+    q = ActivationQuantizer(bits=8, sym=sym, lac=lac, per_tensor=True)
+    q._buffers['maxval'] = torch.empty((), dtype=torch.float16, device='meta')   # `.data =` refuses a meta tensor
+    scale, zero = q.get_scale_zero_pertensor()                                  # minval still on the host
+    assert scale.device.type == 'meta' and zero.device.type == 'meta'
+    q._buffers['minval'] = torch.empty((), dtype=torch.float16, device='meta')
+    scale, zero = q.get_scale_zero_pertensor()
+    assert scale.device.type == 'meta' and scale.numel() == 1
+    assert scale.dtype == (torch.float32 if lac else torch.float16)
+    assert q.promoted_dtype(torch.float16, scale) == scale.dtype
+    assert q.promoted_dtype(torch.bfloat16, torch.ones(1)) == torch.float32      # a loaded fp32 buffer promotes
+    assert q.promoted_dtype(torch.bfloat16, torch.ones((), dtype=torch.float32)) == torch.bfloat16
+
+
+def test_deployed_scale_is_read_once_and_reread_when_replaced():
+    from amct_b200.experimental.quantization.deepseek_v3_2.node import ActivationQuantizer
+    q = ActivationQuantizer(bits=8, sym=False, per_tensor=True)
+    q.load_deploy(torch.tensor([0.5]), torch.tensor([3.0]))
+    first = q.kernel_arguments(torch.float16)
+    assert first['static'] == (0.5, 3.0) and q.kernel_arguments(torch.float16) is first
+    assert q.kernel_arguments(torch.bfloat16)['static'] == (0.5, 3.0)
+    q.load_deploy(torch.tensor([0.25]), torch.tensor([1.0]))
+    assert q.kernel_arguments(torch.float16)['static'] == (0.25, 1.0)
+    q.load_state_dict({**q.state_dict(), 'scale': torch.tensor([2.0])})          # an in-place write is seen too
+    assert q.kernel_arguments(torch.float16)['static'] == (2.0, 1.0)

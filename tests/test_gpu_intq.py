@@ -138,6 +138,52 @@ def test_minmax_observers(dtype, rows, k):
     assert bits_equal(mn, (x / f).amin(1)) and bits_equal(mx, (x / f).amax(1))
 
 
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('rows,k', [(9, 67), (300, 256), (2049, 136)])
+def test_minmax_observers_propagate_nan(dtype, rows, k):
+    """torch.amax / amin / max / min return NaN where an operand is NaN (so the scale rule then raises); the running
+    merge is torch.where(batch > running, batch, running): a NaN batch value is dropped, a NaN running value stays."""
+    g = torch.Generator().manual_seed(7 * rows + k)
+    x = torch.randn(rows, k, generator=g).to(dtype)
+    x[rows // 2, k // 3] = float('nan')
+    x[rows - 1, k - 1] = float('nan')
+    xc = x.cuda()
+
+    def same(a, b):                                     # NaN payloads are not part of the contract
+        a, b = a.cpu().float().reshape(-1), b.float().reshape(-1)
+        return bool((torch.isnan(a) == torch.isnan(b)).all()) and bits_equal(torch.nan_to_num(a), torch.nan_to_num(b))
+
+    mn, mx = ops().minmax(xc, 'tensor')
+    assert torch.isnan(mn).all() and torch.isnan(mx).all()
+    mn, mx = ops().minmax(xc, 'column')
+    assert same(mn, x.amin(0)) and same(mx, x.amax(0)) and int(torch.isnan(mn).sum()) == 2
+    mn, mx = ops().minmax_rows(xc)
+    assert same(mn, x.amin(1)) and same(mx, x.amax(1)) and int(torch.isnan(mx).sum()) == 2
+    # an unaligned view takes the scalar kernels
+    if k > 8:
+        v = x[:, 1:k - 2]
+        mn, mx = ops().minmax(xc[:, 1:k - 2], 'column')
+        assert same(mn, v.amin(0)) and same(mx, v.amax(0))
+        mn, mx = ops().minmax(xc[:, 1:k - 2], 'tensor')
+        assert torch.isnan(mn).all() and torch.isnan(mx).all()
+    with pytest.raises(RuntimeError, match='invalid value inf, nan or zeros'):
+        lo, hi = ops().minmax(xc, 'tensor')
+        ops().scale_offset(hi, lo, True, 'int8')
+    # merge: clean running values + NaN batch -> the NaN is dropped; NaN running values stay
+    clean = torch.randn(rows, k, generator=g).to(dtype)
+    run = ops().minmax(clean.cuda(), 'column')
+    run = (run[0].view(-1), run[1].view(-1))
+    ops().minmax(xc, 'column', running=run)
+    bmax, bmin = x.amax(0), x.amin(0)
+    want_max = torch.where(bmax > clean.amax(0), bmax, clean.amax(0))
+    want_min = torch.where(bmin < clean.amin(0), bmin, clean.amin(0))
+    assert same(run[0], want_min) and same(run[1], want_max)
+    run = ops().minmax(xc, 'column')
+    run = (run[0].view(-1), run[1].view(-1))
+    ops().minmax(clean.cuda(), 'column', running=run)
+    assert int(torch.isnan(run[0]).sum()) == 2 and int(torch.isnan(run[1]).sum()) == 2
+
+
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize('shape', [(5, 64), (2, 7, 72), (3, 33), (1, 4, 16, 40)])
 @pytest.mark.parametrize('per_token,offset,smooth', [(False, False, False), (False, True, True), (True, False, False),

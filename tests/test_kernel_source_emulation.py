@@ -249,7 +249,8 @@ def test_emulated_fake_quant_golden(on_cpu, dtype):
     import test_zy_gpu_dsa_activations as G
     for k in (128, 512, 200):
         G.test_fake_quant_golden(dtype, k)
-    G.test_clip_ratio_and_per_tensor_modules(dtype)
+    for on_device in (True, False):
+        G.test_clip_ratio_and_per_tensor_modules(dtype, on_device)
 
 
 def test_emulated_fake_quant_shapes(on_cpu):

@@ -148,23 +148,32 @@ def test_module_with_learned_clipping():
         q.clip_factor_a_max.data.fill_(CLIP_MAX)
         q.clip_factor_a_min.data.fill_(CLIP_MIN)
         assert bits_equal(q(x.unsqueeze(1)).squeeze(1), GOLD.get(f"fq.bf16.512.lac.{'sym' if sym else 'asym'}"))
+        assert bits_equal(q.cuda()(x.unsqueeze(1)).squeeze(1), GOLD.get(f"fq.bf16.512.lac.{'sym' if sym else 'asym'}"))
 
 
+@pytest.mark.parametrize('on_device', [True, False])
 @pytest.mark.parametrize('dtype', ['fp16', 'bf16', 'fp32'])
-def test_clip_ratio_and_per_tensor_modules(dtype):
+def test_clip_ratio_and_per_tensor_modules(dtype, on_device):
     """ActivationQuantizer with a clip_ratio, and per-tensor with observed bounds (with and without learned clipping:
-    fp32 and activation-dtype arithmetic), through the module, against the reference's outputs."""
+    fp32 and activation-dtype arithmetic), through the module, against the reference's outputs.  The module is
+    moved to the activations' device as a model would be, or left on the host (its bounds and clip parameters
+    then live on different devices)."""
     from amct_b200.experimental.quantization.deepseek_v3_2.node import ActivationQuantizer
+
+    def place(module):
+        return module.cuda() if on_device else module
+
     x = GOLD.get(f'ext.{dtype}.x').cuda()
     for sym in (True, False):
         tag = 'sym' if sym else 'asym'
-        q = ActivationQuantizer(bits=8, sym=sym, lac=False, groupsize=-1, clip_ratio=0.9, per_tensor=False)
+        q = place(ActivationQuantizer(bits=8, sym=sym, lac=False, groupsize=-1, clip_ratio=0.9, per_tensor=False))
         assert bits_equal(q(x), GOLD.get(f'ext.{dtype}.ratio.{tag}'))
         for lac in (False, True):
             q = ActivationQuantizer(bits=8, sym=sym, lac=lac, groupsize=-1, per_tensor=True)
             if lac:
                 q.clip_factor_a_max.data.fill_(CLIP_MAX)
                 q.clip_factor_a_min.data.fill_(CLIP_MIN)
+            q = place(q)
             q.is_observe = True
             q(x[:6])
             q(x[6:])
@@ -173,6 +182,7 @@ def test_clip_ratio_and_per_tensor_modules(dtype):
             scale, zero = q.get_scale_zero_pertensor()
             q.load_deploy(scale, zero)
             assert bits_equal(q(x), GOLD.get(f"ext.{dtype}.tensor.{tag}.{'lac' if lac else 'plain'}"))
+            assert bits_equal(q(x), GOLD.get(f"ext.{dtype}.tensor.{tag}.{'lac' if lac else 'plain'}"))   # kept pair
 
 
 def test_argument_errors():
