@@ -51,17 +51,32 @@ def _rows2d(x):
     return x2, x2.shape[0], k, ld
 
 
+_STATUS_WORDS = {}
+
+
 class Status:
-    """Device word the kernels OR error bits into; read back on demand."""
+    """Device word the kernels OR error bits into, read back by ``raise_if_set``.  One word per (device, stream) is
+    allocated once and shared by all calls on that stream: it is zero between calls because every call that passes
+    it to a kernel reads it back afterwards, in stream order, and clears it if a bit was set."""
 
     def __init__(self, device):
-        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        device = torch.device(device)
+        index = device.index if device.index is not None else (torch.cuda.current_device() if device.type == 'cuda' else -1)
+        key = (device.type, index, _stream().value)
+        word = _STATUS_WORDS.get(key)
+        if word is None:
+            word = torch.zeros(1, dtype=torch.int32, device=device)
+            _STATUS_WORDS[key] = word
+        self.word = word
 
     def ptr(self):
         return _p(self.word)
 
     def raise_if_set(self):
-        if int(self.word.item()) & 1:
+        bits = int(self.word.item())
+        if bits:
+            self.word.zero_()
+        if bits & 1:
             raise RuntimeError(SCALE_ERROR)
 
 
@@ -167,10 +182,10 @@ def minmax(x, axis, running=None):
         merge = 1
     L = _l.load()
     ws = torch.empty(L.amct_minmax_workspace_bytes(c_int64(k)), dtype=torch.uint8, device=x.device)
-    st = Status(x.device)
+    # no status word: a NaN in the input shows in the result, and the scale rule refuses it there
     rc = L.amct_minmax(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld),
                        c_int(_l.AXIS_TENSOR if axis == 'tensor' else _l.AXIS_COLUMN), c_int(merge),
-                       _p(mn), _p(mx), _p(ws), st.ptr(), _stream())
+                       _p(mn), _p(mx), _p(ws), c_void_p(0), _stream())
     _l.check(rc, 'amct_minmax')
     COUNTERS['launches'] += 2
     if axis == 'column':
@@ -310,6 +325,44 @@ def gemm_w8a8(q, w_nk, deq_scale=None, pertoken_scale=None, bias=None, out_dtype
     return out
 
 
+def set_gemm_variant(variant):
+    """Pins the kernel that takes GEMMs with more than 128 rows: 'auto' (by the size of the weight), 'single' (one-CTA
+    kernel) or 'pair' (CTA-pair kernel).  Process-wide; for tests and comparisons."""
+    code = {'auto': 0, 'single': 1, 'pair': 2}[variant]
+    _l.check(_l.load().amct_gemm_set_variant(c_int(code)), 'amct_gemm_set_variant')
+
+
+def _pointer_array(pointers):
+    return (c_void_p * len(pointers))(*[int(p_) for p_ in pointers])
+
+
+def gemm_w8a8_scatter(q, w_nk, deq_scale, pertoken_scale, out_ptrs, slot, rows_per_rank, ld_out, out_dtype=torch.bfloat16,
+                      status=None):
+    """The W8A8 GEMM of a K-sharded Linear whose result is this rank's partial sum: output row r is written to row
+    (slot * rows_per_rank + r % rows_per_rank) of the staging buffer of rank r // rows_per_rank.  out_ptrs: device
+    addresses of every rank's staging buffer [world * rows_per_rank, ld_out] as mapped into this process."""
+    _need_cuda(q, w_nk, deq_scale, pertoken_scale)
+    assert q.dtype == torch.int8 and w_nk.dtype == torch.int8 and q.dim() == 2 and w_nk.dim() == 2
+    q, w_nk = _kmajor(q), _kmajor(w_nk)
+    m, k = q.shape
+    n = w_nk.shape[0]
+    assert w_nk.shape[1] == k
+    deq_scale = deq_scale.reshape(-1).to(torch.float32).contiguous()
+    assert deq_scale.numel() == n
+    if pertoken_scale is not None:
+        pertoken_scale = pertoken_scale.reshape(-1).to(torch.float32).contiguous()
+        assert pertoken_scale.numel() == m
+    prof = _prof_begin()
+    rc = _l.load().amct_gemm_w8a8_scatter(
+        _p(q), _p(w_nk), c_int64(m), c_int64(n), c_int64(k), c_int64(q.stride(0)), c_int64(w_nk.stride(0)),
+        _p(deq_scale), _p(pertoken_scale), _pointer_array(out_ptrs), c_int(len(out_ptrs)), c_int(slot),
+        c_int64(rows_per_rank), c_int(_OUT_KIND[out_dtype]), c_int64(ld_out),
+        _p(status) if status is not None else c_void_p(0), _stream())
+    _l.check(rc, 'amct_gemm_w8a8_scatter')
+    COUNTERS['launches'] += 1
+    _prof_end(prof, 2 * m * n * k)
+
+
 def gemm_f16(a, b_nk, bias=None, out_dtype=None, out=None, status=None):
     """a [M, K] x b_nk [N, K] in fp16 or bf16 -> [M, N], fp32 accumulation."""
     _need_cuda(a, b_nk, bias)
@@ -349,9 +402,8 @@ def minmax_rows(x2d, pre=None, pre_op='none', running=None):
         pre = pre.reshape(-1).to(x2.dtype).contiguous()
         assert pre.numel() == k
     pop = {'none': _l.PRE_NONE, 'mul': _l.PRE_MUL, 'div': _l.PRE_DIV}[pre_op]
-    st = Status(x2.device)
     rc = _l.load().amct_minmax_rows(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), _p(pre), c_int(pop),
-                                    c_int(merge), _p(mn), _p(mx), st.ptr(), _stream())
+                                    c_int(merge), _p(mn), _p(mx), c_void_p(0), _stream())
     _l.check(rc, 'amct_minmax_rows')
     COUNTERS['launches'] += 1
     return mn, mx
@@ -620,6 +672,36 @@ def addnorm_quant_per_token(x, gamma, eps, residual=None, want_norm=False, check
         st.raise_if_set()
     return (q.reshape(x.shape), scale, h.reshape(x.shape) if h is not None else None,
             n.reshape(x.shape) if n is not None else None)
+
+
+def addnorm_quant_per_token_tp(parts, gamma, eps, q_ptrs, scale_ptrs, row0, residual=None):
+    """The tensor-parallel form of addnorm_quant_per_token.  parts [n_parts, rows, K]: partial sums of this rank's rows
+    (n_parts = 1: the rows themselves); x = their fp32 sum in order, rounded once.  The codes / scale of row r are
+    written to row row0 + r of every rank's code buffer [*, K] / scale buffer (q_ptrs / scale_ptrs: device addresses
+    of all ranks' buffers as mapped into this process).  Returns h = x + residual (x itself without residual when
+    n_parts > 1, None when the input already was the residual stream)."""
+    _need_cuda(parts, gamma, residual)
+    if parts.dtype not in (torch.float16, torch.bfloat16):
+        raise _l.BackendError('addnorm_quant_per_token_tp: float16 / bfloat16 only')
+    if parts.dim() != 3 or not parts.is_contiguous():
+        raise ValueError('parts must be a contiguous [n_parts, rows, K] tensor')
+    n_parts, rows, k = parts.shape
+    r2 = None
+    if residual is not None:
+        if tuple(residual.shape) != (rows, k) or residual.dtype != parts.dtype or not residual.is_contiguous():
+            raise ValueError('residual must be a contiguous [rows, K] tensor of the same dtype')
+        r2 = residual
+    gamma = gamma.reshape(-1).to(parts.dtype).contiguous()
+    if gamma.numel() != k:
+        raise ValueError('gamma must have K elements')
+    h = torch.empty((rows, k), dtype=parts.dtype, device=parts.device) if residual is not None else None
+    rc = _l.load().amct_addnorm_quant_pertoken_tp(
+        _p(parts), c_int(n_parts), c_int64(rows * k), _p(r2), c_int(_dt(parts)), c_int64(rows), c_int64(k), c_int64(k),
+        c_int64(k), _p(gamma), ctypes.c_float(eps), _p(h), c_int64(k), _pointer_array(q_ptrs), _pointer_array(scale_ptrs),
+        c_int(len(q_ptrs)), c_int64(row0), c_int64(k), c_void_p(0), _stream())
+    _l.check(rc, 'amct_addnorm_quant_pertoken_tp')
+    COUNTERS['launches'] += 1
+    return h
 
 
 def rope_inplace(x, heads, head_dim, cos, sin):

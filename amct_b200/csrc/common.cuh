@@ -139,4 +139,18 @@ __device__ __forceinline__ float div_by_recip(float x, float s, float y) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// "Done once per device": kernel attributes such as the dynamic shared-memory limit belong to a device's context, so a
+// process that drives several GPUs has to set them on each.  first() returns true the first time it is called with a
+// given device current (a benign race between threads only repeats the idempotent call it guards).
+struct OncePerDevice {
+  bool done[64] = {};
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
+
 }  // namespace amct

@@ -17,6 +17,8 @@ namespace amct {
 
 constexpr int kBM = 128, kBKBytes = 128;
 constexpr int kABytes = kBM * kBKBytes;
+constexpr int kMaxScatterRanks = 16;
+constexpr int kEpiStageBytes = 32 * 128;       // per epilogue warp: 32 rows x 64 16-bit columns, for the scatter mode
 
 enum { KIND_I8 = 0, KIND_BF16 = 1, KIND_F16 = 2 };
 enum { BIAS_NONE = 0, BIAS_I32 = 1, BIAS_F32 = 2, BIAS_F16 = 3, BIAS_BF16 = 4 };
@@ -34,6 +36,13 @@ struct GemmParams {
   int64_t ld_out;              // elements
   int* status;
   int act;                     // 0 none, 1 SwiGLU over interleaved [128 gate | 128 up] column blocks
+  // Scatter mode of a row-parallel (K-sharded) Linear under tensor parallelism, scatter_world > 0: output
+  // row r belongs to rank r / scatter_rows and goes to row (scatter_slot * scatter_rows + r % scatter_rows) of
+  // scatter_out[that rank] (this process's mapping of that rank's buffer, ld_out elements per row); `out` is
+  // not used.  16-bit outputs, n a multiple of 64.
+  int scatter_world, scatter_slot;
+  int64_t scatter_rows;
+  void* scatter_out[kMaxScatterRanks];
 };
 
 // Rasterisation: GROUP m-tiles x all n-tiles per group, m fastest, so that the tiles in flight
@@ -174,6 +183,76 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, uint32_t t_ro
         }
       }
     }
+  }
+}
+
+// The same values as epilogue_rows' 16-bit store, written for links instead of local memory.  In epilogue_rows a
+// lane owns a row, so one store instruction touches 32 rows with 16 bytes each: fine for the local L2, wasteful as
+// 32 small packets on NVLink.  Here 64 columns at a time go through a swizzled 4 KB staging tile in shared memory
+// (`stage`, this warp's own) and leave as whole 128-byte row segments: 8 lanes per row, 4 rows per instruction.
+// Plain st.global to peer-mapped memory; no TMA store, no multicast.  warp_row0 = first of the warp's 32 rows.
+template <int kBN>
+__device__ __forceinline__ void epilogue_rows_scatter(const GemmParams& p, uint32_t t_row, int64_t warp_row0, int lane,
+                                                      int64_t n0, const float* sc, const float* sb, float pt,
+                                                      uint8_t* stage) {
+  static_assert(kBN % 64 == 0, "scatter epilogue works on 64-column chunks");
+#pragma unroll 1
+  for (int c0 = 0; c0 < kBN; c0 += 64) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t r[32];
+      tc05::tmem_ld_32x32(t_row + c0 + half * 32, r);
+      tc05::tmem_ld_wait();
+      uint32_t h[16];
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float y[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int c = c0 + half * 32 + j + t;
+          if (p.kind == KIND_I8) {
+            float v = __fmul_rn((float)(int)r[j + t], sc[c]);
+            if (p.pertoken) v = __fmul_rn(v, pt);
+            if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c]);
+            y[t] = v;
+          } else {
+            float v = __uint_as_float(r[j + t]);
+            if (p.bias_kind != BIAS_NONE) v = __fadd_rn(v, sb[c]);
+            y[t] = v;
+          }
+        }
+        if (p.out_kind == OUT_BF16) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(y[0], y[1]);
+          h[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+        } else {
+          __half2 v = __floats2half2_rn(y[0], y[1]);
+          h[j >> 1] = *reinterpret_cast<uint32_t*>(&v);
+        }
+      }
+      // lane = row: four 16-byte chunks of this half, chunk index XOR (row & 7) so that neither side conflicts
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int chunk = (half * 4 + i) ^ (lane & 7);
+        *reinterpret_cast<uint4*>(stage + lane * 128 + chunk * 16) = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+      }
+    }
+    __syncwarp();
+    const int chunk = lane & 7;
+    const int64_t col = n0 + c0 + chunk * 8;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r_in = it * 4 + (lane >> 3);
+      const uint4 v = *reinterpret_cast<const uint4*>(stage + r_in * 128 + ((chunk ^ (r_in & 7)) * 16));
+      const int64_t row = warp_row0 + r_in;
+      if (row < p.m && col < p.n) {
+        const int64_t owner = row / p.scatter_rows;
+        const int64_t local = row - owner * p.scatter_rows;
+        uint16_t* o = reinterpret_cast<uint16_t*>(p.scatter_out[owner]) +
+                      ((int64_t)p.scatter_slot * p.scatter_rows + local) * p.ld_out + col;
+        *reinterpret_cast<uint4*>(o) = v;
+      }
+    }
+    __syncwarp();
   }
 }
 

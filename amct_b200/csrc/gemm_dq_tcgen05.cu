@@ -412,11 +412,10 @@ static int map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, in
 template <int BN, int STAGES, int XSLOTS, int RSLOTS, int BITS>
 static int launch_dq(const CUtensorMap& mc, const CUtensorMap& mx, const DqParams& p, int grid, cudaStream_t st) {
   const size_t smem = sizeof(DqSmem<BN, STAGES, XSLOTS, RSLOTS>) + 1024;
-  static bool attr = false;
-  if (!attr) {
+  static OncePerDevice attr;
+  if (attr.first()) {
     if (cudaFuncSetAttribute(gemm_dq_tcgen05_kernel<BN, STAGES, XSLOTS, RSLOTS, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return AMCT_ERR_CUDA;
-    attr = true;
   }
   gemm_dq_tcgen05_kernel<BN, STAGES, XSLOTS, RSLOTS, BITS><<<grid, kDqThreads, smem, st>>>(mc, mx, p);
   AMCT_CHECK_LAUNCH();

@@ -321,10 +321,9 @@ extern "C" int amct_gemm_mx(const void* a, const void* sfa_tiled, const void* b,
   p.sfa = reinterpret_cast<const uint8_t*>(sfa_tiled); p.sfb = reinterpret_cast<const uint8_t*>(sfb_tiled);
   p.bias = bias; p.bias_kind = bias_kind; p.out = out; p.out_kind = out_kind; p.ld_out = ld_out; p.status = status;
   const size_t smem = sizeof(Smem) + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static amct::OncePerDevice attr_set;
+  if (attr_set.first()) {
     if (cudaFuncSetAttribute(gemm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AMCT_ERR_CUDA;
-    attr_set = true;
   }
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);

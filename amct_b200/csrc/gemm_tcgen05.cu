@@ -25,7 +25,9 @@
 //   raw            : int32 accumulators as they are
 //   float kinds    : y = acc + bias_f[n]
 #include <cuda.h>
-#include <stdlib.h>
+
+#include <atomic>
+#include <mutex>
 
 #include "gemm_common.cuh"
 
@@ -42,6 +44,7 @@ struct __align__(1024) GemmSmem {
   uint8_t tiles[STAGES][kABytes + BN * kBKBytes];
   float epi_scale[4][BN];
   float epi_bias[4][BN];
+  uint8_t epi_stage[4][kEpiStageBytes];
   uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -156,7 +159,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_full[acc]), acc_phase, abort_flag)) break;
       tc05::fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN;
-      epilogue_rows<kBN>(p, t_row, row, n0, tn, sc, sb, pt);
+      if (p.scatter_world > 0) epilogue_rows_scatter<kBN>(p, t_row, tm * kBM + quarter * 32, lane, n0, sc, sb, pt, s.epi_stage[ew]);
+      else epilogue_rows<kBN>(p, t_row, row, n0, tn, sc, sb, pt);
       tc05::fence_before_sync();
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive(tc05::smem_u32(&s.tmem_empty[acc]));
@@ -195,11 +199,34 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows, k] K-major matrix -> tensor map with a (128 bytes of K) x box_rows box, 128-byte swizzle.
+// [rows, k] K-major matrix -> tensor map with a (128 bytes of K) x box_rows box, 128-byte swizzle.  A tensor map
+// depends only on (base, element size, rows, k, ld, box rows), not on the matrix's contents, and a deployed model
+// calls with the same weights (and usually the same activation buffers) again and again: the last maps are kept
+// in a small table per host thread, so the steady state encodes nothing.
+struct MapKey {
+  const void* base;
+  int64_t rows, k, ld;
+  int esize, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && k == o.k && ld == o.ld && esize == o.esize && box_rows == o.box_rows;
+  }
+};
+constexpr int kMapCacheSlots = 64;
+struct MapCache {
+  MapKey key[kMapCacheSlots];
+  CUtensorMap map[kMapCacheSlots];
+  bool used[kMapCacheSlots] = {};
+};
+
 static int make_map(CUtensorMap* map, const void* base, int esize, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+  if (!aligned16(base) || (ld * esize) % 16 != 0) return AMCT_ERR_ALIGN;
+  static thread_local MapCache cache;
+  const MapKey key{base, rows, k, ld, esize, box_rows};
+  const uint64_t hsh = (reinterpret_cast<uintptr_t>(base) >> 4) * 0x9E3779B97F4A7C15ull + (uint64_t)rows * 31 + (uint64_t)box_rows;
+  const int slot = (int)((hsh >> 32) % kMapCacheSlots);
+  if (cache.used[slot] && cache.key[slot] == key) { *map = cache.map[slot]; return AMCT_OK; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return AMCT_ERR_CUDA;
-  if (!aligned16(base) || (ld * esize) % 16 != 0) return AMCT_ERR_ALIGN;
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)(ld * esize)};
   cuuint32_t box[2] = {(cuuint32_t)(kBKBytes / esize), (cuuint32_t)box_rows};
@@ -207,41 +234,60 @@ static int make_map(CUtensorMap* map, const void* base, int esize, int64_t rows,
   CUtensorMapDataType dt = esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? AMCT_OK : AMCT_ERR_CUDA;
+  if (r != CUDA_SUCCESS) return AMCT_ERR_CUDA;
+  cache.key[slot] = key; cache.map[slot] = *map; cache.used[slot] = true;
+  return AMCT_OK;
 }
 
-// Number of persistent CTAs: one per SM, or fewer when AMCT_GEMM_MAX_CTAS is set.  A job that runs collectives next to
-// its GEMMs (tensor parallelism) leaves a few SMs to the communication kernels that way: a persistent CTA that cannot be
-// placed until a communication kernel has left its SM would delay its whole statically assigned share of the tiles.
-int gemm_cta_budget() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+// Per-device facts, looked up once per device: the SM count and whether each kernel's shared-memory attribute has
+// been raised there (the attribute belongs to the device's context, not to the process).
+constexpr int kMaxGemmDevices = 64;
+struct DeviceFacts {
+  int sms = 0;
+  bool attr_small = false, attr_large = false, attr_pair = false;
+};
+static DeviceFacts g_dev[kMaxGemmDevices];
+static std::mutex g_dev_mutex;
+
+static DeviceFacts* device_facts() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxGemmDevices) return nullptr;
+  DeviceFacts* f = &g_dev[dev];
+  if (!f->sms) {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return nullptr;
+    f->sms = n;
   }
-  const char* e = getenv("AMCT_GEMM_MAX_CTAS");
-  if (e) {
-    const int cap = atoi(e);
-    if (cap >= 2 && cap < n) return cap & ~1;        // even: the pair kernel launches clusters of two
-  }
-  return n;
+  return f;
 }
-static int sm_count() { return gemm_cta_budget(); }
+
+// Persistent CTAs of a GEMM on the current device: one per SM.
+int gemm_cta_budget() {
+  DeviceFacts* f = device_facts();
+  return f ? f->sms : 1;
+}
+
+// Raises the dynamic shared-memory limit of the pair kernel once per device (used by gemm_tcgen05_pair.cu).
+bool gemm_pair_attr_needed() {
+  DeviceFacts* f = device_facts();
+  if (!f || f->attr_pair) return false;
+  f->attr_pair = true;
+  return true;
+}
 
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st);
 
 // Which kernel takes M > 128.  The CTA-pair kernel does more work per clock; at the power limit it
 // wins while the B operand stays in L2 and loses when B streams from HBM (measured on B200), hence
-// the size rule.  AMCT_GEMM_VARIANT=single|pair in the environment overrides it (tests, comparisons).
+// the size rule.  amct_gemm_set_variant pins one of the two (tests, comparisons).
 constexpr int64_t kPairMaxBBytes = 96LL << 20;
+static std::atomic<int> g_variant{AMCT_GEMM_VARIANT_AUTO};
 static bool use_pair_kernel(const GemmParams& p, int esize) {
   if (p.m <= 128) return false;
-  const char* e = getenv("AMCT_GEMM_VARIANT");
-  const char* sm = getenv("AMCT_GEMM_SMEM");
-  if (sm && sm[0] == 's') return false;            // the small-footprint mode exists for the one-CTA kernel only
-  if (e && e[0] == 's') return false;
-  if (e && e[0] == 'p') return true;
+  const int v = g_variant.load(std::memory_order_relaxed);
+  if (v == AMCT_GEMM_VARIANT_SINGLE) return false;
+  if (v == AMCT_GEMM_VARIANT_PAIR) return true;
   return p.n * p.k * esize <= kPairMaxBBytes;
 }
 
@@ -249,6 +295,8 @@ static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b,
   if (p.m == 0 || p.n == 0) return AMCT_OK;
   if (p.k <= 0) return AMCT_ERR_ARG;
   if (p.m > 0x7fffffffLL || p.n > 0x7fffffffLL || p.k > 0x7fffffffLL) return AMCT_ERR_UNSUPPORTED;
+  DeviceFacts* dev = device_facts();
+  if (!dev) return AMCT_ERR_CUDA;
   const int esize = p.kind == KIND_I8 ? 1 : 2;
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, esize, p.m, p.k, ld_a, kBM);
@@ -259,44 +307,28 @@ static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b,
     if (rc != AMCT_OK) return rc;
     return launch_gemm_pair(ma, mb, p, st);
   }
-  rc = make_map(&mb, b, esize, p.n, p.k, ld_b, (p.m <= 128 && p.act == 0) ? kBNSmall : kBNLarge);
-  if (rc != AMCT_OK) return rc;
   const bool small = p.m <= 128 && p.act == 0;
   const int bn = small ? kBNSmall : kBNLarge;
+  rc = make_map(&mb, b, esize, p.n, p.k, ld_b, bn);
+  if (rc != AMCT_OK) return rc;
   const int64_t tiles = ((p.m + kBM - 1) / kBM) * ((p.n + bn - 1) / bn);
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  const int grid = (int)(tiles < dev->sms ? tiles : dev->sms);
   if (small) {
     const size_t smem = sizeof(GemmSmem<kBNSmall, kStagesSmall>) + 1024;
-    static bool attr_small = false;
-    if (!attr_small) {
+    if (!dev->attr_small) {
       if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNSmall, kStagesSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return AMCT_ERR_CUDA;
-      attr_small = true;
+      dev->attr_small = true;
     }
     gemm_tcgen05_kernel<kBNSmall, kStagesSmall><<<grid, kThreads, smem, st>>>(ma, mb, p);
   } else {
-    // AMCT_GEMM_SMEM=small: a three-stage ring (153 KB instead of 201 KB of shared memory per SM), so that the CTAs of a
-    // communication kernel running next to the GEMM fit on the same SMs
-    const char* e = getenv("AMCT_GEMM_SMEM");
-    if (e && e[0] == 's') {
-      const size_t smem = sizeof(GemmSmem<kBNLarge, 3>) + 1024;
-      static bool attr_small3 = false;
-      if (!attr_small3) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNLarge, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-          return AMCT_ERR_CUDA;
-        attr_small3 = true;
-      }
-      gemm_tcgen05_kernel<kBNLarge, 3><<<grid, kThreads, smem, st>>>(ma, mb, p);
-    } else {
-      const size_t smem = sizeof(GemmSmem<kBNLarge, kStagesLarge>) + 1024;
-      static bool attr_large = false;
-      if (!attr_large) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNLarge, kStagesLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-          return AMCT_ERR_CUDA;
-        attr_large = true;
-      }
-      gemm_tcgen05_kernel<kBNLarge, kStagesLarge><<<grid, kThreads, smem, st>>>(ma, mb, p);
+    const size_t smem = sizeof(GemmSmem<kBNLarge, kStagesLarge>) + 1024;
+    if (!dev->attr_large) {
+      if (cudaFuncSetAttribute(gemm_tcgen05_kernel<kBNLarge, kStagesLarge>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return AMCT_ERR_CUDA;
+      dev->attr_large = true;
     }
+    gemm_tcgen05_kernel<kBNLarge, kStagesLarge><<<grid, kThreads, smem, st>>>(ma, mb, p);
   }
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
@@ -348,4 +380,36 @@ extern "C" int amct_gemm_f16(const void* a, const void* b, int dtype, int64_t m,
   p.m = m; p.n = n; p.k = k; p.kind = dtype == AMCT_DTYPE_BF16 ? amct::KIND_BF16 : amct::KIND_F16;
   p.bias = bias; p.bias_kind = bias_kind; p.out = out; p.out_kind = out_kind; p.ld_out = ld_out; p.status = status;
   return amct::launch_gemm(a, b, ld_a, ld_b, p, (cudaStream_t)stream);
+}
+
+extern "C" int amct_gemm_w8a8_scatter(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64_t k, int64_t ld_a,
+                                      int64_t ld_b, const float* deq_scale, const float* pertoken_scale,
+                                      void* const* out_ptrs, int world, int slot, int64_t rows_per_rank, int out_kind,
+                                      int64_t ld_out, int* status, void* stream) {
+  if (m < 0 || n < 0 || k < 0 || ld_a < k || ld_b < k || ld_out < n) return AMCT_ERR_ARG;
+  if (!out_ptrs || world < 1 || world > amct::kMaxScatterRanks || slot < 0 || slot >= world || rows_per_rank <= 0)
+    return AMCT_ERR_ARG;
+  if (m > rows_per_rank * world) return AMCT_ERR_ARG;
+  if (m && n && (!a || !b || !deq_scale)) return AMCT_ERR_ARG;
+  if (out_kind != amct::OUT_BF16 && out_kind != amct::OUT_F16) return AMCT_ERR_UNSUPPORTED;
+  if (n % 64 != 0) return AMCT_ERR_UNSUPPORTED;
+  if ((ld_out * 2) % 16 != 0) return AMCT_ERR_ALIGN;
+  amct::GemmParams p{};
+  p.m = m; p.n = n; p.k = k; p.kind = amct::KIND_I8;
+  p.deq = deq_scale; p.pertoken = pertoken_scale; p.bias_kind = amct::BIAS_NONE;
+  p.out_kind = out_kind; p.ld_out = ld_out; p.status = status;
+  p.scatter_world = world; p.scatter_slot = slot; p.scatter_rows = rows_per_rank;
+  for (int r = 0; r < world; ++r) {
+    if (!out_ptrs[r]) return AMCT_ERR_ARG;
+    if (!amct::aligned16(out_ptrs[r])) return AMCT_ERR_ALIGN;
+    p.scatter_out[r] = out_ptrs[r];
+  }
+  return amct::launch_gemm(a, b, ld_a, ld_b, p, (cudaStream_t)stream);
+}
+
+extern "C" int amct_gemm_set_variant(int variant) {
+  if (variant != AMCT_GEMM_VARIANT_AUTO && variant != AMCT_GEMM_VARIANT_SINGLE && variant != AMCT_GEMM_VARIANT_PAIR)
+    return AMCT_ERR_ARG;
+  amct::g_variant.store(variant, std::memory_order_relaxed);
+  return AMCT_OK;
 }

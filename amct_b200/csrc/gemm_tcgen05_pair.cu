@@ -34,6 +34,7 @@ struct __align__(1024) PairSmem {
   uint8_t tiles[kPairStages][kPairStageBytes];
   float epi_scale[4][kPairBN];
   float epi_bias[4][kPairBN];
+  uint8_t epi_stage[4][kEpiStageBytes];
   uint64_t full[kPairStages], empty[kPairStages], tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -159,7 +160,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_full[acc]), acc_phase, abort_flag)) break;
       tc05::fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBN;
-      epilogue_rows<kBN>(p, t_row, row, n0, tn, sc, sb, pt);
+      if (p.scatter_world > 0)
+        epilogue_rows_scatter<kBN>(p, t_row, tm * 2 * kBM + rank * kBM + quarter * 32, lane, n0, sc, sb, pt, s.epi_stage[ew]);
+      else epilogue_rows<kBN>(p, t_row, row, n0, tn, sc, sb, pt);
       tc05::fence_before_sync();
       __syncwarp();
       if (lane == 0) tc05::mbar_arrive_cluster(tc05::map_to_cta(tc05::smem_u32(&s.tmem_empty[acc]), 0));
@@ -185,7 +188,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   }
 }
 
-int gemm_cta_budget();        // gemm_tcgen05.cu: SM count, or the AMCT_GEMM_MAX_CTAS cap
+int gemm_cta_budget();         // gemm_tcgen05.cu: SM count of the current device
+bool gemm_pair_attr_needed();  // gemm_tcgen05.cu: true once per device
 
 static int max_pairs() {
   const int n = gemm_cta_budget() / 2;
@@ -195,11 +199,9 @@ static int max_pairs() {
 // tma_a: box of 128 rows of A; tma_b: box of 128 rows of B (half a tile).
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
   const size_t smem = sizeof(PairSmem) + 1024;
-  static bool attr_done = false;
-  if (!attr_done) {
+  if (gemm_pair_attr_needed()) {
     if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return AMCT_ERR_CUDA;
-    attr_done = true;
   }
   const int64_t tiles = ((p.m + 2 * kBM - 1) / (2 * kBM)) * ((p.n + kPairBN - 1) / kPairBN);
   const int pairs = (int)(tiles < max_pairs() ? tiles : max_pairs());

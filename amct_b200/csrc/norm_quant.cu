@@ -22,6 +22,7 @@
 namespace amct {
 
 constexpr float kMagicNQ = 12582912.0f;                  // 1.5 * 2^23
+constexpr int kMaxNormRanks = 16;
 
 struct NormQuantParams {
   const void* x;
@@ -34,6 +35,14 @@ struct NormQuantParams {
   int* status;
   int64_t rows, k, ld_x, ld_res, ld_res_out, ld_norm, ld_q;
   float eps;
+  // Tensor-parallel form (TP kernels only).  Input: x holds `parts` partial sums of this rank's rows, one after the
+  // other (part j at x + j * part_stride elements); the row is their fp32 sum in that order, rounded once to T.
+  // Output: the codes and the scale of row r go to row (row0 + r) of EVERY rank's buffers, q_all[d] / scale_all[d]
+  // (this process's mappings of them), so that each rank ends up with all ranks' rows; q / scale are not used.
+  int parts, world;
+  int64_t part_stride, row0;
+  int8_t* q_all[kMaxNormRanks];
+  float* scale_all[kMaxNormRanks];
 };
 
 __device__ __forceinline__ uint32_t nq_pack4(float ra, float rb, float rc, float rd) {
@@ -77,7 +86,7 @@ template <> struct Pack2<__half> {
 // packed two to a register wherever the arithmetic allows: the residual add is the packed add (the
 // exact sum of two 16-bit floats rounded once, which is what an fp32 add followed by the rounding to
 // T gives as well), min / max use the packed NaN-propagating instructions, conversions go pairwise.
-template <typename T, int NV, int NT>
+template <typename T, int NV, int NT, bool TP = false>
 __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
   constexpr int E = 8;
   constexpr int NW = NT / 32;
@@ -95,6 +104,42 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
     for (int j = 0; j < NV; ++j) {
       const int v = tid + j * NT;
       if (v < nvec) h[j] = ld_vec_stream(xr + v * E);
+    }
+    if constexpr (TP) {
+      // sum of the ranks' partial sums: fp32, in rank order, rounded to T once
+      if (p.parts > 1) {
+        float acc[NV][E];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const P2* hp = reinterpret_cast<const P2*>(&h[j]);
+#pragma unroll
+          for (int e = 0; e < E / 2; ++e) { acc[j][2 * e] = __low2float(hp[e]); acc[j][2 * e + 1] = __high2float(hp[e]); }
+        }
+        for (int part = 1; part < p.parts; ++part) {
+          const T* pr = xr + (int64_t)part * p.part_stride;
+          Vec16<T> t[NV];
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            const int v = tid + j * NT;
+            if (v < nvec) t[j] = ld_vec_stream(pr + v * E);
+          }
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            const P2* tp = reinterpret_cast<const P2*>(&t[j]);
+#pragma unroll
+            for (int e = 0; e < E / 2; ++e) {
+              acc[j][2 * e] = __fadd_rn(acc[j][2 * e], __low2float(tp[e]));
+              acc[j][2 * e + 1] = __fadd_rn(acc[j][2 * e + 1], __high2float(tp[e]));
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          P2* hp = reinterpret_cast<P2*>(&h[j]);
+#pragma unroll
+          for (int e = 0; e < E / 2; ++e) hp[e] = Pack2<T>::from_floats(acc[j][2 * e], acc[j][2 * e + 1]);
+        }
+      }
     }
     if (p.residual) {
       const T* rr = reinterpret_cast<const T*>(p.residual) + row * p.ld_res;
@@ -178,12 +223,17 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
     const bool neg_dom = amx < amn;
     float s = __fdiv_rn(neg_dom ? amn : amx, neg_dom ? 128.f : 127.f);
     if (s < AMCT_FLT_EPSILON) s = 1.f;
-    if (tid == 0) {
-      p.scale[row] = s;
-      if (!isfinite(s) && p.status) atomicOr(p.status, 1);
+    if constexpr (TP) {
+      if (tid < p.world) p.scale_all[tid][p.row0 + row] = s;
+      if (tid == 0 && !isfinite(s) && p.status) atomicOr(p.status, 1);
+    } else {
+      if (tid == 0) {
+        p.scale[row] = s;
+        if (!isfinite(s) && p.status) atomicOr(p.status, 1);
+      }
     }
     const float y = __frcp_rn(s);
-    int8_t* qrow = p.q + row * p.ld_q;
+    int8_t* qrow = TP ? nullptr : p.q + row * p.ld_q;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int v = tid + j * NT;
@@ -191,13 +241,19 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
         const P2* hp = reinterpret_cast<const P2*>(&h[j]);
         const uint32_t w0 = nq_quant4(__low2float(hp[0]), __high2float(hp[0]), __low2float(hp[1]), __high2float(hp[1]), s, y);
         const uint32_t w1 = nq_quant4(__low2float(hp[2]), __high2float(hp[2]), __low2float(hp[3]), __high2float(hp[3]), s, y);
-        *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(w0, w1);
+        if constexpr (TP) {
+          // a warp writes 256 contiguous bytes per destination: plain stores into every rank's (peer-mapped) buffer
+          const int64_t off = (p.row0 + row) * p.ld_q + v * E;
+          for (int d = 0; d < p.world; ++d) *reinterpret_cast<uint2*>(p.q_all[d] + off) = make_uint2(w0, w1);
+        } else {
+          *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(w0, w1);
+        }
       }
     }
   }
 }
 
-template <typename T>
+template <typename T, bool TP = false>
 static int launch_norm_quant(const NormQuantParams& p, cudaStream_t st) {
   const int64_t nvec = p.k / 8;
   int dev = 0, sms = 0;
@@ -207,11 +263,11 @@ static int launch_norm_quant(const NormQuantParams& p, cudaStream_t st) {
   int64_t grid = (int64_t)sms * 8;
   if (grid > p.rows) grid = p.rows;
   const unsigned g = (unsigned)grid;
-  if (nvec <= 128) AMCT_LAUNCH(g, 128, st, (p), addnorm_quant_kernel<T, 1, 128>);
-  else if (nvec <= 256) AMCT_LAUNCH(g, 256, st, (p), addnorm_quant_kernel<T, 1, 256>);
-  else if (nvec <= 512) AMCT_LAUNCH(g, 256, st, (p), addnorm_quant_kernel<T, 2, 256>);
-  else if (nvec <= 1024) AMCT_LAUNCH(g, 512, st, (p), addnorm_quant_kernel<T, 2, 512>);
-  else if (nvec <= 2048) AMCT_LAUNCH(g, 512, st, (p), addnorm_quant_kernel<T, 4, 512>);
+  if (nvec <= 128) AMCT_LAUNCH(g, 128, st, (p), addnorm_quant_kernel<T, 1, 128, TP>);
+  else if (nvec <= 256) AMCT_LAUNCH(g, 256, st, (p), addnorm_quant_kernel<T, 1, 256, TP>);
+  else if (nvec <= 512) AMCT_LAUNCH(g, 256, st, (p), addnorm_quant_kernel<T, 2, 256, TP>);
+  else if (nvec <= 1024) AMCT_LAUNCH(g, 512, st, (p), addnorm_quant_kernel<T, 2, 512, TP>);
+  else if (nvec <= 2048) AMCT_LAUNCH(g, 512, st, (p), addnorm_quant_kernel<T, 4, 512, TP>);
   else return AMCT_ERR_UNSUPPORTED;
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
@@ -244,4 +300,38 @@ extern "C" int amct_addnorm_quant_pertoken(const void* x, const void* residual, 
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == AMCT_DTYPE_F16) return amct::launch_norm_quant<__half>(p, st);
   return amct::launch_norm_quant<__nv_bfloat16>(p, st);
+}
+
+extern "C" int amct_addnorm_quant_pertoken_tp(const void* parts, int n_parts, int64_t part_stride, const void* residual,
+                                              int dtype, int64_t rows, int64_t k, int64_t ld_x, int64_t ld_res,
+                                              const void* gamma, float eps, void* residual_out, int64_t ld_res_out,
+                                              int8_t* const* q_all, float* const* scale_all, int world, int64_t row0,
+                                              int64_t ld_q, int* status, void* stream) {
+  if (rows < 0 || k <= 0 || !gamma || row0 < 0) return AMCT_ERR_ARG;
+  if (n_parts < 1 || n_parts > amct::kMaxNormRanks || world < 1 || world > amct::kMaxNormRanks || !q_all || !scale_all)
+    return AMCT_ERR_ARG;
+  if (rows == 0) return AMCT_OK;
+  if (!parts) return AMCT_ERR_ARG;
+  if (dtype != AMCT_DTYPE_F16 && dtype != AMCT_DTYPE_BF16) return AMCT_ERR_UNSUPPORTED;
+  if (k % 8 || k > 2048 * 8) return AMCT_ERR_UNSUPPORTED;
+  if (ld_x < k || ld_q < k || (residual && ld_res < k) || (residual_out && ld_res_out < k)) return AMCT_ERR_ARG;
+  if (residual_out && !residual) return AMCT_ERR_ARG;
+  if (n_parts > 1 && part_stride < rows * ld_x) return AMCT_ERR_ARG;
+  auto ok16 = [](const void* ptr, int64_t ld_elems) { return amct::aligned16(ptr) && (ld_elems * 2) % 16 == 0; };
+  if (!ok16(parts, ld_x) || (part_stride * 2) % 16 || !amct::aligned16(gamma) || (residual && !ok16(residual, ld_res)) ||
+      (residual_out && !ok16(residual_out, ld_res_out)) || ld_q % 8)
+    return AMCT_ERR_ALIGN;
+  amct::NormQuantParams p{};
+  p.x = parts; p.residual = residual; p.gamma = gamma; p.residual_out = residual_out; p.status = status;
+  p.rows = rows; p.k = k; p.ld_x = ld_x; p.ld_res = ld_res; p.ld_res_out = ld_res_out; p.ld_q = ld_q; p.eps = eps;
+  p.parts = n_parts; p.part_stride = part_stride; p.world = world; p.row0 = row0;
+  for (int d = 0; d < world; ++d) {
+    if (!q_all[d] || !scale_all[d]) return AMCT_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(q_all[d]) % 8) return AMCT_ERR_ALIGN;
+    p.q_all[d] = q_all[d];
+    p.scale_all[d] = scale_all[d];
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == AMCT_DTYPE_F16) return amct::launch_norm_quant<__half, true>(p, st);
+  return amct::launch_norm_quant<__nv_bfloat16, true>(p, st);
 }

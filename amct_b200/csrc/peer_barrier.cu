@@ -9,7 +9,8 @@
 // rank that runs ahead by one barrier cannot be mistaken for the current one.  The wait is bounded: after
 // kBarrierLimitNs the lane sets bit 1 of the status word and the kernel returns, so a peer that never arrives
 // costs a wrong result that the host can see, not a hung device.  Once that bit is set, later barriers with the
-// same status word return at once.
+// same status word still signal (so that the peers, whose data is wrong already, do not each wait out their own
+// limit at every barrier that follows) but no longer wait.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -33,11 +34,11 @@ __device__ __forceinline__ uint64_t barrier_timer_ns() {
 __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerFlags flags, int world, int rank, uint32_t seq, int* status) {
   const int t = threadIdx.x;
   if (t >= world || t == rank) return;
+  __threadfence_system();                                            // earlier kernels' writes, before the signal
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.ptr[t] + rank), "r"(seq) : "memory");
   // a barrier that has given up once stays open: the data is already wrong, and every later barrier of a rank
   // that lost its peers would otherwise wait its full limit again
   if (status && (*reinterpret_cast<volatile int*>(status) & 2)) return;
-  __threadfence_system();                                            // earlier kernels' writes, before the signal
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.ptr[t] + rank), "r"(seq) : "memory");
   const uint32_t* mine = flags.ptr[rank] + t;
   const uint64_t t0 = barrier_timer_ns();
   for (;;) {

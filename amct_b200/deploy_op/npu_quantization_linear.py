@@ -113,23 +113,43 @@ class NpuQuantizationLinear(torch.nn.Module):
                 pertoken = pertoken.repeat(x.numel() // (x.shape[-2] * k))
         return self._gemm(q, pertoken, out)
 
+    def _deq_scales(self, n):
+        """deq_scale with one value per output channel.  For one scale for the whole weight (strategy 'tensor') the
+        buffer keeps the reference's one element and the expanded copy is kept until the buffer is replaced or
+        written (no device read on the forward path)."""
+        deq = self.deq_scale
+        if deq.numel() == n:
+            return deq
+        key = (deq.data_ptr(), deq._version, deq.device)
+        cached = getattr(self, '_deq_per_channel', None)
+        if cached is None or cached[0] != key:
+            cached = (key, deq.reshape(-1)[:1].to(torch.float32).expand(n).contiguous())
+            self._deq_per_channel = cached
+        return cached[1]
+
     def _gemm(self, q, pertoken, out=None):
         k = q.shape[-1]
         wq_nk = self.quantized_weight.t()
-        deq = self.deq_scale
-        if deq.numel() != wq_nk.shape[0]:
-            # one scale for the whole weight (strategy 'tensor'): the buffer keeps the reference's one element, the
-            # GEMM epilogue takes one value per output channel
-            cached = getattr(self, '_deq_per_channel', None)
-            if cached is None or cached.device != deq.device or float(cached[0]) != float(deq.reshape(-1)[0]):
-                cached = deq.reshape(-1)[:1].to(torch.float32).expand(wq_nk.shape[0]).contiguous()
-                self._deq_per_channel = cached
-            deq = cached
+        deq = self._deq_scales(wq_nk.shape[0])
         if self.fused_act == 'swiglu':
             res = ops.gemm_w8a8_swiglu(q.reshape(-1, k), wq_nk, deq, pertoken, self.bias, out=out)
             return res.reshape(*q.shape[:-1], -1)
         res = ops.gemm_w8a8(q.reshape(-1, k), wq_nk, deq, pertoken, self.bias, out_dtype=self.output_dtype, out=out)
         return res.reshape(*q.shape[:-1], -1)
+
+    @torch.no_grad()
+    def forward_scatter(self, x, out_ptrs, slot, rows_per_rank, ld_out):
+        """forward() of a K-sharded (row-parallel) Linear under tensor parallelism; not in the reference.  The result is
+        this rank's partial sum, and instead of returning it the GEMM writes output row r into row
+        (slot * rows_per_rank + r % rows_per_rank) of the staging buffer of rank r // rows_per_rank (out_ptrs: the
+        device addresses of every rank's buffer as mapped into this process).  Dynamic per-token scales, no bias."""
+        if not self.dynamic_act or self.bias is not None or self.fused_act is not None:
+            raise RuntimeError('forward_scatter needs dynamic per-token activation scales, no bias and no fused activation')
+        k = x.shape[-1]
+        q, pertoken = ops.quant_dynamic_per_token(x, smooth=getattr(self, 'scale_factor', None), rule=self.dynamic_rule)
+        wq_nk = self.quantized_weight.t()
+        ops.gemm_w8a8_scatter(q.reshape(-1, k), wq_nk, self._deq_scales(wq_nk.shape[0]), pertoken, out_ptrs, slot,
+                              rows_per_rank, ld_out, out_dtype=self.output_dtype)
 
     @torch.no_grad()
     def forward_quantized(self, q, pertoken_scale):

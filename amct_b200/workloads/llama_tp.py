@@ -26,6 +26,13 @@ per-token scales: 1 byte per element instead of 2, and no replicated glue work. 
 and rank that moves 2 x (2 + 1) x T x hidden x (tp-1)/tp bytes instead of the 2 x 4 of two
 bf16 all-reduces.  Otherwise (decode, or T not divisible by tp): one NCCL all-reduce per
 row-parallel Linear on replicated activations.
+
+The token-sharded collectives come in two forms (``comm``).  'nccl': reduce_scatter_tensor / all_gather_into_tensor.
+'push': the compute kernels do the transfers with their own stores into peer-mapped buffers (PeerBuffers): the
+row-parallel GEMM's epilogue writes each partial tile straight into the owning rank's staging slot, so the
+reduce-scatter's bytes cross NVLink tile by tile while the GEMM runs; the add + RMSNorm + quant kernel sums the staged
+partials in fp32 and stores its codes and scales into every rank's buffer, which is the all-gather.  Between them one
+barrier kernel per transfer; no communication library kernel, no copy, no staging sum.
 """
 import math
 from dataclasses import dataclass
@@ -36,11 +43,6 @@ import torch.nn.functional as F
 
 import amct_b200 as amct
 from amct_b200.backend import ops
-
-import os
-
-# how the INT8 codes are handed to the all-gather: as bytes, or (same memory) as 32-bit words
-GATHER_CODES_AS_WORDS = os.environ.get('AMCT_GATHER_WORDS', '0') == '1'
 
 W8A8_DYNAMIC_CFG = {
     'batch_num': 1,
@@ -118,38 +120,58 @@ def apply_rotary(x, cos, sin):
 
 
 class PeerBuffers:
-    """Collectives of the token-sharded prefill done by the copy engines over peer-mapped (symmetric) buffers, so that
-    no communication kernel competes with the GEMMs for SMs: every rank writes its slice / partial into its own
-    buffer, a barrier, every rank PULLS what it needs from the peers' buffers with plain device-to-device copies, a
-    second barrier (the buffers may be overwritten), and a local sum for the reduce-scatter.  The barrier is this
-    library's one-block kernel over peer-mapped flag words (bounded wait, status bit 1 on time-out).  One instance
-    per micro-batch stream; all ranks call its methods in the same order."""
+    """Peer-mapped buffers and the barrier of the 'push' collectives of one (micro-)batch of `rows_total` token rows.
 
-    def __init__(self, group, rows_total, hidden, device):
+    Every rank holds, in memory all ranks have mapped (torch symmetric memory, plain mappings, multicast off):
+      stage[i]   [tp, rows, hidden] bf16   slot j = rank j's partial sums of THIS rank's rows, written by rank j's
+                                           row-parallel GEMM epilogue (i = 0: o_proj, 1: down_proj)
+      codes[i]   [rows_total, hidden] int8 all ranks' codes, slice j written by rank j's add + norm + quant kernel
+      scales[i]  [rows_total] fp32         (i = 0: in front of qkv, 1: in front of gate/up)
+      flags      [tp] int32                barrier words
+    A transfer is complete for its readers after ONE barrier (amct_peer_barrier: release / acquire at system scope,
+    bounded wait, status bit 1 on time-out).  No second barrier is needed before a buffer is written again: between
+    a rank's last read of a buffer and any peer's next write into it lies a later barrier which that rank signals only
+    after the read (two buffers of each kind, four barriers per layer; the argument is spelled out at `barrier`).
+    All ranks call the methods in the same order, on one stream per instance."""
+
+    def __init__(self, group, rows_total, hidden, device, dtype=torch.bfloat16):
         import os
         os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')      # plain peer mappings only: nothing here uses multimem
         import torch.distributed._symmetric_memory as symm
         dist = torch.distributed
         self.tp, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.rows = rows_total // self.tp
-        self.codes = symm.empty((rows_total, hidden), dtype=torch.int8, device=device)
-        self.scales = symm.empty((rows_total,), dtype=torch.float32, device=device)
-        self.partial = symm.empty((rows_total, hidden), dtype=torch.bfloat16, device=device)
+        self.rows, self.hidden = rows_total // self.tp, hidden
+        self.stage = [symm.empty((self.tp, self.rows, hidden), dtype=dtype, device=device) for _ in range(2)]
+        self.codes = [symm.empty((rows_total, hidden), dtype=torch.int8, device=device) for _ in range(2)]
+        self.scales = [symm.empty((rows_total,), dtype=torch.float32, device=device) for _ in range(2)]
         self.flags = symm.empty((self.tp,), dtype=torch.int32, device=device)
         self.flags.zero_()
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        shape = lambda t: tuple(t.shape)
-        handles = {name: symm.rendezvous(getattr(self, name), group) for name in ('codes', 'scales', 'partial', 'flags')}
-        # views of every rank's buffers through this process's mappings of them
-        self.peer_codes = [handles['codes'].get_buffer(r, shape(self.codes), torch.int8) for r in range(self.tp)]
-        self.peer_scales = [handles['scales'].get_buffer(r, shape(self.scales), torch.float32) for r in range(self.tp)]
-        self.peer_partial = [handles['partial'].get_buffer(r, shape(self.partial), torch.bfloat16) for r in range(self.tp)]
-        self.flag_ptrs = [int(p_) for p_ in handles['flags'].buffer_ptrs]
-        self._handles, self.seq = handles, 0
+
+        def peer_pointers(t):
+            handle = symm.rendezvous(t, group)
+            self._handles.append(handle)
+            return [int(p_) for p_ in handle.buffer_ptrs]
+
+        self._handles = []
+        # device addresses of every rank's buffers through this process's mappings of them
+        self.stage_ptrs = [peer_pointers(t) for t in self.stage]
+        self.code_ptrs = [peer_pointers(t) for t in self.codes]
+        self.scale_ptrs = [peer_pointers(t) for t in self.scales]
+        self.flag_ptrs = peer_pointers(self.flags)
+        self.seq = 0
         dist.barrier(group)                                                   # every rank's flags are zero before anyone signals
 
-    def _barrier(self):
+    def barrier(self):
+        """Everything this rank's stream wrote into peers' buffers before this point is visible to the peers' kernels
+        after it, and vice versa.  Reuse without a trailing barrier, per layer L (B1..B4 = the four barriers of a layer:
+        after the o_proj scatter, after the post-attention codes, after the down_proj scatter, after the next layer's
+        pre-attention codes): a peer writes stage[0] in o_proj(L) only after it passed B4(L-1), which this rank signals
+        after its pre-attention kernel of layer L, i.e. after it read stage[0] in layer L-1; codes[0] is written by the
+        peers' pre-attention kernel of L+1 after B3(L), signalled after this rank's qkv GEMM of L; codes[1] by their
+        post-attention kernel of L+1 after B1(L+1), signalled after this rank's gate/up GEMM of L; stage[1] in
+        down_proj(L+1) after B2(L+1), signalled after this rank's pre-attention kernel of L+1, which read it."""
         self.seq += 1
         ops.peer_barrier(self.flag_ptrs, self.rank, self.seq, self.status)
 
@@ -157,31 +179,18 @@ class PeerBuffers:
         """Raise if a barrier of this instance ever gave up waiting (synchronizes the device)."""
         ops.raise_if_timed_out(self.status)
 
-    def local_slices(self):
-        sl = slice(self.rank * self.rows, (self.rank + 1) * self.rows)
-        return self.codes[sl], self.scales[sl]
 
-    def gather_codes(self):
-        """The local slices of codes / scales have been written: fetch everybody else's."""
-        self._barrier()
-        for step in range(1, self.tp):
-            r = (self.rank - step) % self.tp
-            sl = slice(r * self.rows, (r + 1) * self.rows)
-            self.codes[sl].copy_(self.peer_codes[r][sl])
-            self.scales[sl].copy_(self.peer_scales[r][sl])
-        self._barrier()
-        return self.codes, self.scales
+# stands for "the rows are the partial sums lying in the peer-mapped staging buffer" (push collectives)
+STAGED = object()
 
-    def reduce_scatter_partial(self):
-        """self.partial holds this rank's [T, H] partial sums: return the sum over ranks of rows [rank T/tp, ...)."""
-        self._barrier()
-        mine = slice(self.rank * self.rows, (self.rank + 1) * self.rows)
-        staging = torch.empty((self.tp, self.rows, self.partial.shape[1]), dtype=self.partial.dtype, device=self.partial.device)
-        for step in range(self.tp):
-            r = (self.rank - step) % self.tp
-            staging[r].copy_(self.peer_partial[r][mine])
-        self._barrier()
-        return staging.sum(dim=0)
+
+def sum_staged(parts):
+    """fp32 sum of staged partial sums [tp, rows, hidden] in rank order, rounded once: what the add + norm + quant
+    kernel computes from them (used once per step, for the last layer's MLP output)."""
+    acc = parts[0].float()
+    for j in range(1, parts.shape[0]):
+        acc = acc + parts[j].float()
+    return acc.to(parts.dtype)
 
 
 class DecoderLayer(nn.Module):
@@ -218,13 +227,19 @@ class DecoderLayer(nn.Module):
         dist.all_reduce(t, group=self.group)                     # backends without reduce-scatter
         return t[rank * rows:(rank + 1) * rows].contiguous()
 
-    def _addnorm_quant_gather(self, x_loc, gamma, residual_loc, peers=None):
-        """Local rows -> (codes [T, H] int8, scales [T] fp32 of ALL rows, new local residual)."""
+    def _addnorm_quant_gather(self, x_loc, gamma, residual_loc, peers=None, half=0):
+        """Local rows -> (codes [T, H] int8, scales [T] fp32 of ALL rows, new local residual).  With `peers` (push
+        collectives) x_loc is STAGED when the rows to normalise are the partial sums lying in peers.stage[1 - half]
+        (half 0: in front of qkv, the previous layer's down_proj; half 1: in front of gate/up, this layer's o_proj)."""
         if peers is not None:
-            q_loc, s_loc = peers.local_slices()
-            _, _, h, _ = ops.addnorm_quant_per_token(x_loc, gamma, self.shape.rms_eps, residual=residual_loc, out_q=q_loc, out_scale=s_loc)
-            q_all, s_all = peers.gather_codes()
-            return q_all, s_all, (h if h is not None else x_loc)
+            if x_loc is STAGED:
+                parts = peers.stage[1 - half]
+            else:
+                parts = x_loc.unsqueeze(0)
+            h = ops.addnorm_quant_per_token_tp(parts, gamma, self.shape.rms_eps, peers.code_ptrs[half], peers.scale_ptrs[half],
+                                               peers.rank * peers.rows, residual=residual_loc)
+            peers.barrier()
+            return peers.codes[half], peers.scales[half], (h if h is not None else x_loc)
         dist = torch.distributed
         tp, rank = self.tp, dist.get_rank(self.group)
         rows, hid = x_loc.shape
@@ -232,20 +247,18 @@ class DecoderLayer(nn.Module):
         s_all = torch.empty(tp * rows, dtype=torch.float32, device=x_loc.device)
         q_loc, s_loc = q_all[rank * rows:(rank + 1) * rows], s_all[rank * rows:(rank + 1) * rows]
         _, _, h, _ = ops.addnorm_quant_per_token(x_loc, gamma, self.shape.rms_eps, residual=residual_loc, out_q=q_loc, out_scale=s_loc)
-        if GATHER_CODES_AS_WORDS and hid % 4 == 0:
-            # same bytes, gathered as 32-bit words
-            dist.all_gather_into_tensor(q_all.view(torch.int32), q_loc.view(torch.int32), group=self.group)
-        else:
-            dist.all_gather_into_tensor(q_all, q_loc, group=self.group)
+        dist.all_gather_into_tensor(q_all, q_loc, group=self.group)
         dist.all_gather_into_tensor(s_all, s_loc, group=self.group)
         return q_all, s_all, (h if h is not None else x_loc)
 
-    def _row_parallel(self, linear, x, peers):
-        """A row-parallel Linear followed by the sum over ranks, local rows kept."""
+    def _row_parallel(self, linear, x, peers, half):
+        """A row-parallel Linear followed by the sum over ranks, local rows kept.  With `peers` the partial sums are
+        left in the owners' staging buffers (the next add + norm + quant kernel sums them) and STAGED is returned."""
         if peers is None:
             return self._reduce_scatter(linear(x))
-        linear(x, out=peers.partial)
-        return peers.reduce_scatter_partial()
+        linear.forward_scatter(x, peers.stage_ptrs[half], peers.rank, peers.rows, peers.hidden)
+        peers.barrier()
+        return STAGED
 
     def sp_attention_half(self, x_loc, cos, sin, branch_loc, b, s, peers=None):
         """First half of a token-sharded prefill layer: (previous MLP output + residual) -> norm ->
@@ -253,9 +266,9 @@ class DecoderLayer(nn.Module):
         x_loc / branch_loc: this rank's [b s / tp, hidden] rows.  Returns (x_loc, o_loc)."""
         shp, lin = self.shape, self.linears
         if branch_loc is None:
-            q8, ps, x_loc = self._addnorm_quant_gather(x_loc, self.input_norm, None, peers)
+            q8, ps, x_loc = self._addnorm_quant_gather(x_loc, self.input_norm, None, peers, 0)
         else:
-            q8, ps, x_loc = self._addnorm_quant_gather(branch_loc, self.input_norm, x_loc, peers)
+            q8, ps, x_loc = self._addnorm_quant_gather(branch_loc, self.input_norm, x_loc, peers, 0)
         qkv = lin.qkv_proj.forward_quantized(q8, ps).reshape(b, s, -1)
         ops.rope_inplace(qkv, self.heads + self.kv_heads, shp.head_dim, cos, sin)
         q, k, v = qkv.split((self.heads * shp.head_dim, self.kv_heads * shp.head_dim, self.kv_heads * shp.head_dim), dim=-1)
@@ -264,18 +277,18 @@ class DecoderLayer(nn.Module):
         v = v.reshape(b, s, self.kv_heads, shp.head_dim).transpose(1, 2)
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(b * s, self.heads * shp.head_dim)
-        return x_loc, self._row_parallel(lin.o_proj, attn, peers)
+        return x_loc, self._row_parallel(lin.o_proj, attn, peers, 0)
 
     def sp_mlp_half(self, x_loc, o_loc, peers=None):
         """Second half: (attention output + residual) -> norm -> quant -> all-gather -> gate/up with
         SwiGLU -> down_proj -> reduce-scatter.  Returns (x_loc, branch_loc)."""
         lin = self.linears
-        q8, ps, x_loc = self._addnorm_quant_gather(o_loc, self.post_norm, x_loc, peers)
+        q8, ps, x_loc = self._addnorm_quant_gather(o_loc, self.post_norm, x_loc, peers, 1)
         act = lin.gate_up_proj.forward_quantized(q8, ps)
         if not self.fused_swiglu:
             gate, up = act.chunk(2, dim=-1)
             act = F.silu(gate) * up
-        return x_loc, self._row_parallel(lin.down_proj, act, peers)
+        return x_loc, self._row_parallel(lin.down_proj, act, peers, 1)
 
     def forward_seq_parallel(self, x_loc, cos, sin, branch_loc, b, s, peers=None):
         """Prefill with a token-sharded residual stream: x_loc / branch_loc are this rank's
@@ -348,10 +361,10 @@ class LlamaW8A8(nn.Module):
 
     def __init__(self, shape=LLAMA3_70B, tp=1, rank=0, group=None, device='cuda', seed=4, n_layers=None, fused_swiglu=True,
                  fused_glue=True, seq_parallel=True, comm='nccl'):
-        """comm: 'nccl' (reduce-scatter / all-gather kernels) or 'ce' (copy-engine pulls over peer-mapped buffers, see
-        PeerBuffers; meant for micro_batches >= 2, where one micro-batch's copies run beside the other one's GEMMs)."""
+        """comm: collectives of the token-sharded prefill: 'nccl' (reduce-scatter / all-gather kernels) or 'push' (the
+        GEMM epilogue and the add + norm + quant kernel store into peer-mapped buffers themselves, see PeerBuffers)."""
         super().__init__()
-        if comm not in ('nccl', 'ce'):
+        if comm not in ('nccl', 'push'):
             raise ValueError(f'comm={comm!r}')
         self.comm, self._peers = comm, {}
         if shape.n_kv_heads % tp or shape.n_heads % tp or shape.intermediate % tp:
@@ -369,7 +382,7 @@ class LlamaW8A8(nn.Module):
                                     for _ in range(n_layers if n_layers is not None else shape.n_layers))
 
     def _peer_buffers(self, j, rows_total, device):
-        if self.comm != 'ce':
+        if self.comm != 'push':
             return None
         key = (j, rows_total)
         if key not in self._peers:
@@ -391,12 +404,12 @@ class LlamaW8A8(nn.Module):
         b, s = token_ids.shape
         if micro_batches is None:
             # one micro-batch by default: with two (two CUDA streams, ping-pong order) the collectives of one ran next to
-            # the GEMMs of the other only on paper -- measured 27.4 vs 27.9 k tokens/s at 2 GPUs, 68.0 vs 69.8 k at 8
-            # ... with NCCL.  Copy-engine collectives exist to run beside the other micro-batch's GEMMs: two by default
-            micro_batches = 2 if (self.comm == 'ce' and self.seq_parallel and kv_caches is None and b % 2 == 0) else 1
-        if self.comm == 'ce' and micro_batches > 2:
-            # four streams stalled at 8 GPUs (every barrier ran into its time limit); two are what has been measured
-            raise ValueError("comm='ce' runs at most two micro-batch streams")
+            # the GEMMs of the other only on paper (a persistent GEMM fills every SM): measured 27.4 vs 27.9 k tokens/s
+            # at 2 GPUs, 68.0 vs 69.8 k at 8 with NCCL
+            micro_batches = 1
+        if self.comm == 'push' and micro_batches > 2:
+            # more streams than two put spinning barrier blocks of one stream in front of another stream's work
+            raise ValueError("comm='push' runs at most two micro-batch streams")
         pos = torch.arange(past_len, past_len + s, device=token_ids.device)
         cos, sin = rotary_tables(self.shape, pos, token_ids.device)
         sp = self.seq_parallel and kv_caches is None and (b // micro_batches) * s % self.tp == 0 and b % micro_batches == 0
@@ -431,7 +444,7 @@ class LlamaW8A8(nn.Module):
                         xs[j], branches[j] = layer.sp_mlp_half(xs[j], outs[j], peers[j])
             for j, ids in enumerate(parts):
                 with torch.cuda.stream(self._streams[j]):
-                    loc = xs[j] + branches[j]
+                    loc = xs[j] + (sum_staged(peers[j].stage[1]) if branches[j] is STAGED else branches[j])
                     full = torch.empty((ids.numel(), loc.shape[1]), dtype=loc.dtype, device=loc.device)
                     torch.distributed.all_gather_into_tensor(full, loc, group=self.group)
                     xs[j] = full.reshape(ids.shape[0], s, -1)[:, -1:]
@@ -480,7 +493,7 @@ class LlamaW8A8(nn.Module):
         for layer in self.layers:
             x_loc, branch_loc = layer.forward_seq_parallel(x_loc, cos, sin, branch_loc, b, s, peers)
         if branch_loc is not None:
-            x_loc = x_loc + branch_loc
+            x_loc = x_loc + (sum_staged(peers.stage[1]) if branch_loc is STAGED else branch_loc)
         full = torch.empty((b * s, x_loc.shape[1]), dtype=x_loc.dtype, device=x_loc.device)
         torch.distributed.all_gather_into_tensor(full, x_loc.contiguous(), group=self.group)
         return full.reshape(b, s, -1)[:, -1:]

@@ -32,6 +32,8 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+# 320 Linears are converted per rank: keep the per-layer progress lines out of the output
+os.environ.setdefault('AMCT_LOG_LEVEL', 'warning')
 
 METRIC = 'w8a8_llama3_70b_prefill_tokens_per_s'
 UNIT = 'tokens/s'
@@ -53,21 +55,10 @@ def parse():
     ap.add_argument('--mode', default='prefill', choices=['prefill', 'decode'],
                     help='decode: one new token for 64 sequences against a 2048-token KV cache (not the headline metric)')
     ap.add_argument('--no-cuda-graph', action='store_true')
-    ap.add_argument('--comm', choices=('auto', 'nccl', 'ce'), default='auto',
-                    help="collectives of the token-sharded prefill: NCCL kernels, or copy-engine pulls over peer-mapped buffers "
-                         "beside two micro-batch streams (auto: the latter when N > 1, NCCL if one of its barriers times out)")
-    ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (2 streams when N > 1)')
-    ap.add_argument('--no-seq-parallel', action='store_true',
-                    help='A/B only: replicated activations + all-reduce instead of the token-sharded residual stream')
-    ap.add_argument('--torch-profile', default='',
-                    help='diagnostic: after the timed runs, profile one more step with torch.profiler on rank 0 and write the '
-                         'per-kernel totals (text) to this file')
-    ap.add_argument('--gemm-small-smem', action='store_true',
-                    help='A/B only: three-stage GEMM ring, leaving shared memory to communication kernels on the same SMs')
-    ap.add_argument('--gemm-ctas', type=int, default=0,
-                    help='A/B only: cap the persistent GEMM CTAs (AMCT_GEMM_MAX_CTAS), leaving SMs to the NCCL kernels')
-    ap.add_argument('--torch-glue', action='store_true',
-                    help='A/B only: RMSNorm, residual adds and rotary embedding as torch ops instead of the fused kernels')
+    ap.add_argument('--comm', choices=('auto', 'nccl', 'push'), default='auto',
+                    help="collectives of the token-sharded prefill: NCCL kernels, or the compute kernels' own stores into "
+                         "peer-mapped buffers (auto: the latter when N > 1, NCCL if one of its barriers times out)")
+    ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (one stream)')
     return ap.parse_args()
 
 
@@ -185,11 +176,6 @@ def main():
     args = parse()
     if args.impl == 'reference':
         return run_reference(args)
-    if args.gemm_ctas:
-        os.environ['AMCT_GEMM_MAX_CTAS'] = str(args.gemm_ctas)
-    if args.gemm_small_smem:
-        os.environ['AMCT_GEMM_SMEM'] = 'small'
-
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
     local = int(os.environ.get('LOCAL_RANK', '0'))
@@ -200,7 +186,8 @@ def main():
     import torch.distributed as dist
     group = None
     if world > 1:
-        dist.init_process_group('nccl', device_id=dev, timeout=datetime.timedelta(seconds=300))
+        # a stalled collective ends the run after a minute instead of holding the GPUs
+        dist.init_process_group('nccl', device_id=dev, timeout=datetime.timedelta(seconds=60))
         group = dist.group.WORLD
 
     from amct_b200.backend import ops
@@ -208,11 +195,9 @@ def main():
 
     comm = args.comm
     if comm == 'auto':
-        sharded_prefill = world > 1 and args.mode == 'prefill' and not args.no_seq_parallel and not args.torch_glue
-        comm = 'ce' if sharded_prefill else 'nccl'
+        comm = 'push' if (world > 1 and args.mode == 'prefill') else 'nccl'
     t_build = time.time()
-    model = LlamaW8A8(LLAMA3_70B, tp=world, rank=rank, group=group, device=dev, seed=SEED, n_layers=args.layers,
-                      fused_glue=not args.torch_glue, seq_parallel=not args.no_seq_parallel, comm=comm)
+    model = LlamaW8A8(LLAMA3_70B, tp=world, rank=rank, group=group, device=dev, seed=SEED, n_layers=args.layers, comm=comm)
     torch.cuda.synchronize()
     t_build = time.time() - t_build
 
@@ -248,11 +233,11 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    mb = args.micro_batches or (2 if comm == 'ce' else None)
+    mb = args.micro_batches or None
 
     def comm_failed():
-        """True on every rank if a barrier of the copy-engine collectives gave up waiting on any rank."""
-        if world == 1 or model.comm != 'ce':
+        """True on every rank if a barrier of the push collectives gave up waiting on any rank."""
+        if world == 1 or model.comm != 'push':
             return False
         try:
             model.check_comm()
@@ -266,7 +251,7 @@ def main():
     def fall_back(when):
         nonlocal mb
         if rank == 0:
-            print(f'bench.py: a barrier of the copy-engine collectives timed out {when}; measuring with NCCL instead',
+            print(f'bench.py: a barrier of the push collectives timed out {when}; measuring with NCCL instead',
                   file=sys.stderr, flush=True)
         model.comm, mb = 'nccl', (args.micro_batches or None)
         for _ in range(args.warmup):
@@ -317,16 +302,6 @@ def main():
     if comm_failed():
         fall_back('in the timed region')
         ms_total, launches, clocks, ms_e2e = measure()
-    if args.torch_profile:
-        from torch.profiler import profile, ProfilerActivity
-        if world > 1:
-            dist.barrier()
-        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
-            step_resident()
-            torch.cuda.synchronize()
-        if rank == 0:
-            with open(args.torch_profile, 'w') as f:
-                f.write(prof.key_averages().table(sort_by='cuda_time_total', row_limit=40, max_name_column_width=70))
 
     # roofline of the dominant kernel: one more step with CUDA events around every GEMM launch
     ops.GEMM_PROFILE = []

@@ -160,6 +160,11 @@ int amct_gemm_w8a8(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64
                    const float* deq_scale, const float* pertoken_scale, const void* bias, int bias_kind,
                    void* out, int out_kind, int64_t ld_out, int* status, void* stream);
 
+/* Which kernel takes m > 128: chosen by the size of b (AUTO), or pinned to the one-CTA / the CTA-pair kernel
+ * (tests and comparisons).  Process-wide; returns AMCT_ERR_ARG for another value. */
+enum { AMCT_GEMM_VARIANT_AUTO = 0, AMCT_GEMM_VARIANT_SINGLE = 1, AMCT_GEMM_VARIANT_PAIR = 2 };
+int amct_gemm_set_variant(int variant);
+
 /* amct_gemm_w8a8 in per-token mode with a SwiGLU epilogue, for a fused gate/up projection
  * whose weight rows are interleaved in blocks of 128: rows [256 j, 256 j + 128) are gate
  * channels [128 j, 128 j + 128) and the next 128 rows the matching up channels (n % 256 == 0).
@@ -346,11 +351,38 @@ int amct_addnorm_quant_pertoken(const void* x, const void* residual, int dtype, 
 int amct_rope_inplace(void* x, int dtype, int64_t tokens, int64_t ld, int heads, int head_dim,
                       const void* cos_table, const void* sin_table, int64_t seq, void* stream);
 
+/* amct_gemm_w8a8 (per-token mode, no bias, fp16 / bf16 output) for a K-sharded ("row-parallel") Linear under tensor
+ * parallelism, whose [m, n] result is one rank's PARTIAL sum: instead of one output matrix, output row r is
+ * written to row (slot * rows_per_rank + r % rows_per_rank) of out_ptrs[r / rows_per_rank], the staging buffer
+ * [world * rows_per_rank, ld_out] of the rank that owns token rows [j rows_per_rank, (j + 1) rows_per_rank).
+ * out_ptrs is a host array of `world` device pointers (this process's peer mappings of every rank's buffer, its
+ * own included); slot = this rank.  The epilogue stores whole 128-byte row segments with plain st.global, so
+ * the reduce-scatter's transfer runs tile by tile inside the GEMM; the caller orders it against the readers with
+ * amct_peer_barrier.  n % 64 == 0; m <= world * rows_per_rank.  The sharded form of
+ * NpuQuantizationLinear.forward (amct_pytorch/deploy_op/npu_quantization_linear.py:89-103); the reference has no
+ * multi-device path. */
+int amct_gemm_w8a8_scatter(const int8_t* a, const int8_t* b, int64_t m, int64_t n, int64_t k, int64_t ld_a,
+                           int64_t ld_b, const float* deq_scale, const float* pertoken_scale, void* const* out_ptrs,
+                           int world, int slot, int64_t rows_per_rank, int out_kind, int64_t ld_out, int* status,
+                           void* stream);
+
+/* amct_addnorm_quant_pertoken for the token-sharded residual stream of that workload.  Input: `parts` holds
+ * n_parts partial sums of this rank's `rows` rows, part j at parts + j * part_stride elements (what
+ * amct_gemm_w8a8_scatter staged); x = their fp32 sum in that order rounded once to dtype, then as
+ * amct_addnorm_quant_pertoken (residual add, RMSNorm, per-token INT8 rule).  Output: codes and scale of row r go
+ * to row (row0 + r) of EVERY rank's buffers q_all[d] [*, ld_q] / scale_all[d] (host arrays of `world` device
+ * pointers, peer mappings), i.e. the all-gather of the codes happens in this kernel's stores. */
+int amct_addnorm_quant_pertoken_tp(const void* parts, int n_parts, int64_t part_stride, const void* residual,
+                                   int dtype, int64_t rows, int64_t k, int64_t ld_x, int64_t ld_res,
+                                   const void* gamma, float eps, void* residual_out, int64_t ld_res_out,
+                                   int8_t* const* q_all, float* const* scale_all, int world, int64_t row0,
+                                   int64_t ld_q, int* status, void* stream);
+
 /* Barrier number `seq` between the `world` ranks of one node, in stream order, for collectives made of plain
  * device-to-device copies: flag_arrays[r] is rank r's array of `world` zero-initialised 32-bit words in memory every
  * rank has mapped (host array of device pointers, r = 0 .. world-1; world <= 16).  Callers count seq 1, 2, 3 ... the
  * same on every rank.  One 32-thread block; a peer that has not arrived within two seconds sets bit 1 of *status and
- * the kernel returns; with that bit already set the barrier returns at once.  No counterpart in the reference (it
+ * the kernel returns; with that bit already set the barrier still signals its peers but does not wait.  No counterpart in the reference (it
  * has no multi-device path); serves the tensor-parallel workload around NpuQuantizationLinear. */
 int amct_peer_barrier(void* const* flag_arrays, int world, int rank, uint32_t seq, int* status, void* stream);
 

@@ -28,19 +28,12 @@ def status():
     return torch.zeros(1, dtype=torch.int32, device='cuda')
 
 
-@pytest.fixture(params=['auto', 'single', 'pair', 'small_smem', 'capped'])
-def variant(request, monkeypatch):
-    """Which kernel takes M > 128: the size rule, the one-CTA kernel, the CTA-pair kernel, the one-CTA kernel
-    with the three-stage ring, or either with the number of persistent CTAs capped."""
-    for name in ('AMCT_GEMM_VARIANT', 'AMCT_GEMM_SMEM', 'AMCT_GEMM_MAX_CTAS'):
-        monkeypatch.delenv(name, raising=False)
-    if request.param in ('single', 'pair'):
-        monkeypatch.setenv('AMCT_GEMM_VARIANT', request.param)
-    elif request.param == 'small_smem':
-        monkeypatch.setenv('AMCT_GEMM_SMEM', 'small')
-    elif request.param == 'capped':
-        monkeypatch.setenv('AMCT_GEMM_MAX_CTAS', '6')
-    return request.param
+@pytest.fixture(params=['auto', 'single', 'pair'])
+def variant(request):
+    """Which kernel takes M > 128: the size rule, the one-CTA kernel or the CTA-pair kernel."""
+    ops().set_gemm_variant(request.param)
+    yield request.param
+    ops().set_gemm_variant('auto')
 
 
 @pytest.mark.parametrize('m,n,k', SHAPES)
@@ -74,6 +67,37 @@ def test_w8a8_epilogues(m, n, k, out_dtype, mode, variant):
     ops().raise_if_timed_out(st)
     # same fp32 steps in the same order, one final rounding: bit-exact in every output dtype
     assert bits_equal(got, want)
+
+
+@pytest.mark.parametrize('m,n,k,rows_per_rank,world', [(384, 192, 320, 96, 4), (300, 64, 128, 128, 3), (1024, 512, 256, 128, 8),
+                                                       (40, 128, 64, 40, 1), (513, 320, 96, 260, 2)])
+@pytest.mark.parametrize('out_dtype', [torch.bfloat16, torch.float16])
+def test_w8a8_scatter_epilogue_places_rows_in_owner_slots(m, n, k, rows_per_rank, world, out_dtype, variant):
+    """The row-parallel GEMM of the tensor-parallel workload: output row r lands in row (slot * rows_per_rank + r %
+    rows_per_rank) of the staging buffer of rank r // rows_per_rank, with the values amct_gemm_w8a8 stores.  One GPU:
+    the "ranks'" buffers are separate local tensors (tiles straddle owners when rows_per_rank is not a tile multiple)."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a, b = rand_i8(g, m, k).cuda(), rand_i8(g, n, k).cuda()
+    deq = (torch.rand(n, generator=g) * 1e-3 + 1e-4).cuda()
+    pertoken = (torch.rand(m, generator=g) * 0.05 + 0.01).cuda()
+    want = ops().gemm_w8a8(a, b, deq, pertoken, None, out_dtype=out_dtype)
+    ld = n + 8                                                     # staging rows wider than n
+    fill = 7.0
+    for slot in {0, world - 1}:
+        stages = [torch.full((world * rows_per_rank, ld), fill, dtype=out_dtype, device='cuda') for _ in range(world)]
+        st = status()
+        ops().gemm_w8a8_scatter(a, b, deq, pertoken, [t.data_ptr() for t in stages], slot, rows_per_rank, ld,
+                                out_dtype=out_dtype, status=st)
+        ops().raise_if_timed_out(st)
+        for owner in range(world):
+            lo, hi = owner * rows_per_rank, min(m, (owner + 1) * rows_per_rank)
+            got = stages[owner].reshape(world, rows_per_rank, ld)
+            if hi > lo:
+                assert bits_equal(got[slot, :hi - lo, :n], want[lo:hi]), (owner, slot)
+            # nothing else was touched: other slots, rows beyond m, the padding columns
+            untouched = got.clone()
+            untouched[slot, :max(hi - lo, 0), :n] = fill
+            assert bool((untouched == fill).all()), (owner, slot)
 
 
 def test_w8a8_strided_operands_and_repeat():

@@ -64,6 +64,37 @@ def test_addnorm_quant_matches_oracle(dtype, rows, k, with_res):
     assert int(ulp_distance(n, nt).max()) <= 2
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('n_parts,rows,k,world', [(1, 5, 1024, 2), (2, 33, 2048, 2), (4, 20, 8192, 4), (8, 9, 4096, 8), (3, 7, 520, 3)])
+@pytest.mark.parametrize('with_res', [True, False])
+def test_addnorm_quant_tp_sums_parts_and_stores_to_every_rank(dtype, n_parts, rows, k, world, with_res):
+    """The tensor-parallel form: x = fp32 sum of the staged partial sums in rank order, rounded once; after that the
+    very arithmetic of addnorm_quant_per_token (so codes and scales are bit-identical to that kernel on the summed
+    rows); codes and scales are stored into row0 + r of every rank's buffer (here: separate local tensors)."""
+    g = torch.Generator().manual_seed(n_parts * 1000 + rows * 7 + k)
+    parts = (torch.randn(n_parts, rows, k, generator=g) * 1.3).to(dtype)
+    res = (torch.randn(rows, k, generator=g) * 2.0).to(dtype) if with_res else None
+    gamma = (1 + 0.1 * torch.randn(k, generator=g)).to(dtype)
+    acc = parts[0].float()
+    for j in range(1, n_parts):
+        acc = acc + parts[j].float()
+    x_sum = acc.to(dtype)
+    eps, row0, total = 1e-5, 3, rows + 11
+    q_ref, s_ref, h_ref, _ = ops().addnorm_quant_per_token(x_sum.cuda(), gamma.cuda(), eps, residual=None if res is None else res.cuda())
+    q_bufs = [torch.full((total, k), 99, dtype=torch.int8).cuda() for _ in range(world)]
+    s_bufs = [torch.full((total,), -1.0, dtype=torch.float32).cuda() for _ in range(world)]
+    h = ops().addnorm_quant_per_token_tp(parts.cuda(), gamma.cuda(), eps, [t.data_ptr() for t in q_bufs],
+                                         [t.data_ptr() for t in s_bufs], row0, residual=None if res is None else res.cuda())
+    if with_res:
+        assert bits_equal(h, h_ref) and bits_equal(h, x_sum + res)
+    else:
+        assert h is None
+    for d in range(world):
+        assert bits_equal(q_bufs[d][row0:row0 + rows], q_ref) and bits_equal(s_bufs[d][row0:row0 + rows], s_ref)
+        assert bool((q_bufs[d][:row0] == 99).all()) and bool((q_bufs[d][row0 + rows:] == 99).all())
+        assert bool((s_bufs[d][:row0] == -1).all()) and bool((s_bufs[d][row0 + rows:] == -1).all())
+
+
 def test_addnorm_quant_strided_and_batched():
     g = torch.Generator().manual_seed(5)
     big = torch.randn(4, 6, 2048 + 64, generator=g).to(torch.bfloat16).cuda()
