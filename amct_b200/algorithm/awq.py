@@ -10,18 +10,51 @@ GRIDS_NUM = 'grids_num'
 
 def fake_quantize_scaled(weight, scale_awq, quant_config):
     """((W * s) fake-quantized with fresh min-max factors) / s, as process_weights_for_layers
-    (awq.py:30-49) leaves it in layer.weight."""
+    (awq.py:30-49) leaves it in layer.weight.  Channel and group granularity: ONE kernel launch does the multiply by
+    s (rounded to the weight dtype like the reference's tensor op), the min-max factors and the AWQ fake quantization
+    from a single read of W; the tensor granularity needs the tensor-wide bounds first."""
     cfg = quant_config.get('weights_cfg')
     qt, sym, strat, gs = cfg.get('quant_type'), cfg.get('symmetric'), cfg.get('strategy'), cfg.get('group_size')
-    scaled = weight.mul(scale_awq)
     if strat == 'tensor':
+        scaled = weight.mul(scale_awq)
         mn, mx = ops.minmax(scaled, 'tensor')
         s, o = ops.scale_offset(mx, mn, sym, qt)
-        _, _, fq = ops.quant_rows(scaled, qt, sym, strat, gs, scale=s, offset=o, out='fake_awq')
+        _, _, fq = ops.quant_rows(scaled, qt, sym, strat, gs, scale=s, offset=o, out='fake_awq', check=False)
     else:
-        s, o, _ = ops.quant_rows(scaled, qt, sym, strat, gs, out='none')
-        _, _, fq = ops.quant_rows(scaled, qt, sym, strat, gs, scale=s, offset=o, out='fake_awq')
+        _, _, fq = ops.quant_rows(weight, qt, sym, strat, gs, out='fake_awq', pre=scale_awq, pre_op='mul', check=False)
     return fq / scale_awq
+
+
+def _per_unit(weight, granularity, group_size):
+    """weight viewed so that the quant factors broadcast over it: [N, K/g, g] for groups, as it is otherwise."""
+    if granularity != 'group':
+        return weight
+    n, k = weight.shape
+    pad = (-k) % group_size
+    if pad:
+        weight = torch.nn.functional.pad(weight, (0, pad))
+    return weight.reshape(n, -1, group_size)
+
+
+def do_quant(weight, scale_w, offset_w, weight_granularity, group_size=None):
+    """weight / scale_w (+ offset_w) in the weight's dtype, not yet rounded to integers: the first of the three steps the
+    reference composes its AWQ fake quantization from (awq.py:129-149).  The search loop here uses the fused kernel
+    mode instead (AMCT_OUT_FAKE_AWQ: this step, convert_precision and do_dequant in one pass); the step is offered
+    under its own name for callers that used it directly.  Device tensors in, device tensor out."""
+    shape, dtype = weight.shape, weight.dtype
+    t = _per_unit(weight, weight_granularity, group_size) / scale_w
+    if offset_w is not None:
+        t = t + offset_w
+    return t.reshape(shape[0], -1)[:, :shape[1]].to(dtype)
+
+
+def do_dequant(weight, scale, offset, weight_granularity, group_size=None):
+    """(weight - offset) * scale, the last of the three steps (awq.py:152-170)."""
+    shape = weight.shape
+    t = _per_unit(weight, weight_granularity, group_size)
+    if offset is not None:
+        t = t - offset
+    return (t * scale).reshape(shape[0], -1)[:, :shape[1]].to(weight.dtype)
 
 
 def calculate_scale_offset_by_granularity(weight, quant_config):
@@ -58,16 +91,20 @@ def search_scale(inputs, layer, quant_config):
     ori_out = layer(inputs)
     ori_weight = layer.weight.data.clone()
     mean = inputs.abs().contiguous().view(-1, inputs.shape[-1]).mean(0)
-    best, best_loss = None, torch.tensor(float('inf'), device=inputs.device)
+    # the whole search stays on the device: candidate scale, fused scale + fake-quant kernel, the layer's GEMM, the
+    # 4th-power loss, and the running best kept with torch.where -- the host reads one number, after the last candidate
+    best = torch.ones((1, inputs.shape[-1]), dtype=inputs.dtype, device=inputs.device)
+    best_loss = torch.full((), float('inf'), device=inputs.device)
     for grid in range(grids):
         s = mean.pow(grid / grids).clamp(min=1e-4).to(torch.float64).view(1, -1)
         s = s / (s.max() * s.min()).sqrt()
         s = torch.clamp(s.to(inputs.dtype), 1e-4, torch.finfo(inputs.dtype).max)
         layer.weight.data = fake_quantize_scaled(ori_weight, s, quant_config)
         loss = (ori_out - layer(inputs)).float().pow(4).mean()
-        if not torch.isnan(loss) and loss < best_loss:
-            best_loss, best = loss, s
+        better = ~torch.isnan(loss) & (loss < best_loss)
+        best_loss = torch.where(better, loss, best_loss)
+        best = torch.where(better, s, best)
         layer.weight.data = ori_weight
-    if best is None or torch.isinf(best_loss):
+    if bool(torch.isinf(best_loss)):
         raise RuntimeError("Run AWQ error! Got invalid loss.")
     return best

@@ -51,6 +51,7 @@ def load():
         lib.amct_minmax_workspace_bytes.argtypes = [ctypes.c_int64]
         lib.amct_minmax_noalloc_max_k.restype = ctypes.c_int64
         lib.amct_mx_tiled_scale_bytes.restype = ctypes.c_int64
+        lib.amct_mma_peak_ops_per_cta_step.restype = ctypes.c_int64
         _lib = lib
     return _lib
 

@@ -14,7 +14,7 @@ from . import lib as _l
 _DT = {torch.float32: _l.DTYPE_F32, torch.float16: _l.DTYPE_F16, torch.bfloat16: _l.DTYPE_BF16}
 # launches of this library's kernels since the counter was last reset (bench.py reads it)
 COUNTERS = {'launches': 0}
-# when set to a list, every GEMM launch appends (start event, end event, 2*M*N*K)
+# when set to a list, every GEMM launch appends (start event, end event, 2*M*N*K, stream handle)
 GEMM_PROFILE = None
 
 SCALE_ERROR = "Param scale has invalid value inf, nan or zeros!"      # amct_pytorch/quantize_op/utils.py:66-67
@@ -275,7 +275,7 @@ def _prof_end(start, n_ops):
     if start is not None:
         e = torch.cuda.Event(enable_timing=True)
         e.record()
-        GEMM_PROFILE.append((start, e, n_ops))
+        GEMM_PROFILE.append((start, e, n_ops, _stream().value))
 
 
 def _kmajor(t):
@@ -323,6 +323,21 @@ def gemm_w8a8(q, w_nk, deq_scale=None, pertoken_scale=None, bias=None, out_dtype
     COUNTERS['launches'] += 1
     _prof_end(prof, 2 * m * n * k)
     return out
+
+
+MMA_KINDS = {'i8': 0, 'bf16': 1, 'mxf8': 2, 'mxf4': 3}
+
+
+def mma_peak(kind, steps=20000, ctas=None, status=None):
+    """Enqueues the MMA-only kernel (tensor-core peak measurement) and returns the operations it performs."""
+    L = _l.load()
+    if ctas is None:
+        ctas = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    code = MMA_KINDS[kind]
+    rc = L.amct_mma_peak(c_int(code), c_int(steps), c_int(ctas), _p(status) if status is not None else c_void_p(0), _stream())
+    _l.check(rc, 'amct_mma_peak')
+    COUNTERS['launches'] += 1
+    return ctas * steps * int(L.amct_mma_peak_ops_per_cta_step(c_int(code)))
 
 
 def set_gemm_variant(variant):
@@ -538,7 +553,8 @@ def mx_quant(x, fmt, operand='a', tiled=True, rowmajor=True):
     L = _l.load()
     st = None
     if tiled:
-        st = torch.zeros(L.amct_mx_tiled_scale_bytes(c_int64(rows), c_int64(k), c_int(MX_TILE_ROWS[operand])),
+        # the kernel writes the layout's padding itself: no clearing pass over the buffer
+        st = torch.empty(L.amct_mx_tiled_scale_bytes(c_int64(rows), c_int64(k), c_int(MX_TILE_ROWS[operand])),
                          dtype=torch.uint8, device=x.device)
     rc = L.amct_mx_quant(_p(x2), c_int(_dt(x2)), c_int64(rows), c_int64(k), c_int64(ld), c_int(bits), _p(payload),
                          _p(srm), _p(st), c_int(MX_TILE_ROWS[operand]), _stream())
@@ -702,6 +718,25 @@ def addnorm_quant_per_token_tp(parts, gamma, eps, q_ptrs, scale_ptrs, row0, resi
     _l.check(rc, 'amct_addnorm_quant_pertoken_tp')
     COUNTERS['launches'] += 1
     return h
+
+
+def gptq_block(w_block, hinv_block, scale, offset, col_group, bits):
+    """One block of GPTQ's column loop in one launch.  w_block [N, b] fp32 (a column slice of the permuted weight, updated
+    in place), hinv_block [b, b] fp32, scale fp32 / offset int32 [N or 1, G], col_group int32 [b].  Returns err [N, b]."""
+    _need_cuda(w_block, hinv_block, scale, offset, col_group)
+    n, b = w_block.shape
+    assert w_block.dtype == torch.float32 and w_block.stride(1) == 1 and hinv_block.dtype == torch.float32 and hinv_block.stride(1) == 1
+    scale = scale.reshape(scale.shape[0], -1).to(torch.float32).contiguous()
+    if offset is not None:
+        offset = offset.reshape(offset.shape[0], -1).to(torch.int32).contiguous()
+    col_group = col_group.to(torch.int32).contiguous()
+    err = torch.empty((n, b), dtype=torch.float32, device=w_block.device)
+    rc = _l.load().amct_gptq_block(_p(w_block), c_int64(n), c_int64(w_block.stride(0)), c_int(b), _p(hinv_block),
+                                   c_int64(hinv_block.stride(0)), _p(scale), _p(offset), c_int64(scale.shape[1]),
+                                   c_int(1 if scale.shape[0] > 1 else 0), _p(col_group), c_int(bits), _p(err), c_int64(b), _stream())
+    _l.check(rc, 'amct_gptq_block')
+    COUNTERS['launches'] += 1
+    return err
 
 
 def rope_inplace(x, heads, head_dim, cos, sin):

@@ -90,6 +90,26 @@ __device__ __forceinline__ float warp_min(float v) {
   return v;
 }
 
+// NaN-propagating fp32 min / max (one instruction; fminf / fmaxf return the other operand instead).
+__device__ __forceinline__ float fmin_nan(float a, float b) {
+#ifdef AMCT_CUDA_EMU
+  return (a != a || b != b) ? NAN : fminf(a, b);
+#else
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+#endif
+}
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+#ifdef AMCT_CUDA_EMU
+  return (a != a || b != b) ? NAN : fmaxf(a, b);
+#else
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+#endif
+}
+
 // Monotonic float <-> int mapping, so integer atomicMin/Max order floats.
 __device__ __forceinline__ int f2ord(float f) {
   int b = __float_as_int(f);

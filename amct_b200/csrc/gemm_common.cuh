@@ -43,7 +43,18 @@ struct GemmParams {
   int scatter_world, scatter_slot;
   int64_t scatter_rows;
   void* scatter_out[kMaxScatterRanks];
+  // Rows by which the walk over the m-tiles starts later (scatter mode: rank s starts with the rows of rank s + 1,
+  // so that at any moment the ranks write to DIFFERENT owners; all starting at row 0 would aim every rank's
+  // stores at one GPU at a time and the transfer would run at one GPU's ingress bandwidth, not at everybody's).
+  int64_t row_rot;
 };
+
+// the m-tile a kernel works on for the rasterised index tm, with the start of the walk rotated by p.row_rot rows
+__device__ __forceinline__ int64_t rotate_tile_m(const GemmParams& p, int64_t tm, int64_t tiles_m, int tile_rows) {
+  if (p.row_rot == 0) return tm;
+  const int64_t r = (tm + p.row_rot / tile_rows) % tiles_m;
+  return r;
+}
 
 // Rasterisation: GROUP m-tiles x all n-tiles per group, m fastest, so that the tiles in flight
 // at one time share a few A row blocks and a few B row blocks in L2.

@@ -424,6 +424,13 @@ static int launch_dq(const CUtensorMap& mc, const CUtensorMap& mx, const DqParam
 
 }  // namespace amct
 
+namespace amct {
+// w4a16_stream.cu; returns 1 when the shape does not fit it
+int w4a16_stream_try(const void* x, int dtype, const void* codes, int64_t m, int64_t n, int64_t k, int64_t ld_x,
+                     int64_t ld_codes, const void* scale, const void* offset, int group, const void* bias, int bias_kind,
+                     void* out, int out_kind, int64_t ld_out, cudaStream_t st);
+}  // namespace amct
+
 static int run_dq(const void* x, int dtype, const void* codes, int bits, int64_t m, int64_t n, int64_t k, int64_t ld_x,
                   int64_t ld_codes, const void* scale, const void* offset, const void* lut, int group, const void* bias,
                   int bias_kind, void* out, int out_kind, int64_t ld_out, int* status, cudaStream_t st) {
@@ -477,6 +484,15 @@ extern "C" int amct_gemm_w4a16(const void* x, int dtype, const void* codes, int 
                                void* stream) {
   if (bits != 4 && bits != 8) return AMCT_ERR_ARG;
   if (m > 0 && n > 0 && !scale) return AMCT_ERR_ARG;
+  // a handful of tokens: the weight-streaming kernel of w4a16_stream.cu (same values, all SMs busy)
+  if (bits == 4 && m >= 1 && m <= 16 && n > 0 && k > 0 && x && codes && out && group >= 0 && ld_x >= k && ld_out >= n &&
+      ld_codes >= k / 2 && (dtype == AMCT_DTYPE_F16 || dtype == AMCT_DTYPE_BF16) && bias_kind >= amct::BIAS_NONE &&
+      bias_kind <= amct::BIAS_BF16 && bias_kind != amct::BIAS_I32 && (!bias_kind || bias) && out_kind >= amct::OUT_F32 &&
+      out_kind <= amct::OUT_BF16) {
+    const int rc = amct::w4a16_stream_try(x, dtype, codes, m, n, k, ld_x, ld_codes, scale, offset, group, bias, bias_kind, out,
+                                          out_kind, ld_out, (cudaStream_t)stream);
+    if (rc != 1) return rc;
+  }
   return run_dq(x, dtype, codes, bits, m, n, k, ld_x, ld_codes, scale, offset, nullptr, group, bias, bias_kind, out, out_kind,
                 ld_out, status, (cudaStream_t)stream);
 }

@@ -92,6 +92,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int64_t tm, tn;
         tile_coords<kGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+        tm = rotate_tile_m(p, tm, tiles_m, kBM);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
           if (!tc05::mbar_wait(tc05::smem_u32(&s.empty[stage]), phase ^ 1, abort_flag)) { alive = false; break; }
           const uint32_t bar = tc05::smem_u32(&s.full[stage]);
@@ -146,6 +147,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int64_t tm, tn;
       tile_coords<kGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+      tm = rotate_tile_m(p, tm, tiles_m, kBM);
       const int64_t n0 = tn * kBN;
       const int64_t row = tm * kBM + quarter * 32 + lane;
       // stage the per-column factors of this tile (per warp, so only __syncwarp is needed)
@@ -399,6 +401,7 @@ extern "C" int amct_gemm_w8a8_scatter(const int8_t* a, const int8_t* b, int64_t 
   p.deq = deq_scale; p.pertoken = pertoken_scale; p.bias_kind = amct::BIAS_NONE;
   p.out_kind = out_kind; p.ld_out = ld_out; p.status = status;
   p.scatter_world = world; p.scatter_slot = slot; p.scatter_rows = rows_per_rank;
+  p.row_rot = ((int64_t)(slot + 1) % world) * rows_per_rank;
   for (int r = 0; r < world; ++r) {
     if (!out_ptrs[r]) return AMCT_ERR_ARG;
     if (!amct::aligned16(out_ptrs[r])) return AMCT_ERR_ALIGN;

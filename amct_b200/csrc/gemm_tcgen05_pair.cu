@@ -86,6 +86,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       for (int64_t tile = pair_id; tile < num_tiles && alive; tile += num_pairs) {
         int64_t tm, tn;
         tile_coords<kPairGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+        tm = rotate_tile_m(p, tm, tiles_m, 2 * kBM);
         const int row_a = (int)(tm * 2 * kBM + rank * kBM);
         const int row_b = (int)(tn * kBN + rank * (kBN / 2));
         for (int64_t kb = 0; kb < num_kb; ++kb) {
@@ -148,6 +149,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     for (int64_t tile = pair_id; tile < num_tiles; tile += num_pairs) {
       int64_t tm, tn;
       tile_coords<kPairGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+      tm = rotate_tile_m(p, tm, tiles_m, 2 * kBM);
       const int64_t n0 = tn * kBN;
       const int64_t row = tm * 2 * kBM + rank * kBM + quarter * 32 + lane;
       for (int c = lane; c < kBN; c += 32) {

@@ -10,6 +10,8 @@
 //
 // Both directions are elementwise and HBM-bound: encode reads sizeof(T) and writes 1 byte
 // per element, decode the reverse.  Decoding is exact in fp16, bf16 and fp32.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace amct {
@@ -108,11 +110,31 @@ __device__ __forceinline__ uint32_t hif8_lookup(const uint8_t* tab, float x) {
 // CTA (building the 4096 entries in each CTA cost as much as the encoding itself).
 static __device__ __align__(16) uint8_t g_hif8_tab[4096];
 static __device__ __align__(16) float g_hif8_dec[256];
+// bfloat16 input needs no detour through fp32: its top 13 bits (sign, exponent, four mantissa bits) ARE the table
+// index.  g_hif8_tab13[i] = code of the bf16 pattern i << 3 (sign included, -0 and flushed negatives are code 0);
+// g_hif8_fq13[i] = bf16 pattern of decode(that code): fake quantization bf16 -> bf16 is one lookup.
+// Decoded values as 16-bit patterns (decoding is exact in both types): index 0 = bf16, 1 = fp16.
+static __device__ __align__(16) uint8_t g_hif8_tab13[8192];
+static __device__ __align__(16) uint16_t g_hif8_fq13[8192];
+static __device__ __align__(16) uint16_t g_hif8_dec16[2][256];
 
 __global__ void hif8_init_tables() {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < 4096) g_hif8_tab[i] = (uint8_t)hif8_encode(__uint_as_float((uint32_t)i << 19));
-  if (i < 256) g_hif8_dec[i] = hif8_decode(i);
+  if (i < 8192) {
+    const uint32_t code = hif8_encode(__uint_as_float((uint32_t)i << 19));
+    g_hif8_tab13[i] = (uint8_t)code;
+    const __nv_bfloat16 v = __float2bfloat16_rn(hif8_decode(code));
+    g_hif8_fq13[i] = *reinterpret_cast<const uint16_t*>(&v);
+  }
+  if (i < 256) {
+    const float d = hif8_decode(i);
+    g_hif8_dec[i] = d;
+    const __nv_bfloat16 b = __float2bfloat16_rn(d);
+    const __half h = __float2half_rn(d);
+    g_hif8_dec16[0][i] = *reinterpret_cast<const uint16_t*>(&b);
+    g_hif8_dec16[1][i] = *reinterpret_cast<const uint16_t*>(&h);
+  }
 }
 
 // Launch-ordered on `st` before the first use on each device; repeating it is harmless.
@@ -122,7 +144,7 @@ static int ensure_tables(cudaStream_t st) {
   if (cudaGetDevice(&dev) != cudaSuccess) return AMCT_ERR_CUDA;
   if (dev >= 0 && dev < 64 && done[dev]) return AMCT_OK;
   // the tables must be complete before any later kernel on any stream reads them
-  AMCT_LAUNCH(16, 256, st, (), hif8_init_tables);
+  AMCT_LAUNCH(32, 256, st, (), hif8_init_tables);
   AMCT_CHECK_LAUNCH();
   if (cudaStreamSynchronize(st) != cudaSuccess) return AMCT_ERR_CUDA;
   if (dev >= 0 && dev < 64) done[dev] = true;
@@ -204,6 +226,103 @@ __global__ void __launch_bounds__(256) hif8_decode_kernel(const uint8_t* codes, 
   }
 }
 
+// bfloat16 input: the table index is cut straight out of the 16-bit pattern -- (w >> 3) & 0x1FFF and w >> 19 for the two
+// halves of a word -- and the entry already carries the sign.  The one case the index cannot tell apart is a NaN
+// whose payload sits in the three lowest mantissa bits only (it shares its index with Inf); a vector that holds any
+// all-ones exponent, found with three integer instructions per word, is redone element by element.
+// MODE 0: codes; MODE 1: fake quantization (bf16 out).
+template <int MODE>
+__global__ void __launch_bounds__(256) hif8_encode_bf16_kernel(const __nv_bfloat16* x, int64_t n, uint8_t* codes,
+                                                               __nv_bfloat16* fake) {
+  using Entry = typename std::conditional<MODE == 0, uint8_t, uint16_t>::type;
+  __shared__ __align__(16) Entry tab[8192];
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(MODE == 0 ? reinterpret_cast<const void*>(g_hif8_tab13)
+                                                                : reinterpret_cast<const void*>(g_hif8_fq13));
+    constexpr int kVecs = 8192 * (int)sizeof(Entry) / 16;
+    for (int i = threadIdx.x; i < kVecs; i += blockDim.x) reinterpret_cast<uint4*>(tab)[i] = src[i];
+  }
+  __syncthreads();
+  constexpr int U = 4;                                  // 16-byte vectors in flight per thread
+  const int64_t nv = n / 8;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v0 < nv; v0 += stride * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = v0 + u * stride;
+      raw[u] = v < nv ? __ldcs(reinterpret_cast<const uint4*>(x) + v) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = v0 + u * stride;
+      if (v >= nv) break;
+      const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+      uint32_t c[8], special = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        c[2 * j] = tab[(w[j] >> 3) & 0x1FFFu];
+        c[2 * j + 1] = tab[w[j] >> 19];
+        special |= ((w[j] & 0x7F807F80u) + 0x00800080u) & 0x80008000u;      // a half with exponent 0xFF
+      }
+      if (special) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t h = (w[e >> 1] >> (16 * (e & 1))) & 0x7FFFu;
+          if (h > 0x7F80u) c[e] = MODE == 0 ? 0x80u : 0x7FC0u;                // NaN whatever its payload
+        }
+      }
+      if constexpr (MODE == 0) {
+        const uint32_t lo = __byte_perm(__byte_perm(c[0], c[1], 0x0040), __byte_perm(c[2], c[3], 0x0040), 0x5410);
+        const uint32_t hi = __byte_perm(__byte_perm(c[4], c[5], 0x0040), __byte_perm(c[6], c[7], 0x0040), 0x5410);
+        *reinterpret_cast<uint2*>(codes + v * 8) = make_uint2(lo, hi);
+      } else {
+        *reinterpret_cast<uint4*>(fake + v * 8) = make_uint4(__byte_perm(c[0], c[1], 0x5410), __byte_perm(c[2], c[3], 0x5410),
+                                                             __byte_perm(c[4], c[5], 0x5410), __byte_perm(c[6], c[7], 0x5410));
+      }
+    }
+  }
+  // tail (n not a multiple of 8): the first threads of block 0 take one element each
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nv * 8)) {
+    const int64_t i = nv * 8 + threadIdx.x;
+    const uint32_t h = *reinterpret_cast<const uint16_t*>(x + i);
+    uint32_t c = tab[h >> 3];
+    if ((h & 0x7FFFu) > 0x7F80u) c = MODE == 0 ? 0x80u : 0x7FC0u;
+    if constexpr (MODE == 0) codes[i] = (uint8_t)c;
+    else *reinterpret_cast<uint16_t*>(fake + i) = (uint16_t)c;
+  }
+}
+
+// Decoding into a 16-bit type: 16 codes per thread (one 16-byte load, two 16-byte stores), values taken as 16-bit
+// patterns from a 512-byte table.
+template <typename T>
+__global__ void __launch_bounds__(256) hif8_decode16_kernel(const uint8_t* codes, int64_t n, T* out) {
+  __shared__ uint16_t table[256];
+  table[threadIdx.x] = g_hif8_dec16[std::is_same<T, __half>::value ? 1 : 0][threadIdx.x];
+  __syncthreads();
+  const int64_t nv = n / 16;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nv; v += stride) {
+    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(codes) + v);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t d0 = table[w[j] & 0xFFu], d1 = table[(w[j] >> 8) & 0xFFu];
+      const uint32_t d2 = table[(w[j] >> 16) & 0xFFu], d3 = table[w[j] >> 24];
+      o[2 * j] = __byte_perm(d0, d1, 0x5410);
+      o[2 * j + 1] = __byte_perm(d2, d3, 0x5410);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + v * 16);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (int)(n - nv * 16)) {
+    const int64_t i = nv * 16 + threadIdx.x;
+    *reinterpret_cast<uint16_t*>(out + i) = table[codes[i]];
+  }
+}
+
 static unsigned grid_for(int64_t n) {
   int64_t blocks = (n / 8 + 255) / 256;
   if (blocks < 1) blocks = 1;
@@ -215,6 +334,12 @@ template <typename T>
 static int run_encode(const T* x, int64_t n, uint8_t* codes, T* fake, cudaStream_t st) {
   const int rc = ensure_tables(st);
   if (rc != AMCT_OK) return rc;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    if (codes) AMCT_LAUNCH(grid_for(n), 256, st, (x, n, codes, nullptr), hif8_encode_bf16_kernel<0>);
+    else AMCT_LAUNCH(grid_for(n), 256, st, (x, n, nullptr, fake), hif8_encode_bf16_kernel<1>);
+    AMCT_CHECK_LAUNCH();
+    return AMCT_OK;
+  }
   if (codes) AMCT_LAUNCH(grid_for(n), 256, st, (x, n, codes, nullptr), hif8_encode_kernel<T, 0>);
   else AMCT_LAUNCH(grid_for(n), 256, st, (x, n, nullptr, fake), hif8_encode_kernel<T, 1>);
   AMCT_CHECK_LAUNCH();
@@ -250,10 +375,17 @@ extern "C" int amct_hif8_decode(const void* codes, int64_t n, int dtype, void* o
   const int rc = amct::ensure_tables(st);
   if (rc != AMCT_OK) return rc;
   const unsigned grid = amct::grid_for(n);
+  const bool wide = amct::aligned16(codes);                  // 16 codes per thread
   switch (dtype) {
     case AMCT_DTYPE_F32: AMCT_LAUNCH(grid, 256, st, (c, n, (float*)out), amct::hif8_decode_kernel<float>); break;
-    case AMCT_DTYPE_F16: AMCT_LAUNCH(grid, 256, st, (c, n, (__half*)out), amct::hif8_decode_kernel<__half>); break;
-    case AMCT_DTYPE_BF16: AMCT_LAUNCH(grid, 256, st, (c, n, (__nv_bfloat16*)out), amct::hif8_decode_kernel<__nv_bfloat16>); break;
+    case AMCT_DTYPE_F16:
+      if (wide) AMCT_LAUNCH(amct::grid_for(n / 2), 256, st, (c, n, (__half*)out), amct::hif8_decode16_kernel<__half>);
+      else AMCT_LAUNCH(grid, 256, st, (c, n, (__half*)out), amct::hif8_decode_kernel<__half>);
+      break;
+    case AMCT_DTYPE_BF16:
+      if (wide) AMCT_LAUNCH(amct::grid_for(n / 2), 256, st, (c, n, (__nv_bfloat16*)out), amct::hif8_decode16_kernel<__nv_bfloat16>);
+      else AMCT_LAUNCH(grid, 256, st, (c, n, (__nv_bfloat16*)out), amct::hif8_decode_kernel<__nv_bfloat16>);
+      break;
     default: return AMCT_ERR_ARG;
   }
   AMCT_CHECK_LAUNCH();

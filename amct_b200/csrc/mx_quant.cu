@@ -9,15 +9,19 @@
 // block holding NaN or Inf gets scale byte 0xFF, E4M3 elements 0x7F, and E2M1 elements
 // computed from the finite part (NaN -> +0, Inf saturates).
 //
-// Four adjacent lanes own one block (8 elements each): loads and payload stores are
-// fully coalesced 16- / 8- / 4-byte accesses, the block maximum is two shuffles, and
-// the 2^-e scaling is an exact multiply by a constructed power of two.  Scales are
+// One thread owns one 32-element block: 64 (16-bit input) or 128 contiguous bytes are loaded as 16-byte vectors, the
+// block maximum needs no shuffle (packed |x| / max instructions on the 16-bit types), the per-block work (exponent
+// arithmetic, scale addresses) is paid once per 32 elements, the payload leaves as 32 (E4M3) or 16 (E2M1) contiguous
+// bytes, and the 2^-e scaling is an exact multiply by a constructed power of two.  blockIdx.x covers the K blocks of
+// a row, blockIdx.y strides over rows: no thread divides to find its row.  Scales are
 // written row-major [rows, K/32] and, optionally, in the 128 x 4 tiling the
 // block-scaled tensor-core GEMM copies straight into tensor memory: rows are cut into
 // GEMM tiles of `tile_rows` rows (128 for the A operand, 224 for the B operand), each tile
 // into atoms of 128 rows, and an atom holds 4 K blocks of its 128 rows in 512 bytes:
 //     t = r / tile_rows, q = r % tile_rows, atom = t * ceil(tile_rows/128) + q/128
 //     offset(r, kb) = (atom * ceil(K/128) + kb/4) * 512 + (q%32)*16 + ((q%128)/32)*4 + kb%4
+// The padding of that layout (rows of the last atom of a tile that no row maps to, K blocks beyond K/32 in the last
+// group of four) is written as zero by this kernel: the buffer needs no clearing beforehand.
 //
 // HBM traffic per element: sizeof(T) read + 1 (fp8) or 0.5 (fp4) + 1/32 bytes written.
 #include <cuda_fp8.h>
@@ -27,42 +31,107 @@
 
 namespace amct {
 
-template <typename T>
-__device__ __forceinline__ void mx_load8(const T* src, float (&v)[8]) {
-  if constexpr (sizeof(T) == 2) {
-    Vec16<T> raw = ld_vec_stream(src);
+constexpr int kMxBlock = 32;
+
+// |amax| of a 32-element block as fp32 bits (NaN / Inf show as >= 0x7F800000), from the packed vectors.
+template <typename T> struct MxMax;
+template <> struct MxMax<__nv_bfloat16> {
+  __device__ static uint32_t of(const Vec16<__nv_bfloat16> (&raw)[4]) {
+    __nv_bfloat162 m = __habs2(reinterpret_cast<const __nv_bfloat162*>(&raw[0])[0]);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = ElemTraits<T>::to_f(raw.v[e]);
-  } else {
-    Vec16<T> r0 = ld_vec_stream(src), r1 = ld_vec_stream(src + 4);
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) { v[e] = ElemTraits<T>::to_f(r0.v[e]); v[4 + e] = ElemTraits<T>::to_f(r1.v[e]); }
+      for (int e = 0; e < 4; ++e) m = __hmax2_nan(m, __habs2(h[e]));
+    }
+    const float a = __low2float(m), b = __high2float(m);
+    return max(__float_as_uint(a) & 0x7fffffffu, __float_as_uint(b) & 0x7fffffffu);   // a NaN's bits exceed every number's
   }
+};
+template <> struct MxMax<__half> {
+  __device__ static uint32_t of(const Vec16<__half> (&raw)[4]) {
+    __half2 m = __habs2(reinterpret_cast<const __half2*>(&raw[0])[0]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) m = __hmax2_nan(m, __habs2(h[e]));
+    }
+    const float a = __low2float(m), b = __high2float(m);
+    return max(__float_as_uint(a) & 0x7fffffffu, __float_as_uint(b) & 0x7fffffffu);
+  }
+};
+template <> struct MxMax<float> {
+  __device__ static uint32_t of(const Vec16<float> (&raw)[8]) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) m = max(m, __float_as_uint(raw[i].v[e]) & 0x7fffffffu);
+    }
+    return m;
+  }
+};
+
+// 8 scaled values -> 8 E4M3 bytes (two words) or 8 E2M1 nibbles (one word)
+__device__ __forceinline__ uint2 mx_e4m3x8(const float (&s)[8]) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(s[4 * h], s[4 * h + 1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(s[4 * h + 2], s[4 * h + 3]), __NV_SATFINITE, __NV_E4M3);
+    w[h] = lo | (hi << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+__device__ __forceinline__ uint32_t mx_e2m1x8(const float (&s)[8], bool bad) {
+  uint32_t word = 0;
+#pragma unroll
+  for (int e = 0; e < 8; e += 2) {
+    float a = s[e], b = s[e + 1];
+    if (bad) { a = a == a ? a : 0.f; b = b == b ? b : 0.f; }         // E2M1 has no NaN
+    word |= (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest) << (4 * e);
+  }
+  return word;
 }
 
-// One lane's 8 elements of a 32-element block (4 adjacent lanes share the block).
-template <int FMT>
-__device__ __forceinline__ void mx_block(const float (&v)[8], bool valid, int lane, int64_t row, int64_t oct, int64_t k,
-                                         int64_t kb_per_row, int64_t kb4_per_row, bool wide, int tile_rows,
-                                         uint8_t* payload, uint8_t* scales_rm, uint8_t* scales_tiled) {
+// Where a row slot of the loop below lies: its row (or none: padding of the tiled layout) and its tiled-scale offset.
+struct MxSlot {
+  int row;
+  bool is_row;
+  int64_t tiled_off;
+};
+__device__ __forceinline__ MxSlot mx_slot(int slot, bool tiled, int rows, int tile_rows, int atoms_per_tile, int kb4_per_row, int kb) {
+  MxSlot r{slot, true, 0};
+  if (tiled) {
+    const int atom = slot >> 7, q128 = slot & 127;
+    const int tile = atom / atoms_per_tile, atom_in_tile = atom - tile * atoms_per_tile;
+    const int q = atom_in_tile * 128 + q128;                 // row within the tile
+    r.row = tile * tile_rows + q;
+    r.is_row = q < tile_rows && r.row < rows;
+    r.tiled_off = ((int64_t)atom * kb4_per_row + kb / 4) * 512 + (q128 % 32) * 16 + (q128 / 32) * 4 + (kb % 4);
+  }
+  return r;
+}
+
+// One 32-element block, already loaded: shared exponent, payload, scale byte(s).
+template <typename T, int FMT, int NV>
+__device__ __forceinline__ void mx_one_block(const Vec16<T> (&raw)[NV], const MxSlot& sl, int k, int kb, int kb_per_row, int pad_kb,
+                                             uint8_t* payload, uint8_t* scales_rm, uint8_t* scales_tiled) {
   constexpr int EMAX = FMT == 8 ? 8 : 2;
-  // max |v| through the integer order of the magnitude bits: Inf / NaN show up as >= 0x7F800000
-  uint32_t amax_bits = 0;
-#pragma unroll
-  for (int e = 0; e < 8; ++e) amax_bits = max(amax_bits, __float_as_uint(v[e]) & 0x7fffffffu);
-  amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 1));
-  amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 2));
+  constexpr int EV = 16 / (int)sizeof(T);                     // elements per vector
+  uint32_t amax_bits = MxMax<T>::of(raw);
   const bool bad = amax_bits >= 0x7f800000u;
   if (bad) {                                     // rare: the shared exponent comes from the finite part only
     uint32_t fin = 0;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const uint32_t b = __float_as_uint(v[e]) & 0x7fffffffu;
-      fin = max(fin, b < 0x7f800000u ? b : 0u);
+    for (int i = 0; i < NV; ++i) {
+#pragma unroll
+      for (int e = 0; e < EV; ++e) {
+        const uint32_t b = __float_as_uint(ElemTraits<T>::to_f(raw[i].v[e])) & 0x7fffffffu;
+        fin = max(fin, b < 0x7f800000u ? b : 0u);
+      }
     }
-    const unsigned act = __activemask();          // the 4 lanes of a block take this branch together
-    fin = max(fin, __shfl_xor_sync(act, fin, 1));
-    fin = max(fin, __shfl_xor_sync(act, fin, 2));
     amax_bits = fin;
   }
   // biased exponent of amax minus emax = shared_exp + 127; fp32 denormals and zero land on 0
@@ -70,117 +139,81 @@ __device__ __forceinline__ void mx_block(const float (&v)[8], bool valid, int la
   sb = sb < 0 ? 0 : (sb > 254 ? 254 : sb);
   const int field = 254 - sb;                                            // exponent field of 2^-shared_exp
   const float mult = __uint_as_float(field > 0 ? (uint32_t)field << 23 : 0x00400000u);
-  const uint32_t scale_byte = bad ? 0xFFu : (uint32_t)sb;
+  const uint8_t scale_byte = bad ? 0xFFu : (uint8_t)sb;
 
-  if (valid) {
-    float s[8];
+  // ---- payload: 8 elements at a time
+  uint32_t words[FMT == 8 ? 8 : 4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) s[e] = __fmul_rn(v[e], mult);
+  for (int o8 = 0; o8 < 4; ++o8) {
+    float sv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int idx = o8 * 8 + e;
+      sv[e] = __fmul_rn(ElemTraits<T>::to_f(raw[idx / EV].v[idx % EV]), mult);
+    }
     if constexpr (FMT == 8) {
-      uint32_t lo = 0, hi = 0;
-#pragma unroll
-      for (int e = 0; e < 4; e += 2) {
-        lo |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(s[e], s[e + 1]), __NV_SATFINITE, __NV_E4M3) << (8 * e);
-        hi |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(s[4 + e], s[5 + e]), __NV_SATFINITE, __NV_E4M3) << (8 * e);
-      }
-      if (bad) { lo = 0x7F7F7F7Fu; hi = 0x7F7F7F7Fu; }
-      *reinterpret_cast<uint2*>(payload + row * k + oct * 8) = make_uint2(lo, hi);
+      const uint2 w = mx_e4m3x8(sv);
+      words[2 * o8] = bad ? 0x7F7F7F7Fu : w.x;
+      words[2 * o8 + 1] = bad ? 0x7F7F7F7Fu : w.y;
     } else {
-      uint32_t word = 0;
-#pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        float a = s[e], b = s[e + 1];
-        if (bad) { a = a == a ? a : 0.f; b = b == b ? b : 0.f; }         // E2M1 has no NaN
-        word |= (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest) << (4 * e);
-      }
-      *reinterpret_cast<uint32_t*>(payload + row * (k / 2) + oct * 4) = word;
+      words[o8] = mx_e2m1x8(sv, bad);
     }
   }
-
-  const int64_t kb = oct / 4;
-  const uint32_t r32 = (uint32_t)row;                                  // rows < 2^31 (checked on the host)
-  const uint32_t tile = r32 / (uint32_t)tile_rows, tq = r32 - tile * (uint32_t)tile_rows;
-  const int64_t atom = (int64_t)tile * ((tile_rows + 127) / 128) + tq / 128;
-  const int64_t tiled_off = (atom * kb4_per_row + kb / 4) * 512 + (tq % 32) * 16 + ((tq % 128) / 32) * 4 + (kb % 4);
-  if (wide) {
-    const int g16 = lane & ~15;
-    uint32_t word = __shfl_sync(0xffffffffu, scale_byte, g16) | (__shfl_sync(0xffffffffu, scale_byte, g16 + 4) << 8) |
-                    (__shfl_sync(0xffffffffu, scale_byte, g16 + 8) << 16) | (__shfl_sync(0xffffffffu, scale_byte, g16 + 12) << 24);
-    if (valid && (lane & 15) == 0) {
-      if (scales_rm) *reinterpret_cast<uint32_t*>(scales_rm + row * kb_per_row + kb) = word;
-      if (scales_tiled) *reinterpret_cast<uint32_t*>(scales_tiled + tiled_off) = word;
-    }
-  } else if (valid && (lane & 3) == 0) {
-    if (scales_rm) scales_rm[row * kb_per_row + kb] = (uint8_t)scale_byte;
-    if (scales_tiled) scales_tiled[tiled_off] = (uint8_t)scale_byte;
+  if constexpr (FMT == 8) {
+    uint4* dst = reinterpret_cast<uint4*>(payload + (int64_t)sl.row * k + (int64_t)kb * kMxBlock);
+    dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+    dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+  } else {
+    *reinterpret_cast<uint4*>(payload + (int64_t)sl.row * (k / 2) + (int64_t)kb * (kMxBlock / 2)) =
+        make_uint4(words[0], words[1], words[2], words[3]);
+  }
+  if (scales_rm) scales_rm[(int64_t)sl.row * kb_per_row + kb] = scale_byte;
+  if (scales_tiled) {
+    scales_tiled[sl.tiled_off] = scale_byte;
+    for (int j = 1; j <= pad_kb; ++j) scales_tiled[sl.tiled_off + j] = 0;
   }
 }
 
+// blockIdx.x * blockDim.x + threadIdx.x = the K block of the row this thread owns; blockIdx.y strides over row SLOTS,
+// two at a time (both blocks' loads are issued before either is worked on).  Without the tiled layout a slot is a
+// row.  With it, slots enumerate the layout's rows -- tiles x atoms x 128 -- so that the slots no row maps to get
+// their zero padding from the same loop.
 template <typename T, int FMT>
-__global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int64_t rows, int64_t k, int64_t ld, uint8_t* payload,
-                                                       uint8_t* scales_rm, uint8_t* scales_tiled, int tile_rows) {
-  constexpr int U = 2;                                      // blocks in flight per thread
-  const int lane = threadIdx.x & 31;
-  const int64_t oct_per_row = k / 8;
-  const int64_t total = rows * oct_per_row;
-  const int64_t kb_per_row = k / 32;
-  const int64_t kb4_per_row = (kb_per_row + 3) / 4;
-  const bool wide = (kb_per_row % 4) == 0;                  // 4 scale bytes of a row go out as one word
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += stride * U) {
-    float v[U][8];
-    int64_t row[U], oct[U];
-    bool valid[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t w = base + u * stride + threadIdx.x;
-      valid[u] = w < total;
-      row[u] = valid[u] ? w / oct_per_row : 0;
-      oct[u] = valid[u] ? w - row[u] * oct_per_row : 0;
-      if (valid[u]) mx_load8<T>(x + row[u] * ld + oct[u] * 8, v[u]);
-      else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (base + u * stride >= total) break;                // uniform across the block
-      mx_block<FMT>(v[u], valid[u], lane, row[u], oct[u], k, kb_per_row, kb4_per_row, wide, tile_rows, payload, scales_rm,
-                    scales_tiled);
-    }
-  }
-}
-
-// Row-tiled variant for K >= 1024: blockIdx.x picks a 2048-element span of the row,
-// blockIdx.y strides over rows, so no thread ever divides to find its row, and the tile /
-// atom position of the scale layout advances incrementally.
-template <typename T, int FMT>
-__global__ void __launch_bounds__(256) mx_quant_rows_kernel(const T* x, int rows, int k, int64_t ld, uint8_t* payload,
-                                                            uint8_t* scales_rm, uint8_t* scales_tiled, int tile_rows) {
-  constexpr int U = 2;                                      // rows in flight per thread
-  const int lane = threadIdx.x & 31;
-  const int oct_per_row = k / 8;
-  const int oct = blockIdx.x * blockDim.x + threadIdx.x;
-  const bool in_row = oct < oct_per_row;
-  const int kb_per_row = k / 32;
+__global__ void __launch_bounds__(256) mx_quant_kernel(const T* x, int rows, int k, int64_t ld, uint8_t* payload,
+                                                       uint8_t* scales_rm, uint8_t* scales_tiled, int tile_rows, int slots) {
+  constexpr int NV = kMxBlock * (int)sizeof(T) / 16;          // 16-byte vectors per block: 4 or 8
+  constexpr int EV = 16 / (int)sizeof(T);
+  constexpr int U = 2;
+  const int kb_per_row = k / kMxBlock;
   const int kb4_per_row = (kb_per_row + 3) / 4;
-  const bool wide = (kb_per_row % 4) == 0;
-  for (int r0 = blockIdx.y * U; r0 < rows; r0 += gridDim.y * U) {
-    float v[U][8];
+  const int kb = blockIdx.x * blockDim.x + threadIdx.x;
+  const int atoms_per_tile = (tile_rows + 127) / 128;
+  // K blocks this thread zero-fills in the tiled layout besides its own: the rest of the last group of four
+  const int pad_kb = (scales_tiled && kb == kb_per_row - 1) ? kb4_per_row * 4 - kb_per_row : 0;
+  if (kb >= kb_per_row) return;
+  for (int slot0 = blockIdx.y; slot0 < slots; slot0 += U * gridDim.y) {
+    MxSlot sl[U];
+    Vec16<T> raw[U][NV];
+    bool live[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (in_row && r0 + u < rows) mx_load8<T>(x + (int64_t)(r0 + u) * ld + (int64_t)oct * 8, v[u]);
-      else {
+      const int slot = slot0 + u * gridDim.y;
+      live[u] = slot < slots;
+      sl[u] = mx_slot(live[u] ? slot : 0, scales_tiled != nullptr, rows, tile_rows, atoms_per_tile, kb4_per_row, kb);
+      if (live[u] && sl[u].is_row) {
+        const T* src = x + (int64_t)sl[u].row * ld + (int64_t)kb * kMxBlock;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
+        for (int i = 0; i < NV; ++i) raw[u][i] = ld_vec_stream(src + i * EV);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (r0 + u >= rows) break;                            // uniform across the block
-      mx_block<FMT>(v[u], in_row, lane, r0 + u, in_row ? oct : 0, k, kb_per_row, kb4_per_row, wide, tile_rows, payload,
-                    scales_rm, scales_tiled);
+      if (!live[u]) continue;
+      if (!sl[u].is_row) {
+        for (int j = 0; j <= pad_kb; ++j) scales_tiled[sl[u].tiled_off + j] = 0;
+        continue;
+      }
+      mx_one_block<T, FMT, NV>(raw[u], sl[u], k, kb, kb_per_row, pad_kb, payload, scales_rm, scales_tiled);
     }
   }
 }
@@ -188,24 +221,19 @@ __global__ void __launch_bounds__(256) mx_quant_rows_kernel(const T* x, int rows
 template <typename T>
 static int run_mx(const T* x, int64_t rows, int64_t k, int64_t ld, int fmt, uint8_t* payload, uint8_t* srm, uint8_t* st,
                   int tile_rows, cudaStream_t stream) {
-  if (k >= 1024 && rows < (1LL << 30) && k < (1LL << 30)) {
-    dim3 grid((unsigned)((k / 8 + 255) / 256), 1);
-    int64_t gy = (148LL * 8 + grid.x - 1) / grid.x;        // about 8 CTAs per SM
-    const int64_t need = (rows + 1) / 2;
-    if (gy > need) gy = need;
-    grid.y = (unsigned)(gy < 1 ? 1 : gy);
-    if (fmt == 8) AMCT_LAUNCH(grid, 256, stream, (x, (int)rows, (int)k, ld, payload, srm, st, tile_rows), mx_quant_rows_kernel<T, 8>);
-    else AMCT_LAUNCH(grid, 256, stream, (x, (int)rows, (int)k, ld, payload, srm, st, tile_rows), mx_quant_rows_kernel<T, 4>);
-    AMCT_CHECK_LAUNCH();
-    return AMCT_OK;
-  }
-  const int64_t total = rows * (k / 8);
-  int64_t blocks = (total + 511) / 512;
-  if (blocks < 1) blocks = 1;
-  const int64_t cap = 148LL * 8 * 4;
-  if (blocks > cap) blocks = cap;
-  if (fmt == 8) AMCT_LAUNCH((unsigned)blocks, 256, stream, (x, rows, k, ld, payload, srm, st, tile_rows), mx_quant_kernel<T, 8>);
-  else AMCT_LAUNCH((unsigned)blocks, 256, stream, (x, rows, k, ld, payload, srm, st, tile_rows), mx_quant_kernel<T, 4>);
+  if (k >= (1LL << 30)) return AMCT_ERR_UNSUPPORTED;
+  const int kb_per_row = (int)(k / kMxBlock);
+  const int threads = kb_per_row >= 256 ? 256 : ((kb_per_row + 31) / 32) * 32;
+  dim3 grid((unsigned)((kb_per_row + threads - 1) / threads), 1);
+  int64_t slots = rows;
+  if (st) slots = ((rows + tile_rows - 1) / tile_rows) * ((tile_rows + 127) / 128) * 128;
+  if (slots > 0x7fffffffLL) return AMCT_ERR_UNSUPPORTED;
+  int64_t gy = (148LL * 2048 / threads + grid.x - 1) / grid.x;          // every SM full of resident blocks
+  if (gy > slots) gy = slots;
+  if (gy > 65535) gy = 65535;
+  grid.y = (unsigned)(gy < 1 ? 1 : gy);
+  if (fmt == 8) AMCT_LAUNCH(grid, threads, stream, (x, (int)rows, (int)k, ld, payload, srm, st, tile_rows, (int)slots), mx_quant_kernel<T, 8>);
+  else AMCT_LAUNCH(grid, threads, stream, (x, (int)rows, (int)k, ld, payload, srm, st, tile_rows, (int)slots), mx_quant_kernel<T, 4>);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -227,8 +255,7 @@ extern "C" int amct_mx_quant(const void* x, int dtype, int64_t rows, int64_t k, 
   if (scales_tiled && (scale_tile_rows < 32 || scale_tile_rows % 32 != 0)) return AMCT_ERR_ARG;
   const int tr = scales_tiled ? scale_tile_rows : 128;
   const int esize = dtype == AMCT_DTYPE_F32 ? 4 : 2;
-  if (!amct::aligned16(x) || (ld_x * esize) % 16 != 0 || reinterpret_cast<uintptr_t>(payload) % 8 != 0 ||
-      (scales_rowmajor && reinterpret_cast<uintptr_t>(scales_rowmajor) % 4 != 0) ||
+  if (!amct::aligned16(x) || (ld_x * esize) % 16 != 0 || reinterpret_cast<uintptr_t>(payload) % 16 != 0 ||
       (scales_tiled && reinterpret_cast<uintptr_t>(scales_tiled) % 16 != 0))
     return AMCT_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;

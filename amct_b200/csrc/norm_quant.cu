@@ -39,7 +39,7 @@ struct NormQuantParams {
   // other (part j at x + j * part_stride elements); the row is their fp32 sum in that order, rounded once to T.
   // Output: the codes and the scale of row r go to row (row0 + r) of EVERY rank's buffers, q_all[d] / scale_all[d]
   // (this process's mappings of them), so that each rank ends up with all ranks' rows; q / scale are not used.
-  int parts, world;
+  int parts, world, first_dst;
   int64_t part_stride, row0;
   int8_t* q_all[kMaxNormRanks];
   float* scale_all[kMaxNormRanks];
@@ -244,7 +244,10 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
         if constexpr (TP) {
           // a warp writes 256 contiguous bytes per destination: plain stores into every rank's (peer-mapped) buffer
           const int64_t off = (p.row0 + row) * p.ld_q + v * E;
-          for (int d = 0; d < p.world; ++d) *reinterpret_cast<uint2*>(p.q_all[d] + off) = make_uint2(w0, w1);
+          for (int i = 0; i < p.world; ++i) {
+            const int d = (p.first_dst + i) % p.world;        // every rank starts with another destination
+            *reinterpret_cast<uint2*>(p.q_all[d] + off) = make_uint2(w0, w1);
+          }
         } else {
           *reinterpret_cast<uint2*>(qrow + v * E) = make_uint2(w0, w1);
         }
@@ -325,6 +328,7 @@ extern "C" int amct_addnorm_quant_pertoken_tp(const void* parts, int n_parts, in
   p.x = parts; p.residual = residual; p.gamma = gamma; p.residual_out = residual_out; p.status = status;
   p.rows = rows; p.k = k; p.ld_x = ld_x; p.ld_res = ld_res; p.ld_res_out = ld_res_out; p.ld_q = ld_q; p.eps = eps;
   p.parts = n_parts; p.part_stride = part_stride; p.world = world; p.row0 = row0;
+  p.first_dst = (int)((row0 / rows + 1) % world);                 // row0 = rank * rows in the sharded workload
   for (int d = 0; d < world; ++d) {
     if (!q_all[d] || !scale_all[d]) return AMCT_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(q_all[d]) % 8) return AMCT_ERR_ALIGN;

@@ -4,10 +4,12 @@
 // (amct_pytorch/quantize_op/utils.py:111-136), scale rule (utils.py:75-108), codes
 // (amct_pytorch/utils/quant_util.py:57-93), nibble pack, and both fake-quant variants
 // (quant_util.py:162-188; amct_pytorch/algorithm/awq.py:129-170) -- for the common case of a
-// group that fits inside a warp: group / (elements per 16-byte vector) lanes, a power of two,
-// K a multiple of the group.  Every thread owns one 16-byte vector, reduces min / max over its
-// lane group with shuffles, derives the group's scale and offset itself, and quantizes its own
-// elements.  blockIdx.x covers the columns, blockIdx.y strides over rows: no index division.
+// group that fits inside a warp: a power-of-two number of lanes, each owning four adjacent 16-byte
+// vectors (32 elements of a 16-bit type), K a multiple of the group.  Every thread reduces min / max
+// over its lane group with shuffles, derives the group's scale and offset itself, and quantizes its
+// own elements.  blockIdx.x covers the columns, blockIdx.y strides over rows: no index division.
+// The kernel is bound by instruction issue, not by HBM, unless it stays near a dozen instructions
+// per element; hence the packed min / max, the scale rule on the FMA pipe, the saturating packs.
 //
 // Quotients come from rn(1/scale) and two FMA correction steps (div_by_recip in common.cuh: the
 // correctly rounded quotient, i.e. the value of the IEEE division), the rounding is done by adding
@@ -56,37 +58,122 @@ __device__ __noinline__ float4 levels_exact4(float a, float b, float c, float d,
   return make_float4(v[0], v[1], v[2], v[3]);
 }
 
-// 16-bit inputs: min / max of a 16-byte vector with the packed instructions (NaN is tracked
-// separately by the caller, so the NaN-dropping variants are fine here)
-__device__ __forceinline__ void vec_minmax(const Vec16<__nv_bfloat16>& v, float& mn, float& mx) {
+// NaN-propagating min / max of a 16-byte vector (torch.amin / amax return NaN for a group that holds one, and the
+// scale rule then refuses the group): packed instructions for the 16-bit types, min.NaN / max.NaN for fp32.
+__device__ __forceinline__ void vec_minmax(const Vec16<__nv_bfloat16>& v, __nv_bfloat162& mn, __nv_bfloat162& mx) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-  const __nv_bfloat162 a = __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]));
-  const __nv_bfloat162 b = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
-  mn = fminf(mn, fminf(__low2float(a), __high2float(a)));
-  mx = fmaxf(mx, fmaxf(__low2float(b), __high2float(b)));
+  mn = __hmin2_nan(mn, __hmin2_nan(__hmin2_nan(h[0], h[1]), __hmin2_nan(h[2], h[3])));
+  mx = __hmax2_nan(mx, __hmax2_nan(__hmax2_nan(h[0], h[1]), __hmax2_nan(h[2], h[3])));
 }
-__device__ __forceinline__ void vec_minmax(const Vec16<__half>& v, float& mn, float& mx) {
+__device__ __forceinline__ void vec_minmax(const Vec16<__half>& v, __half2& mn, __half2& mx) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
-  const __half2 a = __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]));
-  const __half2 b = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
-  mn = fminf(mn, fminf(__low2float(a), __high2float(a)));
-  mx = fmaxf(mx, fmaxf(__low2float(b), __high2float(b)));
+  mn = __hmin2_nan(mn, __hmin2_nan(__hmin2_nan(h[0], h[1]), __hmin2_nan(h[2], h[3])));
+  mx = __hmax2_nan(mx, __hmax2_nan(__hmax2_nan(h[0], h[1]), __hmax2_nan(h[2], h[3])));
 }
-__device__ __forceinline__ void vec_minmax(const Vec16<float>& v, float& mn, float& mx) {
+template <typename T> struct GroupAcc;          // the per-thread min / max accumulator of a type
+template <> struct GroupAcc<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  __device__ static type init(float v) { return __floats2bfloat162_rn(v, v); }
+  __device__ static float lo(type v) { return __low2float(v); }
+  __device__ static float hi(type v) { return __high2float(v); }
+};
+template <> struct GroupAcc<__half> {
+  using type = __half2;
+  __device__ static type init(float v) { return __floats2half2_rn(v, v); }
+  __device__ static float lo(type v) { return __low2float(v); }
+  __device__ static float hi(type v) { return __high2float(v); }
+};
+template <> struct GroupAcc<float> {
+  using type = float2;                          // x: running min or max, y unused
+  __device__ static type init(float v) { return make_float2(v, v); }
+  __device__ static float lo(type v) { return v.x; }
+  __device__ static float hi(type v) { return v.y; }
+};
+__device__ __forceinline__ void vec_minmax(const Vec16<float>& v, float2& mn, float2& mx) {
 #pragma unroll
-  for (int e = 0; e < 4; ++e) { mn = fminf(mn, v.v[e]); mx = fmaxf(mx, v.v[e]); }
+  for (int e = 0; e < 4; e += 2) {
+    mn.x = fmin_nan(mn.x, v.v[e]); mn.y = fmin_nan(mn.y, v.v[e + 1]);
+    mx.x = fmax_nan(mx.x, v.v[e]); mx.y = fmax_nan(mx.y, v.v[e + 1]);
+  }
 }
 
-// Two adjacent 16-byte vectors per thread; a group spans (1 << lanes_log2) threads of a warp.
-// OUT is the AMCT_OUT_* mode.  In every mode the rounded level is carried as u = level + 1.5 * 2^23,
-// whose low mantissa bits are the level in two's complement.
-template <typename T, int OUT>
-__global__ void __launch_bounds__(256) quant_groups_kernel(GroupParams p) {
+// The scale rule (amct_pytorch/quantize_op/utils.py:75-108) for a group whose bounds are finite, with the two IEEE
+// divisions replaced by the exact FMA sequence of div_by_recip: bound / (a small integer constant) and mn / scale.
+// Both are valid uses: a quotient that is too small to be a normal number only occurs below the rule's epsilon, where
+// the scale is replaced by 1 and the offset by -2^(bits-1) whatever the quotient was; the scale that divides mn is
+// then at least that epsilon, so it and its reciprocal are normal.  Returns the scale; *offset as a float.
+__device__ __forceinline__ float group_qparams(float mx, float mn, int bits, bool symmetric, float* offset) {
+  if (symmetric) {
+    const float amx = fabsf(mx), amn = fabsf(mn);
+    const bool neg_dom = amx < amn;
+    const float bound = neg_dom ? amn : amx;
+    float s;
+    if (neg_dom) {
+      s = __fmul_rn(bound, bits == 8 ? 0.0078125f : 0.125f);                   // / 128 or / 8: exact scaling
+      if (s < 1.17549435e-38f) s = 0.f;                                       // (a subnormal result is below epsilon anyway)
+    } else {
+      const float div = bits == 8 ? 127.f : 7.f;
+      s = div_by_recip(bound, div, bits == 8 ? (1.f / 127.f) : (1.f / 7.f));
+    }
+    if (!(s >= AMCT_FLT_EPSILON)) s = 1.f;
+    *offset = 0.f;
+    return s;
+  }
+  mx = fmaxf(mx, 0.f);
+  mn = fminf(mn, 0.f);
+  const float span = bits == 8 ? 255.f : 15.f, half = bits == 8 ? 128.f : 8.f;
+  float s = div_by_recip(__fsub_rn(mx, mn), span, bits == 8 ? (1.f / 255.f) : (1.f / 15.f));
+  float o = -half;
+  if (s >= AMCT_FLT_EPSILON) {
+    // + 0: the reference's offset is an integer tensor, so a zero offset is +0 (rint(-0.3) is -0, and level - (-0)
+    // would flip the sign of a zero level in the fake-quant outputs)
+    if (mx != mn) o = __fadd_rn(rintf(__fsub_rn(-half, div_by_recip(mn, s, __frcp_rn(s)))), 0.f);
+  } else {
+    s = 1.f;
+  }
+  *offset = o;
+  return s;
+}
+
+// cvt.pack.sat: two signed integers saturated to 4 (8) bits each and packed under what `carry` already holds,
+//   d = (carry << 8 | sat4(hi) << 4 | sat4(lo))      resp.      d = (carry << 16 | sat8(hi) << 8 | sat8(lo))
+// one instruction for the clamp and the packing of two codes.
+__device__ __forceinline__ uint32_t pack_sat_s4(int hi, int lo, uint32_t carry) {
+#ifdef AMCT_CUDA_EMU
+  const int h = hi < -8 ? -8 : hi > 7 ? 7 : hi, l = lo < -8 ? -8 : lo > 7 ? 7 : lo;
+  return (carry << 8) | ((uint32_t)(h & 0xF) << 4) | (uint32_t)(l & 0xF);
+#else
+  uint32_t d;
+  asm("cvt.pack.sat.s4.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(carry));
+  return d;
+#endif
+}
+__device__ __forceinline__ uint32_t pack_sat_s8(int hi, int lo, uint32_t carry) {
+#ifdef AMCT_CUDA_EMU
+  const int h = hi < -128 ? -128 : hi > 127 ? 127 : hi, l = lo < -128 ? -128 : lo > 127 ? 127 : lo;
+  return (carry << 16) | ((uint32_t)(h & 0xFF) << 8) | (uint32_t)(l & 0xFF);
+#else
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(carry));
+  return d;
+#endif
+}
+
+// Four adjacent 16-byte vectors per thread (32 elements of a 16-bit type: the scale rule, which every thread of a
+// group evaluates, is spread over that many elements); a group spans (1 << lanes_log2) threads of a warp.  The row
+// stays packed in T; one vector at a time is unpacked, divided and written.  In every mode the rounded level is
+// carried as u = level + 1.5 * 2^23, whose low mantissa bits are the level in two's complement.
+// COMPUTE: scales and offsets are derived from the data (then |level| <= 2^(bits-1) + 1 before the clamp, no quotient
+// can overflow, and a NaN shows in the group's bounds); otherwise they are given and the levels can be anything.
+template <typename T, int OUT, bool COMPUTE, bool HAS_OFF, bool PRE>
+__global__ void __launch_bounds__(256, 4) quant_groups_kernel(GroupParams p) {
   constexpr int E = ElemTraits<T>::kPerVec;
-  constexpr int VPT = 2, EP = E * VPT;              // vectors / elements per thread
+  constexpr int VPT = 4, EP = E * VPT;              // vectors / elements per thread
   constexpr bool kAwq = OUT == AMCT_OUT_FAKE_AWQ;
   constexpr bool kAwqRounds = kAwq && sizeof(T) == 2;              // the AWQ variant rounds to T before rint()
   constexpr bool kFake = OUT == AMCT_OUT_FAKE || OUT == AMCT_OUT_FAKE_AWQ;
+  constexpr bool kSign = kFake;     // a zero level keeps its sign: rint(-0.3) = -0, and (-0 - 0) * s = -0 (an offset can be 0)
+  using Acc = GroupAcc<T>;
   const int nthr_row = (int)(p.k / EP);             // threads that own part of a row
   const int tcol = blockIdx.x * blockDim.x + threadIdx.x;
   const bool active = tcol < nthr_row;
@@ -94,211 +181,227 @@ __global__ void __launch_bounds__(256) quant_groups_kernel(GroupParams p) {
   const int lane = threadIdx.x & 31;
   const int unit = tcol >> p.lanes_log2;
   const int nunits = nthr_row >> p.lanes_log2;
-  const bool has_off = p.offset != nullptr;
   const float qmax = (float)((1 << (p.bits - 1)) - 1), qmin = -qmax - 1.f;
   const T* __restrict__ pre = reinterpret_cast<const T*>(p.pre);
   const int64_t j0 = (int64_t)tcol * EP;
 
-  float pre_f[EP];
-  if (p.pre_op != AMCT_PRE_NONE && active) {
+  Vec16<T> pre_v[PRE ? VPT : 1];
+  if (PRE && active) {
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const Vec16<T> pv = ld_vec(pre + j0 + i * E);
-#pragma unroll
-      for (int e = 0; e < E; ++e) pre_f[i * E + e] = ElemTraits<T>::to_f(pv.v[e]);
-    }
+    for (int i = 0; i < VPT; ++i) pre_v[i] = ld_vec(pre + j0 + i * E);
   }
 
   for (int64_t row = blockIdx.y; row < p.rows; row += gridDim.y) {
-    float x[EP];
-    float mn = INFINITY, mx = -INFINITY;
-    bool bad = false;
+    Vec16<T> raw[VPT];
     if (active) {
-      Vec16<T> raw[VPT];
 #pragma unroll
       for (int i = 0; i < VPT; ++i) raw[i] = ld_vec_stream(reinterpret_cast<const T*>(p.x) + row * p.ld + j0 + i * E);
-      // one decision per row, not per element: runtime tests inside unrolled loops cost a branch each
-      if (p.pre_op == AMCT_PRE_NONE) {
+      if constexpr (PRE) {
+        // the product / quotient by the SmoothQuant or AWQ factor is a separate torch op in the reference: rounded to T
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
 #pragma unroll
-          for (int e = 0; e < E; ++e) x[i * E + e] = ElemTraits<T>::to_f(raw[i].v[e]);
-          if (p.compute) vec_minmax(raw[i], mn, mx);
+          for (int e = 0; e < E; ++e) {
+            const float a = ElemTraits<T>::to_f(raw[i].v[e]), f = ElemTraits<T>::to_f(pre_v[i].v[e]);
+            raw[i].v[e] = ElemTraits<T>::from_f(p.pre_op == AMCT_PRE_MUL ? __fmul_rn(a, f) : __fdiv_rn(a, f));
+          }
         }
-      } else {
-        if (p.pre_op == AMCT_PRE_MUL) {
-#pragma unroll
-          for (int e = 0; e < EP; ++e) x[e] = round_to<T>(__fmul_rn(ElemTraits<T>::to_f(raw[e / E].v[e % E]), pre_f[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < EP; ++e) x[e] = round_to<T>(__fdiv_rn(ElemTraits<T>::to_f(raw[e / E].v[e % E]), pre_f[e]));
-        }
-#pragma unroll
-        for (int e = 0; e < EP; ++e) { mn = fminf(mn, x[e]); mx = fmaxf(mx, x[e]); }
-      }
-      // x * 0 is NaN exactly for NaN and Inf: one FMA per element finds a NaN anywhere; an Inf
-      // alone is told apart below (it does not raise in the reference when scales are given)
-      float poison = 0.f;
-#pragma unroll
-      for (int e = 0; e < EP; ++e) poison = __fmaf_rn(x[e], 0.f, poison);
-      if (poison != poison) {
-#pragma unroll
-        for (int e = 0; e < EP; ++e) bad |= (x[e] != x[e]);
       }
     } else {
 #pragma unroll
-      for (int e = 0; e < EP; ++e) x[e] = 0.f;
-      mn = mx = 0.f;
+      for (int i = 0; i < VPT; ++i) *reinterpret_cast<uint4*>(&raw[i]) = make_uint4(0, 0, 0, 0);
     }
     float s, o = 0.f;
+    bool bad = false;
     const int64_t uidx = row * nunits + unit;
-    if (p.compute) {
+    if constexpr (COMPUTE) {
+      typename Acc::type vmn = Acc::init(INFINITY), vmx = Acc::init(-INFINITY);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) vec_minmax(raw[i], vmn, vmx);
+      float mn = fmin_nan(Acc::lo(vmn), Acc::hi(vmn)), mx = fmax_nan(Acc::lo(vmx), Acc::hi(vmx));
       for (int w = 1; w < lanes; w <<= 1) {
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, w));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
+        mn = fmin_nan(mn, __shfl_xor_sync(0xffffffffu, mn, w));
+        mx = fmax_nan(mx, __shfl_xor_sync(0xffffffffu, mx, w));
       }
-      int oi;
-      const bool ok = qparams_from_minmax(mx, mn, p.bits, p.symmetric != 0, &s, &oi);
-      o = (float)oi;
+      bool ok;
+      if (isfinite(__fsub_rn(mx, mn))) {
+        s = group_qparams(mx, mn, p.bits, !HAS_OFF, &o);
+        ok = true;
+      } else {
+        // a NaN or an infinite bound: the rule as the other kernels state it (it ends in a refusal either way)
+        int oi;
+        ok = qparams_from_minmax(mx, mn, p.bits, !HAS_OFF, &s, &oi) && mx == mx && mn == mn;
+        o = (float)oi;
+      }
       if (active && (lane & (lanes - 1)) == 0) {
         p.scale[uidx] = s;
-        if (has_off) p.offset[uidx] = oi;
+        if (HAS_OFF) p.offset[uidx] = (int)o;
         if (!ok && p.status) atomicOr(p.status, 1);
       }
-    } else if (active) {
-      s = p.scale[uidx];
-      if (has_off) o = (float)p.offset[uidx];
     } else {
-      s = 1.f;
+      if (active) {
+        s = p.scale[uidx];
+        if (HAS_OFF) o = (float)p.offset[uidx];
+      } else {
+        s = 1.f;
+      }
     }
-    // fminf / fmaxf drop NaN; the reference raises on it
-    if (bad && p.status) atomicOr(p.status, 1);
-    if (OUT == AMCT_OUT_NONE || !active) continue;
+    if (OUT == AMCT_OUT_NONE || !active) {
+      if (!COMPUTE && active && p.status) {
+        // scales given, nothing to write: the input is still checked for NaN like the other paths
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) { const float a = ElemTraits<T>::to_f(raw[i].v[e]); bad |= (a != a); }
+        }
+        if (bad) atomicOr(p.status, 1);
+      }
+      continue;
+    }
 
     // ---- levels, in the reference's order: t = x / s, + offset, (AWQ variant: round to T,) rint, clamp.
-    // The clamp is applied before the rounding: same result, the bounds are integers.  (Even with
-    // scales derived from the group itself it is needed: the largest element can land exactly on
-    // qmax + 0.5, which rounds to the even qmax + 1.)
-    float u[EP];                                   // level + 1.5 * 2^23
-    float sg[kFake ? EP : 1];                      // fake-quant shows the sign of a zero level: rint(-0.3) = -0
+    // The clamp is applied before the rounding where it is a float clamp (same result, the bounds are integers), or
+    // after it by the saturating pack.  Even with scales derived from the group itself it is needed: the largest
+    // element can land exactly on qmax + 0.5, which rounds to the even qmax + 1.
     const float y = __frcp_rn(s);
-    const float o_add = has_off ? o : -0.f;         // adding -0 keeps the sign of a zero quotient
-    bool fast = fabsf(s) >= 1.17549435e-38f && fabsf(y) >= 1.17549435e-38f && isfinite(y) && isfinite(s);
-    if (fast) {
-      float poison = 0.f;
+    const float o_add = HAS_OFF ? o : -0.f;         // adding -0 keeps the sign of a zero quotient
+    const bool fast = fabsf(s) >= 1.17549435e-38f && fabsf(y) >= 1.17549435e-38f && isfinite(y) && isfinite(s);
+    uint32_t words[VPT * (OUT == AMCT_OUT_I8 ? 2 : 1)];               // PACK4: one word per vector, I8: two
 #pragma unroll
-      for (int e = 0; e < EP; ++e) {
-        float q = div_by_recip(x[e], s, y);
-        if (kFake) q = x[e] == 0.f ? __fmul_rn(x[e], y) : q;    // -0.0 / s is -0.0 (the FMA corrections give +0.0)
-        float t = __fadd_rn(q, o_add);
-        poison = __fmaf_rn(t, 0.f, poison);
-        if (kAwqRounds) t = round_to<T>(t);
-        t = fminf(fmaxf(t, qmin), qmax);
-        u[e] = __fadd_rn(t, kMagicG);               // round half to even
-        if (kFake) sg[e] = t;
+    for (int i = 0; i < VPT; ++i) {
+      float x[E], u[E];
+      float sg[kSign ? E : 1];
+#pragma unroll
+      for (int e = 0; e < E; ++e) x[e] = ElemTraits<T>::to_f(raw[i].v[e]);
+      bool vec_fast = fast;
+      if (vec_fast) {
+        float poison = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          float q = div_by_recip(x[e], s, y);
+          if (kSign) q = x[e] == 0.f ? __fmul_rn(x[e], y) : q;    // -0.0 / s is -0.0 (the FMA corrections give +0.0)
+          float t = __fadd_rn(q, o_add);
+          if (!COMPUTE) poison = __fmaf_rn(t, 0.f, poison);        // a NaN or infinite level (x itself, or x / s overflowing)
+          if (kAwqRounds) t = round_to<T>(t);
+          if (!COMPUTE || kFake || OUT == AMCT_OUT_I32) t = fminf(fmaxf(t, qmin), qmax);
+          u[e] = __fadd_rn(t, kMagicG);               // round half to even
+          if (kSign) sg[e] = t;
+        }
+        if (!COMPUTE && poison != poison) vec_fast = false;        // let the IEEE division decide
       }
-      if (poison != poison) fast = false;            // a NaN or infinite quotient: let the IEEE division decide
-    }
-    if (!fast) {
-      const int flags = (has_off ? 1 : 0) | (kAwq ? 2 : 0);
+      if (!vec_fast) {
+        const int flags = (HAS_OFF ? 1 : 0) | (kAwq ? 2 : 0);
 #pragma unroll
-      for (int e = 0; e < EP; e += 4) {
-        const float4 r = levels_exact4<T>(x[e], x[e + 1], x[e + 2], x[e + 3], s, o, flags, qmin, qmax);
-        u[e] = __fadd_rn(r.x, kMagicG); u[e + 1] = __fadd_rn(r.y, kMagicG);
-        u[e + 2] = __fadd_rn(r.z, kMagicG); u[e + 3] = __fadd_rn(r.w, kMagicG);
-        if (kFake) { sg[e] = r.x; sg[e + 1] = r.y; sg[e + 2] = r.z; sg[e + 3] = r.w; }
+        for (int e = 0; e < E; e += 4) {
+          const float4 r = levels_exact4<T>(x[e], x[e + 1], x[e + 2], x[e + 3], s, o, flags, qmin, qmax);
+          u[e] = __fadd_rn(r.x, kMagicG); u[e + 1] = __fadd_rn(r.y, kMagicG);
+          u[e + 2] = __fadd_rn(r.z, kMagicG); u[e + 3] = __fadd_rn(r.w, kMagicG);
+          if (kSign) { sg[e] = r.x; sg[e + 1] = r.y; sg[e + 2] = r.z; sg[e + 3] = r.w; }
+        }
+        if (!COMPUTE) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) bad |= (x[e] != x[e]);
+        }
       }
-    }
-
-    // ---- outputs
-    if (OUT == AMCT_OUT_I8) {
-      int8_t* dst = reinterpret_cast<int8_t*>(p.out) + row * p.ld_out + j0;
+      // ---- this vector's output
+      constexpr int kMagicBits = 0x4B400000;            // 1.5 * 2^23 as an integer: u's bits minus this is the level
+      if constexpr (OUT == AMCT_OUT_PACK4) {
+        // nibble = level + 8; the pack saturates to [-8, 7] in two's complement, flipping bit 3 adds the 8
+        uint32_t w = 0;
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        uint32_t w[E / 4];
+        for (int e = E - 2; e >= 0; e -= 2)
+          w = pack_sat_s4(__float_as_int(u[e + 1]) - kMagicBits, __float_as_int(u[e]) - kMagicBits, w);
+        words[i] = w ^ (E == 8 ? 0x88888888u : 0x8888u);
+      } else if constexpr (OUT == AMCT_OUT_I8) {
 #pragma unroll
         for (int g = 0; g < E / 4; ++g) {
-          const float* q = &u[i * E + 4 * g];
-          w[g] = __byte_perm(__byte_perm(__float_as_uint(q[0]), __float_as_uint(q[1]), 0x0040),
-                             __byte_perm(__float_as_uint(q[2]), __float_as_uint(q[3]), 0x0040), 0x5410);
+          uint32_t w = pack_sat_s8(__float_as_int(u[4 * g + 3]) - kMagicBits, __float_as_int(u[4 * g + 2]) - kMagicBits, 0);
+          words[i * 2 + g] = pack_sat_s8(__float_as_int(u[4 * g + 1]) - kMagicBits, __float_as_int(u[4 * g]) - kMagicBits, w);
         }
-        if constexpr (E == 8) *reinterpret_cast<uint2*>(dst + i * E) = make_uint2(w[0], w[1]);
-        else *reinterpret_cast<uint32_t*>(dst + i * E) = w[0];
-      }
-    } else if (OUT == AMCT_OUT_I32) {
-      int* dst = reinterpret_cast<int*>(p.out) + row * p.ld_out + j0;
-      // sign-extend the 9 low bits that hold the level
+      } else if constexpr (OUT == AMCT_OUT_I32) {
+        int* dst = reinterpret_cast<int*>(p.out) + row * p.ld_out + j0 + i * E;
 #pragma unroll
-      for (int e = 0; e < EP; e += 4)
-        *reinterpret_cast<int4*>(dst + e) = make_int4(((int)__float_as_uint(u[e]) << 23) >> 23, ((int)__float_as_uint(u[e + 1]) << 23) >> 23,
-                                                      ((int)__float_as_uint(u[e + 2]) << 23) >> 23, ((int)__float_as_uint(u[e + 3]) << 23) >> 23);
-    } else if (OUT == AMCT_OUT_PACK4) {
-      uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + row * p.ld_out + j0 / 2;
-      // nibble = level + 8 in [0, 15]; four nibbles are combined as an exact fp32 sum below 2^16
-      // (FMA pipe), whose integer value again sits in the low mantissa bits after adding 1.5 * 2^23
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        uint32_t h[E / 4];
-#pragma unroll
-        for (int g = 0; g < E / 4; ++g) {
-          const float* q = &u[i * E + 4 * g];
-          const float c0 = __fsub_rn(q[0], kMagicG - 8.f), c1 = __fsub_rn(q[1], kMagicG - 8.f);
-          const float c2 = __fsub_rn(q[2], kMagicG - 8.f), c3 = __fsub_rn(q[3], kMagicG - 8.f);
-          const float v4 = __fmaf_rn(__fmaf_rn(__fmaf_rn(c3, 16.f, c2), 16.f, c1), 16.f, c0);
-          h[g] = __float_as_uint(__fadd_rn(v4, kMagicG));
-        }
-        if constexpr (E == 8) *reinterpret_cast<uint32_t*>(dst + i * (E / 2)) = __byte_perm(h[0], h[1], 0x5410);
-        else *reinterpret_cast<uint16_t*>(dst + i * (E / 2)) = (uint16_t)h[0];
-      }
-    } else if (kFake) {  // (level - offset) * scale, rounded once to T
-#pragma unroll
-      for (int i = 0; i < VPT; ++i) {
+        for (int e = 0; e < E; e += 4)
+          *reinterpret_cast<int4*>(dst + e) = make_int4(__float_as_int(u[e]) - kMagicBits, __float_as_int(u[e + 1]) - kMagicBits,
+                                                        __float_as_int(u[e + 2]) - kMagicBits, __float_as_int(u[e + 3]) - kMagicBits);
+      } else if constexpr (kFake) {  // (level - offset) * scale, rounded once to T
         Vec16<T> r;
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-          float d = copysignf(__fsub_rn(u[i * E + e], kMagicG), sg[i * E + e]);
-          if (has_off) d = __fsub_rn(d, o);
+          float d = __fsub_rn(u[e], kMagicG);
+          if (kSign) d = copysignf(d, sg[e]);
+          if (HAS_OFF) d = __fsub_rn(d, o);
           r.v[e] = ElemTraits<T>::from_f(__fmul_rn(d, s));
         }
         *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + row * p.ld_out + j0 + i * E) = *reinterpret_cast<const uint4*>(&r);
       }
     }
+    if constexpr (OUT == AMCT_OUT_PACK4) {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + row * p.ld_out + j0 / 2;
+      if constexpr (E == 8) *reinterpret_cast<uint4*>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
+      else *reinterpret_cast<uint2*>(dst) = make_uint2(words[0] | (words[1] << 16), words[2] | (words[3] << 16));
+    } else if constexpr (OUT == AMCT_OUT_I8) {
+      int8_t* dst = reinterpret_cast<int8_t*>(p.out) + row * p.ld_out + j0;
+      if constexpr (E == 8) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(words[4], words[5], words[6], words[7]);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(words[0], words[2], words[4], words[6]);
+      }
+    }
+    // fminf / fmaxf drop NaN; the reference raises on it
+    if (!COMPUTE && bad && p.status) atomicOr(p.status, 1);
   }
+}
+
+template <typename T, int OUT>
+static void launch_groups_mode(const GroupParams& p, dim3 grid, int threads, cudaStream_t st) {
+  const bool has_off = p.offset != nullptr, pre = p.pre_op != AMCT_PRE_NONE;
+#define AMCT_GROUPS_CASE(C, O, P) \
+  if ((p.compute != 0) == C && has_off == O && pre == P) AMCT_LAUNCH(grid, threads, st, (p), quant_groups_kernel<T, OUT, C, O, P>)
+  AMCT_GROUPS_CASE(true, true, false); AMCT_GROUPS_CASE(true, false, false);
+  AMCT_GROUPS_CASE(false, true, false); AMCT_GROUPS_CASE(false, false, false);
+  AMCT_GROUPS_CASE(true, true, true); AMCT_GROUPS_CASE(true, false, true);
+  AMCT_GROUPS_CASE(false, true, true); AMCT_GROUPS_CASE(false, false, true);
+#undef AMCT_GROUPS_CASE
 }
 
 template <typename T>
 static int launch_groups(GroupParams p, int group, cudaStream_t st) {
   constexpr int E = ElemTraits<T>::kPerVec;
-  if (group % (2 * E) || p.k % group) return 1;
-  const int lanes = group / (2 * E);
+  constexpr int EP = 4 * E;                          // elements per thread
+  if (group % EP || p.k % group) return 1;
+  const int lanes = group / EP;
   if (lanes > 32 || (lanes & (lanes - 1))) return 1;
   if (!aligned16(p.x) || (p.ld * (int64_t)sizeof(T)) % 16 || (p.pre && !aligned16(p.pre))) return 1;
   if (p.k / E > 0x3fffffff || p.rows > 0x7fffffffLL) return 1;
   if (p.out_mode != AMCT_OUT_NONE) {
     const uintptr_t o = reinterpret_cast<uintptr_t>(p.out);
     switch (p.out_mode) {
-      case AMCT_OUT_I8: if (o % E || p.ld_out % E) return 1; break;
+      case AMCT_OUT_I8: if (o % 16 || p.ld_out % 16) return 1; break;
       case AMCT_OUT_I32: if (o % 16 || (p.ld_out * 4) % 16) return 1; break;
-      case AMCT_OUT_PACK4: if (o % (E / 2) || p.ld_out % (E / 2)) return 1; break;
+      case AMCT_OUT_PACK4: if (o % (EP / 2) || p.ld_out % (EP / 2)) return 1; break;
       default: if (o % 16 || (p.ld_out * (int64_t)sizeof(T)) % 16) return 1; break;
     }
   }
   int l2 = 0;
   while ((1 << l2) < lanes) ++l2;
   p.lanes_log2 = l2;
-  const int64_t nthr_row = p.k / (2 * E);
-  dim3 grid((unsigned)((nthr_row + 255) / 256), 1);
-  int64_t gy = (148LL * 4 + grid.x - 1) / grid.x;      // 4 resident blocks per SM (register use)
+  const int64_t nthr_row = p.k / EP;
+  // whole warps; a row shorter than a block's worth of threads gets a smaller block instead of idle warps
+  int threads = (int)(nthr_row >= 256 ? 256 : ((nthr_row + 31) / 32) * 32);
+  dim3 grid((unsigned)((nthr_row + threads - 1) / threads), 1);
+  int64_t gy = (148LL * 2048 / threads + grid.x - 1) / grid.x;      // as many blocks as can be resident
   if (gy > p.rows) gy = p.rows;
   if (gy > 65535) gy = 65535;
   grid.y = (unsigned)(gy < 1 ? 1 : gy);
   switch (p.out_mode) {
-    case AMCT_OUT_NONE: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_NONE>); break;
-    case AMCT_OUT_I8: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_I8>); break;
-    case AMCT_OUT_I32: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_I32>); break;
-    case AMCT_OUT_PACK4: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_PACK4>); break;
-    case AMCT_OUT_FAKE: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_FAKE>); break;
-    case AMCT_OUT_FAKE_AWQ: AMCT_LAUNCH(grid, 256, st, (p), quant_groups_kernel<T, AMCT_OUT_FAKE_AWQ>); break;
+    case AMCT_OUT_NONE: launch_groups_mode<T, AMCT_OUT_NONE>(p, grid, threads, st); break;
+    case AMCT_OUT_I8: launch_groups_mode<T, AMCT_OUT_I8>(p, grid, threads, st); break;
+    case AMCT_OUT_I32: launch_groups_mode<T, AMCT_OUT_I32>(p, grid, threads, st); break;
+    case AMCT_OUT_PACK4: launch_groups_mode<T, AMCT_OUT_PACK4>(p, grid, threads, st); break;
+    case AMCT_OUT_FAKE: launch_groups_mode<T, AMCT_OUT_FAKE>(p, grid, threads, st); break;
+    case AMCT_OUT_FAKE_AWQ: launch_groups_mode<T, AMCT_OUT_FAKE_AWQ>(p, grid, threads, st); break;
     default: return AMCT_ERR_ARG;
   }
   AMCT_CHECK_LAUNCH();

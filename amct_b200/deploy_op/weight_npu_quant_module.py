@@ -4,6 +4,7 @@ import torch
 from torch import nn
 
 from ..backend import ops
+from ..utils import int4pack
 
 
 def check_scale_offset_shape(weight, scale_w, offset_w=None, group_size=None):
@@ -28,9 +29,12 @@ class NpuWeightQuantizedLinear(nn.Module):
 
     Constructor argument and buffers follow
     amct_pytorch/deploy_op/weight_npu_quant_module.py:24-121:
-      quantized_weight  [K, N] int8, or packed INT4 uint8 [K/2, N] (two codes per byte
-                        along K, code + 8, even k in the low nibble) -- both are
-                        transposed views of K-contiguous storage
+      quantized_weight  INT8: [K, N] int8 (a transposed view of K-contiguous storage).
+                        INT4: int32 [K, N / 8], the int4pack form the reference stores (the result of
+                        torch_npu.npu_convert_weight_to_int4pack on the [K, N] codes; int32 [K, N] unpacked when N is
+                        not a multiple of 8), so state dicts go both ways; what the kernels read is the additional,
+                        non-persistent buffer ``weight_payload`` uint8 [N, K / 2] (two codes per byte along K, code
+                        + 8, even k in the low nibble), rebuilt from quantized_weight whenever a state dict is loaded
       scale_w           [K/group, N] (or [1, N]) in the weight dtype
       offset_w          same shape, the NEGATED offset, or None
       bias              [N], fp32 when the weight is bf16
@@ -74,11 +78,16 @@ class NpuWeightQuantizedLinear(nn.Module):
             strategy = 'channel' if scale_w.numel() == n else 'tensor'
             scale_nk = scale_w.reshape(-1, 1)
             offset_nk = None if offset_w is None else offset_w.reshape(-1, 1)
-        out = 'pack4' if wts_type == 'int4' else 'i8'
         _, _, codes = ops.quant_rows(weight, wts_type, offset_w is None, strategy, self.group_size,
-                                     scale=scale_nk, offset=offset_nk, out=out,
+                                     scale=scale_nk, offset=offset_nk, out='i8',
                                      pre=awq, pre_op='div' if awq is not None else 'none')
-        self.register_buffer('quantized_weight', codes.t())
+        if self.wts_bits == 4:
+            codes_kn = codes.t()
+            self.register_buffer('quantized_weight',
+                                 int4pack.to_int4pack(codes_kn) if n % 8 == 0 else codes_kn.to(torch.int32).contiguous())
+            self.register_buffer('weight_payload', int4pack.to_payload(codes), persistent=False)
+        else:
+            self.register_buffer('quantized_weight', codes.t())
 
         if self.group_size is None:
             # per-tensor factors are repeated to one per output channel (the op is per-channel)
@@ -100,14 +109,36 @@ class NpuWeightQuantizedLinear(nn.Module):
         else:
             self.bias = None
 
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        """Accepts every form of ``quantized_weight`` a checkpoint can hold (see int4pack.codes_from_buffer) and derives
+        what the kernels read from it once, here, not on the forward path."""
+        key = prefix + 'quantized_weight'
+        n = self.scale_w.shape[-1]
+        if self.wts_bits == 4 and key in state_dict:
+            codes_kn = int4pack.codes_from_buffer(state_dict[key], n)
+            state_dict = dict(state_dict)
+            state_dict[key] = int4pack.to_int4pack(codes_kn) if n % 8 == 0 else codes_kn.to(torch.int32).contiguous()
+            if tuple(self.quantized_weight.shape) != tuple(state_dict[key].shape):
+                self.quantized_weight = torch.empty_like(state_dict[key], device=self.quantized_weight.device)
+            self.weight_payload = int4pack.to_payload(codes_kn.t().contiguous()).to(self.quantized_weight.device)
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        if self.wts_bits == 8 and self.quantized_weight.stride(0) != 1:
+            # a checkpoint stores [K, N] row-major; the MMA wants K contiguous: transpose once, keep the shape
+            self.quantized_weight = self.quantized_weight.t().contiguous().t()
+
+    def _apply(self, fn, *args, **kwargs):
+        out = super()._apply(fn, *args, **kwargs)
+        if self.wts_bits == 8 and self.quantized_weight.stride(0) != 1:
+            self.quantized_weight = self.quantized_weight.t().contiguous().t()     # .to() / .cuda() copies lose the view's strides
+        return out
+
     @torch.no_grad()
     def forward(self, inputs):
-        from ..torch_npu_shim import npu_weight_quant_batchmatmul
+        from ..torch_npu_shim import weight_quant_matmul
         ori_shape = inputs.shape
         inputs = inputs.to(self.quantized_weight.device).reshape(-1, inputs.shape[-1])
         if self.scale_factor is not None:
             inputs = torch.mul(inputs, self.scale_factor)
-        output = npu_weight_quant_batchmatmul(inputs, self.quantized_weight, self.scale_w,
-                                              antiquant_offset=self.offset_w, bias=self.bias,
-                                              antiquant_group_size=self.group_size)
+        codes_nk = self.weight_payload if self.wts_bits == 4 else self.quantized_weight.t()
+        output = weight_quant_matmul(inputs, codes_nk, self.wts_bits, self.scale_w, self.offset_w, self.bias, self.group_size)
         return output.reshape(*ori_shape[:-1], -1)

@@ -15,9 +15,9 @@ class GPTQuant(BaseQuantizeModule):
 
     The Hessian X^T X accumulates on the device over ``batch_num`` batches; then columns are
     quantized in order of decreasing Hessian diagonal, each column's error being pushed into
-    the columns not yet quantized (blocks of 128).  The per-column fake quantization is the
-    row kernel (quant_dequant_weight, amct_pytorch/utils/quant_util.py:162-188) on the
-    transposed block; the Cholesky factorisations are torch.linalg.
+    the columns not yet quantized (blocks of 128).  The column loop of a block -- fake quantization
+    (quant_dequant_weight, amct_pytorch/utils/quant_util.py:162-188), error, rank-1 update -- is one kernel
+    (amct_gptq_block); the trailing update of a block is one GEMM; the Cholesky factorisations are torch.linalg.
     """
 
     def __init__(self, ori_module, layer_name, quant_config):
@@ -62,12 +62,6 @@ class GPTQuant(BaseQuantizeModule):
         if not torch.isfinite(self.hessian).all():
             raise RuntimeError("{}'s hessian matrix has invalid value, inf or nan.".format(self.layer_name))
 
-    def _fake_quant_column(self, w, scale, offset):
-        """w [N] with one (scale, offset) per row -> quantize-dequantize, fp32."""
-        _, _, fq = ops.quant_rows(w.reshape(-1, 1).contiguous(), self.wts_type, offset is None, 'channel',
-                                  scale=scale.reshape(-1), offset=None if offset is None else offset.reshape(-1), out='fake')
-        return fq.reshape(-1)
-
     def get_opt_weight_and_quant_factor(self):
         cfg = self.quant_config.get('weights_cfg')
         self.group_size = cfg.get('group_size')
@@ -84,36 +78,25 @@ class GPTQuant(BaseQuantizeModule):
 
         scale_w, offset_w = weight_scale_offset(weight, self.wts_type, cfg.get('symmetric'), cfg.get('strategy'),
                                                 self.group_size)
-        w_sorted = weight[:, perm]
+        w_sorted = weight[:, perm].contiguous()             # row-major: the block kernel walks rows
         h = hessian[perm][:, perm]
         diag = torch.arange(columns, device=weight.device)
         h[diag, diag] += self.perc_damp * torch.mean(torch.diag(h))
         h = torch.linalg.cholesky(h)
         h = torch.cholesky_inverse(h)
-        h_inv = torch.linalg.cholesky(h, upper=True)
+        h_inv = torch.linalg.cholesky(h, upper=True).contiguous()       # (the upper factor comes back as a transposed view)
         del h
         self.hessian = None
 
-        def factors(col):
-            """(scale, offset) [N] for the original column index `col`."""
-            if self.group_size:
-                g = int(col) // self.group_size
-                return scale_w[:, g].reshape(-1), None if offset_w is None else offset_w[:, g].reshape(-1)
-            s = scale_w.reshape(-1)
-            o = None if offset_w is None else offset_w.reshape(-1)
-            return (s.expand(n) if s.numel() == 1 else s), (None if o is None else (o.expand(n) if o.numel() == 1 else o))
-
-        perm_host = perm.tolist()
+        # quant factors as [N or 1, G] tables; a block column takes the entry of its original column's group
+        groups = scale_w.shape[1] if self.group_size else 1
+        scale_tab = scale_w.reshape(-1, groups) if self.group_size else scale_w.reshape(-1, 1)
+        offset_tab = None if offset_w is None else (offset_w.reshape(-1, groups) if self.group_size else offset_w.reshape(-1, 1))
+        col_groups = (perm // self.group_size if self.group_size else torch.zeros_like(perm)).to(torch.int32)
+        bits = ops.bits_of(self.wts_type)
         for i1 in range(0, columns, self.block_size):
             i2 = min(i1 + self.block_size, columns)
-            block = w_sorted[:, i1:i2]
-            err_block = torch.zeros_like(block)
-            h_block = h_inv[i1:i2, i1:i2]
-            for i in range(i2 - i1):
-                w = block[:, i]
-                s, o = factors(perm_host[i1 + i])
-                err = (w - self._fake_quant_column(w, s.contiguous(), None if o is None else o.contiguous())) / h_block[i, i]
-                block[:, i:] -= err.unsqueeze(1).matmul(h_block[i, i:].unsqueeze(0))
-                err_block[:, i] = err
+            # the whole column loop of the block is one kernel (one warp per weight row); the trailing update is one GEMM
+            err_block = ops.gptq_block(w_sorted[:, i1:i2], h_inv[i1:i2, i1:i2], scale_tab, offset_tab, col_groups[i1:i2], bits)
             w_sorted[:, i2:] -= err_block.matmul(h_inv[i1:i2, i2:])
         return w_sorted[:, invperm].to(self.weight.dtype), scale_w, offset_w

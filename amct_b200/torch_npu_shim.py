@@ -37,31 +37,49 @@ def npu_quant_matmul(x1, x2, scale, offset=None, bias=None, pertoken_scale=None,
 FUSED_MAX_TOKENS = 512
 
 
-def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, quant_scale=None,
-                                 quant_offset=None, bias=None, antiquant_group_size=0, **_):
-    """x [M, K] (fp16/bf16) times the dequantized weight; weight is int8 [K, N] or packed
-    uint8 [K/2, N] as produced by npu_convert_weight_to_int4pack."""
-    bits = 4 if weight.dtype == torch.uint8 else 8
+def weight_quant_matmul(x, codes_nk, bits, antiquant_scale, antiquant_offset, bias, group_size):
+    """x [..., K] (fp16 / bf16) times the dequantized weight, codes in the kernels' own form: int8 [N, K], or the INT4
+    payload uint8 [N, K / 2]."""
     k = x.shape[-1]
-    codes_nk = _as_nk(weight)
-    # up to FUSED_MAX_TOKENS rows: one kernel, codes dequantized in shared memory ahead of the MMA (the weight is
-    # streamed once, in its packed form).  More rows, or shapes that kernel does not take: dequantize to HBM once and
-    # run the 16-bit GEMM, whose larger tiles win once the work is tensor-bound (measured cross-over 512-1024 rows).
+    # up to FUSED_MAX_TOKENS rows: one kernel that streams the packed weight once (a weight-streaming kernel for up to
+    # 16 rows, codes dequantized in shared memory ahead of the MMA beyond that).  More rows, or shapes those kernels do
+    # not take: dequantize to HBM once and run the 16-bit GEMM, whose larger tiles win once the work is tensor-bound
+    # (measured cross-over 512-1024 rows).
     x2 = x.reshape(-1, k)
     out = None
     if x2.shape[0] <= FUSED_MAX_TOKENS:
-        out = ops.gemm_w4a16(x2, codes_nk, bits, antiquant_scale, antiquant_offset, antiquant_group_size,
-                             bias=bias, out_dtype=x.dtype)
+        out = ops.gemm_w4a16(x2, codes_nk, bits, antiquant_scale, antiquant_offset, group_size, bias=bias, out_dtype=x.dtype)
     if out is None:
-        w = ops.dequant_weight(codes_nk, bits, antiquant_scale.to(x.dtype), antiquant_offset, antiquant_group_size)
-        out = ops.gemm_f16(x.reshape(-1, k), w, bias=bias, out_dtype=x.dtype)
+        w = ops.dequant_weight(codes_nk, bits, antiquant_scale.to(x.dtype), antiquant_offset, group_size)
+        out = ops.gemm_f16(x2, w, bias=bias, out_dtype=x.dtype)
     return out.reshape(*x.shape[:-1], -1)
 
 
+_PAYLOADS = {}
+
+
+def npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None, quant_scale=None,
+                                 quant_offset=None, bias=None, antiquant_group_size=0, **_):
+    """torch_npu's call: weight is int8 [K, N], or INT4 as int32 [K, N / 8] (the result of
+    npu_convert_weight_to_int4pack) -- converted to the kernels' K-major payload on first sight and kept while the
+    tensor lives; the deploy module holds that payload itself and does not come through here."""
+    n = antiquant_scale.shape[-1]
+    if weight.dtype == torch.int8:
+        return weight_quant_matmul(x, _as_nk(weight), 8, antiquant_scale, antiquant_offset, bias, antiquant_group_size)
+    key = (weight.data_ptr(), weight._version, tuple(weight.shape), weight.dtype)
+    payload = _PAYLOADS.get(key)
+    if payload is None:
+        from .utils import int4pack
+        _PAYLOADS.clear()                              # one weight at a time: a cache, not a store
+        payload = int4pack.to_payload(int4pack.codes_from_buffer(weight, n).t().contiguous())
+        _PAYLOADS[key] = payload
+    return weight_quant_matmul(x, payload, 4, antiquant_scale, antiquant_offset, bias, antiquant_group_size)
+
+
 def npu_convert_weight_to_int4pack(weight, inner_k_tiles=0):
-    """int32 codes [K, N] in [-8, 7] -> uint8 [K/2, N] (a transposed view of [N, K/2])."""
-    u = (weight + 8).to(torch.uint8)
-    return (u[0::2] | (u[1::2] << 4)).t().contiguous().t()
+    """int32 codes [K, N] in [-8, 7] -> int32 [K, N / 8], eight nibbles per word along N."""
+    from .utils import int4pack
+    return int4pack.to_int4pack(weight)
 
 
 class _Npu:

@@ -50,7 +50,7 @@ def parse():
     ap.add_argument('--layers', type=int, default=80, help='debug only: fewer layers is not the benchmark')
     ap.add_argument('--batch', type=int, default=BATCH)
     ap.add_argument('--seq', type=int, default=SEQ)
-    ap.add_argument('--cpu-sample-tokens', type=int, default=4096)
+    ap.add_argument('--cpu-sample-tokens', type=int, default=2048)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--mode', default='prefill', choices=['prefill', 'decode'],
                     help='decode: one new token for 64 sequences against a 2048-token KV cache (not the headline metric)')
@@ -72,62 +72,129 @@ def measured_peaks():
 
 
 # ----------------------------------------------------------------------------- CPU arm
-def cpu_linear_path(tokens, threads=None):
-    """Times the CPU oracle of one decoder layer's four quantized Linears (TP=1 shapes)
-    over `tokens` rows: dynamic per-token quantization + INT32 GEMM + dequant epilogue."""
-    # a launcher may have pinned OMP_NUM_THREADS=1: use every core this process may run on
-    threads = threads or len(os.sched_getaffinity(0))
-    from oracle import intq, npu_ops
-    from amct_b200.workloads.llama_tp import LLAMA3_70B as sh
-    if threads:
-        torch.set_num_threads(threads)
-    g = torch.Generator().manual_seed(SEED)
-    dims = [(sh.hidden, (sh.n_heads + 2 * sh.n_kv_heads) * sh.head_dim), (sh.n_heads * sh.head_dim, sh.hidden),
-            (sh.hidden, 2 * sh.intermediate), (sh.intermediate, sh.hidden)]
-    layers = []
-    for k, n in dims:
-        w_kn = torch.randint(-128, 128, (k, n), generator=g, dtype=torch.int8)
-        layers.append((torch.randn(tokens, k, generator=g).to(torch.bfloat16), w_kn, torch.rand(n, generator=g) * 1e-3))
+REF_DIR = os.path.join(ROOT, 'baseline', '_ref')
 
-    def run():
-        for x, w_kn, sw in layers:
-            q, s = intq.dynamic_per_token(x)
-            npu_ops.npu_quant_matmul(q, w_kn, sw, s, None, torch.bfloat16, fast=True)
 
-    run()
-    t0 = time.perf_counter()
-    run()
-    return time.perf_counter() - t0
+def _register_cpu_torch_npu():
+    """``torch_npu`` for the reference on a machine without an NPU: the four ops of its deploy path as the CPU
+    statement in oracle/npu_ops.py gives them (INT8 GEMM through torch's CPU int8 kernel, all host threads)."""
+    import types
+    from oracle import npu_ops
+    mod = types.ModuleType('torch_npu')
+    mod.npu_quantize = npu_ops.npu_quantize
+    mod.npu_quant_matmul = lambda x1, x2, scale=None, pertoken_scale=None, bias=None, output_dtype=torch.bfloat16, **kw: \
+        npu_ops.npu_quant_matmul(x1, x2, scale, pertoken_scale, bias, output_dtype, fast=True)
+    mod.npu_weight_quant_batchmatmul = npu_ops.npu_weight_quant_batchmatmul
+    mod.npu_convert_weight_to_int4pack = lambda w, inner_k_tiles=0: npu_ops.npu_convert_weight_to_int4pack(w)
+    mod.npu = types.SimpleNamespace(is_available=lambda: False, empty_cache=lambda: None)
+    sys.modules['torch_npu'] = mod
+    if not hasattr(torch.Tensor, 'npu'):
+        torch.Tensor.npu = lambda self, *a, **k: self
+
+
+class _LayerLinears(torch.nn.Module):
+    """The four quantized Linears of one decoder layer at TP = 1 (fused q/k/v and gate/up as the GPU arm has them),
+    each fed its own input: what the reference's quantize() / convert() operate on."""
+
+    def __init__(self, shape, gen):
+        super().__init__()
+        dims = {'qkv_proj': (shape.hidden, (shape.n_heads + 2 * shape.n_kv_heads) * shape.head_dim),
+                'o_proj': (shape.n_heads * shape.head_dim, shape.hidden),
+                'gate_up_proj': (shape.hidden, 2 * shape.intermediate),
+                'down_proj': (shape.intermediate, shape.hidden)}
+        for name, (k, n) in dims.items():
+            lin = torch.nn.Linear(k, n, bias=False, dtype=torch.bfloat16)
+            lin.weight.data = torch.empty(n, k).normal_(0, 0.02, generator=gen).to(torch.bfloat16)
+            setattr(self, name, lin)
+
+    def forward(self, x_hidden, x_inter):
+        return (self.qkv_proj(x_hidden), self.o_proj(x_hidden), self.gate_up_proj(x_hidden), self.down_proj(x_inter))
+
+
+class ReferenceLinearPath:
+    """The reference's own W8A8 deploy path on the host cores: ``amct_pytorch.quantize`` (MinMaxQuant, per-channel INT8
+    weights, per-token INT8 activations) -> one calibration forward -> ``amct_pytorch.convert`` ->
+    ``NpuQuantizationLinear.forward`` (amct_pytorch/deploy_op/npu_quantization_linear.py:89-103), imported unmodified
+    from baseline/_ref.  The package's calls into torch_npu land in oracle/npu_ops.py (the reference ships no
+    implementation of them).  One step = the four Linears of one layer over `tokens` rows; a prefill step of the
+    benchmark is 80 layers x 65536 rows of exactly this work plus attention and norms, which are left out."""
+
+    def __init__(self, tokens):
+        if not os.path.isdir(os.path.join(REF_DIR, 'amct_pytorch')):
+            raise FileNotFoundError(f'{REF_DIR}/amct_pytorch missing: install the reference with pip --target baseline/_ref')
+        torch.set_num_threads(len(os.sched_getaffinity(0)))      # a launcher may have pinned OMP_NUM_THREADS=1
+        _register_cpu_torch_npu()
+        os.environ.setdefault('AMCT_LOG_LEVEL', 'warning')
+        cwd = os.getcwd()
+        import tempfile
+        os.chdir(tempfile.mkdtemp(prefix='amct_ref_'))           # the reference writes its log directory into the cwd
+        try:
+            sys.path.insert(0, REF_DIR)
+            import amct_pytorch
+        finally:
+            sys.path.remove(REF_DIR)
+            os.chdir(cwd)
+        from amct_b200.workloads.llama_tp import LLAMA3_70B as sh
+        g = torch.Generator().manual_seed(SEED)
+        self.tokens = tokens
+        self.model = _LayerLinears(sh, g)
+        self.x_hidden = torch.randn(tokens, sh.hidden, generator=g).to(torch.bfloat16)
+        self.x_inter = torch.randn(tokens, sh.intermediate, generator=g).to(torch.bfloat16)
+        cfg = {'batch_num': 1, 'quant_cfg': {'weights': {'type': 'int8', 'symmetric': True, 'strategy': 'channel'},
+                                             'inputs': {'type': 'int8', 'symmetric': True, 'strategy': 'token'}},
+               'algorithm': {'minmax'}}
+        amct_pytorch.quantize(self.model, cfg)
+        with torch.no_grad():
+            self.model(self.x_hidden, self.x_inter)              # calibration
+        amct_pytorch.convert(self.model)
+        kinds = {type(m).__name__ for m in self.model.children()}
+        if kinds != {'NpuQuantizationLinear'}:
+            raise RuntimeError(f'the reference left {kinds} after convert()')
+
+    def step(self):
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            self.model(self.x_hidden, self.x_inter)
+        return time.perf_counter() - t0
 
 
 def cpu_baseline(tokens, n_layers):
-    sec_per_layer = cpu_linear_path(tokens)
+    path = ReferenceLinearPath(tokens)
+    path.step()
+    sec_per_layer = path.step()
     tok_s = tokens / (sec_per_layer * n_layers)
-    return {'value': tok_s, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
-            'sample': f'CPU oracle (torch CPU, int8 GEMM via torch._int_mm) of the 4 quantized Linears of one decoder '
-                      f'layer over {tokens} tokens, {sec_per_layer:.3f} s; scaled x{n_layers} layers; attention/norms excluded',
+    return {'value': tok_s, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'reference',
+            'sample': f'the reference package (baseline/_ref) quantize -> convert -> NpuQuantizationLinear.forward, torch_npu '
+                      f'ops from the CPU oracle (INT8 GEMM via torch._int_mm), 4 Linears of one decoder layer over {tokens} '
+                      f'tokens: {sec_per_layer:.3f} s; scaled x{n_layers} layers; attention/norms excluded',
             'host_cpus': os.cpu_count()}
 
 
 def run_reference(args):
-    """--impl reference: the CPU statement of the path on the host cores, bounded sample per step."""
+    """--impl reference: the reference's own CPU path on the host cores, a bounded sample per step (rank 0 only)."""
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
     tokens = args.cpu_sample_tokens
-    for _ in range(min(args.warmup, 1)):
-        cpu_linear_path(tokens)
-    times = [cpu_linear_path(tokens) for _ in range(args.steps)]
+    try:
+        path = ReferenceLinearPath(tokens)
+    except Exception as exc:                                     # noqa: BLE001 -- reported, not hidden
+        print(json.dumps({'impl': 'reference', 'unavailable': f'{type(exc).__name__}: {exc}'[:300]}), flush=True)
+        return
+    for _ in range(args.warmup):
+        path.step()
+    times = [path.step() for _ in range(args.steps)]
     sec = statistics.mean(times)
     tok_s = tokens / (sec * 80)
+    sample = (f'reference package from baseline/_ref, 4 quantized Linears of one decoder layer (TP=1 shapes) over {tokens} tokens '
+              f'per step ({sec:.3f} s), scaled x80 layers; attention / norms excluded; torch_npu ops from the CPU oracle')
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': tok_s, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': args.steps,
         'warmup': args.warmup, 'ms_per_step': (BATCH * SEQ) / tok_s * 1e3, 'higher_is_better': True, 'scaling': 'strong',
         'vs_baseline': None, 'dtype': 'int8', 'data': 'synthetic',
         'config': {'workload': 'llama3-70b W8A8 prefill, batch 32 x seq 2048, 80 layers (Linear path only on CPU)',
                    'parallelism': 'cpu'},
-        'cpu_baseline': {'value': tok_s, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
-                         'sample': f'4 quantized Linears of one decoder layer over {tokens} tokens per step, scaled x80 layers'},
+        'cpu_baseline': {'value': tok_s, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'reference', 'sample': sample},
         'e2e': {'value': tok_s, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
@@ -307,10 +374,34 @@ def main():
     ops.GEMM_PROFILE = []
     (eager_resident if graph is not None else step_resident)()
     torch.cuda.synchronize()
-    gemm_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in ops.GEMM_PROFILE)
-    gemm_ops = sum(o for _, _, o in ops.GEMM_PROFILE)
+    # per stream: launches of one stream do not overlap each other, launches of different streams do (their event
+    # intervals then include waiting for the other stream's kernel), so only a single-stream step gives a kernel rate
+    per_stream = {}
+    for e0, e1, _, stream in ops.GEMM_PROFILE:
+        per_stream[stream] = per_stream.get(stream, 0.0) + e0.elapsed_time(e1)
+    gemm_ms = max(per_stream.values()) if per_stream else 0.0
+    gemm_ops = sum(rec[2] for rec in ops.GEMM_PROFILE) / max(len(per_stream), 1)
     n_gemm = len(ops.GEMM_PROFILE)
+    gemm_streams = len(per_stream)
     ops.GEMM_PROFILE = None
+
+    # the tensor pipe's own INT8 rate on this GPU, measured after the timed region: the MMA-only kernel (no loads, no
+    # stores) back to back for about two seconds, rate of the second half (at the power limit, like the step above)
+    mma_only = None
+    if world == 1:
+        st_word = torch.zeros(1, dtype=torch.int32, device=dev)
+        ops.mma_peak('i8', 20000, status=st_word)
+        torch.cuda.synchronize()
+        rates, t_end = [], time.time() + 2.0
+        while time.time() < t_end:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            n_ops = ops.mma_peak('i8', 20000, status=st_word)
+            e1.record()
+            torch.cuda.synchronize()
+            rates.append(n_ops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        if not int(st_word.item()) & 2:
+            mma_only = statistics.median(rates[len(rates) // 2:])
 
     if rank != 0:
         if world > 1:
@@ -346,7 +437,12 @@ def main():
         'roofline': {'bound': 'tensor', 'kernel': 'gemm_tcgen05_kernel (kind::i8)', 'achieved': achieved, 'peak': peak,
                      'unit': 'TOP/s', 'frac': (achieved / peak) if achieved else None, 'traffic': traffic,
                      'traffic_note': traffic_note, 'launches_per_step': n_gemm, 'gemm_ms_per_step': gemm_ms,
-                     'peak_source': f'2 x bf16_tflops_sustained ({bf16_sus}) of {src}; no direct INT8 peak measurement'},
+                     'gemm_streams': gemm_streams,
+                     'peak_source': f'2 x bf16_tflops_sustained ({bf16_sus}) of {src}',
+                     'mma_only_int8_tops': mma_only,
+                     'frac_of_mma_only': (achieved / mma_only) if (achieved and mma_only) else None,
+                     'mma_only_note': 'tcgen05.mma kind::i8 issued back to back by one CTA per SM on operands resident in shared '
+                                      'memory (no loads, no stores), sustained for 2 s on this GPU after the timed region'},
         'clocks': clocks,
     }
     if world == 1 and not args.no_cpu_baseline:

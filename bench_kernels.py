@@ -107,8 +107,10 @@ def steady_case(name, fn, secs, nops=None, nbytes=None, out=None):
         out.flush()
 
 
-def report(name, med, best, nbytes=None, nops=None, out=None, peak_mult=1.0):
+def report(name, med, best, nbytes=None, nops=None, out=None, peak_mult=1.0, extra=None):
     rec = {'case': name, 'ms_median': round(med, 5), 'ms_best': round(best, 5)}
+    if extra:
+        rec['cpu_baseline'] = extra
     if nbytes is not None:
         gbs = nbytes / (med * 1e-3) / 1e9
         rec.update(bound='hbm', bytes=nbytes, achieved=round(gbs, 1), unit='GB/s', peak=HBM, frac=round(gbs / HBM, 4))
@@ -122,6 +124,164 @@ def report(name, med, best, nbytes=None, nops=None, out=None, peak_mult=1.0):
     if out:
         out.write(line + '\n')
         out.flush()
+
+
+def mma_peak_lines(out):
+    """The MMA-only kernel for every kind, 3 s each, with the SM clock sampled through NVML: TOP/s and TOP/s per MHz."""
+    import threading
+    import time
+    import pynvml
+    pynvml.nvmlInit()
+    h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+    status = torch.zeros(1, dtype=torch.int32, device='cuda')
+    for kind in ('bf16', 'i8', 'mxf8', 'mxf4'):
+        steps = 20000
+        for _ in range(2):
+            nops = ops.mma_peak(kind, steps, status=status)
+        torch.cuda.synchronize()
+        samples, stop = [], []
+
+        def sampler():
+            while not stop:
+                samples.append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM), pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0))
+                time.sleep(0.02)
+        th = threading.Thread(target=sampler)
+        th.start()
+        times, t_end = [], time.time() + 3.0
+        while time.time() < t_end:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ops.mma_peak(kind, steps, status=status)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        stop.append(1)
+        th.join()
+        ops.raise_if_timed_out(status)
+        clk = statistics.median(c for c, _ in samples) if samples else None
+        first, last = min(times[:3]), statistics.median(times[len(times) // 2:])
+        rec = {'case': f'mma_peak {kind} (tcgen05.mma only, operands resident in shared memory)', 'launches': len(times),
+               'burst_tops': round(nops / (first * 1e-3) / 1e12, 1), 'sustained_tops': round(nops / (last * 1e-3) / 1e12, 1),
+               'sm_mhz_median': clk, 'power_w_max': max((p for _, p in samples), default=None),
+               'sustained_tops_per_mhz': round(nops / (last * 1e-3) / 1e12 / clk, 3) if clk else None,
+               'measured_bf16_burst': BF16, 'convention_multiple': {'bf16': 1, 'i8': 2, 'mxf8': 2, 'mxf4': 4}[kind]}
+        line = json.dumps(rec)
+        print(line, flush=True)
+        if out:
+            out.write(line + '\n')
+            out.flush()
+
+
+def c4_layer_line(out):
+    """Config 4: one Llama-3-8B decoder layer, SmoothQuant a = 0.5 from a 128 x 2048-token random calibration pass, then
+    HiFloat8 weights and activations on all seven Linears; evaluation batch 8 x 2048 (seed 3).  Tokens/s of the layer."""
+    from amct_b200.workloads import llama_hif8
+    os.environ.setdefault('AMCT_LOG_LEVEL', 'warning')
+    work = llama_hif8.build(calib_sequences=128, calib_seq=2048, calib_batch=8)
+    ids = torch.randint(0, work.layer.shape.vocab, (8, 2048), generator=torch.Generator().manual_seed(3)).cuda()
+    for _ in range(3):
+        work(ids)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(10):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        work(ids)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    med = statistics.median(times)
+    flops = work.linear_flops_per_token() * ids.numel()
+    rec = {'case': 'c4 llama3-8b layer, SmoothQuant 0.5 + HiFloat8 on 7 Linears, batch 8 x 2048', 'ms_median': round(med, 4),
+           'tokens_per_s': round(ids.numel() / (med * 1e-3), 1), 'linear_tflops': round(flops / (med * 1e-3) / 1e12, 1),
+           'frac_of_bf16_peak': round(flops / (med * 1e-3) / 1e12 / BF16, 4), 'calibration': 'L_cal = 2048, 128 sequences, 16 batches of 8',
+           'peak_source': SRC}
+    line = json.dumps(rec)
+    print(line, flush=True)
+    if out:
+        out.write(line + '\n')
+
+
+_REF = {}
+
+
+def reference_package():
+    """The reference package from baseline/_ref (None when it is not installed)."""
+    if 'mod' not in _REF:
+        ref_dir = os.path.join(ROOT, 'baseline', '_ref')
+        _REF['mod'] = None
+        if os.path.isdir(os.path.join(ref_dir, 'amct_pytorch')):
+            import tempfile
+            cwd = os.getcwd()
+            os.chdir(tempfile.mkdtemp(prefix='amct_ref_'))
+            sys.path.insert(0, ref_dir)
+            try:
+                import amct_pytorch.quantize_op.utils as qu
+                import amct_pytorch.utils.quant_util as qutil
+                _REF['mod'] = (qu, qutil)
+            except Exception:                                   # noqa: BLE001 -- no reference, no CPU line
+                pass
+            finally:
+                sys.path.remove(ref_dir)
+                os.chdir(cwd)
+    return _REF['mod']
+
+
+def cpu_baseline_for(name):
+    """The reference's own function for a kernel line, timed on the host cores on a bounded sample (rows cut so that one
+    call takes about a second); MX and HiFloat8 have no reference code: the CPU oracle stands in (kind 'port')."""
+    import time
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn, unit_bytes, rows, what, kind):
+        fn()
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        return {'value': round(unit_bytes * rows / dt / 1e9, 3), 'unit': 'GB/s', 'cores': torch.get_num_threads(), 'kind': kind,
+                'sample': f'{what}, {rows} rows, {dt:.3f} s'}
+    ref = reference_package()
+    if name.startswith('quant_dynamic_pertoken') and ref:
+        qu, qutil = ref
+        k = 8192
+        x = torch.randn(16384, k, generator=g).to(torch.bfloat16)
+
+        def fn():
+            mx, mn = x.amax(1, keepdim=True), x.amin(1, keepdim=True)
+            s, _ = qu.calculate_scale_offset(mx, mn, True, 'int8')
+            return qutil.convert_dtype(x / s, 'int8')
+        return timed(fn, k * 3 + 4, x.shape[0], 'reference amax/amin + calculate_scale_offset + convert_dtype', 'reference')
+    if (name.startswith('weight_quant_i4') or name.startswith('weight_codes_i4')) and ref:
+        qu, qutil = ref
+        w = (torch.randn(16384, 4096, generator=g) * 0.02).to(torch.bfloat16)
+
+        def fn():
+            mn, mx = qu.get_weight_min_max_by_granularity(w, {'weights_cfg': {'strategy': 'group', 'group_size': 128}})
+            s, o = qu.calculate_scale_offset(mx, mn, False, 'int4')
+            return qutil.quant_weight(w, 'int4', s, o, 128)
+        try:
+            return timed(fn, 4096 * 2.5, w.shape[0], 'reference group min/max + calculate_scale_offset + quant_weight', 'reference')
+        except Exception:                                       # noqa: BLE001
+            return None
+    if name.startswith('fake_quant') and ref:
+        qu, qutil = ref
+        from oracle import intq
+        w = (torch.randn(16384, 4096, generator=g) * 0.02).to(torch.bfloat16)
+        s, o = intq.weight_scale_offset(w, 'int4', False, 'group', 128)
+        qp = {'weights_cfg': {'quant_type': 'int4', 'group_size': 128}}
+        return timed(lambda: qutil.quant_dequant_weight(w, qp, s, o), 4096 * 4, w.shape[0], 'reference quant_dequant_weight', 'reference')
+    if name.startswith('mx_quant'):
+        from oracle import mx
+        fmt = 'fp8' if ' fp8 ' in name else 'fp4'
+        x = torch.randn(4096 if fmt == 'fp8' else 1024, 8192, generator=g).to(torch.bfloat16)
+        return timed(lambda: mx.quantize(x, fmt), 8192 * (3 if fmt == 'fp8' else 2.5), x.shape[0], 'CPU oracle mx.quantize', 'port')
+    if name.startswith('hif8_encode'):
+        from oracle import hif8
+        x = torch.randn(256, 14336, generator=g).float().numpy()
+        return timed(lambda: hif8.encode(x), 14336 * 3, x.shape[0], 'CPU oracle hif8.encode', 'port')
+    return None
 
 
 def cases():
@@ -238,6 +398,19 @@ def cases():
            lambda x: (lambda: ops.hif8_fake_quant(x)), dict(nbytes=16384 * 4096 * 4))
     yield ('hif8_decode [14336x4096] -> bf16', lambda: torch.randint(0, 256, (14336, 4096), device='cuda', dtype=torch.uint8),
            lambda c: (lambda: ops.hif8_decode(c)), dict(nbytes=14336 * 4096 * 3))
+    # ---- HiFloat8 Linear (config 4 shapes, 16384 tokens): weight codes decoded ahead of the bf16 MMA.  Timed: the whole
+    # weight side of HiFloat8Linear.forward for an already fake-quantized activation: decode the codes, multiply.
+    for n, k, tag in ((4096, 4096, 'q / o'), (14336, 4096, 'gate / up'), (4096, 14336, 'down')):
+        def setup_h(n=n, k=k):
+            w = randn(n, k, torch.bfloat16, 0.02)
+            return ops.hif8_fake_quant(randn(16384, k, torch.bfloat16)), ops.hif8_encode(w), torch.empty(16384, n, device='cuda', dtype=torch.bfloat16)
+        yield (f'hif8 linear (decode + gemm) c4 {tag} 16384x{n}x{k} bf16', setup_h,
+               lambda t: (lambda: ops.gemm_f16(t[0], ops.hif8_decode(t[1], dtype=torch.bfloat16), out=t[2])),
+               dict(nops=2 * 16384 * n * k, peak_mult=1.0))
+    def setup_lut():
+        return randn(256, 4096, torch.bfloat16), ops.hif8_encode(randn(14336, 4096, torch.bfloat16, 0.02)), torch.empty(256, 14336, device='cuda', dtype=torch.bfloat16)
+    yield ('gemm_lut8 (hif8 codes decoded in shared memory) c4 gate 256x14336x4096 bf16', setup_lut,
+           lambda t: (lambda: ops.gemm_hif8_weight(t[0], t[1], out=t[2])), dict(nops=2 * 256 * 14336 * 4096, peak_mult=1.0))
     # ---- weight dequant (stage 1 of the weight-only Linear)
     def setup_dq():
         codes = torch.randint(0, 256, (11008, 2048), device='cuda', dtype=torch.uint8)
@@ -279,8 +452,15 @@ def main():
     ap.add_argument('--out', default='')
     ap.add_argument('--steady', type=float, default=0.0, help='seconds of back-to-back launches per case')
     ap.add_argument('--library-refs', action='store_true', help='add cuBLASLt / cuBLAS reference lines (context only)')
+    ap.add_argument('--mma-peak', action='store_true', help='only the MMA-only tensor-core peak measurement (all four kinds)')
+    ap.add_argument('--c4-layer', action='store_true', help='only the SmoothQuant + HiFloat8 Llama-3-8B layer (config 4): tokens/s')
+    ap.add_argument('--cpu', action='store_true', help='add a cpu_baseline (the reference function on the host cores, bounded sample) to the lines that have one')
     args = ap.parse_args()
     out = open(args.out, 'w') if args.out else None
+    if args.mma_peak:
+        return mma_peak_lines(out)
+    if args.c4_layer:
+        return c4_layer_line(out)
     todo = list(cases())
     if args.library_refs:
         for m, n, k in ((16384, 8192, 8192),):
@@ -303,7 +483,8 @@ def main():
             torch.cuda.empty_cache()
             continue
         med, best = time_case(fn, args.reps)
-        report(name, med, best, out=out, **kw)
+        extra = cpu_baseline_for(name) if args.cpu else None
+        report(name, med, best, out=out, extra=extra, **kw)
         del data, fn
         torch.cuda.empty_cache()
 

@@ -330,6 +330,17 @@ int amct_dsa_rotate_fakequant(const void* x, int dtype, int64_t rows, int64_t k,
                               int bits, int symmetric, int mode, float a, float b, void* out, int64_t ld_out,
                               void* stream);
 
+/* GPTQ: the column-by-column update of one block of b <= 128 (permuted) weight columns, the inner loop of
+ * amct_pytorch/quantize_op/gptq_module.py:137-151, in one launch.  w [n, ldw] fp32 holds the block's columns and is
+ * updated in place: for i = 0 .. b-1: q = quant_dequant(w[:, i]) (amct_pytorch/utils/quant_util.py:162-188, fp32);
+ * e = (w[:, i] - q) / hinv[i, i]; w[:, i:b] -= e (x) hinv[i, i:b]; err[:, i] = e.  hinv [b, ldh]: the block's corner of
+ * the upper Cholesky factor of the inverse Hessian.  scale fp32 / offset int32 (NULL: symmetric): [n, factors_ld]
+ * when row_factors, else [1, factors_ld]; block column i uses column col_group[i] of them (the group of its
+ * original index).  The trailing update w[:, i2:] -= err @ hinv[i1:i2, i2:] stays with the caller (one GEMM). */
+int amct_gptq_block(float* w, int64_t n, int64_t ldw, int b, const float* hinv, int64_t ldh, const float* scale,
+                    const int* offset, int64_t factors_ld, int row_factors, const int* col_group, int bits,
+                    float* err, int64_t lde, void* stream);
+
 /* ---- Glue of the sharded deploy workload (no counterpart in the reference) ---- */
 
 /* h = x + residual (rounded to dtype; residual may be NULL: h = x); n = round(h * rstd * gamma) with
@@ -350,6 +361,14 @@ int amct_addnorm_quant_pertoken(const void* x, const void* residual, int dtype, 
  * is rounded to dtype, like the same expression in torch ops. */
 int amct_rope_inplace(void* x, int dtype, int64_t tokens, int64_t ld, int heads, int head_dim,
                       const void* cos_table, const void* sin_table, int64_t seq, void* stream);
+
+/* Tensor-core peak of the device, measured (no counterpart in the reference): `ctas` CTAs (one per SM) each issue
+ * `steps` K blocks of four tcgen05.mma (M128 x N256, or N224 for the block-scaled kinds, x 32 bytes of K) back to
+ * back on operands resident in shared memory: no loads, no stores.  kind: 0 INT8, 1 bf16, 2 MXFP8 (E4M3, E8M0 block
+ * scales), 3 MXFP4.  The caller times the launch; one launch performs
+ * ctas * steps * amct_mma_peak_ops_per_cta_step(kind) operations.  Bit 1 of *status: a bounded wait expired. */
+int amct_mma_peak(int kind, int steps, int ctas, int* status, void* stream);
+int64_t amct_mma_peak_ops_per_cta_step(int kind);
 
 /* amct_gemm_w8a8 (per-token mode, no bias, fp16 / bf16 output) for a K-sharded ("row-parallel") Linear under tensor
  * parallelism, whose [m, n] result is one rank's PARTIAL sum: instead of one output matrix, output row r is

@@ -86,7 +86,18 @@ def npu_weight_quant_batchmatmul(x, wq_kn, antiquant_scale, antiquant_offset=Non
 
 
 def npu_convert_weight_to_int4pack(w_kn_int32):
-    """[K, N] int32 codes in [-8, 7] -> uint8 [K/2, N]: u = q + 8, row 2j in the
+    """[K, N] int32 codes in [-8, 7] -> int32 [K, N / 8]: eight two's-complement nibbles per word along N, column
+    8 j + i in bits [4 i, 4 i + 4) of word j -- the form the device op hands back to
+    amct_pytorch/deploy_op/weight_npu_quant_module.py:53-57 and a deployed checkpoint stores."""
+    k, n = w_kn_int32.shape
+    nib = (w_kn_int32.to(torch.int64) & 0xF).reshape(k, n // 8, 8)
+    word = sum(nib[..., i] << (4 * i) for i in range(8))
+    word = torch.where(word >= 2 ** 31, word - 2 ** 32, word)
+    return word.to(torch.int32)
+
+
+def pack_int4_along_k(w_kn_int32):
+    """[K, N] int32 codes in [-8, 7] -> uint8 [K/2, N], the payload this build's kernels read: u = q + 8, row 2j in the
     low nibble and row 2j+1 in the high nibble of byte [j, n] (low nibble =
     first element, as the in-tree ``pack_4bit`` does, amct_pytorch/experimental/
     quantization/DeepSeekV3.2/deploy.py:109-125).  Pairing along K and the bias

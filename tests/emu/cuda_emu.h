@@ -10,6 +10,7 @@
 // kernels above).  __shared__ becomes a static variable (one block is alive at a time).  The arithmetic intrinsics
 // map to the IEEE operations they name (compile with -ffp-contract=off); fmaf is the C library's exact one.
 #pragma once
+#define AMCT_CUDA_EMU 1          // the few helpers that are one PTX instruction on the GPU state its effect in C++ here
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>

@@ -219,8 +219,16 @@ def test_deploy_modules_against_golden():
                 assert bits_equal(got, want), (case, attr)
         want_q = G.get(f'{tag}/fc1.d.quantized_weight')
         got_q = net.fc1.quantized_weight
-        if case == 'w4_group_asym':                 # reference keeps int32 codes; here they are packed
-            got_q = npu_ops.unpack_int4(got_q.cpu())
+        if case == 'w4_group_asym':
+            # the reference's test double of npu_convert_weight_to_int4pack left the int32 codes unpacked; the buffer
+            # holds what the device op returns for them (int32, eight nibbles per word along N), and the kernels' own
+            # K-major payload sits beside it
+            from amct_b200.utils import int4pack
+            assert got_q.dtype == torch.int32 and got_q.shape == (want_q.shape[0], want_q.shape[1] // 8)
+            assert bits_equal(got_q, npu_ops.npu_convert_weight_to_int4pack(want_q))
+            assert bits_equal(net.fc1.weight_payload, npu_ops.pack_int4_along_k(want_q).t().contiguous())
+            assert 'fc1.weight_payload' not in net.state_dict()
+            got_q = int4pack.from_int4pack(got_q.cpu()).to(torch.int32)
         assert bits_equal(got_q.contiguous(), want_q), (case, 'quantized_weight')
 
         # forward of the first deploy layer vs the oracle's backend ops

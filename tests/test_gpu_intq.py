@@ -60,7 +60,7 @@ def test_weight_paths_golden(dname, qt, sym, strat):
     assert bits_equal(fake_awq, G.get(tag + '/fake_awq'))
     if qt == 'int4':
         _, _, packed = ops().quant_rows(w, qt, sym, strat, gs, scale=s, offset=o, out='pack4')
-        want = npu_ops.npu_convert_weight_to_int4pack(gold.t().contiguous()).t()
+        want = npu_ops.pack_int4_along_k(gold.t().contiguous()).t()
         assert bits_equal(packed, want.contiguous())
 
 
@@ -221,7 +221,7 @@ def test_dequant_weight_oracle(bits, group, offset, dtype):
     o = torch.randint(-8, 8, (ng, n), generator=g).to(dtype) if offset else None
     want = npu_ops.dequant_weight(q_kn, s, o, group, dtype).t().contiguous()
     if bits == 4:
-        codes = npu_ops.npu_convert_weight_to_int4pack(q_kn).t().contiguous()
+        codes = npu_ops.pack_int4_along_k(q_kn).t().contiguous()
     else:
         codes = q_kn.to(torch.int8).t().contiguous()
     got = ops().dequant_weight(codes.cuda(), bits, s.cuda(), dev(o), group)
@@ -341,6 +341,10 @@ def test_group_weight_quant_oracle(dtype, qt, sym, rows, k, gs):
         assert bits_equal(fake, intq.fake_quant(wp, qt, s, o, gs))
         _, _, fake_awq = ops().quant_rows(w.cuda(), qt, sym, 'group', gs, scale=s.cuda(), offset=dev(o), out='fake_awq', **kw)
         assert bits_equal(fake_awq, intq.fake_quant_awq(wp, qt, s, o, gs))
+        # factors and fake quantization from one read of the weight (what the AWQ search launches per candidate)
+        for mode, want_fake in (('fake', intq.fake_quant(wp, qt, s, o, gs)), ('fake_awq', intq.fake_quant_awq(wp, qt, s, o, gs))):
+            s4, o4, fake4 = ops().quant_rows(w.cuda(), qt, sym, 'group', gs, out=mode, **kw)
+            assert bits_equal(s4.reshape(s.shape), s) and bits_equal(fake4, want_fake), mode
 
 
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])

@@ -30,6 +30,25 @@ def tiled_to_rowmajor(tiled, rows, k, tile_rows=128):
     return torch.from_numpy(t[off])
 
 
+def padding_is_zero(tiled, rows, k, tile_rows=128):
+    """Every byte of the tiled layout that no (row, K block) maps to is zero (the GEMM copies whole atoms)."""
+    kb = k // 32
+    kb4 = (kb + 3) // 4
+    t = tiled.cpu().numpy().copy()
+    r = np.arange(rows)[:, None]
+    c = np.arange(kb)[None, :]
+    q = r % tile_rows
+    atom = (r // tile_rows) * ((tile_rows + 127) // 128) + q // 128
+    t[(atom * kb4 + c // 4) * 512 + (q % 32) * 16 + ((q % 128) // 32) * 4 + c % 4] = 0
+    return not t.any()
+
+
+def dirty_allocator(nbytes):
+    """Leaves a freed block full of 0xAB behind, so that the next torch.empty of that size does not start out zero."""
+    junk = torch.full((nbytes,), 0xAB, dtype=torch.uint8).cuda()
+    del junk
+
+
 def make_input(rows, k, dtype, seed):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(rows, k, generator=g) * torch.exp(torch.randn(rows, 1, generator=g) * 3)
@@ -46,12 +65,14 @@ def make_input(rows, k, dtype, seed):
 def test_mx_quant_matches_oracle(fmt, dtype, rows, k):
     x = make_input(rows, k, dtype, rows * 7 + k)
     want_p, want_s = mx.quantize(x, fmt)
+    dirty_allocator(((rows + 127) // 128) * ((k // 32 + 3) // 4) * 512)
     got_p, got_s, got_t = ops().mx_quant(x.cuda(), fmt)
     assert torch.equal(got_s.cpu(), want_s)
     assert torch.equal(got_p.cpu(), want_p)
-    assert torch.equal(tiled_to_rowmajor(got_t, rows, k), want_s)
+    assert torch.equal(tiled_to_rowmajor(got_t, rows, k), want_s) and padding_is_zero(got_t, rows, k)
+    dirty_allocator(((rows + 223) // 224) * 2 * ((k // 32 + 3) // 4) * 512)
     _, _, got_tb = ops().mx_quant(x.cuda(), fmt, operand='b')
-    assert torch.equal(tiled_to_rowmajor(got_tb, rows, k, 224), want_s)
+    assert torch.equal(tiled_to_rowmajor(got_tb, rows, k, 224), want_s) and padding_is_zero(got_tb, rows, k, 224)
 
 
 @pytest.mark.parametrize('fmt', ['fp8', 'fp4'])

