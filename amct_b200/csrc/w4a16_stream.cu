@@ -10,7 +10,8 @@
 //     step of K: several hundred small CTAs, all resident at once (five per SM), so the whole weight is requested
 //     in a single wave and the partial sums of a tile meet in shared memory, in warp order (deterministic; no
 //     workspace, no atomics);
-//   * streams the codes with 16-byte loads straight into registers, four steps ahead of their use, dequantizes them
+//   * streams the codes with 16-byte loads straight into registers, three or four steps ahead of their use (all
+//     addresses are per-thread base pointers plus one 32-bit counter that advances by a constant), dequantizes them
 //     there with packed 16-bit arithmetic -- (nibble | 0x4300) is the bf16 number 128 + nibble, a packed add of
 //     (offset - 8 - 128) is exact, a packed multiply by the scale rounds once: bit for bit the value
 //     amct_dequant_weight stores -- and multiplies with mma.sync.m16n8k16 (weights as the 16-row operand, tokens as the
@@ -46,7 +47,6 @@ template <> struct WsType<__nv_bfloat16> {
   static constexpr uint32_t kMagic = 0x43004300u;       // bf16 128.0 twice
   static constexpr float kMagicValue = 128.f;
   __device__ static P2 from_float(float v) { return __floats2bfloat162_rn(v, v); }
-  __device__ static P2 dup(__nv_bfloat16 v) { return __halves2bfloat162(v, v); }
   __device__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -58,13 +58,19 @@ template <> struct WsType<__half> {
   static constexpr uint32_t kMagic = 0x64006400u;       // fp16 1024.0 twice
   static constexpr float kMagicValue = 1024.f;
   __device__ static P2 from_float(float v) { return __floats2half2_rn(v, v); }
-  __device__ static P2 dup(__half v) { return __halves2half2(v, v); }
   __device__ static void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 };
+
+// one 16-bit half of v in both halves of a packed pair
+template <typename P2>
+__device__ __forceinline__ P2 ws_dup(uint32_t v, uint32_t selector) {
+  const uint32_t d = __byte_perm(v, 0u, selector);
+  return *reinterpret_cast<const P2*>(&d);
+}
 
 // pair s of a word of eight nibbles: codes (s, s + 4) as two 16-bit numbers magic + nibble, then (+ add) * mul
 template <typename T>
@@ -82,9 +88,11 @@ __global__ void __launch_bounds__(kWsThreads, 5) w4a16_stream_kernel(WsParams p)
   __shared__ float part[kWsWarps][16][NT * 8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, c = lane & 3;
-  // this CTA's 16 weight rows; rows beyond n read the last row (their results are not stored)
+  // this CTA's 16 weight rows.  MMA rows r and r + 8 (the two rows a lane holds) are the ADJACENT weight rows
+  // n0 + 2r and n0 + 2r + 1, so that their scales (and offsets) are one 4-byte load; n is even, and a pair beyond n
+  // reads the last pair (its results are not stored)
   const int n0 = blockIdx.x * 16;
-  const int row_a = min(n0 + r, p.n - 1), row_b = min(n0 + r + 8, p.n - 1);
+  const int row_a = min(n0 + 2 * r, p.n - 2), row_b = row_a + 1;
   const T* scale = reinterpret_cast<const T*>(p.scale);
   const T* offset = reinterpret_cast<const T*>(p.offset);
   const T* x = reinterpret_cast<const T*>(p.x);
@@ -99,58 +107,75 @@ __global__ void __launch_bounds__(kWsThreads, 5) w4a16_stream_kernel(WsParams p)
 #pragma unroll
   for (int gq = 0; gq < NT; ++gq) xrow[gq] = x + (int64_t)((r + 8 * gq) < p.m ? (r + 8 * gq) : 0) * p.ld_x;
 
-  constexpr int DEPTH = 4;                               // steps in flight per warp (32 bytes of codes per thread each)
+  constexpr int DEPTH = NT == 1 ? 4 : 3;                 // steps in flight per warp (32 bytes of codes per thread each); what fits the registers
   uint4 qa[DEPTH], qb[DEPTH];
-  T sca[DEPTH], scb[DEPTH], ofa[DEPTH], ofb[DEPTH];     // the group's scale and offset of both rows travel with the codes
-  auto issue = [&](int i, int slot) {
-    const int kk = (warp + i * kWsWarps) * kWsStepK + 32 * c;      // first k of this thread's 32 codes: they lie in one group
-    qa[slot] = __ldcs(reinterpret_cast<const uint4*>(p.codes + (int64_t)row_a * p.ld_codes + kk / 2));
-    qb[slot] = __ldcs(reinterpret_cast<const uint4*>(p.codes + (int64_t)row_b * p.ld_codes + kk / 2));
-    const int64_t g = kk >> p.group_shift;
-    sca[slot] = scale[g * p.n + row_a];
-    scb[slot] = scale[g * p.n + row_b];
-    if (offset) { ofa[slot] = offset[g * p.n + row_a]; ofb[slot] = offset[g * p.n + row_b]; }
+  uint32_t sc2[DEPTH], of2[DEPTH];                      // the group's scale and offset of both rows travel with the codes
+  // Everything that moves from step to step is one 32-bit counter: the first k of this thread's 32 codes (they lie in
+  // one group), advancing by kWsWarps * kWsStepK per step.  Code, activation and factor addresses are that counter
+  // added to per-thread base pointers fixed here.
+  const int k_first = warp * kWsStepK + 32 * c;
+  const uint8_t* code_a = p.codes + (int64_t)row_a * p.ld_codes;
+  const uint8_t* code_b = p.codes + (int64_t)row_b * p.ld_codes;
+  const T* scale_a = scale + row_a;
+  const T* offset_a = offset ? offset + row_a : nullptr;
+  auto issue = [&](int kk, int slot) {
+    qa[slot] = __ldcs(reinterpret_cast<const uint4*>(code_a + (kk >> 1)));
+    qb[slot] = __ldcs(reinterpret_cast<const uint4*>(code_b + (kk >> 1)));
+    const int g = (kk >> p.group_shift) * p.n;          // fits an int: checked on the host
+    sc2[slot] = __ldg(reinterpret_cast<const uint32_t*>(scale_a + g));      // rows a (low half) and b
+    if (offset) of2[slot] = __ldg(reinterpret_cast<const uint32_t*>(offset_a + g));
   };
+  // one step: dequantize the 2 x 32 codes of slot d in registers and feed them to the tensor cores
+  const P2 bias2 = WsType<T>::from_float(-8.f - WsType<T>::kMagicValue);
+  auto step = [&](int kk, int d, bool refill) {
+    // offset - 8 - magic is an integer of small magnitude: exact in T, formed with one packed add
+    const P2 mul_a = ws_dup<P2>(sc2[d], 0x1010), mul_b = ws_dup<P2>(sc2[d], 0x3232);
+    const P2 add_a = offset ? __hadd2(ws_dup<P2>(of2[d], 0x1010), bias2) : bias2;
+    const P2 add_b = offset ? __hadd2(ws_dup<P2>(of2[d], 0x3232), bias2) : bias2;
+    const uint32_t wa[4] = {qa[d].x, qa[d].y, qa[d].z, qa[d].w};
+    const uint32_t wb[4] = {qb[d].x, qb[d].y, qb[d].z, qb[d].w};
+    if (refill) issue(kk + DEPTH * kWsWarps * kWsStepK, d);      // the slot just read
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 xv[NT];
+#pragma unroll
+      for (int gq = 0; gq < NT; ++gq) {
+        const uint4 in = __ldg(reinterpret_cast<const uint4*>(xrow[gq] + kk) + j);
+        // elements (0,4) (1,5) (2,6) (3,7): the order in which ws_pair hands out the nibbles
+        xv[gq] = make_uint4(__byte_perm(in.x, in.z, 0x5410), __byte_perm(in.x, in.z, 0x7632),
+                            __byte_perm(in.y, in.w, 0x5410), __byte_perm(in.y, in.w, 0x7632));
+      }
+      uint32_t a[4];
+      a[0] = ws_pair<T>(wa[j], 0, add_a, mul_a); a[1] = ws_pair<T>(wb[j], 0, add_b, mul_b);
+      a[2] = ws_pair<T>(wa[j], 1, add_a, mul_a); a[3] = ws_pair<T>(wb[j], 1, add_b, mul_b);
+#pragma unroll
+      for (int gq = 0; gq < NT; ++gq) WsType<T>::mma(acc[gq], a, xv[gq].x, xv[gq].y);
+      a[0] = ws_pair<T>(wa[j], 2, add_a, mul_a); a[1] = ws_pair<T>(wb[j], 2, add_b, mul_b);
+      a[2] = ws_pair<T>(wa[j], 3, add_a, mul_a); a[3] = ws_pair<T>(wb[j], 3, add_b, mul_b);
+#pragma unroll
+      for (int gq = 0; gq < NT; ++gq) WsType<T>::mma(acc[gq], a, xv[gq].z, xv[gq].w);
+    }
+  };
+
+  constexpr int kStride = kWsWarps * kWsStepK;
 #pragma unroll
   for (int i = 0; i < DEPTH; ++i) {
-    if (i < my_steps) issue(i, i);
+    if (i < my_steps) issue(k_first + i * kStride, i);
   }
-
-  for (int i0 = 0; i0 < my_steps; i0 += DEPTH) {
+  int kk = k_first, left = my_steps;
+  // full rounds of DEPTH steps that all refill their slot, then the rounds that run the ring dry
+  for (; left >= 2 * DEPTH; left -= DEPTH) {
 #pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      const int i = i0 + d;
-      if (i >= my_steps) break;
-      // offset - 8 - magic is an integer of small magnitude: exact in T, formed with one packed add
-      const P2 bias2 = WsType<T>::from_float(-8.f - WsType<T>::kMagicValue);
-      const P2 mul_a = WsType<T>::dup(sca[d]), mul_b = WsType<T>::dup(scb[d]);
-      const P2 add_a = offset ? __hadd2(WsType<T>::dup(ofa[d]), bias2) : bias2;
-      const P2 add_b = offset ? __hadd2(WsType<T>::dup(ofb[d]), bias2) : bias2;
-      const uint32_t wa[4] = {qa[d].x, qa[d].y, qa[d].z, qa[d].w};
-      const uint32_t wb[4] = {qb[d].x, qb[d].y, qb[d].z, qb[d].w};
-      if (i + DEPTH < my_steps) issue(i + DEPTH, d);     // refill the slot just read
-      const int kx = (warp + i * kWsWarps) * kWsStepK + 32 * c;
+    for (int d = 0; d < DEPTH; ++d, kk += kStride) step(kk, d, true);
+  }
+  if (left > DEPTH) {                                    // DEPTH < left < 2 DEPTH: the first left - DEPTH steps still refill
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 xv[NT];
+    for (int d = 0; d < DEPTH; ++d, kk += kStride) step(kk, d, d < left - DEPTH);
+    left -= DEPTH;
+  }
 #pragma unroll
-        for (int gq = 0; gq < NT; ++gq) {
-          const uint4 in = __ldg(reinterpret_cast<const uint4*>(xrow[gq] + kx + 8 * j));
-          // elements (0,4) (1,5) (2,6) (3,7): the order in which ws_pair hands out the nibbles
-          xv[gq] = make_uint4(__byte_perm(in.x, in.z, 0x5410), __byte_perm(in.x, in.z, 0x7632),
-                              __byte_perm(in.y, in.w, 0x5410), __byte_perm(in.y, in.w, 0x7632));
-        }
-        uint32_t a[4];
-        a[0] = ws_pair<T>(wa[j], 0, add_a, mul_a); a[1] = ws_pair<T>(wb[j], 0, add_b, mul_b);
-        a[2] = ws_pair<T>(wa[j], 1, add_a, mul_a); a[3] = ws_pair<T>(wb[j], 1, add_b, mul_b);
-#pragma unroll
-        for (int gq = 0; gq < NT; ++gq) WsType<T>::mma(acc[gq], a, xv[gq].x, xv[gq].y);
-        a[0] = ws_pair<T>(wa[j], 2, add_a, mul_a); a[1] = ws_pair<T>(wb[j], 2, add_b, mul_b);
-        a[2] = ws_pair<T>(wa[j], 3, add_a, mul_a); a[3] = ws_pair<T>(wb[j], 3, add_b, mul_b);
-#pragma unroll
-        for (int gq = 0; gq < NT; ++gq) WsType<T>::mma(acc[gq], a, xv[gq].z, xv[gq].w);
-      }
-    }
+  for (int d = 0; d < DEPTH; ++d, kk += kStride) {
+    if (d < left) step(kk, d, false);
   }
 
   // ---- the four warps' partial sums of the tile meet in shared memory and are added in warp order
@@ -164,9 +189,10 @@ __global__ void __launch_bounds__(kWsThreads, 5) w4a16_stream_kernel(WsParams p)
     const int t = i >> 4, rr = i & 15;                   // consecutive threads: consecutive output channels of one token
     const int n = n0 + rr;
     if (n >= p.n) continue;
-    float sum = part[0][rr][t];
+    const int mr = (rr >> 1) + 8 * (rr & 1);              // the MMA row that held weight row n0 + rr
+    float sum = part[0][mr][t];
 #pragma unroll
-    for (int w = 1; w < kWsWarps; ++w) sum = __fadd_rn(sum, part[w][rr][t]);
+    for (int w = 1; w < kWsWarps; ++w) sum = __fadd_rn(sum, part[w][mr][t]);
     if (p.bias_kind == AMCT_BIAS_F32) sum = __fadd_rn(sum, reinterpret_cast<const float*>(p.bias)[n]);
     else if (p.bias_kind == AMCT_BIAS_F16) sum = __fadd_rn(sum, __half2float(reinterpret_cast<const __half*>(p.bias)[n]));
     else if (p.bias_kind == AMCT_BIAS_BF16) sum = __fadd_rn(sum, __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]));
@@ -190,10 +216,12 @@ static int ws_launch(const WsParams& p, cudaStream_t st) {
 int w4a16_stream_try(const void* x, int dtype, const void* codes, int64_t m, int64_t n, int64_t k, int64_t ld_x,
                      int64_t ld_codes, const void* scale, const void* offset, int group, const void* bias, int bias_kind,
                      void* out, int out_kind, int64_t ld_out, cudaStream_t st) {
-  if (m < 1 || m > 16 || n < 1 || k < kWsStepK || k % kWsStepK) return 1;
+  if (m < 1 || m > 16 || n < 2 || n % 2 || k < kWsStepK || k % kWsStepK) return 1;
   if (n > 0x7fffffffLL / 2 || k > 0x3fffffffLL) return 1;
+  if (group && (k / group) * n > 0x7fffffffLL) return 1;                        // factor indices are ints in the kernel
   if (group && (group < 32 || (group & (group - 1)) || k % group)) return 1;      // a power of two: the group of a k is a shift
   if (!aligned16(x) || (ld_x * 2) % 16 || !aligned16(codes) || ld_codes % 16) return 1;
+  if (reinterpret_cast<uintptr_t>(scale) % 4 || reinterpret_cast<uintptr_t>(offset) % 4) return 1;   // factor pairs: 4-byte loads
   WsParams p{};
   p.x = x; p.codes = reinterpret_cast<const uint8_t*>(codes); p.scale = scale; p.offset = offset; p.bias = bias; p.out = out;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;

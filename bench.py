@@ -6,8 +6,11 @@
 One step = one prefill forward of batch 32 x seq 2048 random tokens through 80
 decoder layers whose Linears are NpuQuantizationLinear deploy modules (dynamic
 per-token INT8 activation quantization + tcgen05 INT8 GEMM + dequant epilogue),
-tensor-parallel over the N ranks with NCCL all-reduce.  Total work is fixed as N
-grows (strong scaling).  Weights are random-init, data synthetic.
+tensor-parallel over the N ranks with a token-sharded residual stream: the row-parallel
+GEMMs store their partial tiles into the owning rank's peer-mapped buffer and the add +
+norm + quant kernel stores its codes to every rank (--comm push), or NCCL reduce-scatter /
+all-gather (--comm nccl).  Total work is fixed as N grows (strong scaling).  Weights are
+random-init, data synthetic.
 
 Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
   e2e           same metric with the token ids copied from pinned host memory and the
@@ -15,7 +18,7 @@ Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
   roofline      the dominant kernel (INT8 GEMM): achieved = algorithmic 2*M*N*K of every
                 launch / its CUDA-event duration, measured live in a separate profiled
                 pass of the same step; peak = 2 x the measured bf16 tensor peak
-  cpu_baseline  the CPU oracle of the same Linear path on a bounded sample (rank 0, N=1)
+  cpu_baseline  the reference package's own Linear path on the host cores, bounded sample (rank 0, N=1)
   clocks        SM clock / throttle reasons sampled with nvidia-smi during the timed region
   gpu_launches  launches of this repository's kernels inside the timed region
 """
@@ -411,10 +414,11 @@ def main():
     value = tokens * args.steps / (ms_total / 1e3)
     achieved = gemm_ops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
     peak = 2 * bf16_sus
-    # DRAM traffic of the dominant launch (the gate/up GEMM, 57344 x 8192 weights): ncu measured
-    # dram__bytes_read + dram__bytes_write = 2.865 GB for 8192 token rows (profiles/gemm_pair_vs_single_steady_state.md);
-    # the B operand is re-streamed once per 2048-row group and A / C grow with the rows, so a launch's
-    # traffic is proportional to its rows.  Only quoted for the unsharded prefill shape it was captured on.
+    # DRAM traffic of the dominant launch (the gate/up GEMM, 57344 x 8192 weights).  The full launch (65536 token rows,
+    # 25 ms, 4.7 GB of operands) is too large for a multi-pass profiler capture; dram__bytes_read + dram__bytes_write
+    # was captured for 8192 token rows (`bench_kernels.py --only "gemm_w8a8 swiglu c5 gate+up 8192x"`).  The B operand
+    # is re-streamed once per 2048-row group and A / C grow with the rows, so a launch's traffic is proportional to
+    # its rows.  Only quoted for the unsharded prefill shape it was captured on.
     traffic, traffic_note = None, None
     if world == 1 and args.mode == 'prefill':
         rows = args.batch * args.seq

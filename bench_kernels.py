@@ -356,6 +356,17 @@ def cases():
         kw = dict(nops=2 * m * n * k, peak_mult=2.0) if m > 128 else dict(nbytes=n * k + m * k + m * n * (4 if od == torch.float32 else 2))
         yield (f'gemm_w8a8 {tag} {m}x{n}x{k} -> {str(od)[6:]}', setup,
                lambda t: (lambda: ops.gemm_w8a8(t[0], t[1], t[2], t[3], None, out=t[4])), kw)
+    # ---- W8A8 gate/up GEMM with the SwiGLU epilogue (the dominant launch of the 70B prefill step; the 8192-row case is
+    #      the one small enough for a profiler capture, its DRAM traffic scales with the rows)
+    for m in (8192, 65536):
+        def setup_sw(m=m):
+            a = torch.randint(-128, 128, (m, 8192), device='cuda', dtype=torch.int8)
+            b = torch.randint(-128, 128, (57344, 8192), device='cuda', dtype=torch.int8)
+            return (a, b, torch.rand(57344, device='cuda') * 1e-3, torch.rand(m, device='cuda'),
+                    torch.empty(m, 28672, device='cuda', dtype=torch.bfloat16))
+        yield (f'gemm_w8a8 swiglu c5 gate+up {m}x57344x8192 -> bf16 [{m}x28672]', setup_sw,
+               lambda t: (lambda: ops.gemm_w8a8_swiglu(t[0], t[1], t[2], t[3], None, out=t[4])),
+               dict(nops=2 * m * 57344 * 8192, peak_mult=2.0))
     # ---- 16-bit GEMM
     for m, n, k, tag in ((8192, 8192, 8192, 'square'), (4096, 11008, 4096, 'c2 M=4096'), (128, 11008, 4096, 'c2 M=128'),
                          (16384, 14336, 4096, 'c4 gate')):
