@@ -191,11 +191,18 @@ struct SrcRows {
   static constexpr int kElems = ElemTraits<T>::kPerVec;      // elements per 16-byte load
   const T* base;
   int64_t ld;
-  __device__ __forceinline__ void load_vec(int64_t row, int64_t v, float* f, bool stream) const {
-    const T* q = base + row * ld + v * kElems;
-    const Vec16<T> raw = stream ? ld_vec_stream(q) : ld_vec(q);
+  // the 16 bytes of vector v of a row as loaded, and their values
+  __device__ __forceinline__ uint4 load_raw(int64_t row, int64_t v, bool stream) const {
+    const uint4* q = reinterpret_cast<const uint4*>(base + row * ld + v * kElems);
+    return stream ? __ldcs(q) : __ldg(q);
+  }
+  __device__ __forceinline__ void expand(const uint4& raw, int64_t, int64_t, float* f) const {
+    const Vec16<T>& t = *reinterpret_cast<const Vec16<T>*>(&raw);
 #pragma unroll
-    for (int e = 0; e < kElems; ++e) f[e] = ElemTraits<T>::to_f(raw.v[e]);
+    for (int e = 0; e < kElems; ++e) f[e] = ElemTraits<T>::to_f(t.v[e]);
+  }
+  __device__ __forceinline__ void load_vec(int64_t row, int64_t v, float* f, bool stream) const {
+    expand(load_raw(row, v, stream), row, v, f);
   }
   __device__ __forceinline__ float load_one(int64_t row, int64_t j) const { return ElemTraits<T>::to_f(base[row * ld + j]); }
 };
@@ -207,10 +214,15 @@ struct SrcFp8Blocks {
   const float* scale;
   int64_t ld_scale;
   int block;
-  __device__ __forceinline__ void load_vec(int64_t row, int64_t v, float* f, bool stream) const {
-    const float s = __ldg(scale + (row / block) * ld_scale + (v * 16) / block);
+  __device__ __forceinline__ uint4 load_raw(int64_t row, int64_t v, bool stream) const {
     const uint4* q = reinterpret_cast<const uint4*>(base + row * ld + v * 16);
-    const uint4 raw = stream ? __ldcs(q) : __ldg(q);
+    return stream ? __ldcs(q) : __ldg(q);
+  }
+  __device__ __forceinline__ void load_vec(int64_t row, int64_t v, float* f, bool stream) const {
+    expand(load_raw(row, v, stream), row, v, f);
+  }
+  __device__ __forceinline__ void expand(const uint4& raw, int64_t row, int64_t v, float* f) const {
+    const float s = __ldg(scale + (row / block) * ld_scale + (v * 16) / block);
     const uint32_t word[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -340,8 +352,165 @@ __global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_kernel(CkptRowParam
   }
 }
 
+// ---- rows short enough to stay in registers -----------------------------------------------------------------------
+// Every thread keeps the (up to NV) 16-byte vectors it owns of the row -- of both rows for INT4 -- as loaded: all
+// loads are issued before the first use, the row is read from memory once, and the second pass works from
+// registers.  A row whose scale is a normal number and whose quotients stay far below 2^22 (every row of a real
+// checkpoint) takes a short path per element: the exact FMA division, the rounding to T, a clamp, and the magic-add
+// rounding, packed by cvt.pack.  For such a row no quotient is NaN or infinite, and round-then-clamp equals
+// clamp-then-round because the bounds are integers, so the levels are those of ckpt_level.  Any other row (all
+// zeros, NaN / Inf, a denormal scale, a tiny clip factor) goes through ckpt_level element by element.
+constexpr float kCkptMagic = 12582912.f;                      // 1.5 * 2^23
+constexpr int kCkptMagicBits = 0x4B400000;
+
+template <int NROW>
+__device__ __forceinline__ void block_max_nan(float (&v)[NROW], float (*red)[kRowThreads / 32]) {
+#pragma unroll
+  for (int r = 0; r < NROW; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[r] = fmax_nan(v[r], __shfl_xor_sync(0xffffffffu, v[r], o));
+    if ((threadIdx.x & 31) == 0) red[r][threadIdx.x >> 5] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < NROW; ++r) {
+    float m = red[r][0];
+#pragma unroll
+    for (int i = 1; i < kRowThreads / 32; ++i) m = fmax_nan(m, red[r][i]);
+    v[r] = m;
+  }
+}
+
+template <typename T, typename SRC, int NROW, int NV>
+__global__ void __launch_bounds__(kRowThreads) ckpt_rowquant_reg_kernel(CkptRowParams p, SRC src) {
+  constexpr int E = SRC::kElems;
+  __shared__ float red[NROW][kRowThreads / 32];
+  __shared__ float red_sum[kRowThreads / 32];
+  const int tid = threadIdx.x;
+  const int64_t row0 = (int64_t)blockIdx.x * NROW;
+  const float qmax = (float)((1 << (p.bits - 1)) - 1);
+  const int nvec = (int)(p.k / E);
+
+  uint4 raw[NROW][NV];
+#pragma unroll
+  for (int r = 0; r < NROW; ++r) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = tid + i * kRowThreads;
+      raw[r][i] = v < nvec ? src.load_raw(row0 + r, v, true) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+
+  // pass 1: max |w| per row; a NaN anywhere makes it NaN, as torch.max does
+  float amax[NROW];
+#pragma unroll
+  for (int r = 0; r < NROW; ++r) {
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = tid + i * kRowThreads;
+      if (v < nvec) {
+        float f[E];
+        src.expand(raw[r][i], row0 + r, v, f);
+#pragma unroll
+        for (int e = 0; e < E; ++e) m = fmax_nan(m, fabsf(f[e]));
+      }
+    }
+    amax[r] = m;
+  }
+  block_max_nan<NROW>(amax, red);
+
+  CkptScale u[NROW];
+  bool regular[NROW];
+#pragma unroll
+  for (int r = 0; r < NROW; ++r) {
+    float a = amax[r];
+    if (p.use_clip) a = round_to<T>(__fmul_rn(a, p.clip));                     // deploy.py:132-133
+    u[r] = make_scale(round_to<T>(__fdiv_rn(a, qmax)));                        // deploy.py:134
+    // |x / s| <= amax * |1 / s| (1 + 2^-22) for every x of the row
+    regular[r] = u[r].recip != 0.f && __fmul_rn(amax[r], fabsf(u[r].recip)) < 2097152.f;
+  }
+
+  // pass 2, from registers
+  float acc[NROW];
+#pragma unroll
+  for (int r = 0; r < NROW; ++r) acc[r] = 0.f;
+  int8_t* out_row = p.codes + (int64_t)blockIdx.x * p.ld_codes;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = tid + i * kRowThreads;
+    if (v >= nvec) continue;
+    int lvl[NROW][E];
+#pragma unroll
+    for (int r = 0; r < NROW; ++r) {
+      float f[E];
+      src.expand(raw[r][i], row0 + r, v, f);
+      if (regular[r]) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          float t = round_to<T>(div_by_recip(f[e], u[r].s, u[r].recip));
+          t = __fadd_rn(fminf(fmaxf(t, -qmax), qmax), kCkptMagic);
+          lvl[r][e] = __float_as_int(t) - kCkptMagicBits;
+          if (NROW == 2) acc[r] = __fadd_rn(acc[r], ckpt_bias_term<T>(__fsub_rn(t, kCkptMagic), u[r].s));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float l = ckpt_level<T>(f[e], u[r], qmax);
+          lvl[r][e] = (int)l;
+          if (NROW == 2) acc[r] = __fadd_rn(acc[r], ckpt_bias_term<T>(l, u[r].s));
+        }
+      }
+    }
+    uint32_t words[E / 4];
+#pragma unroll
+    for (int g = 0; g < E / 4; ++g) {
+      uint32_t w = 0;
+      if (NROW == 1) {
+        w = pack_sat_s8(lvl[0][4 * g + 3], lvl[0][4 * g + 2], 0);
+        w = pack_sat_s8(lvl[0][4 * g + 1], lvl[0][4 * g], w);
+      } else {
+#pragma unroll
+        for (int e = 3; e >= 0; --e) w = pack_sat_s4(lvl[NROW - 1][4 * g + e], lvl[0][4 * g + e], w);   // deploy.py:117-123
+      }
+      words[g] = w;
+    }
+    store_codes<E>(out_row + (int64_t)v * E, reinterpret_cast<const int8_t*>(words));
+  }
+
+  if (NROW == 1) {
+    if (tid == 0) reinterpret_cast<float*>(p.scale)[row0] = u[0].s;            // deploy.py:146
+  } else {
+#pragma unroll
+    for (int r = 0; r < NROW; ++r) {
+      const float total = block_sum(acc[r], red_sum);     // exact for 16-bit T and the row lengths that fit here
+      if (tid == 0) {
+        p.bias[row0 + r] = round_to<T>(total);                                  // deploy.py:156
+        reinterpret_cast<unsigned long long*>(p.scale)[row0 + r] =
+            (unsigned long long)__float_as_uint(u[r].s);                        // deploy.py:93-106
+      }
+    }
+  }
+}
+
+
 template <typename T, typename SRC>
 static int launch_rowquant(const CkptRowParams& p, const SRC& src, bool vec, cudaStream_t st) {
+  const int64_t nvec = vec ? p.k / SRC::kElems : 0;
+  if (vec && nvec <= 4 * kRowThreads) {                 // the row fits the registers of a CTA
+    const bool two = nvec <= 2 * kRowThreads;
+    if (p.bits == 8) {
+      const unsigned grid = (unsigned)p.rows;
+      if (two) AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_reg_kernel<T, SRC, 1, 2>);
+      else AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_reg_kernel<T, SRC, 1, 4>);
+    } else {
+      const unsigned grid = (unsigned)(p.rows / 2);
+      if (two) AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_reg_kernel<T, SRC, 2, 2>);
+      else AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_reg_kernel<T, SRC, 2, 4>);
+    }
+    AMCT_CHECK_LAUNCH();
+    return AMCT_OK;
+  }
   if (p.bits == 8) {
     const unsigned grid = (unsigned)p.rows;
     if (vec) AMCT_LAUNCH(grid, kRowThreads, st, (p, src), ckpt_rowquant_kernel<T, SRC, true, 1>);

@@ -157,6 +157,47 @@ __device__ __forceinline__ float div_by_recip(float x, float s, float y) {
   return __fmaf_rn(__fmaf_rn(-s, q1, x), y, q1);
 }
 
+// cvt.pack.sat: two signed integers saturated to 4 (8) bits each and packed under what `carry` already holds,
+//   d = (carry << 8 | sat4(hi) << 4 | sat4(lo))      resp.      d = (carry << 16 | sat8(hi) << 8 | sat8(lo))
+// one instruction for the clamp and the packing of two codes.
+__device__ __forceinline__ uint32_t pack_sat_s4(int hi, int lo, uint32_t carry) {
+#ifdef AMCT_CUDA_EMU
+  const int h = hi < -8 ? -8 : hi > 7 ? 7 : hi, l = lo < -8 ? -8 : lo > 7 ? 7 : lo;
+  return (carry << 8) | ((uint32_t)(h & 0xF) << 4) | (uint32_t)(l & 0xF);
+#else
+  uint32_t d;
+  asm("cvt.pack.sat.s4.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(carry));
+  return d;
+#endif
+}
+__device__ __forceinline__ uint32_t pack_sat_s8(int hi, int lo, uint32_t carry) {
+#ifdef AMCT_CUDA_EMU
+  const int h = hi < -128 ? -128 : hi > 127 ? 127 : hi, l = lo < -128 ? -128 : lo > 127 ? 127 : lo;
+  return (carry << 16) | ((uint32_t)(h & 0xFF) << 8) | (uint32_t)(l & 0xFF);
+#else
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(carry));
+  return d;
+#endif
+}
+
+// 32 values -> 16 words of packed 16-bit outputs
+__device__ __forceinline__ void epi_pack16(const float (&y)[32], bool to_bf16, uint32_t (&h)[16]) {
+  if (to_bf16) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+      h[j] = *reinterpret_cast<uint32_t*>(&v);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      __half2 v = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
+      h[j] = *reinterpret_cast<uint32_t*>(&v);
+    }
+  }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // "Done once per device": kernel attributes such as the dynamic shared-memory limit belong to a device's context, so a

@@ -184,7 +184,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
       const int64_t n0 = tn * kBN;
       const int64_t row = tm * kBM + quarter * 32 + lane;
-      for (int c = lane; c < kBN; c += 32) sb[c] = (p.bias_kind && n0 + c < p.n) ? bias_at(p.bias, p.bias_kind, n0 + c) : 0.f;
+      // no bias is staged as -0.0f: x + (-0.0f) is x for every x, so the loop below adds unconditionally (an epilogue
+      // warp is alone on its scheduler: a branch per element would cost its full latency each time)
+      for (int c = lane; c < kBN; c += 32) sb[c] = (p.bias_kind && n0 + c < p.n) ? bias_at(p.bias, p.bias_kind, n0 + c) : -0.f;
       __syncwarp();
       if (!tc05::mbar_wait(tc05::smem_u32(&s.tmem_full[acc]), acc_phase, abort_flag)) break;
       tc05::fence_after_sync();
@@ -197,11 +199,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (row < p.m && n0 + c0 < p.n) {
           float y[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = __uint_as_float(r[j]);
-            if (p.bias_kind) v = __fadd_rn(v, sb[c0 + j]);
-            y[j] = v;
-          }
+          for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(__uint_as_float(r[j]), sb[c0 + j]);
           const int64_t nleft = p.n - (n0 + c0);
           const int64_t off = row * p.ld_out + n0 + c0;
           if (p.out_kind == 0) {
@@ -215,16 +213,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             }
           } else {
             uint32_t h[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (p.out_kind == 2) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
-                h[j] = *reinterpret_cast<uint32_t*>(&v);
-              } else {
-                __half2 v = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
-                h[j] = *reinterpret_cast<uint32_t*>(&v);
-              }
-            }
+            epi_pack16(y, p.out_kind == 2, h);
             uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + off;
             if (nleft >= 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll

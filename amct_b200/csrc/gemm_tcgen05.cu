@@ -154,7 +154,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       for (int c = lane; c < kBN; c += 32) {
         const int64_t n = n0 + c;
         sc[c] = (p.deq && n < p.n) ? p.deq[n] : 1.f;
-        sb[c] = (p.bias_kind != BIAS_NONE && n < p.n) ? bias_at(p.bias, p.bias_kind, n) : 0.f;
+        sb[c] = staged_bias(p, n);
       }
       const float pt = (p.pertoken && row < p.m) ? p.pertoken[row] : 1.f;
       __syncwarp();

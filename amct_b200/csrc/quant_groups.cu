@@ -135,30 +135,6 @@ __device__ __forceinline__ float group_qparams(float mx, float mn, int bits, boo
   return s;
 }
 
-// cvt.pack.sat: two signed integers saturated to 4 (8) bits each and packed under what `carry` already holds,
-//   d = (carry << 8 | sat4(hi) << 4 | sat4(lo))      resp.      d = (carry << 16 | sat8(hi) << 8 | sat8(lo))
-// one instruction for the clamp and the packing of two codes.
-__device__ __forceinline__ uint32_t pack_sat_s4(int hi, int lo, uint32_t carry) {
-#ifdef AMCT_CUDA_EMU
-  const int h = hi < -8 ? -8 : hi > 7 ? 7 : hi, l = lo < -8 ? -8 : lo > 7 ? 7 : lo;
-  return (carry << 8) | ((uint32_t)(h & 0xF) << 4) | (uint32_t)(l & 0xF);
-#else
-  uint32_t d;
-  asm("cvt.pack.sat.s4.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(carry));
-  return d;
-#endif
-}
-__device__ __forceinline__ uint32_t pack_sat_s8(int hi, int lo, uint32_t carry) {
-#ifdef AMCT_CUDA_EMU
-  const int h = hi < -128 ? -128 : hi > 127 ? 127 : hi, l = lo < -128 ? -128 : lo > 127 ? 127 : lo;
-  return (carry << 16) | ((uint32_t)(h & 0xFF) << 8) | (uint32_t)(l & 0xFF);
-#else
-  uint32_t d;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(carry));
-  return d;
-#endif
-}
-
 // Four adjacent 16-byte vectors per thread (32 elements of a 16-bit type: the scale rule, which every thread of a
 // group evaluates, is spread over that many elements); a group spans (1 << lanes_log2) threads of a warp.  The row
 // stays packed in T; one vector at a time is unpacked, divided and written.  In every mode the rounded level is

@@ -82,17 +82,19 @@ __device__ __forceinline__ uint32_t ws_pair(uint32_t w, int s, typename WsType<T
 }
 
 // NT: token groups of 8 (1: up to 8 tokens, 2: up to 16).
-template <typename T, int NT>
+template <typename T, int NT, bool PAIR>
 __global__ void __launch_bounds__(kWsThreads, 5) w4a16_stream_kernel(WsParams p) {
   using P2 = typename WsType<T>::P2;
   __shared__ float part[kWsWarps][16][NT * 8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, c = lane & 3;
   // this CTA's 16 weight rows.  MMA rows r and r + 8 (the two rows a lane holds) are the ADJACENT weight rows
-  // n0 + 2r and n0 + 2r + 1, so that their scales (and offsets) are one 4-byte load; n is even, and a pair beyond n
-  // reads the last pair (its results are not stored)
+  // n0 + 2r and n0 + 2r + 1, so that their scales (and offsets) are one 4-byte load when n is even and the factor
+  // arrays are 4-byte aligned (PAIR; two 2-byte loads otherwise); rows beyond n read the last rows (their
+  // results are not stored)
   const int n0 = blockIdx.x * 16;
-  const int row_a = min(n0 + 2 * r, p.n - 2), row_b = row_a + 1;
+  const int row_a = min(n0 + 2 * r, PAIR ? p.n - 2 : p.n - 1), row_b = min(row_a + 1, p.n - 1);
+  const int b_step = row_b - row_a;
   const T* scale = reinterpret_cast<const T*>(p.scale);
   const T* offset = reinterpret_cast<const T*>(p.offset);
   const T* x = reinterpret_cast<const T*>(p.x);
@@ -122,8 +124,17 @@ __global__ void __launch_bounds__(kWsThreads, 5) w4a16_stream_kernel(WsParams p)
     qa[slot] = __ldcs(reinterpret_cast<const uint4*>(code_a + (kk >> 1)));
     qb[slot] = __ldcs(reinterpret_cast<const uint4*>(code_b + (kk >> 1)));
     const int g = (kk >> p.group_shift) * p.n;          // fits an int: checked on the host
-    sc2[slot] = __ldg(reinterpret_cast<const uint32_t*>(scale_a + g));      // rows a (low half) and b
-    if (offset) of2[slot] = __ldg(reinterpret_cast<const uint32_t*>(offset_a + g));
+    if (PAIR) {                                         // rows a (low half) and b
+      sc2[slot] = __ldg(reinterpret_cast<const uint32_t*>(scale_a + g));
+      if (offset) of2[slot] = __ldg(reinterpret_cast<const uint32_t*>(offset_a + g));
+    } else {
+      const uint16_t* s16 = reinterpret_cast<const uint16_t*>(scale_a + g);
+      sc2[slot] = (uint32_t)__ldg(s16) | ((uint32_t)__ldg(s16 + b_step) << 16);
+      if (offset) {
+        const uint16_t* o16 = reinterpret_cast<const uint16_t*>(offset_a + g);
+        of2[slot] = (uint32_t)__ldg(o16) | ((uint32_t)__ldg(o16 + b_step) << 16);
+      }
+    }
   };
   // one step: dequantize the 2 x 32 codes of slot d in registers and feed them to the tensor cores
   const P2 bias2 = WsType<T>::from_float(-8.f - WsType<T>::kMagicValue);
@@ -204,9 +215,10 @@ __global__ void __launch_bounds__(kWsThreads, 5) w4a16_stream_kernel(WsParams p)
 }
 
 template <typename T, int NT>
-static int ws_launch(const WsParams& p, cudaStream_t st) {
+static int ws_launch(const WsParams& p, bool pair, cudaStream_t st) {
   const unsigned tiles = (unsigned)((p.n + 15) / 16);
-  w4a16_stream_kernel<T, NT><<<tiles, kWsThreads, 0, st>>>(p);
+  if (pair) w4a16_stream_kernel<T, NT, true><<<tiles, kWsThreads, 0, st>>>(p);
+  else w4a16_stream_kernel<T, NT, false><<<tiles, kWsThreads, 0, st>>>(p);
   AMCT_CHECK_LAUNCH();
   return AMCT_OK;
 }
@@ -216,20 +228,21 @@ static int ws_launch(const WsParams& p, cudaStream_t st) {
 int w4a16_stream_try(const void* x, int dtype, const void* codes, int64_t m, int64_t n, int64_t k, int64_t ld_x,
                      int64_t ld_codes, const void* scale, const void* offset, int group, const void* bias, int bias_kind,
                      void* out, int out_kind, int64_t ld_out, cudaStream_t st) {
-  if (m < 1 || m > 16 || n < 2 || n % 2 || k < kWsStepK || k % kWsStepK) return 1;
+  if (m < 1 || m > 16 || n < 1 || k < kWsStepK || k % kWsStepK) return 1;
   if (n > 0x7fffffffLL / 2 || k > 0x3fffffffLL) return 1;
   if (group && (k / group) * n > 0x7fffffffLL) return 1;                        // factor indices are ints in the kernel
   if (group && (group < 32 || (group & (group - 1)) || k % group)) return 1;      // a power of two: the group of a k is a shift
   if (!aligned16(x) || (ld_x * 2) % 16 || !aligned16(codes) || ld_codes % 16) return 1;
-  if (reinterpret_cast<uintptr_t>(scale) % 4 || reinterpret_cast<uintptr_t>(offset) % 4) return 1;   // factor pairs: 4-byte loads
   WsParams p{};
   p.x = x; p.codes = reinterpret_cast<const uint8_t*>(codes); p.scale = scale; p.offset = offset; p.bias = bias; p.out = out;
   p.m = (int)m; p.n = (int)n; p.k = (int)k;
   p.group_shift = 31;
   if (group) { p.group_shift = 0; while ((1 << p.group_shift) < group) ++p.group_shift; }
+  // both rows' factors with one 4-byte load
+  const bool pair = n % 2 == 0 && reinterpret_cast<uintptr_t>(scale) % 4 == 0 && reinterpret_cast<uintptr_t>(offset) % 4 == 0;
   p.ld_x = ld_x; p.ld_codes = ld_codes; p.ld_out = ld_out; p.bias_kind = bias_kind; p.out_kind = out_kind;
-  if (dtype == AMCT_DTYPE_BF16) return m <= 8 ? ws_launch<__nv_bfloat16, 1>(p, st) : ws_launch<__nv_bfloat16, 2>(p, st);
-  if (dtype == AMCT_DTYPE_F16) return m <= 8 ? ws_launch<__half, 1>(p, st) : ws_launch<__half, 2>(p, st);
+  if (dtype == AMCT_DTYPE_BF16) return m <= 8 ? ws_launch<__nv_bfloat16, 1>(p, pair, st) : ws_launch<__nv_bfloat16, 2>(p, pair, st);
+  if (dtype == AMCT_DTYPE_F16) return m <= 8 ? ws_launch<__half, 1>(p, pair, st) : ws_launch<__half, 2>(p, pair, st);
   return 1;
 }
 

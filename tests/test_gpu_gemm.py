@@ -303,3 +303,33 @@ def test_swiglu_epilogue_matches_unfused_path(variant):
     want_cpu = torch.nn.functional.silu(rb[:, :, 0].reshape(m, inter)) * rb[:, :, 1].reshape(m, inter)
     err = ((fused.cpu().float() - want_cpu.float()).abs().max() / want_cpu.float().abs().max()).item()
     assert err < TOL_16, err
+
+
+def test_swiglu_epilogue_extreme_gates(variant):
+    """Gate values at the ends of the range (1 + exp(-g) huge, then infinite; g of the largest bf16 magnitudes) next to
+    ordinary values in the same 32-column chunk: bit-identical to the unfused sequence."""
+    from amct_b200.deploy_op.npu_quantization_linear import interleave_gate_up
+    g = torch.Generator().manual_seed(22)
+    m, inter, k = 256, 256, 128
+    a = rand_i8(g, m, k)
+    a[::2] = 0                                              # rows whose outputs are exactly the bias
+    wg, wu = rand_i8(g, inter, k), rand_i8(g, inter, k)
+    w = interleave_gate_up(wg, wu).cuda()
+    deq = (torch.rand(2 * inter, generator=g) * 2e-4 + 1e-5).cuda()
+    pt = (torch.rand(m, generator=g) * 0.05 + 0.01).cuda()
+    gate_bias = torch.randn(inter, generator=g) * 0.1
+    extremes = torch.tensor([-3.0e38, -1000., -100., -90., -88.5, -88., -87.5, -87., -86., -85.5, -85., -84., -80., -40., 40., 80.,
+                             88., 100., 1000., 3.0e38])
+    gate_bias[5:5 + len(extremes)] = extremes               # inside the first chunk and across its end
+    gate_bias[130:130 + len(extremes)] = extremes
+    up_bias = torch.randn(inter, generator=g) * 0.1
+    bias = interleave_gate_up(gate_bias.reshape(-1, 1), up_bias.reshape(-1, 1)).reshape(-1).to(torch.bfloat16).cuda()
+    st = status()
+    fused = ops().gemm_w8a8_swiglu(a.cuda(), w, deq, pt, bias, status=st)
+    plain = ops().gemm_w8a8(a.cuda(), w, deq, pt, bias, out_dtype=torch.bfloat16, status=st)
+    ops().raise_if_timed_out(st)
+    blocks = plain.reshape(m, inter // 128, 2, 128)
+    gate, up = blocks[:, :, 0].reshape(m, inter), blocks[:, :, 1].reshape(m, inter)
+    assert float(gate.float().min()) < -1e38 and float(gate.float().max()) > 1e38
+    want = torch.nn.functional.silu(gate) * up
+    assert bits_equal(fused, want)

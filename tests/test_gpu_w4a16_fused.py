@@ -56,9 +56,9 @@ def test_fused_w4a16_matches_oracle_and_two_kernel_route(dtype, bits, group, asy
 @pytest.mark.parametrize('group,asym', [(128, True), (32, True), (64, False), (0, True)])
 @pytest.mark.parametrize('m,n,k', [(1, 16, 128), (5, 130, 384), (8, 1000, 1024), (9, 256, 2048), (16, 408, 1152), (3, 129, 8192)])
 def test_streaming_kernel_for_up_to_16_tokens(dtype, group, asym, m, n, k):
-    """INT4 weights and at most 16 tokens take the weight-streaming kernel (K slices of a row block summed through
-    the cluster's shared memory): every slice count (K / 128 = 1, 3, 8, 16, 9, 64 steps), ragged N, one or two token
-    groups, all group sizes; against the oracle, against the two-kernel route, and bit-identical from run to run."""
+    """INT4 weights and at most 16 tokens take the weight-streaming kernel (the K steps of a 16-row tile dealt to four
+    warps, their partial sums added in warp order): every step count (K / 128 = 1, 3, 8, 16, 9, 64), ragged and odd N,
+    one or two token groups, all group sizes; against the oracle, against the two-kernel route, and bit-identical from run to run."""
     if group and k % group:
         pytest.skip('K is not a multiple of the group')
     g = torch.Generator().manual_seed(m * 5 + n + k + group)
