@@ -36,7 +36,6 @@ namespace amct {
 // two tile shapes: 128 x 256 with a 4-stage ring (large M), and 128 x 64 with an 8-stage ring for
 // M <= 128, where the job is to stream the weight once: more, smaller tiles keep every SM loading
 constexpr int kBNLarge = 256, kStagesLarge = 4, kBNSmall = 64, kStagesSmall = 8;
-constexpr int kGroupM = 16;                      // rasterisation: 16 m-tiles x all n-tiles per group
 constexpr int kThreads = 192;
 
 template <int BN, int STAGES>
@@ -91,7 +90,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool alive = true;
       for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         int64_t tm, tn;
-        tile_coords<kGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+        tile_coords(p.group_m, tile, tiles_m, tiles_n, &tm, &tn);
         tm = rotate_tile_m(p, tm, tiles_m, kBM);
         for (int64_t kb = 0; kb < num_kb; ++kb) {
           if (!tc05::mbar_wait(tc05::smem_u32(&s.empty[stage]), phase ^ 1, abort_flag)) { alive = false; break; }
@@ -146,7 +145,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t acc = 0, acc_phase = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int64_t tm, tn;
-      tile_coords<kGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+      tile_coords(p.group_m, tile, tiles_m, tiles_n, &tm, &tn);
       tm = rotate_tile_m(p, tm, tiles_m, kBM);
       const int64_t n0 = tn * kBN;
       const int64_t row = tm * kBM + quarter * 32 + lane;
@@ -293,7 +292,8 @@ static bool use_pair_kernel(const GemmParams& p, int esize) {
   return p.n * p.k * esize <= kPairMaxBBytes;
 }
 
-static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b, const GemmParams& p, cudaStream_t st) {
+static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b, const GemmParams& params, cudaStream_t st) {
+  GemmParams p = params;
   if (p.m == 0 || p.n == 0) return AMCT_OK;
   if (p.k <= 0) return AMCT_ERR_ARG;
   if (p.m > 0x7fffffffLL || p.n > 0x7fffffffLL || p.k > 0x7fffffffLL) return AMCT_ERR_UNSUPPORTED;
@@ -307,12 +307,14 @@ static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b,
     // CTA pairs on 256 x 256 tiles: each CTA loads 128 rows of A and 128 rows (half a tile) of B
     rc = make_map(&mb, b, esize, p.n, p.k, ld_b, 128);
     if (rc != AMCT_OK) return rc;
+    p.group_m = group_m_tiles(p.k * esize, 2 * kBM);
     return launch_gemm_pair(ma, mb, p, st);
   }
   const bool small = p.m <= 128 && p.act == 0;
   const int bn = small ? kBNSmall : kBNLarge;
   rc = make_map(&mb, b, esize, p.n, p.k, ld_b, bn);
   if (rc != AMCT_OK) return rc;
+  p.group_m = group_m_tiles(p.k * esize, kBM);
   const int64_t tiles = ((p.m + kBM - 1) / kBM) * ((p.n + bn - 1) / bn);
   const int grid = (int)(tiles < dev->sms ? tiles : dev->sms);
   if (small) {

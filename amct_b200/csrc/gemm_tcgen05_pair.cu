@@ -26,7 +26,7 @@
 
 namespace amct {
 
-constexpr int kPairStages = 6, kPairBN = 256, kPairGroupM = 8, kPairThreads = 192;
+constexpr int kPairStages = 6, kPairBN = 256, kPairThreads = 192;
 constexpr int kPairBHalfBytes = 128 * kBKBytes;
 constexpr int kPairStageBytes = kABytes + kPairBHalfBytes;        // per CTA
 
@@ -85,7 +85,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       bool alive = true;
       for (int64_t tile = pair_id; tile < num_tiles && alive; tile += num_pairs) {
         int64_t tm, tn;
-        tile_coords<kPairGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+        tile_coords(p.group_m, tile, tiles_m, tiles_n, &tm, &tn);
         tm = rotate_tile_m(p, tm, tiles_m, 2 * kBM);
         const int row_a = (int)(tm * 2 * kBM + rank * kBM);
         const int row_b = (int)(tn * kBN + rank * (kBN / 2));
@@ -148,7 +148,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     uint32_t acc = 0, acc_phase = 0;
     for (int64_t tile = pair_id; tile < num_tiles; tile += num_pairs) {
       int64_t tm, tn;
-      tile_coords<kPairGroupM>(tile, tiles_m, tiles_n, &tm, &tn);
+      tile_coords(p.group_m, tile, tiles_m, tiles_n, &tm, &tn);
       tm = rotate_tile_m(p, tm, tiles_m, 2 * kBM);
       const int64_t n0 = tn * kBN;
       const int64_t row = tm * 2 * kBM + rank * kBM + quarter * 32 + lane;
