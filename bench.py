@@ -62,6 +62,9 @@ def parse():
                     help="collectives of the token-sharded prefill: NCCL kernels, or the compute kernels' own stores into "
                          "peer-mapped buffers (auto: the latter when N > 1, NCCL if one of its barriers times out)")
     ap.add_argument('--micro-batches', type=int, default=0, help='0 = automatic (one stream)')
+    ap.add_argument('--kernel-totals', default=None, metavar='FILE',
+                    help='after the measurement, run one more step under torch.profiler (CUDA activities) and write '
+                         "rank 0's per-kernel totals to FILE")
     return ap.parse_args()
 
 
@@ -388,6 +391,21 @@ def main():
     gemm_streams = len(per_stream)
     ops.GEMM_PROFILE = None
 
+    if args.kernel_totals:
+        # per-kernel device time of one step (rank 0's view; every rank runs the step).  Not a timing run: the profiler
+        # skews the ranks against each other, so waiting inside barriers and collectives reads longer than it is.
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            (eager_resident if graph is not None else step_resident)()
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.kernel_totals, 'w') as f:
+                f.write(f'{args.mode}, {args.layers} layers, tp{world}, collectives {model.comm if world > 1 else None}: '
+                        f'{ms_total / args.steps:.2f} ms per step outside the profiler\n')
+                f.write(prof.key_averages().table(sort_by='cuda_time_total', row_limit=20, max_name_column_width=60))
+        barrier()
+
     # the tensor pipe's own INT8 rate on this GPU, measured after the timed region: the MMA-only kernel (no loads, no
     # stores) back to back for about two seconds, rate of the second half (at the power limit, like the step above)
     mma_only = None
@@ -416,14 +434,13 @@ def main():
     peak = 2 * bf16_sus
     # DRAM traffic of the dominant launch (the gate/up GEMM, 57344 x 8192 weights).  The full launch (65536 token rows,
     # 25 ms, 4.7 GB of operands) is too large for a multi-pass profiler capture; dram__bytes_read + dram__bytes_write
-    # was captured for 8192 token rows (`bench_kernels.py --only "gemm_w8a8 swiglu c5 gate+up 8192x"`).  The B operand
-    # is re-streamed once per 2048-row group and A / C grow with the rows, so a launch's traffic is proportional to
-    # its rows.  Only quoted for the unsharded prefill shape it was captured on.
+    # was captured for 8192 token rows (`bench_kernels.py --only "gemm_w8a8 swiglu c5 gate+up 8192x"`): 1.022 GB read,
+    # 0.457 GB written.  The B operand is re-streamed once per 4096-row group of m-tiles and A / C grow with the rows,
+    # so a launch's traffic is proportional to its rows.  Only quoted for the unsharded prefill shape it was captured on.
     traffic, traffic_note = None, None
     if world == 1 and args.mode == 'prefill':
         rows = args.batch * args.seq
-        # captured with a plain bf16 epilogue (1.949 GB read, 0.916 GB written); the SwiGLU epilogue writes half the columns
-        traffic = (1.949e9 + 0.916e9 / 2) * rows / 8192.0
+        traffic = (1.022e9 + 0.457e9) * rows / 8192.0
         traffic_note = ('bytes per gate/up GEMM launch: ncu dram read + write of the 8192-row case scaled by rows; '
                         'algorithmic A + B + C of that launch is %.3g' % (rows * 8192.0 + 57344 * 8192.0 + rows * 28672 * 2.0))
     line = {

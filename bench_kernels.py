@@ -465,6 +465,8 @@ def main():
     ap.add_argument('--library-refs', action='store_true', help='add cuBLASLt / cuBLAS reference lines (context only)')
     ap.add_argument('--mma-peak', action='store_true', help='only the MMA-only tensor-core peak measurement (all four kinds)')
     ap.add_argument('--c4-layer', action='store_true', help='only the SmoothQuant + HiFloat8 Llama-3-8B layer (config 4): tokens/s')
+    ap.add_argument('--gemm-variant', default='auto', choices=['auto', 'single', 'pair'],
+                    help='pin the kernel that takes GEMMs with more than 128 rows (one-CTA or CTA-pair) for a comparison')
     ap.add_argument('--cpu', action='store_true', help='add a cpu_baseline (the reference function on the host cores, bounded sample) to the lines that have one')
     args = ap.parse_args()
     out = open(args.out, 'w') if args.out else None
@@ -472,6 +474,7 @@ def main():
         return mma_peak_lines(out)
     if args.c4_layer:
         return c4_layer_line(out)
+    ops.set_gemm_variant(args.gemm_variant)
     todo = list(cases())
     if args.library_refs:
         for m, n, k in ((16384, 8192, 8192),):
