@@ -180,6 +180,13 @@ class PeerBuffers:
         ops.raise_if_timed_out(self.status)
 
 
+def any_rank(flag, group, device):
+    """Logical OR of a per-rank flag over the group, the same answer on every rank."""
+    t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=device)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
+    return bool(t.item())
+
+
 # stands for "the rows are the partial sums lying in the peer-mapped staging buffer" (push collectives)
 STAGED = object()
 
@@ -390,9 +397,21 @@ class LlamaW8A8(nn.Module):
         return self._peers[key]
 
     def check_comm(self):
-        """Raise if any barrier of the copy-engine collectives timed out since the model was built (synchronizes)."""
+        """Raise if any barrier of the push collectives timed out since the model was built (synchronizes)."""
         for peers in self._peers.values():
             peers.check()
+
+    def comm_failed_anywhere(self):
+        """True on EVERY rank if a barrier of the push collectives gave up waiting on ANY rank: the ranks must agree
+        before one of them changes the sequence of collectives it issues (switching to NCCL, repeating a step)."""
+        if self.tp == 1 or self.comm != 'push':
+            return False
+        try:
+            self.check_comm()
+            failed = False
+        except RuntimeError:
+            failed = True
+        return any_rank(failed, self.group, self.embed.device)
 
     @torch.no_grad()
     def forward(self, token_ids, kv_caches=None, past_len=0, micro_batches=None):

@@ -310,16 +310,7 @@ def main():
 
     def comm_failed():
         """True on every rank if a barrier of the push collectives gave up waiting on any rank."""
-        if world == 1 or model.comm != 'push':
-            return False
-        try:
-            model.check_comm()
-            bad = 0
-        except RuntimeError:
-            bad = 1
-        flag = torch.tensor([bad], device=dev, dtype=torch.int32)
-        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
-        return bool(flag.item())
+        return world > 1 and model.comm_failed_anywhere()
 
     def fall_back(when):
         nonlocal mb

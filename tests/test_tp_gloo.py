@@ -126,3 +126,41 @@ def test_shard_dims():
     # total Linear work is independent of tp
     work = lambda d: sum(k * n for k, n in d.values())
     assert work(d1) == 8 * work(d8)
+
+
+def _agree_worker(rank, world, port, ret):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    from amct_b200.workloads import llama_tp
+
+    class Model:                                            # the two attributes and the method the agreement uses
+        tp, comm, group = world, 'push', dist.group.WORLD
+        embed = torch.zeros(1)
+
+        def __init__(self, failed):
+            self.failed = failed
+
+        def check_comm(self):
+            if self.failed:
+                raise RuntimeError('a device-side wait timed out')
+
+    out = []
+    for failing_rank in (None, 1, 0):
+        m = Model(failed=(rank == failing_rank))
+        out.append(llama_tp.LlamaW8A8.comm_failed_anywhere(m))
+    m = Model(failed=True)
+    m.comm = 'nccl'                                         # nothing to agree on without the push collectives
+    out.append(llama_tp.LlamaW8A8.comm_failed_anywhere(m))
+    ret[rank] = out
+    dist.destroy_process_group()
+
+
+def test_every_rank_learns_of_a_barrier_timeout_on_any_rank():
+    """The switch from the push collectives to NCCL (bench.py) must be taken by all ranks or by none: a time-out seen by
+    one rank, forced here on the host, is reported on both."""
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(_agree_worker, args=(world, 29533, ret), nprocs=world, join=True)
+    for rank in range(world):
+        assert ret[rank] == [False, True, True, False], (rank, ret[rank])
