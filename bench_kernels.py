@@ -386,6 +386,18 @@ def cases():
         kw = dict(nbytes=nbytes) if m <= 128 else dict(nops=2 * m * 11008 * 4096, peak_mult=1.0)
         yield (f'gemm_w4a16 fused c2 M={m} {m}x11008x4096 g128 bf16', setup_w4,
                lambda t: (lambda: ops.gemm_w4a16(t[0], t[1], 4, t[2], t[3], 128, out=t[4])), kw)
+    # ---- the same Linear through the shim's routing for many tokens: dequantize once, then the 16-bit GEMM
+    for m in (1024, 4096):
+        def setup_w4r(m=m):
+            n, k = 11008, 4096
+            codes = torch.randint(0, 256, (n, k // 2), device='cuda', dtype=torch.uint8)
+            sc = (torch.rand(k // 128, n, device='cuda') * 0.01 + 0.002).to(torch.bfloat16)
+            off = torch.randint(-8, 8, (k // 128, n), device='cuda').to(torch.bfloat16)
+            return randn(m, k, torch.bfloat16), codes, sc, off
+        from amct_b200 import torch_npu_shim
+        yield (f'w4a16 linear (dequant + gemm, the route for M > 128) c2 M={m} {m}x11008x4096 g128 bf16', setup_w4r,
+               lambda t: (lambda: torch_npu_shim.weight_quant_matmul(t[0], t[1], 4, t[2], t[3], None, 128)),
+               dict(nops=2 * m * 11008 * 4096, peak_mult=1.0))
     # ---- MX quantization and block-scaled GEMM (config 3 shapes)
     for fmt, pb in (('fp8', 1.0), ('fp4', 0.5)):
         for r, k, opnd, tag in ((8192, 8192, 'a', 'c3 act'), (28672, 8192, 'b', 'c3 weight')):
