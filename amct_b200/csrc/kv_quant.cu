@@ -16,6 +16,8 @@
 // FMA contraction.
 //
 // Algorithmic HBM bytes per element: sizeof(in) read + sizeof(out) written.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace amct {
@@ -34,6 +36,7 @@ struct DsaParams {
 
 struct DsaRow {
   float scale, recip, zero, qlo, qhi;
+  bool fast;     // the scale a normal number and every quotient of the row finite and below 2^21: no NaN, no overflow to handle
 };
 
 // torch promotes to fp32 when the bounds or the scale meet a one-element fp32 tensor (the clip parameter, a loaded
@@ -97,6 +100,10 @@ __device__ __forceinline__ DsaRow dsa_row_params(float row_max, float row_min, c
   const float y = __frcp_rn(r.scale);
   const bool ok = fabsf(r.scale) >= 1.17549435e-38f && fabsf(y) >= 1.17549435e-38f && isfinite(y) && isfinite(r.scale);
   r.recip = ok ? y : 0.f;
+  // |v / scale| <= max|v| * |1 / scale| (1 + 2^-22) for every value of the row; with a given (static) scale the row's
+  // extrema are not known here
+  const float reach = __fmul_rn(fmaxf(fabsf(row_max), fabsf(row_min)), fabsf(y));
+  r.fast = ok && !dsa_static(p) && reach < 2097152.f;
   return r;
 }
 
@@ -104,6 +111,19 @@ __device__ __forceinline__ DsaRow dsa_row_params(float row_max, float row_min, c
 template <typename T>
 __device__ __forceinline__ float dsa_fake_quant(float v, const DsaRow& r, const DsaParams& p) {
   const bool f32 = dsa_fp32_math(p);
+  if (r.fast) {
+    // No quotient of this row is NaN, infinite or beyond 2^21: the exact FMA division, no NaN to carry through the clamp.
+    const float t = round_c<T>(div_by_recip(v, r.scale, r.recip), f32);
+    if (p.symmetric) {
+      // clamp before rounding (the bounds are integers, so the order does not matter); round half to even by adding and
+      // subtracting 1.5 * 2^23, which also turns a -0 level into +0 as round_ste does; one rounding of scale * level to
+      // T (rounding a value of T to T again changes nothing)
+      const float level = __fsub_rn(__fadd_rn(fminf(fmaxf(t, r.qlo), r.qhi), 12582912.f), 12582912.f);
+      return round_to<T>(__fmul_rn(r.scale, level));
+    }
+    const float level = fminf(fmaxf(round_c<T>(__fadd_rn(rintf(t), r.zero), f32), r.qlo), r.qhi);
+    return round_to<T>(__fmul_rn(r.scale, round_c<T>(__fsub_rn(level, r.zero), f32)));
+  }
   float q;
   if (r.recip != 0.f) {
     q = div_by_recip(v, r.scale, r.recip);
@@ -125,6 +145,14 @@ __device__ __forceinline__ float dsa_fake_quant(float v, const DsaRow& r, const 
 }
 
 constexpr int kDsaWarps = 4;
+
+// an input element as a value of the output dtype (what `.to(dtype)` of the caller leaves): no rounding to do when the
+// two are the same type
+template <typename TIN, typename TOUT>
+__device__ __forceinline__ float as_out(TIN v) {
+  if constexpr (std::is_same<TIN, TOUT>::value) return ElemTraits<TIN>::to_f(v);
+  else return round_to<TOUT>(ElemTraits<TIN>::to_f(v));
+}
 
 // EPL consecutive elements of T <-> floats, with the widest naturally aligned accesses when `wide` is set
 // (the caller has checked that every row starts on a multiple of EPL * sizeof(T) bytes, up to 16).
@@ -169,66 +197,65 @@ __device__ __forceinline__ void store_run(T* p, const float* v, bool wide) {
   }
 }
 
-// Rotation (+ cast + fake quantization): k = 32 * EPL, lane l holds the EPL consecutive elements from l * EPL, and
-// one warp works on RPW rows at a time so that enough loads are in flight (RPW * EPL = 16 values per lane).
-// The transform is the same whichever index bits sit in the lane number: every bit gets its butterfly.
-template <typename TIN, typename TOUT, int EPL, int RPW>
+// Rotation (+ cast + fake quantization): a row of k = LPR * EPL elements lies on LPR lanes of a warp, lane l of the
+// row holding the EPL consecutive elements from l * EPL, and a warp works on 32 / LPR rows side by side.  Sixteen
+// elements per lane wherever k allows: the per-row work (bounds, scale rule) and the shuffle stages are then shared by
+// 16 elements, and 32 bytes per lane are in flight.  The transform is the same whichever index bits sit in the lane
+// number: every bit gets its butterfly, lowest bit first.
+template <typename TIN, typename TOUT, int EPL, int LPR>
 __global__ void __launch_bounds__(kDsaWarps * 32) dsa_rotate_quant_kernel(DsaParams p, int wide_in, int wide_out) {
+  constexpr int RPW = 32 / LPR;                                 // rows per warp
   const int lane = threadIdx.x & 31;
-  const int64_t row0 = ((int64_t)blockIdx.x * kDsaWarps + (threadIdx.x >> 5)) * RPW;
-  if (row0 >= p.rows) return;                                 // whole warps leave together
-  float v[RPW][EPL];
+  const int sub = lane & (LPR - 1);                             // lane within its row
+  const int64_t row = ((int64_t)blockIdx.x * kDsaWarps + (threadIdx.x >> 5)) * RPW + lane / LPR;
+  const bool live = row < p.rows;                               // dead rows compute on zeros: the shuffles need every lane
+  float v[EPL];
+  if (live) {
+    load_run<TIN, EPL>(reinterpret_cast<const TIN*>(p.x) + row * p.ld_x + sub * EPL, v, wide_in != 0);
+  } else {
 #pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    if (row0 + r < p.rows) {
-      load_run<TIN, EPL>(reinterpret_cast<const TIN*>(p.x) + (row0 + r) * p.ld_x + lane * EPL, v[r], wide_in != 0);
-    } else {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) v[r][e] = 0.f;
-    }
+    for (int e = 0; e < EPL; ++e) v[e] = 0.f;
   }
+  // butterflies over the index bits held in the register number ...
 #pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    // butterflies over the index bits held in the register number ...
-#pragma unroll
-    for (int m = 1; m < EPL; m <<= 1) {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        if ((e & m) == 0) {
-          const float a = v[r][e], c = v[r][e | m];
-          v[r][e] = __fadd_rn(a, c);
-          v[r][e | m] = __fsub_rn(a, c);
-        }
-      }
-    }
-    // ... and over the bits held in the lane number
-#pragma unroll
-    for (int m = 1; m < 32; m <<= 1) {
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[r][e], m);
-        v[r][e] = (lane & m) ? __fsub_rn(other, v[r][e]) : __fadd_rn(v[r][e], other);
-      }
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    // scale, round to the input dtype (the rotation's result), then to the output dtype (.half() of the caller)
-    float hi = -INFINITY, lo = INFINITY;
+  for (int m = 1; m < EPL; m <<= 1) {
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
-      v[r][e] = round_to<TOUT>(round_to<TIN>(__fmul_rn(v[r][e], p.had_entry)));
-      hi = fmaxf(hi, v[r][e]);
-      lo = fminf(lo, v[r][e]);
+      if ((e & m) == 0) {
+        const float a = v[e], c = v[e | m];
+        v[e] = __fadd_rn(a, c);
+        v[e | m] = __fsub_rn(a, c);
+      }
     }
-    if (p.bits != 16) {
-      const DsaRow q = dsa_row_params<TOUT>(warp_max(hi), warp_min(lo), p);
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) v[r][e] = dsa_fake_quant<TOUT>(v[r][e], q, p);
-    }
-    if (row0 + r < p.rows)
-      store_run<TOUT, EPL>(reinterpret_cast<TOUT*>(p.out) + (row0 + r) * p.ld_out + lane * EPL, v[r], wide_out != 0);
   }
+  // ... and over the bits held in the lane number (the partners stay inside the row's LPR lanes)
+#pragma unroll
+  for (int m = 1; m < LPR; m <<= 1) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
+      v[e] = (sub & m) ? __fsub_rn(other, v[e]) : __fadd_rn(v[e], other);
+    }
+  }
+  // scale, round to the input dtype (the rotation's result), then to the output dtype (.half() of the caller)
+  float hi = -INFINITY, lo = INFINITY;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    v[e] = round_to<TOUT>(round_to<TIN>(__fmul_rn(v[e], p.had_entry)));
+    hi = fmaxf(hi, v[e]);
+    lo = fminf(lo, v[e]);
+  }
+  if (p.bits != 16) {
+#pragma unroll
+    for (int m = 1; m < LPR; m <<= 1) {
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, m));
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, m));
+    }
+    const DsaRow q = dsa_row_params<TOUT>(hi, lo, p);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = dsa_fake_quant<TOUT>(v[e], q, p);
+  }
+  if (live) store_run<TOUT, EPL>(reinterpret_cast<TOUT*>(p.out) + row * p.ld_out + sub * EPL, v, wide_out != 0);
 }
 
 // Fake quantization alone (any k): pass 1 takes the bounds, pass 2 re-reads the row (an L1 / L2 hit).
@@ -251,7 +278,7 @@ __global__ void __launch_bounds__(kDsaWarps * 32) dsa_fakequant_kernel(DsaParams
       const Vec16<TIN> raw = ld_vec(x + i * E);
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        const float f = round_to<TOUT>(ElemTraits<TIN>::to_f(raw.v[e]));
+        const float f = as_out<TIN, TOUT>(raw.v[e]);
         hi = fmaxf(hi, f);
         lo = fminf(lo, f);
       }
@@ -270,10 +297,7 @@ __global__ void __launch_bounds__(kDsaWarps * 32) dsa_fakequant_kernel(DsaParams
       const Vec16<TIN> raw = ld_vec_stream(x + i * E);
       Vec16<TOUT> o;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        const float f = round_to<TOUT>(ElemTraits<TIN>::to_f(raw.v[e]));
-        o.v[e] = ElemTraits<TOUT>::from_f(dsa_fake_quant<TOUT>(f, r, p));
-      }
+      for (int e = 0; e < E; ++e) o.v[e] = ElemTraits<TOUT>::from_f(dsa_fake_quant<TOUT>(as_out<TIN, TOUT>(raw.v[e]), r, p));
       *reinterpret_cast<uint4*>(out + i * E) = *reinterpret_cast<const uint4*>(&o);
     }
   } else {
@@ -289,21 +313,25 @@ static int launch_dsa(const DsaParams& p, int rotate, cudaStream_t st) {
   const unsigned grid = (unsigned)((p.rows + kDsaWarps - 1) / kDsaWarps);
   const int threads = kDsaWarps * 32;
   if (rotate) {
-    // a lane's run of k / 32 elements can be moved with wide accesses when every run starts on a multiple of its size
+    // a lane's run of EPL elements can be moved with wide accesses when every run starts on a multiple of its size
+    const int epl = p.k >= 128 ? 16 : (int)(p.k / 8);            // 16 elements per lane from k = 128 on; 8 lanes per row below
     auto run_aligned = [&](const void* base, int64_t ld, size_t elem) {
-      const int64_t run = (p.k / 32) * (int64_t)elem;
+      const int64_t run = epl * (int64_t)elem;
       const int64_t need = run >= 16 ? 16 : run;
       return need >= 4 && reinterpret_cast<uintptr_t>(base) % need == 0 && (ld * (int64_t)elem) % need == 0;
     };
     const int wi = run_aligned(p.x, p.ld_x, sizeof(TIN)) ? 1 : 0;
     const int wo = run_aligned(p.out, p.ld_out, sizeof(TOUT)) ? 1 : 0;
-    auto blocks = [&](int rpw) { return (unsigned)((p.rows + (int64_t)kDsaWarps * rpw - 1) / ((int64_t)kDsaWarps * rpw)); };
+    auto blocks = [&](int lpr) {
+      const int64_t rows_per_block = (int64_t)kDsaWarps * (32 / lpr);
+      return (unsigned)((p.rows + rows_per_block - 1) / rows_per_block);
+    };
     switch (p.k) {
-      case 32: AMCT_LAUNCH(blocks(4), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 1, 4>); break;
-      case 64: AMCT_LAUNCH(blocks(4), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 2, 4>); break;
-      case 128: AMCT_LAUNCH(blocks(4), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 4, 4>); break;
-      case 256: AMCT_LAUNCH(blocks(2), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 8, 2>); break;
-      case 512: AMCT_LAUNCH(blocks(1), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 16, 1>); break;
+      case 32: AMCT_LAUNCH(blocks(8), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 4, 8>); break;
+      case 64: AMCT_LAUNCH(blocks(8), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 8, 8>); break;
+      case 128: AMCT_LAUNCH(blocks(8), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 16, 8>); break;
+      case 256: AMCT_LAUNCH(blocks(16), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 16, 16>); break;
+      case 512: AMCT_LAUNCH(blocks(32), threads, st, (p, wi, wo), dsa_rotate_quant_kernel<TIN, TOUT, 16, 32>); break;
       default: return AMCT_ERR_UNSUPPORTED;
     }
   } else {
