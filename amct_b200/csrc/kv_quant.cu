@@ -8,12 +8,13 @@
 //     quant_dsa.py:118-119);
 //   * the indexer's chain rotate -> .half() -> fake_quant (quant_dsa.py:75-82) in one pass over the row.
 //
-// One warp owns one row (a token, or a token-head of the indexer).  Arithmetic follows torch's dtypes: without
+// One warp owns one row (a token) of the plain fake quantization; a rotated row (a token-head of the indexer) lies on
+// k / 16 lanes.  Arithmetic follows torch's dtypes: without
 // learned clipping every step is rounded to the activation dtype; with it the fp32 clip parameter promotes the
 // bounds and all later steps to fp32 and only the result is cast back.  round_ste(t) = (round(t) - t) + t is
 // exact except that it turns a zero into +0, which the symmetric path reproduces.  A NaN quotient stays NaN through the
-// clamp as in torch; a NaN INPUT is not treated like torch's amax (which makes the whole row NaN).  Compiled without
-// FMA contraction.
+// clamp as in torch, and a NaN INPUT makes its row's bounds, scale and outputs NaN as torch's amax does.  Compiled
+// without FMA contraction.
 //
 // Algorithmic HBM bytes per element: sizeof(in) read + sizeof(out) written.
 #include <type_traits>
@@ -59,7 +60,7 @@ template <typename T>
 __device__ __forceinline__ DsaRow dsa_row_params(float row_max, float row_min, const DsaParams& p) {
   const bool f32 = dsa_fp32_math(p);
   const bool clip = p.mode == AMCT_DSA_LEARNED_CLIP;
-  float hi = fmaxf(row_max, 0.f), lo = fminf(row_min, 0.f);
+  float hi = fmax_nan(row_max, 0.f), lo = fmin_nan(row_min, 0.f);          // torch.clamp keeps a NaN bound
   if (p.mode == AMCT_DSA_CLIP_RATIO) {                          // node.py:198-200, in the activation dtype
     hi = round_to<T>(__fmul_rn(hi, p.a));
     lo = round_to<T>(__fmul_rn(lo, p.a));
@@ -242,14 +243,14 @@ __global__ void __launch_bounds__(kDsaWarps * 32) dsa_rotate_quant_kernel(DsaPar
 #pragma unroll
   for (int e = 0; e < EPL; ++e) {
     v[e] = round_to<TOUT>(round_to<TIN>(__fmul_rn(v[e], p.had_entry)));
-    hi = fmaxf(hi, v[e]);
-    lo = fminf(lo, v[e]);
+    hi = fmax_nan(hi, v[e]);
+    lo = fmin_nan(lo, v[e]);
   }
   if (p.bits != 16) {
 #pragma unroll
     for (int m = 1; m < LPR; m <<= 1) {
-      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, m));
-      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, m));
+      hi = fmax_nan(hi, __shfl_xor_sync(0xffffffffu, hi, m));
+      lo = fmin_nan(lo, __shfl_xor_sync(0xffffffffu, lo, m));
     }
     const DsaRow q = dsa_row_params<TOUT>(hi, lo, p);
 #pragma unroll
@@ -279,18 +280,23 @@ __global__ void __launch_bounds__(kDsaWarps * 32) dsa_fakequant_kernel(DsaParams
 #pragma unroll
       for (int e = 0; e < E; ++e) {
         const float f = as_out<TIN, TOUT>(raw.v[e]);
-        hi = fmaxf(hi, f);
-        lo = fminf(lo, f);
+        hi = fmax_nan(hi, f);
+        lo = fmin_nan(lo, f);
       }
     }
   } else {
     for (int64_t j = lane; j < p.k; j += 32) {
       const float f = round_to<TOUT>(ElemTraits<TIN>::to_f(x[j]));
-      hi = fmaxf(hi, f);
-      lo = fminf(lo, f);
+      hi = fmax_nan(hi, f);
+      lo = fmin_nan(lo, f);
     }
   }
-  const DsaRow r = dsa_row_params<TOUT>(warp_max(hi), warp_min(lo), p);
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) {                           // a NaN anywhere in the row reaches its bounds, as in torch.amax
+    hi = fmax_nan(hi, __shfl_xor_sync(0xffffffffu, hi, m));
+    lo = fmin_nan(lo, __shfl_xor_sync(0xffffffffu, lo, m));
+  }
+  const DsaRow r = dsa_row_params<TOUT>(hi, lo, p);
 
   if (VEC) {
     for (int64_t i = lane; i < nvec; i += 32) {

@@ -262,6 +262,7 @@ def test_emulated_fake_quant_shapes(on_cpu):
             G.test_fake_quant_oracle(dtype, shape)
     G.test_fake_quant_strided_and_cast()
     G.test_fake_quant_scale_underflow_keeps_nan()
+    G.test_fake_quant_nan_input_makes_the_row_nan()
 
 
 def test_emulated_rotation_and_chain(on_cpu):

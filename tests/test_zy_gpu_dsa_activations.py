@@ -77,6 +77,27 @@ def test_fake_quant_scale_underflow_keeps_nan():
     assert bits_equal(torch.where(keep, got, torch.zeros_like(got)), torch.where(keep, want, torch.zeros_like(want)))
 
 
+def test_fake_quant_nan_input_makes_the_row_nan():
+    """torch.amax / amin carry a NaN of the row into its bounds, so scale and every output of that row are NaN; the
+    other rows are untouched.  Plain and rotated path, symmetric and asymmetric."""
+    gen = torch.Generator().manual_seed(46)
+    for dtype in (torch.bfloat16, torch.float16):
+        x = torch.randn(9, 128, generator=gen).to(dtype)
+        x[2, 17] = float('nan')
+        x[5, 127] = float('nan')
+        for kwargs, ref in (({}, ()), ({'bits': 4}, (4,)),
+                            ({'symmetric': False, 'clip_max_sigmoid': SIG_MAX, 'clip_min_sigmoid': SIG_MIN}, (8, False, True, CLIP_MAX, CLIP_MIN))):
+            got = ops().dsa_rotate_fakequant(x.cuda(), **kwargs).cpu()
+            want = O.activation_fake_quant(x, *ref)
+            assert bool(torch.isnan(want[2]).all()) and bool(torch.isnan(want[5]).all())
+            assert bool((torch.isnan(got) == torch.isnan(want)).all())
+            keep = ~torch.isnan(want)
+            assert bits_equal(torch.where(keep, got, torch.zeros_like(got)), torch.where(keep, want, torch.zeros_like(want)))
+        rot = ops().dsa_rotate_fakequant(x.cuda(), rotate=True, out_dtype=torch.float16).cpu()
+        assert bool(torch.isnan(rot[2]).all()) and bool(torch.isnan(rot[5]).all())
+        assert not bool(torch.isnan(rot[[0, 1, 3, 4, 6, 7, 8]]).any())
+
+
 def test_fake_quant_strided_and_cast():
     gen = torch.Generator().manual_seed(42)
     big = torch.randn(9, 300, generator=gen).to(torch.bfloat16)
