@@ -49,6 +49,10 @@ struct GemmParams {
   int64_t row_rot;
   // Rasterisation: m-tiles per group (set by the launcher from the bytes of an A row block, see group_m_tiles).
   int group_m;
+  // Rows of A a tile load brings in: 128, or 64 when the whole problem has at most 64 rows (a decode batch).  The MMA
+  // still works on 128 rows; rows 64..127 of the shared-memory tile then hold whatever was there, which only reaches
+  // accumulator rows that are never stored, and every CTA's A traffic is halved (set by the launcher).
+  int a_box_rows;
 };
 
 // m-tiles per rasterisation group: as many as keep the group's A panel (group x tile_rows x K bytes) near 32 MB,

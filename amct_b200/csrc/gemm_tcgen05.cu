@@ -52,7 +52,7 @@ struct __align__(1024) GemmSmem {
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
-  constexpr int kBN = BN, kStages = STAGES, kStageBytes = kABytes + BN * kBKBytes;
+  constexpr int kBN = BN, kStages = STAGES;
   constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulators; a power of two >= 32
   using Smem = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -95,7 +95,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         for (int64_t kb = 0; kb < num_kb; ++kb) {
           if (!tc05::mbar_wait(tc05::smem_u32(&s.empty[stage]), phase ^ 1, abort_flag)) { alive = false; break; }
           const uint32_t bar = tc05::smem_u32(&s.full[stage]);
-          tc05::mbar_expect_tx(bar, kStageBytes);
+          tc05::mbar_expect_tx(bar, (uint32_t)(p.a_box_rows * kBKBytes + BN * kBKBytes));
           const uint32_t dst = tc05::smem_u32(&s.tiles[stage][0]);
           tc05::tma_load_2d(dst, &tma_a, bar, (int)(kb * bk), (int)(tm * kBM));
           tc05::tma_load_2d(dst + kABytes, &tma_b, bar, (int)(kb * bk), (int)(tn * kBN));
@@ -301,7 +301,8 @@ static int launch_gemm(const void* a, const void* b, int64_t ld_a, int64_t ld_b,
   if (!dev) return AMCT_ERR_CUDA;
   const int esize = p.kind == KIND_I8 ? 1 : 2;
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, a, esize, p.m, p.k, ld_a, kBM);
+  p.a_box_rows = p.m <= 64 ? 64 : kBM;
+  int rc = make_map(&ma, a, esize, p.m, p.k, ld_a, p.a_box_rows);
   if (rc != AMCT_OK) return rc;
   if (use_pair_kernel(p, esize)) {
     // CTA pairs on 256 x 256 tiles: each CTA loads 128 rows of A and 128 rows (half a tile) of B
