@@ -362,7 +362,10 @@ def cases():
         def setup_sw(m=m):
             a = torch.randint(-128, 128, (m, 8192), device='cuda', dtype=torch.int8)
             b = torch.randint(-128, 128, (57344, 8192), device='cuda', dtype=torch.int8)
-            return (a, b, torch.rand(57344, device='cuda') * 1e-3, torch.rand(m, device='cuda'),
+            # scales that put the gate values at a few units, as in a model: with random INT8 operands the accumulators
+            # are of the order of 5e5, and gates of +-100 would send every exp / division of the epilogue down its
+            # out-of-range path
+            return (a, b, torch.rand(57344, device='cuda') * 1e-5, torch.rand(m, device='cuda'),
                     torch.empty(m, 28672, device='cuda', dtype=torch.bfloat16))
         yield (f'gemm_w8a8 swiglu c5 gate+up {m}x57344x8192 -> bf16 [{m}x28672]', setup_sw,
                lambda t: (lambda: ops.gemm_w8a8_swiglu(t[0], t[1], t[2], t[3], None, out=t[4])),
