@@ -230,6 +230,12 @@ __device__ __forceinline__ void epilogue_rows_scatter(const GemmParams& p, uint3
                                                       int64_t n0, const float* sc, const float* sb, float pt,
                                                       uint8_t* stage) {
   static_assert(kBN % 64 == 0, "scatter epilogue works on 64-column chunks");
+  // where the warp's rows go: worked out once per tile (a 64-bit division), not once per store
+  const int64_t owner0 = warp_row0 / p.scatter_rows, local0 = warp_row0 - owner0 * p.scatter_rows;
+  const bool one_owner = local0 + 32 <= p.scatter_rows && owner0 < p.scatter_world;
+  uint16_t* owner_base = one_owner ? reinterpret_cast<uint16_t*>(p.scatter_out[owner0]) +
+                                         ((int64_t)p.scatter_slot * p.scatter_rows + local0) * p.ld_out
+                                   : nullptr;
 #pragma unroll 1
   for (int c0 = 0; c0 < kBN; c0 += 64) {
 #pragma unroll
@@ -251,17 +257,29 @@ __device__ __forceinline__ void epilogue_rows_scatter(const GemmParams& p, uint3
     __syncwarp();
     const int chunk = lane & 7;
     const int64_t col = n0 + c0 + chunk * 8;
+    if (col < p.n) {
+      if (one_owner) {
+        // the warp's 32 rows belong to one rank: one base pointer, no division per row
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int r_in = it * 4 + (lane >> 3);
-      const uint4 v = *reinterpret_cast<const uint4*>(stage + r_in * 128 + ((chunk ^ (r_in & 7)) * 16));
-      const int64_t row = warp_row0 + r_in;
-      if (row < p.m && col < p.n) {
-        const int64_t owner = row / p.scatter_rows;
-        const int64_t local = row - owner * p.scatter_rows;
-        uint16_t* o = reinterpret_cast<uint16_t*>(p.scatter_out[owner]) +
-                      ((int64_t)p.scatter_slot * p.scatter_rows + local) * p.ld_out + col;
-        *reinterpret_cast<uint4*>(o) = v;
+        for (int it = 0; it < 8; ++it) {
+          const int r_in = it * 4 + (lane >> 3);
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + r_in * 128 + ((chunk ^ (r_in & 7)) * 16));
+          if (warp_row0 + r_in < p.m) *reinterpret_cast<uint4*>(owner_base + (int64_t)r_in * p.ld_out + col) = v;
+        }
+      } else {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r_in = it * 4 + (lane >> 3);
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + r_in * 128 + ((chunk ^ (r_in & 7)) * 16));
+          const int64_t row = warp_row0 + r_in;
+          if (row < p.m) {
+            const int64_t owner = row / p.scatter_rows;
+            const int64_t local = row - owner * p.scatter_rows;
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.scatter_out[owner]) +
+                          ((int64_t)p.scatter_slot * p.scatter_rows + local) * p.ld_out + col;
+            *reinterpret_cast<uint4*>(o) = v;
+          }
+        }
       }
     }
     __syncwarp();
