@@ -245,7 +245,8 @@ __global__ void __launch_bounds__(NT) addnorm_quant_kernel(NormQuantParams p) {
           // a warp writes 256 contiguous bytes per destination: plain stores into every rank's (peer-mapped) buffer
           const int64_t off = (p.row0 + row) * p.ld_q + v * E;
           for (int i = 0; i < p.world; ++i) {
-            const int d = (p.first_dst + i) % p.world;        // every rank starts with another destination
+            int d = p.first_dst + i;                          // every rank starts with another destination
+            if (d >= p.world) d -= p.world;
             *reinterpret_cast<uint2*>(p.q_all[d] + off) = make_uint2(w0, w1);
           }
         } else {
