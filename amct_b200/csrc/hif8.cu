@@ -350,9 +350,9 @@ static int run_encode(const T* x, int64_t n, uint8_t* codes, T* fake, cudaStream
 
 // x [n] contiguous -> HiF8 codes [n] (codes != NULL) or fake-quantized values in x's dtype (fake != NULL).
 extern "C" int amct_hif8_encode(const void* x, int dtype, int64_t n, void* codes, void* fake, void* stream) {
-  if (n < 0 || (!codes) == (!fake)) return AMCT_ERR_ARG;
-  if (n == 0) return AMCT_OK;
-  if (!x) return AMCT_ERR_ARG;
+  if (n < 0) return AMCT_ERR_ARG;
+  if (n == 0) return AMCT_OK;                                 // an empty tensor has no storage: its pointers are null
+  if ((!codes) == (!fake) || !x) return AMCT_ERR_ARG;
   if (!amct::aligned16(x) || (codes && reinterpret_cast<uintptr_t>(codes) % 8) || (fake && !amct::aligned16(fake)))
     return AMCT_ERR_ALIGN;
   cudaStream_t st = (cudaStream_t)stream;
