@@ -159,13 +159,14 @@ def test_emulated_decoder_glue(on_cpu):
 def test_emulated_edge_cases(on_cpu):
     """tests/test_zy_gpu_edge_cases.py through the full library (the group kernel takes the group-wise requests)."""
     import test_zy_gpu_edge_cases as G
-    assert run_gpu_tests(G, skip=('test_w8a8_linear_with_one_scale_for_the_whole_weight',)) >= 10
+    assert run_gpu_tests(G, skip=('test_w8a8_linear_with_one_scale_for_the_whole_weight', 'test_zero_rows_through_the_gemms')) >= 10
 
 
 def test_emulated_edge_cases_general_kernels(rows_on_cpu):
-    """The same through the general row kernels alone."""
+    """The same through the general row kernels alone (that library holds no other entry point)."""
     import test_zy_gpu_edge_cases as G
-    assert run_gpu_tests(G, skip=('test_w8a8_linear_with_one_scale_for_the_whole_weight',)) >= 10
+    assert run_gpu_tests(G, skip=('test_w8a8_linear_with_one_scale_for_the_whole_weight', 'test_zero_rows_through_the_gemms',
+                                  'test_zero_rows_are_a_no_op_in_the_quantizers')) >= 10
 
 
 def test_emulated_hifloat8(on_cpu):

@@ -73,34 +73,46 @@ def test_w8a8_linear_with_one_scale_for_the_whole_weight(dynamic):
         assert float((got.float() - ref).abs().max()) < 0.05 * float(ref.abs().max())
 
 
-def test_zero_rows_are_a_no_op_everywhere():
-    """An empty batch (zero token rows) goes through every activation-side entry point without a launch error and
-    comes back with zero rows of the right width and dtype."""
-    o = ops()
-    k, n = 128, 256
-    x = torch.empty(0, k, dtype=torch.bfloat16, device='cuda')
+def _check_empty(cases):
     failures = []
-
-    def check(name, fn, shape, dtype):
+    for name, fn, shape, dtype in cases:
         try:
             out = fn()
-            torch.cuda.synchronize()
+            out.cpu()                                                 # any launch error surfaces here
             if tuple(out.shape) != shape or out.dtype != dtype:
                 failures.append((name, tuple(out.shape), out.dtype))
         except Exception as exc:                                      # noqa: BLE001 -- collected, reported together
             failures.append((name, repr(exc)[:120]))
-
-    check('quant_dynamic_per_token', lambda: o.quant_dynamic_per_token(x)[0], (0, k), torch.int8)
-    check('quantize_static', lambda: o.quantize_static(x, torch.ones(1, device='cuda'), torch.zeros(1, device='cuda')), (0, k), torch.int8)
-    check('addnorm_quant_per_token', lambda: o.addnorm_quant_per_token(x, torch.ones(k, dtype=torch.bfloat16, device='cuda'), 1e-5)[0],
-          (0, k), torch.int8)
-    check('hif8_encode', lambda: o.hif8_encode(x), (0, k), torch.uint8)
-    check('hif8_fake_quant', lambda: o.hif8_fake_quant(x), (0, k), torch.bfloat16)
-    check('dsa_rotate_fakequant', lambda: o.dsa_rotate_fakequant(x), (0, k), torch.bfloat16)
-    check('dsa_rotate_fakequant rotate', lambda: o.dsa_rotate_fakequant(x, rotate=True, out_dtype=torch.float16), (0, k), torch.float16)
-    w = torch.randint(-128, 128, (n, k), dtype=torch.int8, device='cuda')
-    q = torch.empty(0, k, dtype=torch.int8, device='cuda')
-    check('gemm_w8a8', lambda: o.gemm_w8a8(q, w, torch.ones(n, device='cuda'), torch.empty(0, device='cuda'), None), (0, n), torch.bfloat16)
-    wf = torch.randn(n, k, device='cuda').to(torch.bfloat16)
-    check('gemm_f16', lambda: o.gemm_f16(x, wf), (0, n), torch.bfloat16)
     assert not failures, failures
+
+
+def test_zero_rows_are_a_no_op_in_the_quantizers():
+    """An empty batch (zero token rows) goes through every activation-side quantizer without a launch error and comes
+    back with zero rows of the right width and dtype."""
+    o = ops()
+    k = 128
+    x = torch.empty(0, k, dtype=torch.bfloat16).cuda()
+    one, zero = torch.ones(1).cuda(), torch.zeros(1).cuda()
+    gamma = torch.ones(k, dtype=torch.bfloat16).cuda()
+    _check_empty([
+        ('quant_dynamic_per_token', lambda: o.quant_dynamic_per_token(x)[0], (0, k), torch.int8),
+        ('quantize_static', lambda: o.quantize_static(x, one, zero), (0, k), torch.int8),
+        ('addnorm_quant_per_token', lambda: o.addnorm_quant_per_token(x, gamma, 1e-5)[0], (0, k), torch.int8),
+        ('hif8_encode', lambda: o.hif8_encode(x), (0, k), torch.uint8),
+        ('hif8_fake_quant', lambda: o.hif8_fake_quant(x), (0, k), torch.bfloat16),
+        ('dsa_rotate_fakequant', lambda: o.dsa_rotate_fakequant(x), (0, k), torch.bfloat16),
+        ('dsa_rotate_fakequant rotate', lambda: o.dsa_rotate_fakequant(x, rotate=True, out_dtype=torch.float16), (0, k), torch.float16),
+    ])
+
+
+def test_zero_rows_through_the_gemms():
+    o = ops()
+    k, n = 128, 256
+    w = torch.randint(-128, 128, (n, k), dtype=torch.int8).cuda()
+    q = torch.empty(0, k, dtype=torch.int8).cuda()
+    x = torch.empty(0, k, dtype=torch.bfloat16).cuda()
+    wf = torch.randn(n, k).to(torch.bfloat16).cuda()
+    _check_empty([
+        ('gemm_w8a8', lambda: o.gemm_w8a8(q, w, torch.ones(n).cuda(), torch.empty(0).cuda(), None), (0, n), torch.bfloat16),
+        ('gemm_f16', lambda: o.gemm_f16(x, wf), (0, n), torch.bfloat16),
+    ])
